@@ -1,0 +1,124 @@
+"""Regenerate the golden vectors under tests/golden/ from the reference's own
+pure-Python modules (run in the build container, where the reference checkout
+is mounted; the GPU box never needs it).
+
+    python tests/golden/make_golden.py [/path/to/reference]
+
+Outputs (all small):
+  nvfp4_pack.npz      inputs and packed data/scales from reference pack_nvfp4
+  nvfp4_swizzle.npz   scale_offsets / swizzle_scales for the shapes the
+                      reference validator uses
+  program.npz         linear_streams outputs for a few stage lists
+  calibration.json    ActivationCalibration.finalize / cache_key / fp32_descale
+"""
+import importlib.util
+import json
+import sys
+from pathlib import Path
+
+import numpy as np
+
+HERE = Path(__file__).resolve().parent
+REF = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+
+
+def load(name):
+    spec = importlib.util.spec_from_file_location("ref_" + name, REF / "native_pi0" / f"{name}.py")
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["ref_" + name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def bf16_round(x):
+    """Round FP32 to the nearest BF16 (ties to even), returned as FP32."""
+    u = np.asarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000
+    return u.astype(np.uint32).view(np.float32)
+
+
+def main():
+    q = load("quantization")
+    out = {}
+    cases = []
+    # config-1 distribution: N(0,1) with 0.1 % entries x20 (activations, nearest) and
+    # N(0,0.02) weights (ceil), BF16-rounded, seed 0; reduced sizes for the fixture.
+    rng = np.random.default_rng(0)
+    x = rng.normal(size=(51, 1024)).astype(np.float32)
+    mask = rng.random(x.shape) < 0.001
+    x[mask] *= 20
+    x = bf16_round(x)
+    w = bf16_round(rng.normal(scale=0.02, size=(96, 1024)).astype(np.float32))
+    cases.append(("cfg1_x", x, dict(row_alignment=128)))
+    cases.append(("cfg1_w", w, dict(scale_policy="ceil")))
+    cases.append(("cfg1_w_gs", w, dict(scale_policy="ceil", global_scale=float(np.abs(w).max() / (6 * 448)))))
+    # tie-heavy inputs: exact E2M1 midpoints times assorted block scales
+    mids = np.array([.25, .75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, 7.0, 0.1, 0.0, -.25, -1.25, -2.5, -5.0, -6.0], np.float32)
+    t = np.stack([mids * s for s in (1.0, .9375, .8125, 1.75, 3.5, 2 ** -9, 2 ** -10, 448.0, 500.0, 1e-12)])
+    cases.append(("ties", t.astype(np.float32), dict()))
+    cases.append(("ties_ceil", t.astype(np.float32), dict(scale_policy="ceil")))
+    r2 = np.random.default_rng(7)
+    cases.append(("ragged", r2.normal(size=(3, 4304)).astype(np.float32), dict(global_scale=.125, column_alignment=64)))
+    cases.append(("wide_range", (r2.normal(size=(16, 256)) * np.exp(r2.normal(size=(16, 256)) * 4)).astype(np.float32), dict()))
+    cases.append(("wide_range_ceil", (r2.normal(size=(16, 256)) * np.exp(r2.normal(size=(16, 256)) * 4)).astype(np.float32), dict(scale_policy="ceil")))
+    meta = {}
+    for name, arr, kw in cases:
+        p = q.pack_nvfp4(arr, **kw)
+        out[name + "_in"] = arr
+        out[name + "_data"] = p.data
+        out[name + "_scales"] = p.scales
+        if arr.size <= 8192:
+            out[name + "_deq"] = p.dequantize()
+        meta[name] = kw
+    np.savez_compressed(HERE / "nvfp4_pack.npz", **out)
+    (HERE / "nvfp4_pack.json").write_text(json.dumps(meta, indent=1, sort_keys=True))
+
+    sw = {}
+    for rows, blocks in ((1, 1), (128, 4), (129, 5), (51, 64), (256, 72), (768, 128), (300, 269)):
+        lin = np.random.default_rng(rows * 1000 + blocks).integers(0, 127, size=(rows, blocks), dtype=np.uint8)
+        sw[f"lin_{rows}_{blocks}"] = lin
+        sw[f"swz_{rows}_{blocks}"] = q.swizzle_scales(lin)
+    sw["offsets_130_9"] = q.scale_offsets(130, 9)
+    g = np.arange(12).reshape(3, 4)
+    sw["interleave"] = q.interleave_gate_up(g, g + 100)
+    np.savez_compressed(HERE / "nvfp4_swizzle.npz", **sw)
+
+    prog = load("program")
+    pr = {}
+    lists = {
+        "a": [(120, 2048), (96, 16384), (1536, 2048), (8, 1024)],
+        "b": [(20, 1024), (8, 2048), (64, 1024), (8, 4096), (7, 64)] * 3,
+        "c": [(1, 64)],
+    }
+    for key, lst in lists.items():
+        for workers in (1, 20, 148):
+            code = prog.linear_streams([prog.LinearWork(t, k) for t, k in lst], workers)
+            pr[f"{key}_{workers}"] = code
+    np.savez_compressed(HERE / "program.npz", **pr)
+    (HERE / "program.json").write_text(json.dumps(lists))
+
+    cal = load("calibration")
+    c = cal.ActivationCalibration()
+    rr = np.random.default_rng(3)
+    obs = []
+    for sample in ("cam_a", "cam_b", "cam_c"):
+        for step in range(4):
+            v = (rr.normal(size=8) * (step + 1) * 37).astype(np.float32)
+            c.observe("expert.0.qkv", v, sample=sample, step=step)
+            obs.append(("expert.0.qkv", v.tolist(), sample, step))
+        v = (rr.normal(size=5) * 3).astype(np.float32)
+        c.observe("prefix.qkv", v, sample=sample)
+        obs.append(("prefix.qkv", v.tolist(), sample, None))
+    gold = {
+        "observations": obs,
+        "finalize_99_9": c.finalize(required_steps=range(4)),
+        "finalize_50": c.finalize(percentile=50),
+        "cache_key": cal.cache_key("abc", {"steps": 10, "views": 3}, "obs-v1"),
+        "fp32_descale": float(cal.fp32_descale(.0123, .0456)),
+    }
+    (HERE / "calibration.json").write_text(json.dumps(gold, indent=1, sort_keys=True))
+    print("golden vectors written to", HERE)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,102 @@
+"""Static stream compiler and calibration records against reference golden outputs."""
+import json
+import tempfile
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from native_pi0.calibration import ActivationCalibration, cache_key, checkpoint_digest, fp32_descale
+from native_pi0.program import LinearWork, linear_streams, program_summary, validate_streams
+
+
+def test_linear_streams_match_reference(golden_dir):
+    gold = np.load(golden_dir / "program.npz")
+    lists = json.loads((golden_dir / "program.json").read_text())
+    for key, lst in lists.items():
+        for workers in (1, 20, 148):
+            code = linear_streams([LinearWork(t, k) for t, k in lst], workers)
+            np.testing.assert_array_equal(code, gold[f"{key}_{workers}"])
+            assert validate_streams(code, [t for t, _ in lst])
+            s = program_summary(code)
+            assert s["compute_tiles"] == sum(t for t, _ in lst)
+            assert s["workers"] == workers and not s["dynamic_fetch"]
+
+
+def test_linear_streams_errors():
+    for workers in (0, 149, 1.5):
+        with pytest.raises(ValueError):
+            linear_streams([LinearWork(1, 64)], workers)
+    for bad in ([], [LinearWork(0, 64)], [LinearWork(1, 32)], [LinearWork(1, 96)]):
+        with pytest.raises(ValueError):
+            linear_streams(bad, 4)
+
+
+def test_validator_rejects_corrupt_programs():
+    code = linear_streams([LinearWork(10, 64), LinearWork(7, 128)], 4)
+    tiles = [10, 7]
+    assert validate_streams(code, tiles)
+    broken = code.copy()
+    broken[0, 0, 3] += 1                       # overlapping coverage
+    with pytest.raises(ValueError):
+        validate_streams(broken, tiles)
+    broken = code.copy()
+    broken[1, 0, 0] = 0                        # a missing producer range
+    with pytest.raises(ValueError):
+        validate_streams(broken, tiles)
+    broken = code.copy()
+    broken[2, 0, 1], broken[2, 1, 1] = 1, 0    # stage order reversed
+    with pytest.raises(ValueError):
+        validate_streams(broken, tiles)
+
+
+def test_calibration_matches_reference(golden_dir):
+    gold = json.loads((golden_dir / "calibration.json").read_text())
+    c = ActivationCalibration()
+    for op, values, sample, step in gold["observations"]:
+        c.observe(op, values, sample=sample, step=step)
+    assert c.finalize(required_steps=range(4)) == gold["finalize_99_9"]
+    assert c.finalize(percentile=50) == gold["finalize_50"]
+    assert cache_key("abc", {"views": 3, "steps": 10}, "obs-v1") == gold["cache_key"]
+    assert float(fp32_descale(.0123, .0456)) == gold["fp32_descale"]
+
+
+def test_calibration_known_answers():             # reference test_calibration.py:10-51
+    c = ActivationCalibration()
+    for sample in ("camera_a", "camera_b"):
+        for step in range(10):
+            c.observe("expert.0.qkv", [0, -(step + 1) * 448], sample=sample, step=step)
+    rec = c.finalize(percentile=100, required_steps=range(10))["expert.0.qkv"]
+    assert rec["fp8_scale"] == 10 and rec["per_step_max"]["9"] == 4480
+    assert rec["observations"] == 2 and rec["amax_records_above_range"] == 0
+    assert c.finalize(percentile=0)["expert.0.qkv"]["fp8_scale"] == 1
+    with pytest.raises(ValueError):
+        c.finalize(required_steps=range(11))
+    with pytest.raises(ValueError):
+        c.observe("expert.0.qkv", [1], sample="camera_a", step=0)
+    z = ActivationCalibration()
+    z.observe("prefix.qkv", [0], sample="zero")
+    assert z.finalize()["prefix.qkv"]["fp8_scale"] > 0
+    for v in (float("nan"), float("inf")):
+        with pytest.raises(ValueError):
+            z.observe("bad", [v], sample="bad")
+    assert fp32_descale(.0123, .0456) == np.float32(.0123) * np.float32(.0456)
+    with pytest.raises(ValueError):
+        fp32_descale(1e30, 1e30)
+
+
+def test_checkpoint_identity():
+    with tempfile.TemporaryDirectory() as d:
+        p = Path(d) / "model.safetensors"
+        p.write_bytes(b"a" * 70000)
+        before = checkpoint_digest([p])
+        with p.open("r+b") as f:
+            f.seek(69999)
+            f.write(b"b")
+        after = checkpoint_digest([p])
+        assert before != after
+        k = cache_key(after, {"steps": 10, "views": 3}, "observations-v1")
+        assert k == cache_key(after, {"views": 3, "steps": 10}, "observations-v1")
+        assert k != cache_key(after, {"steps": 5, "views": 3}, "observations-v1")
+        with pytest.raises(ValueError):
+            checkpoint_digest([])
