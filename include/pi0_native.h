@@ -1,0 +1,186 @@
+/* C ABI of libpi0_native.so - the B200 (sm_100a) pi0 inference engine.
+ *
+ * Every function returns a cudaError_t as int (0 = success).  Argument errors return
+ * cudaErrorInvalidValue (1); a device that is not compute capability 10.x, or more workers than SMs,
+ * returns cudaErrorInvalidConfiguration (9); a handle used on another device returns
+ * cudaErrorInvalidDevice (101); launching on a capturing stream returns
+ * cudaErrorStreamCaptureUnsupported (900).  On failure *handle is set to NULL.  destroy_*(NULL) succeeds.
+ *
+ * Ownership: the caller owns every tensor it passes (weights, activations, caches, outputs) and keeps it
+ * alive while the handle lives; the library owns only its programs, counters, tensor maps and status words.
+ * Calls on one handle must be stream ordered.  All pointers are device pointers unless noted.
+ *
+ * The entry points mirror the ctypes surface of the reference project (file:line of the interface each one
+ * replaces is given); extensions that the reference has no counterpart for are marked "extension".
+ */
+#ifndef PI0_NATIVE_H
+#define PI0_NATIVE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------------------
+ * NVFP4 block-scaled GEMM:  out[M,N] = epilogue(alpha * deq(A)[M,K] . deq(B)[N,K]^T)
+ * A, B: packed E2M1 (two per byte, low nibble first) [M, K/2], [N, K/2];  sfa, sfb: E4M3 block scales in the
+ * 128x4 swizzled atom layout;  M, N multiples of 128, K a multiple of 64;  default output FP32 [M, N].
+ * Replaces: native_pi0/nvfp4_probe.cu:293-401 (create_resident_fp4, launch_resident_fp4,
+ * configure_resident_fp4_bf16, configure_resident_fp4_quantized, resident_fp4_resources,
+ * destroy_resident_fp4), bound in native_pi0/primitives.py:57-112.
+ */
+int create_resident_fp4(void** handle, const void* a, const void* b, const void* sfa, const void* sfb, void* out,
+                        int m, int n, int k, int workers, float alpha);
+int launch_resident_fp4(void* handle, void* stream);
+/* BF16 output [M, N] = alpha*acc + residual + bias, rounded once.  bias BF16 [N], residual BF16 [M, N]. */
+int configure_resident_fp4_bf16(void* handle, const void* bias, const void* residual, void* out);
+/* NVFP4 output: packed [M, No/2] + swizzled scales; activation 0 none, 1 GELU(tanh), 2 GeGLU over interleaved
+ * gate/up columns (No = N/2), 3 ReLU^2; otherwise No = N.  global_scale is the output's tensor scale. */
+int configure_resident_fp4_quantized(void* handle, const void* bias, const void* residual, void* out, void* scales,
+                                     float global_scale, int activation);
+int resident_fp4_resources(void* handle, int* values, int count);
+int destroy_resident_fp4(void* handle);
+/* extension: fused QKV epilogue - BF16 Q [M, ldq] (heads stored pair-interleaved), rotate-half RoPE with BF16
+ * cos/sin [rows, head_dim], K and V rows written to cache_k/cache_v [*, head_dim] at row cache_base + r.
+ * Replaces the BF16 path's configure_dense_qkv_rope (native_pi0/dense.cu:231-253). */
+int configure_resident_fp4_qkv_rope(void* handle, void* out_q, int ldq, const void* cos, const void* sin, void* cache_k,
+                                    void* cache_v, int q_cols, int head_dim, int cache_base);
+/* extension: logical row count (rows >= this are never stored) and output tile width (128, 64 or 32). */
+int configure_resident_fp4_rows(void* handle, int rows);
+int configure_resident_fp4_tile(void* handle, int block_n);
+
+/* ------------------------------------------------------------------------------------------------------
+ * LayerNorm / RMSNorm producer -> NVFP4 (format 4) or BF16 (format 16).
+ * Replaces: native_pi0/norm.cu:138-176 (create_norm, launch_norm, destroy_norm), bound in
+ * native_pi0/normalization.py:43-66.  Supported subset: BF16 input (fp16 == 0), no fused residual
+ * (residual, residual_output NULL), no AWQ inverse scale, formats 4 and 16, legacy_ties == 0; anything
+ * else returns cudaErrorInvalidValue.  gamma/beta are FP32 [width]; RMSNorm gamma already holds 1+w.
+ */
+int create_norm(void** handle, const void* input, const void* residual, const float* gamma, const float* beta,
+                const float* inverse_scale, void* residual_output, void* output, void* scales, int rows, int width,
+                int workers, int fp16, int format, int layer, int round_norm, int round_residual, int legacy_ties,
+                float epsilon, float global_scale);
+int launch_norm(void* handle, void* stream);
+int destroy_norm(void* handle);
+/* extension: skip normalisation (plain BF16 -> NVFP4 quantiser); policy 0 nearest, 1 ceil (weights). */
+int configure_norm_quantize_only(void* handle, int policy);
+/* extension: also store the normalised rows as BF16 [rows, width]. */
+int configure_norm_bf16_copy(void* handle, void* out_bf16);
+/* extension: input row stride (elements), FP4 output row stride (bytes), scale-layout blocks per row. */
+int configure_norm_layout(void* handle, int ld_in, int ld_out, int out_blocks);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Attention (MHA / GQA / MQA), BF16 in, FP32 softmax, BF16 out.
+ * Replaces: native_pi0/attention.cu:544-666 (create_attention, launch_attention, destroy_attention,
+ * configure_attention_splits, configure_attention_cache, attention_resources), bound in
+ * native_pi0/attention.py:60-110.  Supported subset: BF16 (fp16 == 0); biases, in-kernel RoPE tables and
+ * boolean masks must be NULL (RoPE is fused into the QKV projection epilogue); head_dim 72 or 256.
+ * prefix >= 0 selects the pi0 suffix mask (query 0 sees keys [0, prefix]); prefix < 0: no mask.
+ * Element (b, r, h, d) of q is q[((b*nq + r)*ldq) + h*hd + d]; keys likewise with ldkv and nk.
+ */
+int create_attention(void** handle, const void* q, const void* k, const void* v, const void* q_bias, const void* k_bias,
+                     const void* v_bias, const void* q_cos, const void* q_sin, const void* k_cos, const void* k_sin,
+                     void* out, const void* mask, int batches, int nq, int nk, int heads, int kv_heads, int head_dim,
+                     int ldq, int ldkv, int out_ld, int fp16, int workers, int prefix, float scale);
+int launch_attention(void* handle, void* stream);
+int destroy_attention(void* handle);
+int attention_resources(int* values, int count);
+/* Split the key range into `splits` parts; partial (o, m, l) go to library-owned scratch and a merge stage
+ * produces the output. */
+int configure_attention_splits(void* handle, int splits);
+/* Read keys/values from a KV cache [rows, head_dim] (BF16) instead of k/v; rows = total keys visible. */
+int configure_attention_cache(void* handle, const void* cache_k, const void* cache_v, int rows, int prefix_rows);
+/* extension: also quantise the output rows to NVFP4 (head_dim 256 only). */
+int configure_attention_fp4_output(void* handle, void* out_fp4, void* scales, int ld_bytes, int out_blocks,
+                                   float global_scale);
+/* extension: handle of the merge stage owned by an attention handle with splits > 1 (NULL otherwise). */
+int attention_merge_handle(void* handle, void** merge);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Small FP32 operators (the reference's NativeTensorOp modes 5, 6, 8, 10: native_pi0/model.cu:95-183,
+ * created from native_pi0/model.py:95-104,136-145).  extension: each is an operator handle of its own.
+ */
+/* patch embedding: images FP32 [views,224,224,3] (NULL = bound at launch), weight FP32 [588, width] with
+ * k = (dy*14+dx)*3+c, bias FP32 [width], pos FP32 [256, width], out BF16 [views*256, width]. */
+int create_patch_embed(void** handle, const float* images, const float* weight, const float* bias, const float* pos,
+                       void* out, int views, int width, int workers);
+/* token embedding rows: out[row_base+i, :] = bf16(table[tokens[i], :] * scale); tokens NULL = bound at launch. */
+int create_token_embed(void** handle, const long long* tokens, const void* table, void* out, int count, int width,
+                       int row_base, int vocab, float scale, int workers);
+/* out[r, n] = f(sum_k x[r + x_row_offset, k] w[n, k]);  flags: 1 x is BF16, 2 out is BF16, 4 SiLU, 8 multiply by
+ * rsqrt(mean(x^2)+eps), 16 Euler update out = prev + dt*value.  slot 0: x pointer, 2: launch state, 3: launch
+ * noise; prev_slot 3: previous value is the launch noise. */
+int create_linear32(void** handle, const void* x, const float* w, const float* bias, const float* prev, void* out,
+                    int rows, int n, int k, int ldx, int ldo, int flags, int slot, int prev_slot, int x_row_offset,
+                    float dt, float eps, int workers);
+/* expert input rows: row 0 = state embedding, rows 1..chunk = action embeddings, BF16 [*, width]. */
+int create_suffix_assemble(void** handle, const float* state_emb, const float* action_emb, void* out, int chunk,
+                           int width, int workers);
+int launch_op(void* handle, void* stream);      /* any operator handle, as a one-stage program */
+int destroy_op(void* handle);
+/* tiles, 128-row bands and K-cost of an operator handle (what the stream compiler needs). */
+int op_geometry(void* handle, int* tiles, int* bands, int* cost);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Whole-model program: one persistent launch over static per-worker instruction streams.
+ * Replaces: native_pi0/model.cu:188-303 (create_native_model, launch_native_model,
+ * read_native_model_timings, destroy_native_model), bound in native_pi0/model.py:286,303-305,318-337.
+ * NativeSpec is versioned against the reference's struct (native_pi0/model.cu:8-12): every stage is an
+ * operator handle, with up to four producer stages and a wait mode each (0 = same 128-row band, 1 = all).
+ * code: int32 [workers, length, 32] = {opcode, stage, first_tile, tile_count, 0...}; opcode 0 ends a stream.
+ */
+typedef struct NativeSpec {
+    int kind;            /* 0 GEMM, 1 attention, 2 norm, 3 small operator, 4 split-KV merge */
+    void* handle;
+    int sources[4];      /* producer stage index or -1 */
+    int modes[4];
+} NativeSpec;
+int create_native_model(void** handle, int count, const NativeSpec* specs, const int* code, int workers, int length);
+int launch_native_model(void* handle, void* stream, const float* images, const float* state, const float* noise,
+                        const long long* tokens);
+/* extension: run only stages [begin, end); producers before `begin` are taken as complete.  new_epoch != 0
+ * starts a new forward pass (first range of a pass). */
+int launch_native_model_range(void* handle, void* stream, const float* images, const float* state, const float* noise,
+                              const long long* tokens, int begin, int end, int new_epoch);
+/* per-instruction clock stamps, int64 [workers, length, 2] (start, end); enable before the launch to record. */
+int enable_native_model_timings(void* handle, int enable);
+int read_native_model_timings(void* handle, long long* out, size_t count);
+/* extension: synchronises the device and returns {code, worker, stage, band, observed, expected, aborted, epoch};
+ * code 0 ok, 1 dependency wait timed out, 2 pipeline barrier timed out, 3 bad instruction.  A non-zero status
+ * is cleared and the counters are reset so the handle stays usable. */
+int read_native_model_status(void* handle, int* values, int count);
+/* extension: counters uint32 [n] and the expected value per counter for the current epoch. */
+int read_native_model_counters(void* handle, unsigned int* counts, unsigned int* expected, int n, int* total);
+/* extension: time budget of every device-side wait in nanoseconds (default 2e9). */
+int set_native_model_wait_budget(void* handle, unsigned long long nanoseconds);
+int destroy_native_model(void* handle);
+
+/* Chain of GEMM stages in one launch with row-band counters.
+ * Replaces: native_pi0/native.cu:174-236 (create_native_linear, launch_native_linear, read_native_linear,
+ * destroy_native_linear), bound in native_pi0/linear.py:37-45. */
+int create_native_linear(void** handle, int count, void* const* stages, const int* parents, const int* code, int workers,
+                         int length);
+int launch_native_linear(void* handle, void* stream);
+int read_native_linear(void* handle, unsigned long long* counters, int count, unsigned long long* epoch);
+int destroy_native_linear(void* handle);
+
+/* ------------------------------------------------------------------------------------------------------
+ * extension: stand-alone BF16 -> NVFP4 quantiser (setup-time weight packing on the device).
+ * in BF16 [rows, ld_in]; out packed [rows, width/2]; scales swizzled with `out_blocks` blocks per row;
+ * policy 0 nearest, 1 ceil.  Bit-exact with pack_nvfp4 (native_pi0/quantization.py:48-93). */
+int quantize_nvfp4(const void* in, void* out, void* scales, int rows, int width, int ld_in, int out_blocks,
+                   float global_scale, int policy, void* stream);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Launch counting through CUPTI driver callbacks (proves "one launch per forward").
+ * Replaces: native_pi0/launch_trace.cpp:25-47, bound in native_pi0/launch_trace.py:7-17.  Returns CUptiResult. */
+int begin_launch_trace(void** handle);
+int end_launch_trace(void* handle, int* count, char* symbol, int symbol_bytes);
+const char* launch_trace_error(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PI0_NATIVE_H */

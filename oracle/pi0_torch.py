@@ -1,0 +1,386 @@
+"""PyTorch restatement of the pi0 forward pass (TEST INFRASTRUCTURE; runs on CPU or GPU).
+
+Two modes over the same state dict (OpenPI ``PI0Pytorch`` parameter names):
+
+* ``mode="bf16"``  - the BF16 eager model the reference compares against
+  (``benchmarks/openpi_backend.py:29-81`` ``fixed_sample``: prefix forward with ``use_cache=True``,
+  then ``steps`` Euler updates ``x += dt * v`` with ``dt = -1/steps`` from ``t = 1``).
+  OpenPI itself (Physical-Intelligence/openpi@215abfb2) is a network dependency of the reference and is
+  not available offline, so this is a restatement of its architecture as the reference's own model
+  builder walks it (``native_pi0/model.py:154-278``): SigLIP-So400m/14 blocks, PaliGemma projector,
+  Gemma-2B prefix, Gemma-300M action expert, state / action / time heads.  **Parity of this mode
+  with upstream OpenPI is unpinned** (no golden tensors exist for it).
+* ``mode="nvfp4"`` - the same graph with the engine's numerics: every transformer linear consumes an
+  NVFP4 fake-quantised activation (``nearest`` block scales, tensor scale 1) and an NVFP4
+  fake-quantised weight (``ceil`` block scales, tensor scale amax/(6*448)), accumulates in FP32, and
+  applies the epilogue roundings the kernels apply.  This is the "dequantised-NVFP4 math" oracle
+  (the reference's per-op form is ``deq(A) @ deq(B).T``, ``scripts/validate_nvfp4.py:49``).
+
+Conventions taken from the reference code: GELU tanh form (``native_pi0/dense.cu:53``); Gemma RMSNorm
+gamma = 1 + w (``model.py:129``); attention scale head_dim**-0.5; rotate-half RoPE over the whole head,
+base 10000 (``model.py:147-152``); suffix mask: state query sees prefix + itself, action queries see
+everything (``attention.cu:342``); time embedding 512 log-spaced periods 0.004..4.0, [sin | cos]
+(``model.py:259-263``); token embeddings * sqrt(width) (``model.py:238-239``); patch embedding, norm
+parameters and the state / action / time heads in FP32 (``README.md:93-94``).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+
+@dataclass
+class Pi0Dims:
+    views: int = 3
+    vision_layers: int = 27
+    vision_width: int = 1152
+    vision_mlp: int = 4304
+    vision_heads: int = 16
+    width: int = 2048
+    mlp: int = 16384
+    heads: int = 8
+    head_dim: int = 256
+    prefix_layers: int = 18
+    vocab: int = 257152
+    expert_width: int = 1024
+    expert_mlp: int = 4096
+    expert_layers: int = 18
+    action_dim: int = 32
+    ln_eps: float = 1e-6
+    rms_eps: float = 1e-6
+    rope_base: float = 10000.0
+
+
+VP = "paligemma_with_expert.paligemma.vision_tower.vision_model."
+PJ = "paligemma_with_expert.paligemma.multi_modal_projector.linear."
+LM = "paligemma_with_expert.paligemma.language_model."
+EX = "paligemma_with_expert.gemma_expert.model."
+
+
+def init_state_dict(dims: Pi0Dims, seed=0, device="cpu", dtype=torch.bfloat16):
+    """Random-init parameters: weights, biases and embeddings N(0, 0.02); LayerNorm weight 1 + N(0, 0.02);
+    Gemma RMSNorm weight N(0, 0.02) (gamma = 1 + w).  FP32 for patch embedding, norms and the heads."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    sd = {}
+
+    def put(name, shape, base=0.0, fp32=False):
+        t = torch.randn(shape, generator=g, dtype=torch.float32) * 0.02 + base
+        sd[name] = t.to(device=device, dtype=torch.float32 if fp32 else dtype)
+
+    d = dims
+    put(VP + "embeddings.patch_embedding.weight", (d.vision_width, 3, 14, 14), fp32=True)
+    put(VP + "embeddings.patch_embedding.bias", (d.vision_width,), fp32=True)
+    put(VP + "embeddings.position_embedding.weight", (256, d.vision_width), fp32=True)
+    for i in range(d.vision_layers):
+        p = f"{VP}encoder.layers.{i}."
+        for ln in ("layer_norm1", "layer_norm2"):
+            put(p + ln + ".weight", (d.vision_width,), 1.0, fp32=True)
+            put(p + ln + ".bias", (d.vision_width,), fp32=True)
+        for proj in ("q_proj", "k_proj", "v_proj", "out_proj"):
+            put(p + f"self_attn.{proj}.weight", (d.vision_width, d.vision_width))
+            put(p + f"self_attn.{proj}.bias", (d.vision_width,))
+        put(p + "mlp.fc1.weight", (d.vision_mlp, d.vision_width))
+        put(p + "mlp.fc1.bias", (d.vision_mlp,))
+        put(p + "mlp.fc2.weight", (d.vision_width, d.vision_mlp))
+        put(p + "mlp.fc2.bias", (d.vision_width,))
+    put(VP + "post_layernorm.weight", (d.vision_width,), 1.0, fp32=True)
+    put(VP + "post_layernorm.bias", (d.vision_width,), fp32=True)
+    put(PJ + "weight", (d.width, d.vision_width))
+    put(PJ + "bias", (d.width,))
+    put(LM + "embed_tokens.weight", (d.vocab, d.width))
+    for prefix, layers, width, mlp in ((LM, d.prefix_layers, d.width, d.mlp), (EX, d.expert_layers, d.expert_width, d.expert_mlp)):
+        for i in range(layers):
+            p = f"{prefix}layers.{i}."
+            put(p + "input_layernorm.weight", (width,), fp32=True)
+            put(p + "post_attention_layernorm.weight", (width,), fp32=True)
+            put(p + "self_attn.q_proj.weight", (d.heads * d.head_dim, width))
+            put(p + "self_attn.k_proj.weight", (d.head_dim, width))
+            put(p + "self_attn.v_proj.weight", (d.head_dim, width))
+            put(p + "self_attn.o_proj.weight", (width, d.heads * d.head_dim))
+            put(p + "mlp.gate_proj.weight", (mlp, width))
+            put(p + "mlp.up_proj.weight", (mlp, width))
+            put(p + "mlp.down_proj.weight", (width, mlp))
+        put(prefix + "norm.weight", (width,), fp32=True)
+    w = d.expert_width
+    put("state_proj.weight", (w, d.action_dim), fp32=True)
+    put("state_proj.bias", (w,), fp32=True)
+    put("action_in_proj.weight", (w, d.action_dim), fp32=True)
+    put("action_in_proj.bias", (w,), fp32=True)
+    put("action_time_mlp_in.weight", (w, 2 * w), fp32=True)
+    put("action_time_mlp_in.bias", (w,), fp32=True)
+    put("action_time_mlp_out.weight", (w, w), fp32=True)
+    put("action_time_mlp_out.bias", (w,), fp32=True)
+    put("action_out_proj.weight", (d.action_dim, w), fp32=True)
+    put("action_out_proj.bias", (d.action_dim,), fp32=True)
+    return sd
+
+
+# ---------------------------------------------------------------------------------------------------
+# NVFP4 fake quantisation in torch, byte-for-byte the arithmetic of native_pi0/quantization.py:48-93.
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def _ue4m3_table(device):
+    codes = torch.arange(127, device=device)
+    mant = (codes & 7).double()
+    expo = (codes >> 3).double()
+    return torch.where(expo == 0, mant * 2.0 ** -9, (1 + mant / 8) * torch.pow(torch.tensor(2.0, dtype=torch.float64, device=device), expo - 7)).float()
+
+
+def _nearest_even(values, table):
+    hi = torch.searchsorted(table, values.contiguous()).clamp(0, table.numel() - 1)
+    lo = (hi - 1).clamp(min=0)
+    dl, dh = values - table[lo], table[hi] - values
+    return torch.where((dl < dh) | ((dl == dh) & ((lo & 1) == 0)), lo, hi)
+
+
+def quantize_codes(x, policy="nearest", global_scale=1.0):
+    """FP32 [..., K] (K % 16 == 0) -> (E2M1 codes incl. sign bit, uint8 [..., K]; scale codes uint8 [..., K/16])."""
+    x = x.float()
+    table = _ue4m3_table(x.device)
+    e2m1 = torch.tensor(_E2M1, device=x.device)
+    gs = torch.tensor(global_scale, dtype=torch.float32, device=x.device)
+    xs = x * (torch.tensor(1.0, device=x.device) / gs)
+    blocks = xs.reshape(*x.shape[:-1], x.shape[-1] // 16, 16)
+    desired = blocks.abs().amax(-1) * torch.tensor(1 / 6, dtype=torch.float32, device=x.device)
+    if policy == "ceil":
+        codes = torch.searchsorted(table, desired.contiguous()).clamp(0, 126)
+    else:
+        codes = _nearest_even(desired, table)
+    scale = table[codes]
+    recip = torch.where(scale > 0, 1.0 / scale, torch.zeros_like(scale))
+    normalized = blocks * recip.unsqueeze(-1)
+    normalized = torch.where(scale.unsqueeze(-1) > 0, normalized, torch.zeros_like(normalized))
+    q = _nearest_even(normalized.abs(), e2m1)
+    q = q | (torch.signbit(normalized).long() << 3)
+    return q.reshape(x.shape).to(torch.uint8), codes.to(torch.uint8)
+
+
+def fake_quant(x, policy="nearest", global_scale=1.0):
+    """Quantise to NVFP4 and decode again (FP32 result, same shape)."""
+    q, codes = quantize_codes(x, policy, global_scale)
+    table = _ue4m3_table(x.device)
+    e2m1 = torch.tensor(_E2M1, device=x.device)
+    mag = e2m1[(q & 7).long()]
+    val = torch.where((q & 8) != 0, -mag, mag)
+    val = val.reshape(*x.shape[:-1], x.shape[-1] // 16, 16) * table[codes.long()].unsqueeze(-1)
+    return (val * torch.tensor(global_scale, dtype=torch.float32, device=x.device)).reshape(x.shape)
+
+
+def weight_global_scale(w):
+    """Tensor scale used for weights: the largest block scale lands on the top E4M3 code."""
+    return max(float(w.float().abs().max()) / (6.0 * 448.0), 1e-30)
+
+
+def pad_cols(x, multiple):
+    k = x.shape[-1]
+    pk = -(-k // multiple) * multiple
+    return x if pk == k else F.pad(x, (0, pk - k))
+
+
+# ---------------------------------------------------------------------------------------------------
+def rope_tables(positions, head_dim, base, dtype=torch.bfloat16, inv_freq_dtype=torch.float32):
+    """cos/sin [rows, head_dim] as the Gemma rotary module produces them: angles in FP32, emb = cat(f, f),
+    tables cast to the activation dtype.  ``inv_freq_dtype=torch.bfloat16`` reproduces a model whose
+    inverse-frequency buffer was cast to BF16 (``native_pi0/model.py:147-152``)."""
+    device = positions.device
+    inv = 1.0 / (base ** (torch.arange(0, head_dim, 2, dtype=torch.float32, device=device) / head_dim))
+    inv = inv.to(inv_freq_dtype).float()
+    freqs = positions.float()[:, None] * inv[None, :]
+    emb = torch.cat((freqs, freqs), dim=-1)
+    return emb.cos().to(dtype), emb.sin().to(dtype)
+
+
+def apply_rope(x, cos, sin):
+    """x [rows, heads, hd]; BF16 arithmetic as eager PyTorch does it: each product and the sum round to BF16."""
+    half = x.shape[-1] // 2
+    rot = torch.cat((-x[..., half:], x[..., :half]), dim=-1)
+    return (x * cos[:, None, :]) + (rot * sin[:, None, :])
+
+
+def time_embedding(t, width, device):
+    """``model.py:259-263``: 512 (width/2) periods log-spaced 0.004..4.0, [sin | cos], FP64 then FP32."""
+    fraction = torch.linspace(0.0, 1.0, width // 2, dtype=torch.float64, device=device)
+    period = 0.004 * (4.0 / 0.004) ** fraction
+    angle = float(t) / period * (2.0 * math.pi)
+    return torch.cat((angle.sin(), angle.cos())).float()
+
+
+class Pi0Torch:
+    def __init__(self, dims: Pi0Dims, state_dict, mode="bf16", compute_dtype=torch.bfloat16, rope_inv_freq_dtype=torch.float32):
+        assert mode in ("bf16", "nvfp4")
+        self.d, self.sd, self.mode = dims, state_dict, mode
+        self.dt = compute_dtype                 # activation dtype of the bf16 mode (float32 for a fast CPU baseline)
+        self.rope_inv_freq_dtype = rope_inv_freq_dtype
+        self._wq = {}
+        self.landmarks = {}
+
+    # ----- linear layers ---------------------------------------------------------------------------
+    def _qweight(self, name, w):
+        if name not in self._wq:
+            gs = weight_global_scale(w)
+            self._wq[name] = fake_quant(pad_cols(w.float(), 64), "ceil", gs)
+        return self._wq[name]
+
+    def linear(self, x, name, bias=True, weight=None):
+        """BF16 mode: y = x W^T + b in the activation dtype.  NVFP4 mode: FP32 accumulator of fake-quantised
+        operands (+ bias), *not yet rounded* - the caller applies the epilogue."""
+        w = self.sd[name + ".weight"] if weight is None else weight
+        b = self.sd.get(name + ".bias") if bias else None
+        if self.mode == "bf16":
+            return F.linear(x.to(self.dt), w.to(self.dt), None if b is None else b.to(self.dt))
+        wq = self._qweight(name, w)
+        xq = fake_quant(pad_cols(x.float(), 64), "nearest", 1.0)
+        y = xq @ wq.T
+        return y if b is None else y + b.float()
+
+    def act(self, y):
+        """Round an FP32 epilogue value to the BF16 activation (identity in bf16 mode)."""
+        return y.to(torch.bfloat16) if self.mode == "nvfp4" else y
+
+    # ----- attention -------------------------------------------------------------------------------
+    def attention(self, q, k, v, scale, mask=None):
+        """q [Nq,H,d], k/v [Nk,Hk,d] -> [Nq,H,d].  BF16 mode mirrors eager: BF16 scores, FP32 softmax, BF16 PV."""
+        groups = q.shape[1] // k.shape[1]
+        k = k.repeat_interleave(groups, 1)
+        v = v.repeat_interleave(groups, 1)
+        if self.mode == "nvfp4":
+            s = torch.einsum("qhd,khd->hqk", q.float(), k.float()) * scale
+            if mask is not None:
+                s = s.masked_fill(~mask[None], float("-inf"))
+            p = torch.softmax(s, dim=-1)
+            return torch.einsum("hqk,khd->qhd", p, v.float()).to(torch.bfloat16)
+        s = torch.einsum("qhd,khd->hqk", q, k) * scale
+        if mask is not None:
+            s = s.masked_fill(~mask[None], torch.finfo(s.dtype).min)
+        p = torch.softmax(s.float(), dim=-1).to(q.dtype)
+        return torch.einsum("hqk,khd->qhd", p, v)
+
+    # ----- SigLIP ----------------------------------------------------------------------------------
+    def vision(self, images):
+        """images FP32 [views,224,224,3] NHWC in [-1,1] -> tokens [views*256, vision_width]."""
+        d, sd = self.d, self.sd
+        x = images.permute(0, 3, 1, 2).float()
+        x = F.conv2d(x, sd[VP + "embeddings.patch_embedding.weight"].float(), sd[VP + "embeddings.patch_embedding.bias"].float(), stride=14)
+        x = x.flatten(2).transpose(1, 2) + sd[VP + "embeddings.position_embedding.weight"].float()[None]
+        x = x.reshape(-1, d.vision_width).to(self.dt if self.mode == "bf16" else torch.bfloat16)
+        self.landmarks["patch"] = x
+        hd = d.vision_width // d.vision_heads
+        views = images.shape[0]
+        for i in range(d.vision_layers):
+            p = f"{VP}encoder.layers.{i}."
+            y = F.layer_norm(x.float(), (d.vision_width,), sd[p + "layer_norm1.weight"].float(), sd[p + "layer_norm1.bias"].float(), d.ln_eps).to(x.dtype)
+            q = self.act(self.linear(y, p + "self_attn.q_proj"))
+            k = self.act(self.linear(y, p + "self_attn.k_proj"))
+            v = self.act(self.linear(y, p + "self_attn.v_proj"))
+            outs = []
+            for b in range(views):
+                sl = slice(b * 256, (b + 1) * 256)
+                outs.append(self.attention(q[sl].reshape(256, d.vision_heads, hd), k[sl].reshape(256, d.vision_heads, hd),
+                                           v[sl].reshape(256, d.vision_heads, hd), hd ** -0.5))
+            a = torch.cat(outs).reshape(-1, d.vision_width)
+            o = self.linear(a, p + "self_attn.out_proj")
+            x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+            y = F.layer_norm(x.float(), (d.vision_width,), sd[p + "layer_norm2.weight"].float(), sd[p + "layer_norm2.bias"].float(), d.ln_eps).to(x.dtype)
+            h = self.linear(y, p + "mlp.fc1")
+            h = F.gelu(h.float(), approximate="tanh") if self.mode == "nvfp4" else F.gelu(h, approximate="tanh")
+            o = self.linear(h, p + "mlp.fc2")
+            x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+            self.landmarks[f"vision.{i}"] = x
+        y = F.layer_norm(x.float(), (d.vision_width,), sd[VP + "post_layernorm.weight"].float(), sd[VP + "post_layernorm.bias"].float(), d.ln_eps).to(x.dtype)
+        return self.act(self.linear(y, PJ[:-1]))
+
+    # ----- Gemma -----------------------------------------------------------------------------------
+    def rms(self, x, w):
+        xf = x.float()
+        y = xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + self.d.rms_eps) * (1.0 + w.float())
+        return y.to(x.dtype)
+
+    def gemma_layer(self, x, prefix, i, cos, sin, cache, mask, kv_only=False):
+        """One decoder layer on rows x [N, width].  ``cache`` = (K, V) of earlier rows or None.  Returns (x, (K, V))."""
+        d, sd = self.d, self.sd
+        p = f"{prefix}layers.{i}."
+        y = self.rms(x, sd[p + "input_layernorm.weight"])
+        k = self.act(self.linear(y, p + "self_attn.k_proj", bias=False)).reshape(-1, 1, d.head_dim)
+        v = self.act(self.linear(y, p + "self_attn.v_proj", bias=False)).reshape(-1, 1, d.head_dim)
+        k = apply_rope(k, cos, sin)
+        if cache is not None:
+            k_all, v_all = torch.cat((cache[0], k)), torch.cat((cache[1], v))
+        else:
+            k_all, v_all = k, v
+        if kv_only:
+            return x, (k, v)
+        q = self.act(self.linear(y, p + "self_attn.q_proj", bias=False)).reshape(-1, d.heads, d.head_dim)
+        q = apply_rope(q, cos, sin)
+        a = self.attention(q, k_all, v_all, d.head_dim ** -0.5, mask).reshape(x.shape[0], -1)
+        o = self.linear(a, p + "self_attn.o_proj", bias=False)
+        x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+        y = self.rms(x, sd[p + "post_attention_layernorm.weight"])
+        gate = self.linear(y, p + "mlp.gate_proj", bias=False)
+        up = self.linear(y, p + "mlp.up_proj", bias=False)
+        h = F.gelu(gate.float(), approximate="tanh") * up.float() if self.mode == "nvfp4" else F.gelu(gate, approximate="tanh") * up
+        o = self.linear(h, p + "mlp.down_proj", bias=False)
+        x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+        return x, (k, v)
+
+    def prefix(self, images, tokens):
+        d, sd = self.d, self.sd
+        x = self.vision(images)
+        self.landmarks["image_tokens"] = x
+        if tokens is not None and tokens.numel():
+            emb = sd[LM + "embed_tokens.weight"][tokens.reshape(-1)]
+            emb = (emb.to(x.dtype) * math.sqrt(d.width)).to(x.dtype)
+            x = torch.cat((x, emb))
+        rows = x.shape[0]
+        cos, sin = rope_tables(torch.arange(rows, device=x.device), d.head_dim, d.rope_base, torch.bfloat16 if self.mode == "nvfp4" else x.dtype, self.rope_inv_freq_dtype)
+        caches = []
+        for i in range(d.prefix_layers):
+            x, kv = self.gemma_layer(x, LM, i, cos, sin, None, None, kv_only=(i == d.prefix_layers - 1))
+            caches.append(kv)
+            self.landmarks[f"prefix.{i}"] = x
+        return caches
+
+    def denoise_step(self, caches, state_emb, actions, t, prefix_rows):
+        d, sd = self.d, self.sd
+        w = d.expert_width
+        chunk = actions.shape[0]
+        a_emb = F.linear(actions.float(), sd["action_in_proj.weight"].float(), sd["action_in_proj.bias"].float())
+        t_emb = time_embedding(t, w, actions.device)[None].expand(chunk, -1)
+        h = F.linear(torch.cat((a_emb, t_emb), dim=-1), sd["action_time_mlp_in.weight"].float(), sd["action_time_mlp_in.bias"].float())
+        h = F.silu(h)
+        h = F.linear(h, sd["action_time_mlp_out.weight"].float(), sd["action_time_mlp_out.bias"].float())
+        adt = torch.bfloat16 if self.mode == "nvfp4" else self.dt
+        x = torch.cat((state_emb, h)).to(adt)
+        rows = chunk + 1
+        cos, sin = rope_tables(torch.arange(prefix_rows, prefix_rows + rows, device=x.device), d.head_dim, d.rope_base, adt, self.rope_inv_freq_dtype)
+        mask = torch.ones(rows, prefix_rows + rows, dtype=torch.bool, device=x.device)
+        mask[0, prefix_rows + 1:] = False
+        for i in range(d.expert_layers):
+            x, _ = self.gemma_layer(x, EX, i, cos, sin, caches[i], mask)
+        xf = x[1:].float()
+        if self.mode == "nvfp4":
+            # engine: FP32 projection of the BF16 rows with (1+w) folded, times the row's 1/rms
+            y = (xf * (1.0 + sd[EX + "norm.weight"].float())) * torch.rsqrt(xf.square().mean(-1, keepdim=True) + d.rms_eps)
+        else:
+            y = self.rms(x[1:], sd[EX + "norm.weight"]).float()
+        return F.linear(y, sd["action_out_proj.weight"].float(), sd["action_out_proj.bias"].float())
+
+    @torch.no_grad()
+    def sample_actions(self, images, state, noise, tokens=None, steps=10):
+        """images [views,224,224,3], state [1,32], noise [1,chunk,32], tokens [1,T] -> actions FP32 [1,chunk,32]."""
+        self.landmarks = {}
+        caches = self.prefix(images, tokens)
+        prefix_rows = caches[0][0].shape[0]
+        state_emb = F.linear(state.float(), self.sd["state_proj.weight"].float(), self.sd["state_proj.bias"].float())
+        x = noise[0].float().clone()
+        t = torch.tensor(1.0, dtype=torch.float32)
+        dt = torch.tensor(-1.0 / steps, dtype=torch.float32)
+        for step in range(steps):
+            v = self.denoise_step(caches, state_emb, x, float(t), prefix_rows)
+            x = x + dt.to(x.device) * v
+            self.landmarks[f"actions.{step}"] = x.clone()
+            t = t + dt
+        return x[None]

@@ -1,0 +1,342 @@
+// Attention instruction: softmax(scale * Q K^T + mask) V for one (batch, head, 128-query tile, KV split).
+//
+// Eight warps, 16 query rows each. K/V stream through shared memory in 64-key chunks (cp.async, double buffered);
+// QK^T and PV run on the tensor cores (mma.sync m16n8k16, BF16 in, FP32 accumulate) with an online softmax in the
+// exp2 domain. MQA/GQA: the KV head is head / (heads / kv_heads). The pi0 suffix mask hides keys beyond `prefix` from
+// query row 0 (the state token). With splits > 1 the tile writes un-normalised FP32 partials (o, m, l) for OP_MERGE;
+// otherwise it normalises, rounds to BF16, and optionally quantises the rows to NVFP4 in the same pass.
+#pragma once
+#include "vm_core.cuh"
+
+namespace pi0 {
+
+constexpr int kAttnQRows = 128;
+constexpr int kAttnChunk = 64;
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;       // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack2_bf16(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <int HD>
+__device__ __forceinline__ void attn_load_rows(__nv_bfloat16* dst, const __nv_bfloat16* src, int ld, int rows_total,
+                                               int row0, int valid_rows, int head_dim) {
+    // rows_total rows of HD (padded) elements into dst[row][HD+8]; rows >= valid_rows and columns >= head_dim are zero.
+    constexpr int LD = HD + 8, CPR = HD / 8;
+    for (int i = threadIdx.x; i < rows_total * CPR; i += kThreads) {
+        const int r = i / CPR, c = i - r * CPR;
+        const bool ok = r < valid_rows && c * 8 < head_dim;
+        const __nv_bfloat16* s = ok ? src + static_cast<size_t>(row0 + r) * ld + c * 8 : src;
+        cp_async16(dst + r * LD + c * 8, s, ok);
+    }
+}
+
+template <int HD>
+__device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
+    constexpr int LD = HD + 8;
+    constexpr int KSTEPS = HD / 16;           // along the head dimension
+    constexpr int ONT = HD / 8;               // output n-tiles
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(data);
+    __nv_bfloat16* sK = sQ + kAttnQRows * LD;
+    __nv_bfloat16* sV = sK + 2 * kAttnChunk * LD;
+
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    const int split = tile % a.splits;
+    const int t2 = tile / a.splits;
+    const int head = t2 % a.heads;
+    const int qbg = t2 / a.heads;
+    const int qtiles = (a.nq + kAttnQRows - 1) / kAttnQRows;
+    const int batch = qbg / qtiles, qt = qbg - batch * qtiles;
+    const int q0 = qt * kAttnQRows;
+    const int q_valid = min(kAttnQRows, a.nq - q0);
+    const int kvh = head / (a.heads / a.kv_heads);
+    const int per = (a.nk + a.splits - 1) / a.splits;
+    const int k_begin = split * per, k_end = min(a.nk, k_begin + per);
+    const int nchunks = (max(k_end - k_begin, 0) + kAttnChunk - 1) / kAttnChunk;
+
+    const __nv_bfloat16* qsrc = static_cast<const __nv_bfloat16*>(a.q) + static_cast<size_t>(batch) * a.q_batch_rows * a.ldq + head * a.head_dim;
+    const __nv_bfloat16* ksrc = static_cast<const __nv_bfloat16*>(a.k) + static_cast<size_t>(batch) * a.kv_batch_rows * a.ldkv + kvh * a.head_dim;
+    const __nv_bfloat16* vsrc = static_cast<const __nv_bfloat16*>(a.v) + static_cast<size_t>(batch) * a.kv_batch_rows * a.ldkv + kvh * a.head_dim;
+
+    attn_load_rows<HD>(sQ, qsrc, a.ldq, kAttnQRows, q0, q_valid, a.head_dim);
+    if (nchunks > 0) {
+        attn_load_rows<HD>(sK, ksrc, a.ldkv, kAttnChunk, k_begin, min(kAttnChunk, k_end - k_begin), a.head_dim);
+        attn_load_rows<HD>(sV, vsrc, a.ldkv, kAttnChunk, k_begin, min(kAttnChunk, k_end - k_begin), a.head_dim);
+    }
+    cp_async_commit();
+
+    float o[ONT][4];
+#pragma unroll
+    for (int j = 0; j < ONT; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const float sl2 = a.scale * 1.4426950408889634f;
+    const bool warp_active = warp * 16 < q_valid;
+    const int row_a = warp * 16 + (lane >> 2);            // local query rows of this thread: row_a, row_a + 8
+    const __nv_bfloat16* q_lane = sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + (lane >> 4) * 8;
+
+    for (int c = 0; c < nchunks; ++c) {
+        const int buf = c & 1;
+        if (c + 1 < nchunks) {
+            const int kb = k_begin + (c + 1) * kAttnChunk;
+            attn_load_rows<HD>(sK + (buf ^ 1) * kAttnChunk * LD, ksrc, a.ldkv, kAttnChunk, kb, min(kAttnChunk, k_end - kb), a.head_dim);
+            attn_load_rows<HD>(sV + (buf ^ 1) * kAttnChunk * LD, vsrc, a.ldkv, kAttnChunk, kb, min(kAttnChunk, k_end - kb), a.head_dim);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        if (warp_active) {
+            const __nv_bfloat16* kbuf = sK + buf * kAttnChunk * LD;
+            const __nv_bfloat16* vbuf = sV + buf * kAttnChunk * LD;
+            const int key_base = k_begin + c * kAttnChunk;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                if (key_base + half * 32 >= k_end) break;
+                float s[4][4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
+                const __nv_bfloat16* k_lane = kbuf + (half * 32 + (lane & 7) + (lane >> 4) * 8) * LD + ((lane >> 3) & 1) * 8;
+#pragma unroll
+                for (int kk = 0; kk < KSTEPS; ++kk) {
+                    uint32_t qa[4];
+                    ldsm_x4(qa, q_lane + kk * 16);
+#pragma unroll
+                    for (int jp = 0; jp < 2; ++jp) {
+                        uint32_t kb4[4];
+                        ldsm_x4(kb4, k_lane + jp * 16 * LD + kk * 16);
+                        mma_bf16(s[2 * jp], qa, kb4[0], kb4[1]);
+                        mma_bf16(s[2 * jp + 1], qa, kb4[2], kb4[3]);
+                    }
+                }
+                // scale, mask, online softmax
+                float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const int key = key_base + half * 32 + j * 8 + 2 * (lane & 3) + (e & 1);
+                        const int qrow = q0 + row_a + (e >> 1) * 8;
+                        bool visible = key < k_end;
+                        if (a.prefix >= 0 && qrow == 0 && key > a.prefix) visible = false;
+                        float val = visible ? s[j][e] * sl2 : -INFINITY;
+                        s[j][e] = val;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], val);
+                    }
+                }
+                float corr[2], m_use[2];
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+                    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+                    const float m_new = fmaxf(m_run[r], mx[r]);
+                    m_use[r] = m_new == -INFINITY ? 0.f : m_new;
+                    corr[r] = exp2f(m_run[r] - m_use[r]);
+                    m_run[r] = m_new;
+                }
+                float psum[2] = {0.f, 0.f};
+                uint32_t pa[2][4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float p0 = exp2f(s[j][0] - m_use[0]), p1 = exp2f(s[j][1] - m_use[0]);
+                    const float p2 = exp2f(s[j][2] - m_use[1]), p3 = exp2f(s[j][3] - m_use[1]);
+                    psum[0] += p0 + p1;
+                    psum[1] += p2 + p3;
+                    pa[j >> 1][(j & 1) * 2 + 0] = pack2_bf16(p0, p1);
+                    pa[j >> 1][(j & 1) * 2 + 1] = pack2_bf16(p2, p3);
+                }
+#pragma unroll
+                for (int r = 0; r < 2; r++) l_run[r] = l_run[r] * corr[r] + psum[r];
+#pragma unroll
+                for (int j = 0; j < ONT; j++) {
+                    o[j][0] *= corr[0]; o[j][1] *= corr[0];
+                    o[j][2] *= corr[1]; o[j][3] *= corr[1];
+                }
+                const __nv_bfloat16* v_lane = vbuf + (half * 32 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + (lane >> 4) * 8;
+#pragma unroll
+                for (int ks = 0; ks < 2; ++ks) {
+#pragma unroll
+                    for (int dp = 0; dp < ONT / 2; ++dp) {
+                        uint32_t vb4[4];
+                        ldsm_x4_trans(vb4, v_lane + ks * 16 * LD + dp * 16);
+                        mma_bf16(o[2 * dp], pa[ks], vb4[0], vb4[1]);
+                        mma_bf16(o[2 * dp + 1], pa[ks], vb4[2], vb4[3]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (nchunks == 0) { cp_async_wait<0>(); __syncthreads(); }
+
+    // quad-reduce the row sums
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 1);
+        l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
+    }
+
+    if (a.splits > 1) {
+        if (warp_active) {
+            float* po = a.partial_o + static_cast<size_t>(tile) * kAttnQRows * a.head_dim;
+            float* pml = a.partial_ml + static_cast<size_t>(tile) * kAttnQRows * 2;
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const int row = row_a + r * 8;
+                if (row < q_valid) {
+#pragma unroll
+                    for (int j = 0; j < ONT; j++) {
+                        const int col = j * 8 + 2 * (lane & 3);
+                        if (col < a.head_dim)
+                            *reinterpret_cast<float2*>(po + static_cast<size_t>(row) * a.head_dim + col) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+                    }
+                    if ((lane & 3) == 0) {
+                        pml[row * 2] = m_run[r];
+                        pml[row * 2 + 1] = l_run[r];
+                    }
+                }
+            }
+        }
+        return;
+    }
+
+    // normalise, round to BF16, stage the tile in the (now free) Q rows of this warp
+    if (warp_active) {
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
+            __nv_bfloat16* dst = sQ + (row_a + r * 8) * LD + 2 * (lane & 3);
+#pragma unroll
+            for (int j = 0; j < ONT; j++)
+                *reinterpret_cast<uint32_t*>(dst + j * 8) = pack2_bf16(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+        }
+    }
+    __syncthreads();
+    const size_t grow0 = static_cast<size_t>(batch) * a.q_batch_rows + q0;
+    if (a.out) {
+        const int cpr = a.head_dim / 8;
+        for (int i = threadIdx.x; i < q_valid * cpr; i += kThreads) {
+            const int r = i / cpr, c = i - r * cpr;
+            uint4 val = *reinterpret_cast<const uint4*>(sQ + r * LD + c * 8);
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(a.out) + (grow0 + r) * a.ldo + head * a.head_dim + c * 8) = val;
+        }
+    }
+    if (a.out_fp4) {
+        const int bpr = a.head_dim / 16;
+        for (int i = threadIdx.x; i < q_valid * bpr; i += kThreads) {
+            const int r = i / bpr, b = i - r * bpr;
+            const uint4* sp = reinterpret_cast<const uint4*>(sQ + r * LD + b * 16);
+            uint4 u0 = sp[0], u1 = sp[1];
+            const uint32_t w[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+            float v[16];
+#pragma unroll
+            for (int e = 0; e < 8; e++) {
+                float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[e]));
+                v[2 * e] = f.x * a.out_inv_gs;
+                v[2 * e + 1] = f.y * a.out_inv_gs;
+            }
+            uint32_t code;
+            uint2 bytes = quantize_block16(v, 0, code);
+            const int grow = static_cast<int>(grow0) + r;
+            const int col = head * a.head_dim + b * 16;
+            *reinterpret_cast<uint2*>(a.out_fp4 + static_cast<size_t>(grow) * a.ld_fp4 + (col >> 1)) = bytes;
+            a.out_scales[scale_offset(grow, col >> 4, a.out_blocks)] = static_cast<uint8_t>(code);
+        }
+    }
+}
+
+__device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
+                                                 int stage_index, int first, int count) {
+    const AttnParams& a = st.p.attn;
+    int current_band = -1;
+    for (int t = first; t < first + count; ++t) {
+        const int band = tile_band(st, t);
+        if (band != current_band) {
+            if (!cta_wait_sources(prog, ctl, st, stage_index, band)) return;
+            current_band = band;
+        }
+        if (a.head_dim > 128) attn_tile<256>(a, t, data);
+        else attn_tile<80>(a, t, data);
+        cta_publish_tile(prog, st, t);
+    }
+}
+
+// Split-KV merge: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s, one head per tile.
+__device__ __forceinline__ void merge_tile(const MergeParams& g, int head) {
+    const int bpr = g.head_dim / 16;
+    for (int i = threadIdx.x; i < g.nq * bpr; i += kThreads) {
+        const int r = i / bpr, b = i - r * bpr;
+        float big = -INFINITY;
+        for (int s = 0; s < g.splits; s++) big = fmaxf(big, __ldcg(g.partial_ml + (static_cast<size_t>(head * g.splits + s) * kAttnQRows + r) * 2));
+        float acc[16];
+#pragma unroll
+        for (int e = 0; e < 16; e++) acc[e] = 0.f;
+        float denom = 0.f;
+        for (int s = 0; s < g.splits; s++) {
+            const size_t t = static_cast<size_t>(head * g.splits + s);
+            const float m = __ldcg(g.partial_ml + (t * kAttnQRows + r) * 2), l = __ldcg(g.partial_ml + (t * kAttnQRows + r) * 2 + 1);
+            if (m == -INFINITY) continue;
+            const float w = exp2f(m - big);
+            denom += w * l;
+            const float4* src = reinterpret_cast<const float4*>(g.partial_o + (t * kAttnQRows + r) * g.head_dim + b * 16);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                float4 x = __ldcg(src + q);
+                acc[4 * q] += w * x.x; acc[4 * q + 1] += w * x.y; acc[4 * q + 2] += w * x.z; acc[4 * q + 3] += w * x.w;
+            }
+        }
+        const float inv = denom > 0.f ? 1.f / denom : 0.f;
+        float v[16];
+#pragma unroll
+        for (int e = 0; e < 16; e++) v[e] = bf16_round(acc[e] * inv);
+        const int col = head * g.head_dim + b * 16;
+        if (g.out) {
+            uint32_t w[8];
+#pragma unroll
+            for (int e = 0; e < 8; e++) w[e] = pack2_bf16(v[2 * e], v[2 * e + 1]);
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(r) * g.ldo + col);
+            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+        if (g.out_fp4) {
+#pragma unroll
+            for (int e = 0; e < 16; e++) v[e] *= g.out_inv_gs;
+            uint32_t code;
+            uint2 bytes = quantize_block16(v, 0, code);
+            *reinterpret_cast<uint2*>(g.out_fp4 + static_cast<size_t>(r) * g.ld_fp4 + (col >> 1)) = bytes;
+            g.out_scales[scale_offset(r, col >> 4, g.out_blocks)] = static_cast<uint8_t>(code);
+        }
+    }
+}
+
+__device__ __forceinline__ void merge_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage_index,
+                                                  int first, int count) {
+    if (!cta_wait_sources(prog, ctl, st, stage_index, 0)) return;
+    for (int t = first; t < first + count; ++t) {
+        merge_tile(st.p.merge, t);
+        cta_publish_tile(prog, st, t);
+    }
+}
+
+}  // namespace pi0

@@ -1,0 +1,270 @@
+// NVFP4 block-scaled GEMM instruction:  out[M,N] = epilogue(alpha * deq(A)[M,K] . deq(B)[N,K]^T)
+//
+//   warp 0 / lane 0 : TMA producer  - operand tiles (128 B swizzled rows) and scale atoms into a 5-stage ring
+//   warp 1 / lane 0 : MMA issuer    - tcgen05.cp (scales smem->TMEM) + tcgen05.mma kind::mxf4nvf4, K = 64 each
+//   warps 4..7      : epilogue      - tcgen05.ld of a 128xN FP32 accumulator (one row per thread), fused math, stores
+//
+// Two TMEM accumulators alternate, so the epilogue of tile t overlaps the MMAs of tile t+1. Pipeline positions live in
+// registers (PipeState) and carry over from one instruction to the next; barriers are never re-initialised.
+#pragma once
+#include "vm_core.cuh"
+
+namespace pi0 {
+
+__device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
+                                              int stage_index, int first, int count, PipeState& ps) {
+    const GemmParams& g = st.p.gemm;
+    const int kstages = (g.k_groups + 3) >> 2;
+    const uint32_t b_bytes = static_cast<uint32_t>(g.block_n) * 128u;
+    int current_band = -1;
+    for (int t = first; t < first + count; ++t) {
+        const int m_tile = t / g.n_tiles, n_tile = t - m_tile * g.n_tiles;
+        const int band = tile_band(st, t);
+        if (band != current_band) {
+            if (!wait_sources(prog, ctl, st, stage_index, band)) return;
+            fence_proxy_async_global();
+            current_band = band;
+        }
+        const int sfb_tile = (n_tile * g.block_n) >> 7;
+        for (int ks = 0; ks < kstages; ++ks) {
+            const uint32_t s = ps.prod_it % kStages, phase = (ps.prod_it / kStages) & 1u;
+            if (!mbar_wait(prog, ctl, &ctl->empty[s], phase ^ 1u, stage_index)) return;
+            const int groups = min(4, g.k_groups - ks * 4);
+            uint8_t* slot = data + s * kStageBytes;
+            mbar_expect_tx(&ctl->full[s], kTileABytes + b_bytes + 2u * groups * 512u);
+            tma_load_2d(slot, g.tmap_a, &ctl->full[s], ks * 128, m_tile * 128);
+            tma_load_2d(slot + kTileABytes, g.tmap_b, &ctl->full[s], ks * 128, n_tile * g.block_n);
+            bulk_load(slot + 2 * kTileABytes, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4) * 512,
+                      groups * 512u, &ctl->full[s]);
+            bulk_load(slot + 2 * kTileABytes + kSfBytes, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4) * 512,
+                      groups * 512u, &ctl->full[s]);
+            ps.prod_it++;
+        }
+    }
+}
+
+__device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem, const StageDesc& st,
+                                         int stage_index, int first, int count, PipeState& ps) {
+    const GemmParams& g = st.p.gemm;
+    const int kstages = (g.k_groups + 3) >> 2;
+    for (int t = first; t < first + count; ++t) {
+        const int n_tile = t % g.n_tiles;
+        const uint32_t buf = ps.mma_tile & 1u, acc_phase = (ps.mma_tile >> 1) & 1u;
+        if (!mbar_wait(prog, ctl, &ctl->acc_empty[buf], acc_phase ^ 1u, stage_index)) return;
+        tc_fence_after();
+        const uint32_t d = tmem + buf * 128u;
+        // Scale rows of a narrow B tile sit in the 32-row sub-column of their 128-row atom.
+        const uint32_t sfb_sub = static_cast<uint32_t>((n_tile * g.block_n) & 127) >> 5;
+        for (int ks = 0; ks < kstages; ++ks) {
+            const uint32_t s = ps.mma_it % kStages, phase = (ps.mma_it / kStages) & 1u;
+            if (!mbar_wait(prog, ctl, &ctl->full[s], phase, stage_index)) return;
+            tc_fence_after();
+            const int groups = min(4, g.k_groups - ks * 4);
+            const uint32_t a_addr = smem_u32(data + s * kStageBytes);
+            const uint32_t b_addr = a_addr + kTileABytes;
+            const uint32_t sfa_addr = a_addr + 2 * kTileABytes;
+            const uint32_t sfb_addr = sfa_addr + kSfBytes;
+            const uint64_t a_desc = umma_desc_k_sw128(a_addr), b_desc = umma_desc_k_sw128(b_addr);
+            for (int gi = 0; gi < groups; ++gi) {
+                const uint32_t sfa_t = tmem + kSfCol0 + (s * 4 + gi) * 8;
+                const uint32_t sfb_t = sfa_t + 4;
+                tc_copy_sf(sfa_t, umma_desc_sf(sfa_addr + gi * 512));
+                tc_copy_sf(sfb_t, umma_desc_sf(sfb_addr + gi * 512));
+                // 64 FP4 = 32 bytes along K inside the 128-byte swizzled row: advance the start address by 2 units.
+                tc_mma_nvfp4(d, a_desc + 2u * gi, b_desc + 2u * gi, g.idesc, sfa_t, sfb_t + sfb_sub,
+                             static_cast<uint32_t>((ks | gi) != 0));
+            }
+            tc_commit(&ctl->empty[s]);     // slot reusable once these MMAs have read it
+            ps.mma_it++;
+        }
+        tc_commit(&ctl->acc_full[buf]);    // accumulator complete
+        ps.mma_tile++;
+    }
+}
+
+// ---- epilogue helpers ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pack_bf16x2(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
+    __nv_bfloat162 h = *reinterpret_cast<__nv_bfloat162*>(&u);
+    return __bfloat1622float2(h);
+}
+__device__ __forceinline__ float gelu_sigmoid(float x) {
+    // x * sigmoid(2u), u = sqrt(2/pi)(x + 0.044715 x^3): identical to the tanh form.
+    float z = 1.5957691216057308f * x * (1.f + 0.044715f * x * x);
+    return x / (1.f + __expf(-z));
+}
+
+// One 32-column chunk of one accumulator row (thread == row).
+__device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const uint32_t (&raw)[32], int row, int col0,
+                                                    bool row_ok) {
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(raw[i]) * g.alpha;
+    if (!row_ok) return;
+    if (g.epilogue == EPI_F32) {
+        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + static_cast<size_t>(row) * g.ldo + col0);
+#pragma unroll
+        for (int i = 0; i < 8; i++) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        return;
+    }
+    if (g.epilogue == EPI_GEGLU_FP4) {
+        // interleaved (gate, up) column pairs -> 16 outputs = one scale block
+        float h[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) h[i] = gelu_sigmoid(v[2 * i]) * v[2 * i + 1] * g.out_inv_gs;
+        uint32_t code;
+        uint2 bytes = quantize_block16(h, 0, code);
+        const int out_col = col0 >> 1;
+        *reinterpret_cast<uint2*>(static_cast<uint8_t*>(g.out) + static_cast<size_t>(row) * g.ldo + (out_col >> 1)) = bytes;
+        g.out_scales[scale_offset(row, out_col >> 4, g.out_blocks)] = static_cast<uint8_t>(code);
+        return;
+    }
+    if (g.bias) {
+        const uint4* b = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(g.bias) + col0);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint4 u = __ldg(b + i);
+            float2 f;
+            f = unpack_bf16x2(u.x); v[8 * i + 0] += f.x; v[8 * i + 1] += f.y;
+            f = unpack_bf16x2(u.y); v[8 * i + 2] += f.x; v[8 * i + 3] += f.y;
+            f = unpack_bf16x2(u.z); v[8 * i + 4] += f.x; v[8 * i + 5] += f.y;
+            f = unpack_bf16x2(u.w); v[8 * i + 6] += f.x; v[8 * i + 7] += f.y;
+        }
+    }
+    if (g.residual) {
+        const uint4* r = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(g.residual) +
+                                                        static_cast<size_t>(row) * g.ldr + col0);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint4 u = __ldcg(r + i);
+            float2 f;
+            f = unpack_bf16x2(u.x); v[8 * i + 0] += f.x; v[8 * i + 1] += f.y;
+            f = unpack_bf16x2(u.y); v[8 * i + 2] += f.x; v[8 * i + 3] += f.y;
+            f = unpack_bf16x2(u.z); v[8 * i + 4] += f.x; v[8 * i + 5] += f.y;
+            f = unpack_bf16x2(u.w); v[8 * i + 6] += f.x; v[8 * i + 7] += f.y;
+        }
+    }
+    if (g.epilogue == EPI_BF16) {
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(row) * g.ldo + col0);
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+            dst[i] = make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                                pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+        return;
+    }
+    if (g.epilogue == EPI_FP4) {
+        if (g.act == 1) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = gelu_sigmoid(v[i]);
+        } else if (g.act == 3) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) { float r = fmaxf(v[i], 0.f); v[i] = r * r; }
+        }
+        uint32_t words[4];
+        uint32_t codes = 0;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            float h[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) h[i] = v[16 * half + i] * g.out_inv_gs;
+            uint32_t code;
+            uint2 bytes = quantize_block16(h, 0, code);
+            words[2 * half] = bytes.x;
+            words[2 * half + 1] = bytes.y;
+            codes |= code << (8 * half);
+        }
+        *reinterpret_cast<uint4*>(static_cast<uint8_t*>(g.out) + static_cast<size_t>(row) * g.ldo + (col0 >> 1)) =
+            make_uint4(words[0], words[1], words[2], words[3]);
+        *reinterpret_cast<uint16_t*>(g.out_scales + scale_offset(row, col0 >> 4, g.out_blocks)) = static_cast<uint16_t>(codes);
+        return;
+    }
+    // EPI_QKV_ROPE: values are first rounded to BF16 (the projection output), then rotated.
+    {
+        const int hd = g.head_dim, half = hd >> 1;
+        const int kv0 = g.q_cols;                      // K columns [kv0, kv0+hd), V columns [kv0+hd, kv0+2hd)
+        const bool is_v = col0 >= kv0 + hd;
+        const bool is_k = !is_v && col0 >= kv0;
+        const int in_head = is_v ? col0 - kv0 - hd : (is_k ? col0 - kv0 : col0 % hd);
+        uint32_t packed[16];
+        if (is_v) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) packed[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+        } else {
+            // Q and K heads are stored pair-interleaved: column 2i holds original dim i, column 2i+1 holds dim i+hd/2.
+            const __nv_bfloat16* cs = static_cast<const __nv_bfloat16*>(g.rope_cos) + static_cast<size_t>(row) * hd;
+            const __nv_bfloat16* sn = static_cast<const __nv_bfloat16*>(g.rope_sin) + static_cast<size_t>(row) * hd;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int dim = (in_head >> 1) + i;
+                float x1 = bf16_round(v[2 * i]), x2 = bf16_round(v[2 * i + 1]);
+                float c1 = __bfloat162float(cs[dim]), s1 = __bfloat162float(sn[dim]);
+                float c2 = __bfloat162float(cs[dim + half]), s2 = __bfloat162float(sn[dim + half]);
+                float o1 = bf16_round(x1 * c1) + bf16_round(-x2 * s1);
+                float o2 = bf16_round(x2 * c2) + bf16_round(x1 * s2);
+                packed[i] = pack_bf16x2(o1, o2);
+            }
+        }
+        __nv_bfloat16* dst;
+        if (is_v) dst = static_cast<__nv_bfloat16*>(g.cache_v) + static_cast<size_t>(g.cache_base + row) * hd + in_head;
+        else if (is_k) dst = static_cast<__nv_bfloat16*>(g.cache_k) + static_cast<size_t>(g.cache_base + row) * hd + in_head;
+        else dst = static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(row) * g.ldo + col0;
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+        for (int i = 0; i < 4; i++) d4[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+    }
+}
+
+__device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, uint32_t tmem, const StageDesc& st,
+                                              int stage_index, int first, int count, PipeState& ps) {
+    const GemmParams& g = st.p.gemm;
+    const int quarter = (threadIdx.x >> 5) & 3;          // TMEM lane quarter this warp may read
+    const int lane = lane_id();
+    for (int t = first; t < first + count; ++t) {
+        const int m_tile = t / g.n_tiles, n_tile = t - m_tile * g.n_tiles;
+        const uint32_t buf = ps.epi_tile & 1u, phase = (ps.epi_tile >> 1) & 1u;
+        if (!mbar_wait(prog, ctl, &ctl->acc_full[buf], phase, stage_index)) return;
+        tc_fence_after();
+        const int row = m_tile * 128 + quarter * 32 + lane;
+        const bool row_ok = row < g.rows;
+        const uint32_t taddr = tmem + buf * 128u + (static_cast<uint32_t>(quarter * 32) << 16);
+        const int chunks = g.block_n >> 5;
+        for (int c = 0; c < chunks; ++c) {
+            uint32_t raw[32];
+            tmem_ld32(taddr + c * 32, raw);
+            tmem_ld_wait();
+            if (c == chunks - 1) {
+                // every column of this accumulator is in registers: hand the buffer back to the MMA lane
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
+            }
+            gemm_epilogue_chunk(g, raw, row, n_tile * g.block_n + c * 32, row_ok);
+        }
+        // each epilogue warp publishes its own 32 rows (a GEMM tile counts 4 units): no CTA barrier on this path
+        fence_proxy_async_global();
+        __syncwarp();
+        if (lane == 0) publish_tile(prog, st, t);
+        ps.epi_tile++;
+    }
+}
+
+// Dispatch of one GEMM instruction onto the warp roles. Warps 2 and 3 have no role and fall through.
+__device__ __forceinline__ void gemm_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem,
+                                                 const StageDesc& st, int stage_index, int first, int count,
+                                                 PipeState& ps) {
+    const int warp = threadIdx.x >> 5;
+    if (warp == 0) {
+        if (lane_id() == 0) gemm_producer(prog, ctl, data, st, stage_index, first, count, ps);
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane_id() == 0) gemm_mma(prog, ctl, data, tmem, st, stage_index, first, count, ps);
+        __syncwarp();
+    } else if (warp >= 4) {
+        gemm_epilogue(prog, ctl, tmem, st, stage_index, first, count, ps);
+    }
+}
+
+}  // namespace pi0

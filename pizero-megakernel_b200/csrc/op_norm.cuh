@@ -1,0 +1,127 @@
+// Fused LayerNorm / RMSNorm -> NVFP4 producer (also plain BF16 -> NVFP4 quantisation).
+//
+// One warp per row, eight rows per tile. A lane owns the 16-element scale blocks lane, lane+32, ...; each block is two
+// 16-byte loads, statistics are warp-shuffle reductions in FP32, and a block leaves as one 8-byte store of E2M1 codes
+// plus one E4M3 scale byte in the swizzled 128x4 atom layout.
+#pragma once
+#include "vm_core.cuh"
+
+namespace pi0 {
+
+constexpr int kNormRowsPerTile = 8;
+constexpr int kNormMaxBlocksPerLane = 4;     // normalising modes: width <= 2048
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ void load_block16(const __nv_bfloat16* src, float (&v)[16]) {
+    const uint4* p = reinterpret_cast<const uint4*>(src);
+    uint4 a = __ldcg(p), b = __ldcg(p + 1);
+    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+        float2 f = __bfloat1622float2(h);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+}
+
+__device__ __forceinline__ void store_block16(const NormParams& n, int row, int block, float (&v)[16]) {
+    if (n.out_bf16) {
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(n.out_bf16) + static_cast<size_t>(row) * n.width + block * 16);
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    if (n.out) {
+#pragma unroll
+        for (int i = 0; i < 16; i++) v[i] *= n.inv_gs;
+        uint32_t code;
+        uint2 bytes = quantize_block16(v, n.policy, code);
+        *reinterpret_cast<uint2*>(n.out + static_cast<size_t>(row) * n.ld_out + block * 8) = bytes;
+        n.out_scales[scale_offset(row, block, n.out_blocks)] = static_cast<uint8_t>(code);
+    }
+}
+
+__device__ __forceinline__ void norm_row(const NormParams& n, int row) {
+    const int lane = lane_id();
+    const int blocks = n.width >> 4;
+    const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(n.in) + static_cast<size_t>(row) * n.ld_in;
+    if (n.mode == 2) {                       // quantise only: stream blocks, nothing cached
+        for (int b = lane; b < blocks; b += 32) {
+            float v[16];
+            load_block16(src + b * 16, v);
+            store_block16(n, row, b, v);
+        }
+        return;
+    }
+    float cache[kNormMaxBlocksPerLane][16];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < kNormMaxBlocksPerLane; j++) {
+        const int b = lane + 32 * j;
+        if (b < blocks) {
+            load_block16(src + b * 16, cache[j]);
+#pragma unroll
+            for (int i = 0; i < 16; i++) sum += cache[j][i];
+        }
+    }
+    const float inv_width = 1.f / static_cast<float>(n.width);
+    const float mean = n.mode == 1 ? warp_sum(sum) * inv_width : 0.f;
+    float sq = 0.f;
+#pragma unroll
+    for (int j = 0; j < kNormMaxBlocksPerLane; j++) {
+        const int b = lane + 32 * j;
+        if (b < blocks) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                float d = cache[j][i] - mean;
+                sq += d * d;
+            }
+        }
+    }
+    const float rstd = rsqrtf(warp_sum(sq) * inv_width + n.eps);
+#pragma unroll
+    for (int j = 0; j < kNormMaxBlocksPerLane; j++) {
+        const int b = lane + 32 * j;
+        if (b < blocks) {
+            float v[16];
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                float y = (cache[j][i] - mean) * rstd;
+                if (n.gamma) y *= n.gamma[b * 16 + i];
+                if (n.beta) y += n.beta[b * 16 + i];
+                v[i] = n.round_norm ? bf16_round(y) : y;
+            }
+            store_block16(n, row, b, v);
+        }
+    }
+}
+
+__device__ __forceinline__ void norm_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage_index,
+                                                 int first, int count) {
+    const NormParams& n = st.p.norm;
+    const int warp = threadIdx.x >> 5;
+    int current_band = -1;
+    for (int t = first; t < first + count; ++t) {
+        const int band = tile_band(st, t);
+        if (band != current_band) {
+            if (!cta_wait_sources(prog, ctl, st, stage_index, band)) return;
+            current_band = band;
+        }
+        const int row = t * kNormRowsPerTile + warp;
+        if (row < n.rows) norm_row(n, row);
+        cta_publish_tile(prog, st, t);
+    }
+}
+
+}  // namespace pi0

@@ -1,0 +1,152 @@
+// Small FP32 operators around the transformer blocks: patch embedding, token embedding, FP32 linears with fused
+// SiLU / RMS factor / Euler update, and the expert-input assembly. All are CTA-wide, coalesced CUDA-core code.
+#pragma once
+#include "vm_core.cuh"
+#include "op_norm.cuh"
+
+namespace pi0 {
+
+constexpr int kPatchTokens = 16;      // tokens per tile
+constexpr int kPatchCols = 256;       // output columns per tile (one per thread)
+constexpr int kPatchK = 14 * 14 * 3;  // 588
+
+// out[t, n] = sum_k patch[t, k] * W[k, n] + bias[n] + pos[t % 256, n];  k = (dy*14 + dx)*3 + c, images are NHWC.
+__device__ __forceinline__ void patch_tile(const PatchParams& p, const float* images, int tile, uint8_t* data) {
+    float* sp = reinterpret_cast<float*>(data);                    // [16][588]
+    const int ntiles = (p.width + kPatchCols - 1) / kPatchCols;
+    const int tt = tile / ntiles, nt = tile - tt * ntiles;
+    for (int i = threadIdx.x; i < kPatchTokens * kPatchK; i += kThreads) {
+        const int tok = i / kPatchK, k = i - tok * kPatchK;
+        const int dy = k / 42, rem = k - dy * 42;
+        const int t = tt * kPatchTokens + tok;
+        const int view = t >> 8, pidx = t & 255, py = pidx >> 4, px = pidx & 15;
+        sp[i] = images[((static_cast<size_t>(view) * 224 + py * 14 + dy) * 224 + px * 14) * 3 + rem];
+    }
+    __syncthreads();
+    const int n = nt * kPatchCols + threadIdx.x;
+    if (n < p.width) {
+        float acc[kPatchTokens];
+#pragma unroll
+        for (int i = 0; i < kPatchTokens; i++) acc[i] = 0.f;
+        for (int k = 0; k < kPatchK; k++) {
+            const float w = __ldg(p.weight + static_cast<size_t>(k) * p.width + n);
+#pragma unroll
+            for (int i = 0; i < kPatchTokens; i++) acc[i] = fmaf(sp[i * kPatchK + k], w, acc[i]);
+        }
+        const float b = p.bias[n];
+#pragma unroll
+        for (int i = 0; i < kPatchTokens; i++) {
+            const int t = tt * kPatchTokens + i;
+            const float y = acc[i] + b + p.pos[static_cast<size_t>(t & 255) * p.width + n];
+            static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(t) * p.width + n] = __float2bfloat16_rn(y);
+        }
+    }
+}
+
+__device__ __forceinline__ void patch_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
+                                                  int stage_index, int first, int count) {
+    const PatchParams& p = st.p.patch;
+    const float* images = p.images ? p.images : prog.in.images;
+    if (!cta_wait_sources(prog, ctl, st, stage_index, 0)) return;
+    for (int t = first; t < first + count; ++t) {
+        patch_tile(p, images, t, data);
+        cta_publish_tile(prog, st, t);
+    }
+}
+
+// Token rows: out[row_base + i, :] = bf16(table[token_i, :] * scale); eight tokens per tile, one warp each.
+__device__ __forceinline__ void embed_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage_index,
+                                                  int first, int count) {
+    const EmbedParams& e = st.p.embed;
+    const long long* tokens = e.tokens ? e.tokens : prog.in.tokens;
+    if (!cta_wait_sources(prog, ctl, st, stage_index, 0)) return;
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    for (int t = first; t < first + count; ++t) {
+        const int i = t * 8 + warp;
+        if (i < e.count) {
+            long long tok = tokens[i];
+            tok = tok < 0 ? 0 : (tok >= e.vocab ? e.vocab - 1 : tok);
+            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(e.table) + static_cast<size_t>(tok) * e.width;
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(e.out) + static_cast<size_t>(e.row_base + i) * e.width;
+            for (int c = lane; c < e.width; c += 32) dst[c] = __float2bfloat16_rn(__bfloat162float(src[c]) * e.scale);
+        }
+        cta_publish_tile(prog, st, t);
+    }
+}
+
+// out[r, n] = f(sum_k x[r, k] * W[n, k]); one output column per warp, eight columns per tile, rows in groups of 16.
+__device__ __forceinline__ void linear32_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st,
+                                                     int stage_index, int first, int count) {
+    const Linear32Params& p = st.p.lin;
+    const void* xbase = p.slot == 2 ? static_cast<const void*>(prog.in.state)
+                        : p.slot == 3 ? static_cast<const void*>(prog.in.noise) : p.x;
+    const float* prev = p.prev_slot == 3 ? prog.in.noise : p.prev;
+    if (!cta_wait_sources(prog, ctl, st, stage_index, 0)) return;
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    for (int t = first; t < first + count; ++t) {
+        const int n = t * 8 + warp;
+        if (n < p.n) {
+            const float* wrow = p.w + static_cast<size_t>(n) * p.k;
+            for (int r0 = 0; r0 < p.rows; r0 += 16) {
+                float acc[16], ss[16];
+#pragma unroll
+                for (int i = 0; i < 16; i++) { acc[i] = 0.f; ss[i] = 0.f; }
+                for (int k0 = lane * 4; k0 < p.k; k0 += 128) {
+                    const float4 w4 = __ldg(reinterpret_cast<const float4*>(wrow + k0));
+#pragma unroll
+                    for (int i = 0; i < 16; i++) {
+                        const int r = r0 + i;
+                        if (r < p.rows) {
+                            float4 x4;
+                            const size_t off = static_cast<size_t>(r + p.x_row_offset) * p.ldx + k0;
+                            if (p.x_bf16) {
+                                uint2 u = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(xbase) + off));
+                                float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.x));
+                                float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.y));
+                                x4 = make_float4(a.x, a.y, b.x, b.y);
+                            } else {
+                                x4 = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(xbase) + off));
+                            }
+                            acc[i] += x4.x * w4.x + x4.y * w4.y + x4.z * w4.z + x4.w * w4.w;
+                            if (p.rms) ss[i] += x4.x * x4.x + x4.y * x4.y + x4.z * x4.z + x4.w * x4.w;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const int r = r0 + i;
+                    if (r >= p.rows) break;
+                    float v = warp_sum(acc[i]);
+                    if (p.rms) v *= rsqrtf(warp_sum(ss[i]) / static_cast<float>(p.k) + p.eps);
+                    if (lane == 0) {
+                        if (p.bias) v += p.bias[n];
+                        if (p.silu) v = v / (1.f + expf(-v));
+                        if (p.euler) v = __fadd_rn(__ldcg(prev + static_cast<size_t>(r) * p.n + n), __fmul_rn(p.dt, v));
+                        if (p.out_bf16) static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = __float2bfloat16_rn(v);
+                        else static_cast<float*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = v;
+                    }
+                }
+            }
+        }
+        cta_publish_tile(prog, st, t);
+    }
+}
+
+// Expert input: row 0 = state embedding, rows 1..chunk = action/time embeddings, as BF16. Eight rows per tile.
+__device__ __forceinline__ void suffix_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage_index,
+                                                   int first, int count) {
+    const SuffixParams& p = st.p.suffix;
+    if (!cta_wait_sources(prog, ctl, st, stage_index, 0)) return;
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    for (int t = first; t < first + count; ++t) {
+        const int r = t * 8 + warp;
+        if (r <= p.chunk) {
+            const float* src = r == 0 ? p.state_emb : p.action_emb + static_cast<size_t>(r - 1) * p.width;
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.out) + static_cast<size_t>(r) * p.width;
+            for (int c = lane; c < p.width; c += 32) dst[c] = __float2bfloat16_rn(__ldcg(src + c));
+        }
+        cta_publish_tile(prog, st, t);
+    }
+}
+
+}  // namespace pi0

@@ -1,0 +1,950 @@
+// Host runtime and C ABI of libpi0_native.so: operator handles, program assembly (counters, expected
+// contributions, compacted instruction streams), TMA tensor maps and the single persistent launch.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <memory>
+#include <vector>
+
+#include "../../include/pi0_native.h"
+#include "vm_kernel.cuh"
+
+namespace pi0 {
+namespace {
+
+constexpr uint32_t kOpMagic = 0x7069304f;       // "pi0O"
+constexpr uint32_t kProgramMagic = 0x70693050;  // "pi0P"
+
+int check_device(int* device_out) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    cudaDeviceProp prop{};
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return e;
+    if (prop.major != 10) return cudaErrorInvalidConfiguration;
+    *device_out = device;
+    return cudaSuccess;
+}
+int sm_count(int device) {
+    int n = 0;
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
+    return n;
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiled encoder() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+// Packed FP4 matrix [rows, k/2] bytes, boxes of 128 bytes x box_rows with the 128-byte swizzle.
+int encode_operand(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+    EncodeTiled fn = encoder();
+    if (!fn) return cudaErrorNotSupported;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(k / 2)};
+    cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+struct Program;
+
+struct Op {
+    uint32_t magic = kOpMagic;
+    int device = 0;
+    int workers = 1;
+    int cost = 64;                     // K-like weight for the stream compiler
+    StageDesc desc{};
+    // GEMM bookkeeping (tensor maps are rebuilt when the tile width changes)
+    const void *a = nullptr, *b = nullptr;
+    int m = 0, n = 0, k = 0;
+    CUtensorMap* maps = nullptr;       // device: [0] = A, [1] = B
+    // attention bookkeeping
+    Op* merge = nullptr;               // owned merge stage (splits > 1)
+    float* partial_o = nullptr;
+    float* partial_ml = nullptr;
+    Program* solo = nullptr;           // lazily built one/two-stage program for stand-alone launches
+    bool solo_dirty = true;
+};
+
+struct Program {
+    uint32_t magic = kProgramMagic;
+    int device = 0;
+    int workers = 0, length = 0;
+    std::vector<StageDesc> stages;
+    std::vector<unsigned int> expected;
+    StageDesc* d_stages = nullptr;
+    int4* d_code = nullptr;
+    unsigned int* d_counters = nullptr;
+    unsigned int* d_expected = nullptr;
+    VmStatus* d_status = nullptr;
+    long long* d_timings = nullptr;
+    bool timings_on = false;
+    unsigned int epoch = 0;
+    unsigned long long budget_ns = 2000000000ull;
+    ~Program() {
+        cudaFree(d_stages);
+        cudaFree(d_code);
+        cudaFree(d_counters);
+        cudaFree(d_expected);
+        cudaFree(d_status);
+        cudaFree(d_timings);
+    }
+};
+
+int units_of(const StageDesc& d) { return d.kind == OP_GEMM ? 4 : 1; }
+
+// Fill counter bookkeeping of a stage from its geometry.
+void finish_desc(StageDesc& d) {
+    d.units_per_tile = units_of(d);
+    for (int i = 0; i < kMaxSources; i++) {
+        d.src[i] = -1;
+        d.src_mode[i] = SRC_ALL_BANDS;
+    }
+}
+
+// Least-loaded contiguous tile ranges, the same policy as native_pi0.program.linear_streams.
+std::vector<int> compile_streams(const std::vector<std::pair<int, int>>& work, int workers, int* length_out) {
+    std::vector<std::vector<int>> rows(workers);
+    std::vector<long long> load(workers, 0);
+    for (size_t s = 0; s < work.size(); s++) {
+        int tiles = work[s].first, k = work[s].second;
+        int parts = std::min(workers, tiles), small = tiles / parts, extra = tiles % parts;
+        std::vector<int> order(workers);
+        for (int i = 0; i < workers; i++) order[i] = i;
+        std::stable_sort(order.begin(), order.end(), [&](int x, int y) { return load[x] < load[y]; });
+        int start = 0;
+        for (int r = 0; r < parts; r++) {
+            int w = order[r], count = small + (r < extra ? 1 : 0);
+            rows[w].insert(rows[w].end(), {1, static_cast<int>(s), start, count});
+            load[w] += static_cast<long long>(count) * k;
+            start += count;
+        }
+    }
+    size_t length = 1;
+    for (auto& r : rows) length = std::max(length, r.size() / 4);
+    std::vector<int> code(static_cast<size_t>(workers) * length * 4, 0);
+    for (int w = 0; w < workers; w++) std::copy(rows[w].begin(), rows[w].end(), code.begin() + static_cast<size_t>(w) * length * 4);
+    *length_out = static_cast<int>(length);
+    return code;
+}
+
+// Build a program from stage descriptors (sources already set) and compact int4 instructions.
+int build_program(Program** out, int device, const std::vector<StageDesc>& stages_in, const std::vector<int>& code4,
+                  int workers, int length) {
+    auto prog = std::make_unique<Program>();
+    prog->device = device;
+    prog->workers = workers;
+    prog->length = length;
+    prog->stages = stages_in;
+    int counters = 0;
+    for (auto& d : prog->stages) {
+        d.counter_base = counters;
+        counters += d.bands;
+    }
+    prog->expected.assign(counters, 0);
+    for (auto& d : prog->stages)
+        for (int t = 0; t < d.tiles; t++) prog->expected[d.counter_base + std::min(t / d.band_div, d.bands - 1)] += d.units_per_tile;
+    // static validation: stage order per worker, every tile exactly once, sources earlier than consumers
+    std::vector<std::vector<int>> cover(prog->stages.size());
+    for (size_t s = 0; s < prog->stages.size(); s++) {
+        cover[s].assign(prog->stages[s].tiles, 0);
+        for (int i = 0; i < kMaxSources; i++)
+            if (prog->stages[s].src[i] >= static_cast<int>(s)) return cudaErrorInvalidValue;
+    }
+    for (int w = 0; w < workers; w++) {
+        int last = -1;
+        bool ended = false;
+        for (int i = 0; i < length; i++) {
+            const int* ins = &code4[(static_cast<size_t>(w) * length + i) * 4];
+            if (ins[0] == 0) { ended = true; continue; }
+            if (ended) return cudaErrorInvalidValue;
+            int s = ins[1];
+            if (s < 0 || s >= static_cast<int>(prog->stages.size()) || s < last) return cudaErrorInvalidValue;
+            if (ins[3] < 1 || ins[2] < 0 || ins[2] + ins[3] > prog->stages[s].tiles) return cudaErrorInvalidValue;
+            for (int t = ins[2]; t < ins[2] + ins[3]; t++) cover[s][t]++;
+            last = s;
+        }
+    }
+    for (auto& c : cover)
+        for (int v : c)
+            if (v != 1) return cudaErrorInvalidValue;
+
+    cudaError_t e = cudaMalloc(&prog->d_stages, sizeof(StageDesc) * prog->stages.size());
+    if (e == cudaSuccess) e = cudaMalloc(&prog->d_code, sizeof(int4) * static_cast<size_t>(workers) * length);
+    if (e == cudaSuccess) e = cudaMalloc(&prog->d_counters, sizeof(unsigned int) * std::max(counters, 1));
+    if (e == cudaSuccess) e = cudaMalloc(&prog->d_expected, sizeof(unsigned int) * std::max(counters, 1));
+    if (e == cudaSuccess) e = cudaMalloc(&prog->d_status, sizeof(VmStatus));
+    if (e == cudaSuccess) e = cudaMemcpy(prog->d_stages, prog->stages.data(), sizeof(StageDesc) * prog->stages.size(), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(prog->d_code, code4.data(), sizeof(int4) * static_cast<size_t>(workers) * length, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemset(prog->d_counters, 0, sizeof(unsigned int) * std::max(counters, 1));
+    if (e == cudaSuccess && counters) e = cudaMemcpy(prog->d_expected, prog->expected.data(), sizeof(unsigned int) * counters, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemset(prog->d_status, 0, sizeof(VmStatus));
+    if (e == cudaSuccess) {
+        static bool configured[64] = {};
+        if (device < 64 && !configured[device]) {
+            e = cudaFuncSetAttribute(pi0_vm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+            configured[device] = e == cudaSuccess;
+        }
+    }
+    if (e != cudaSuccess) return e;
+    *out = prog.release();
+    return cudaSuccess;
+}
+
+int launch_program(Program* prog, cudaStream_t stream, LaunchInputs in, int begin, int end, bool new_epoch) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device != prog->device) return cudaErrorInvalidDevice;
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    e = cudaStreamIsCapturing(stream, &capture);
+    if (e != cudaSuccess) return e;
+    if (capture != cudaStreamCaptureStatusNone) return cudaErrorStreamCaptureUnsupported;
+    if (new_epoch) {
+        if (prog->epoch >= (1u << 20)) {          // keep expected * epoch far from 2^32
+            e = cudaMemsetAsync(prog->d_counters, 0, sizeof(unsigned int) * std::max<size_t>(prog->expected.size(), 1), stream);
+            if (e != cudaSuccess) return e;
+            prog->epoch = 0;
+        }
+        prog->epoch++;
+    }
+    VmProgram p{};
+    p.stages = prog->d_stages;
+    p.code = prog->d_code;
+    p.counters = prog->d_counters;
+    p.expected = prog->d_expected;
+    p.status = prog->d_status;
+    p.timings = prog->timings_on ? prog->d_timings : nullptr;
+    p.num_stages = static_cast<int>(prog->stages.size());
+    p.length = prog->length;
+    p.epoch = prog->epoch;
+    p.stage_begin = begin;
+    p.stage_end = end;
+    p.wait_budget_ns = prog->budget_ns;
+    p.in = in;
+    pi0_vm_kernel<<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
+    return cudaGetLastError();
+}
+
+Op* as_op(void* h) {
+    Op* op = static_cast<Op*>(h);
+    return op && op->magic == kOpMagic ? op : nullptr;
+}
+Program* as_program(void* h) {
+    Program* p = static_cast<Program*>(h);
+    return p && p->magic == kProgramMagic ? p : nullptr;
+}
+
+int new_op(Op** out, int workers) {
+    int device = 0;
+    int e = check_device(&device);
+    if (e) return e;
+    if (workers < 1 || workers > sm_count(device)) return cudaErrorInvalidConfiguration;
+    Op* op = new Op();
+    op->device = device;
+    op->workers = workers;
+    *out = op;
+    return cudaSuccess;
+}
+
+void free_op(Op* op) {
+    if (!op) return;
+    if (op->merge) free_op(op->merge);
+    delete op->solo;
+    cudaFree(op->maps);
+    cudaFree(op->partial_o);
+    cudaFree(op->partial_ml);
+    op->magic = 0;
+    delete op;
+}
+
+int gemm_refresh(Op* op) {
+    GemmParams& g = op->desc.p.gemm;
+    CUtensorMap host[2];
+    int e = encode_operand(&host[0], op->a, op->m, op->k, 128);
+    if (!e) e = encode_operand(&host[1], op->b, op->n, op->k, g.block_n);
+    if (e) return e;
+    if (!op->maps) {
+        cudaError_t ce = cudaMalloc(&op->maps, 2 * sizeof(CUtensorMap));
+        if (ce != cudaSuccess) return ce;
+    }
+    cudaError_t ce = cudaMemcpy(op->maps, host, sizeof(host), cudaMemcpyHostToDevice);
+    if (ce != cudaSuccess) return ce;
+    g.tmap_a = op->maps;
+    g.tmap_b = op->maps + 1;
+    g.m_tiles = op->m / 128;
+    g.n_tiles = op->n / g.block_n;
+    g.k_groups = op->k / 64;
+    const char* fmt_env = getenv("PI0_FP4_FORMAT_CODE");
+    const uint32_t fmt = fmt_env ? static_cast<uint32_t>(atoi(fmt_env)) & 7u : 1u;    // E2M1 for kind::mxf4nvf4
+    g.idesc = (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(g.block_n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+    op->desc.tiles = g.m_tiles * g.n_tiles;
+    op->desc.bands = g.m_tiles;
+    op->desc.band_div = g.n_tiles;
+    op->cost = op->k;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+
+// Stand-alone program of one operator (plus its merge stage when the attention is split).
+int solo_program(Op* op) {
+    if (op->solo && !op->solo_dirty) return cudaSuccess;
+    delete op->solo;
+    op->solo = nullptr;
+    std::vector<StageDesc> stages{op->desc};
+    std::vector<std::pair<int, int>> work{{op->desc.tiles, op->cost}};
+    if (op->merge) {
+        StageDesc m = op->merge->desc;
+        m.src[0] = 0;
+        m.src_mode[0] = SRC_ALL_BANDS;
+        stages.push_back(m);
+        work.push_back({m.tiles, 64});
+    }
+    int length = 0;
+    std::vector<int> code = compile_streams(work, op->workers, &length);
+    int e = build_program(&op->solo, op->device, stages, code, op->workers, length);
+    if (!e) op->solo_dirty = false;
+    return e;
+}
+
+int launch_solo(void* handle, void* stream) {
+    Op* op = as_op(handle);
+    if (!op) return cudaErrorInvalidValue;
+    int device = 0;
+    cudaError_t ce = cudaGetDevice(&device);
+    if (ce != cudaSuccess) return ce;
+    if (device != op->device) return cudaErrorInvalidDevice;
+    int e = solo_program(op);
+    if (e) return e;
+    return launch_program(op->solo, static_cast<cudaStream_t>(stream), LaunchInputs{}, 0, static_cast<int>(op->solo->stages.size()), true);
+}
+
+int destroy_checked(void* handle) {
+    if (!handle) return cudaSuccess;
+    Op* op = as_op(handle);
+    if (!op) return cudaErrorInvalidValue;
+    int device = 0;
+    cudaError_t ce = cudaGetDevice(&device);
+    if (ce != cudaSuccess) return ce;
+    if (device != op->device) return cudaErrorInvalidDevice;
+    free_op(op);
+    return cudaSuccess;
+}
+
+__global__ void quantize_rows_kernel(NormParams n) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row < n.rows) norm_row(n, row);
+}
+
+}  // namespace
+}  // namespace pi0
+
+using namespace pi0;
+
+// =====================================================================================================
+extern "C" int create_resident_fp4(void** handle, const void* a, const void* b, const void* sfa, const void* sfb, void* out,
+                                   int m, int n, int k, int workers, float alpha) {
+    if (!handle) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (!a || !b || !sfa || !sfb || !out || m < 128 || m % 128 || n < 128 || n % 128 || k < 64 || k % 64 ||
+        !std::isfinite(alpha) || alpha <= 0)
+        return cudaErrorInvalidValue;
+    Op* op = nullptr;
+    int e = new_op(&op, workers);
+    if (e) return e;
+    op->a = a; op->b = b; op->m = m; op->n = n; op->k = k;
+    StageDesc& d = op->desc;
+    d.kind = OP_GEMM;
+    finish_desc(d);
+    GemmParams& g = d.p.gemm;
+    g.sfa = static_cast<const uint8_t*>(sfa);
+    g.sfb = static_cast<const uint8_t*>(sfb);
+    g.block_n = 128;
+    g.alpha = alpha;
+    g.epilogue = EPI_F32;
+    g.rows = m;
+    g.out = out;
+    g.ldo = n;
+    g.out_inv_gs = 1.f;
+    e = gemm_refresh(op);
+    if (e) { free_op(op); return e; }
+    *handle = op;
+    return cudaSuccess;
+}
+extern "C" int launch_resident_fp4(void* handle, void* stream) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM) return cudaErrorInvalidValue;
+    return launch_solo(handle, stream);
+}
+extern "C" int configure_resident_fp4_bf16(void* handle, const void* bias, const void* residual, void* out) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || !out) return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    g.epilogue = EPI_BF16;
+    g.bias = bias; g.residual = residual; g.ldr = op->n;
+    g.out = out; g.ldo = op->n;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_resident_fp4_quantized(void* handle, const void* bias, const void* residual, void* out, void* scales,
+                                                float global_scale, int activation) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || !out || !scales || !std::isfinite(global_scale) || global_scale <= 0 ||
+        activation < 0 || activation > 3)
+        return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    if (activation == 2 && (bias || residual || op->n % 256)) return cudaErrorInvalidValue;
+    const int width = activation == 2 ? op->n / 2 : op->n;
+    g.epilogue = activation == 2 ? EPI_GEGLU_FP4 : EPI_FP4;
+    g.act = activation == 2 ? 0 : activation;
+    g.bias = bias; g.residual = residual; g.ldr = op->n;
+    g.out = out; g.ldo = width / 2;
+    g.out_scales = static_cast<uint8_t*>(scales);
+    g.out_blocks = width / 16;
+    g.out_inv_gs = 1.f / global_scale;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_resident_fp4_qkv_rope(void* handle, void* out_q, int ldq, const void* cos, const void* sin,
+                                               void* cache_k, void* cache_v, int q_cols, int head_dim, int cache_base) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || !cos || !sin || !cache_k || !cache_v || head_dim < 32 || head_dim % 32 ||
+        q_cols < 0 || q_cols % head_dim || q_cols + 2 * head_dim != op->n || (q_cols && !out_q) || cache_base < 0)
+        return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    g.epilogue = EPI_QKV_ROPE;
+    g.bias = nullptr; g.residual = nullptr;
+    g.out = out_q; g.ldo = ldq;
+    g.rope_cos = cos; g.rope_sin = sin;
+    g.cache_k = cache_k; g.cache_v = cache_v;
+    g.q_cols = q_cols; g.head_dim = head_dim; g.cache_base = cache_base;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_resident_fp4_rows(void* handle, int rows) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || rows < 1 || rows > op->m) return cudaErrorInvalidValue;
+    op->desc.p.gemm.rows = rows;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_resident_fp4_tile(void* handle, int block_n) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || (block_n != 128 && block_n != 64 && block_n != 32)) return cudaErrorInvalidValue;
+    op->desc.p.gemm.block_n = block_n;
+    return gemm_refresh(op);
+}
+extern "C" int resident_fp4_resources(void* handle, int* values, int count) {
+    Op* op = as_op(handle);
+    if (!op || !values || count < 8) return cudaErrorInvalidValue;
+    cudaFuncAttributes attr{};
+    cudaError_t e = cudaFuncGetAttributes(&attr, pi0_vm_kernel);
+    if (e != cudaSuccess) return e;
+    cudaDeviceProp prop{};
+    e = cudaGetDeviceProperties(&prop, op->device);
+    if (e != cudaSuccess) return e;
+    values[0] = attr.numRegs;
+    values[1] = static_cast<int>(attr.sharedSizeBytes);
+    values[2] = kSmemBytes;
+    values[3] = static_cast<int>(attr.localSizeBytes);
+    values[4] = 1;
+    values[5] = kThreads;
+    values[6] = prop.maxThreadsPerMultiProcessor;
+    values[7] = prop.multiProcessorCount;
+    return cudaSuccess;
+}
+extern "C" int destroy_resident_fp4(void* handle) { return destroy_checked(handle); }
+
+// =====================================================================================================
+extern "C" int create_norm(void** handle, const void* input, const void* residual, const float* gamma, const float* beta,
+                           const float* inverse_scale, void* residual_output, void* output, void* scales, int rows, int width,
+                           int workers, int fp16, int format, int layer, int round_norm, int round_residual, int legacy_ties,
+                           float epsilon, float global_scale) {
+    (void)round_residual;
+    if (!handle) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (!input || !output || rows < 1 || width < 16 || width % 16 || (format != 4 && format != 16) || (format == 4 && !scales) ||
+        fp16 || residual || residual_output || inverse_scale || legacy_ties || !std::isfinite(epsilon) || epsilon <= 0 ||
+        !std::isfinite(global_scale) || global_scale <= 0 || width > 2048)
+        return cudaErrorInvalidValue;
+    Op* op = nullptr;
+    int e = new_op(&op, workers);
+    if (e) return e;
+    StageDesc& d = op->desc;
+    d.kind = OP_NORM;
+    finish_desc(d);
+    d.tiles = (rows + kNormRowsPerTile - 1) / kNormRowsPerTile;
+    d.bands = (rows + kBandRows - 1) / kBandRows;
+    d.band_div = kBandRows / kNormRowsPerTile;
+    NormParams& n = d.p.norm;
+    n.in = input; n.gamma = gamma; n.beta = beta;
+    n.rows = rows; n.width = width;
+    n.mode = layer ? 1 : 0;
+    n.round_norm = round_norm;
+    n.eps = epsilon;
+    n.inv_gs = 1.f / global_scale;
+    n.policy = 0;
+    if (format == 4) { n.out = static_cast<uint8_t*>(output); n.out_scales = static_cast<uint8_t*>(scales); }
+    else n.out_bf16 = output;
+    n.out_blocks = width / 16;
+    n.ld_in = width;
+    n.ld_out = width / 2;
+    *handle = op;
+    return cudaSuccess;
+}
+extern "C" int launch_norm(void* handle, void* stream) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_NORM) return cudaErrorInvalidValue;
+    return launch_solo(handle, stream);
+}
+extern "C" int destroy_norm(void* handle) { return destroy_checked(handle); }
+extern "C" int configure_norm_quantize_only(void* handle, int policy) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_NORM || (policy != 0 && policy != 1)) return cudaErrorInvalidValue;
+    op->desc.p.norm.mode = 2;
+    op->desc.p.norm.policy = policy;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_norm_bf16_copy(void* handle, void* out_bf16) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_NORM) return cudaErrorInvalidValue;
+    op->desc.p.norm.out_bf16 = out_bf16;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_norm_layout(void* handle, int ld_in, int ld_out, int out_blocks) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_NORM) return cudaErrorInvalidValue;
+    NormParams& n = op->desc.p.norm;
+    if (ld_in < n.width || ld_in % 8 || ld_out < n.width / 2 || ld_out % 8 || out_blocks < n.width / 16) return cudaErrorInvalidValue;
+    n.ld_in = ld_in; n.ld_out = ld_out; n.out_blocks = out_blocks;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+
+// =====================================================================================================
+static void attention_geometry(Op* op) {
+    AttnParams& a = op->desc.p.attn;
+    const int qtiles = (a.nq + kAttnQRows - 1) / kAttnQRows;
+    op->desc.tiles = a.batches * qtiles * a.heads * a.splits;
+    op->desc.bands = a.batches * qtiles;
+    op->desc.band_div = a.heads * a.splits;
+    op->cost = std::max(64, ((a.nk / a.splits) * a.head_dim / 64 + 63) / 64 * 64);
+    op->solo_dirty = true;
+}
+extern "C" int create_attention(void** handle, const void* q, const void* k, const void* v, const void* q_bias, const void* k_bias,
+                                const void* v_bias, const void* q_cos, const void* q_sin, const void* k_cos, const void* k_sin,
+                                void* out, const void* mask, int batches, int nq, int nk, int heads, int kv_heads, int head_dim,
+                                int ldq, int ldkv, int out_ld, int fp16, int workers, int prefix, float scale) {
+    if (!handle) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (!q || !k || !v || !out || q_bias || k_bias || v_bias || q_cos || q_sin || k_cos || k_sin || mask || fp16 || batches < 1 ||
+        nq < 1 || nk < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads || (head_dim != 72 && head_dim != 256) ||
+        ldq < heads * head_dim || ldq % 8 || ldkv < kv_heads * head_dim || ldkv % 8 || out_ld < heads * head_dim || out_ld % 8 ||
+        !std::isfinite(scale) || scale <= 0 || (prefix >= 0 && batches != 1))
+        return cudaErrorInvalidValue;
+    Op* op = nullptr;
+    int e = new_op(&op, workers);
+    if (e) return e;
+    StageDesc& d = op->desc;
+    d.kind = OP_ATTN;
+    finish_desc(d);
+    AttnParams& a = d.p.attn;
+    a.q = q; a.k = k; a.v = v; a.out = out;
+    a.ldq = ldq; a.ldkv = ldkv; a.ldo = out_ld;
+    a.batches = batches; a.nq = nq; a.nk = nk;
+    a.q_batch_rows = nq; a.kv_batch_rows = nk;
+    a.heads = heads; a.kv_heads = kv_heads; a.head_dim = head_dim;
+    a.scale = scale;
+    a.prefix = prefix >= 0 ? prefix : -1;
+    a.splits = 1;
+    a.out_inv_gs = 1.f;
+    attention_geometry(op);
+    *handle = op;
+    return cudaSuccess;
+}
+extern "C" int launch_attention(void* handle, void* stream) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN) return cudaErrorInvalidValue;
+    return launch_solo(handle, stream);
+}
+extern "C" int destroy_attention(void* handle) { return destroy_checked(handle); }
+extern "C" int attention_resources(int* values, int count) {
+    if (!values || count < 4) return cudaErrorInvalidValue;
+    cudaFuncAttributes attr{};
+    cudaError_t e = cudaFuncGetAttributes(&attr, pi0_vm_kernel);
+    if (e != cudaSuccess) return e;
+    values[0] = attr.numRegs;
+    values[1] = static_cast<int>(attr.localSizeBytes);
+    values[2] = kSmemBytes;
+    values[3] = kThreads;
+    return cudaSuccess;
+}
+extern "C" int configure_attention_splits(void* handle, int splits) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN || splits < 1 || splits > 64) return cudaErrorInvalidValue;
+    AttnParams& a = op->desc.p.attn;
+    if (splits > 1 && (a.batches != 1 || a.nq > kAttnQRows || a.head_dim % 16)) return cudaErrorInvalidValue;
+    if (op->merge) { free_op(op->merge); op->merge = nullptr; }
+    cudaFree(op->partial_o); op->partial_o = nullptr;
+    cudaFree(op->partial_ml); op->partial_ml = nullptr;
+    void* final_out = a.splits > 1 && false ? nullptr : a.out;
+    a.splits = splits;
+    if (splits > 1) {
+        const size_t tasks = static_cast<size_t>(a.heads) * splits;
+        cudaError_t e = cudaMalloc(&op->partial_o, tasks * kAttnQRows * a.head_dim * sizeof(float));
+        if (e == cudaSuccess) e = cudaMalloc(&op->partial_ml, tasks * kAttnQRows * 2 * sizeof(float));
+        if (e != cudaSuccess) return e;
+        a.partial_o = op->partial_o;
+        a.partial_ml = op->partial_ml;
+        Op* mg = new Op();
+        mg->device = op->device;
+        mg->workers = op->workers;
+        mg->desc.kind = OP_MERGE;
+        finish_desc(mg->desc);
+        mg->desc.tiles = a.heads;
+        mg->desc.bands = 1;
+        mg->desc.band_div = a.heads;
+        MergeParams& g = mg->desc.p.merge;
+        g.partial_o = op->partial_o; g.partial_ml = op->partial_ml;
+        g.heads = a.heads; g.nq = a.nq; g.head_dim = a.head_dim; g.splits = splits;
+        g.out = final_out; g.ldo = a.ldo;
+        g.out_fp4 = a.out_fp4; g.out_scales = a.out_scales; g.out_blocks = a.out_blocks; g.out_inv_gs = a.out_inv_gs; g.ld_fp4 = a.ld_fp4;
+        op->merge = mg;
+    }
+    attention_geometry(op);
+    return cudaSuccess;
+}
+extern "C" int configure_attention_cache(void* handle, const void* cache_k, const void* cache_v, int rows, int prefix_rows) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN || !cache_k || !cache_v || rows < 1 || prefix_rows < 0 || prefix_rows > rows) return cudaErrorInvalidValue;
+    AttnParams& a = op->desc.p.attn;
+    if (a.batches != 1 || a.kv_heads != 1) return cudaErrorInvalidValue;
+    a.k = cache_k; a.v = cache_v; a.ldkv = a.head_dim; a.nk = rows; a.kv_batch_rows = rows;
+    attention_geometry(op);
+    return cudaSuccess;
+}
+extern "C" int configure_attention_fp4_output(void* handle, void* out_fp4, void* scales, int ld_bytes, int out_blocks, float global_scale) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN || !out_fp4 || !scales || !std::isfinite(global_scale) || global_scale <= 0) return cudaErrorInvalidValue;
+    AttnParams& a = op->desc.p.attn;
+    if (a.head_dim % 16 || ld_bytes < a.heads * a.head_dim / 2 || out_blocks < a.heads * a.head_dim / 16) return cudaErrorInvalidValue;
+    a.out_fp4 = static_cast<uint8_t*>(out_fp4); a.out_scales = static_cast<uint8_t*>(scales);
+    a.ld_fp4 = ld_bytes; a.out_blocks = out_blocks; a.out_inv_gs = 1.f / global_scale;
+    if (op->merge) {
+        MergeParams& g = op->merge->desc.p.merge;
+        g.out_fp4 = a.out_fp4; g.out_scales = a.out_scales; g.ld_fp4 = ld_bytes; g.out_blocks = out_blocks; g.out_inv_gs = a.out_inv_gs;
+    }
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int attention_merge_handle(void* handle, void** merge) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN || !merge) return cudaErrorInvalidValue;
+    *merge = op->merge;
+    return cudaSuccess;
+}
+
+// =====================================================================================================
+extern "C" int create_patch_embed(void** handle, const float* images, const float* weight, const float* bias, const float* pos,
+                                  void* out, int views, int width, int workers) {
+    if (!handle) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (!weight || !bias || !pos || !out || views < 1 || width < 1) return cudaErrorInvalidValue;
+    Op* op = nullptr;
+    int e = new_op(&op, workers);
+    if (e) return e;
+    StageDesc& d = op->desc;
+    d.kind = OP_PATCH;
+    finish_desc(d);
+    const int ntiles = (width + kPatchCols - 1) / kPatchCols;
+    d.tiles = views * 256 / kPatchTokens * ntiles;
+    d.bands = views * 256 / kBandRows;
+    d.band_div = kBandRows / kPatchTokens * ntiles;
+    op->cost = 576;
+    d.p.patch = PatchParams{images, weight, bias, pos, out, views, width};
+    *handle = op;
+    return cudaSuccess;
+}
+extern "C" int create_token_embed(void** handle, const long long* tokens, const void* table, void* out, int count, int width,
+                                  int row_base, int vocab, float scale, int workers) {
+    if (!handle) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (!table || !out || count < 1 || width < 1 || row_base < 0 || vocab < 1) return cudaErrorInvalidValue;
+    Op* op = nullptr;
+    int e = new_op(&op, workers);
+    if (e) return e;
+    StageDesc& d = op->desc;
+    d.kind = OP_EMBED;
+    finish_desc(d);
+    d.tiles = (count + 7) / 8;
+    d.bands = 1;
+    d.band_div = d.tiles;
+    d.p.embed = EmbedParams{tokens, table, out, count, width, row_base, vocab, scale};
+    *handle = op;
+    return cudaSuccess;
+}
+extern "C" int create_linear32(void** handle, const void* x, const float* w, const float* bias, const float* prev, void* out,
+                               int rows, int n, int k, int ldx, int ldo, int flags, int slot, int prev_slot, int x_row_offset,
+                               float dt, float eps, int workers) {
+    if (!handle) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (!w || !out || rows < 1 || n < 1 || k < 4 || k % 4 || ldx < k || ldo < n || (slot != 0 && slot != 2 && slot != 3) ||
+        (slot == 0 && !x) || (prev_slot != 0 && prev_slot != 3) || ((flags & 16) && prev_slot == 0 && !prev) || x_row_offset < 0)
+        return cudaErrorInvalidValue;
+    Op* op = nullptr;
+    int e = new_op(&op, workers);
+    if (e) return e;
+    StageDesc& d = op->desc;
+    d.kind = OP_LINEAR32;
+    finish_desc(d);
+    d.tiles = (n + 7) / 8;
+    d.bands = 1;
+    d.band_div = d.tiles;
+    op->cost = std::max(64, (k * rows / 16 + 63) / 64 * 64);
+    Linear32Params& p = d.p.lin;
+    p.x = x; p.w = w; p.bias = bias; p.prev = prev; p.out = out;
+    p.rows = rows; p.n = n; p.k = k; p.ldx = ldx; p.ldo = ldo;
+    p.x_bf16 = flags & 1; p.out_bf16 = (flags >> 1) & 1; p.silu = (flags >> 2) & 1; p.rms = (flags >> 3) & 1; p.euler = (flags >> 4) & 1;
+    p.slot = slot; p.prev_slot = prev_slot; p.x_row_offset = x_row_offset; p.dt = dt; p.eps = eps;
+    *handle = op;
+    return cudaSuccess;
+}
+extern "C" int create_suffix_assemble(void** handle, const float* state_emb, const float* action_emb, void* out, int chunk,
+                                      int width, int workers) {
+    if (!handle) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (!state_emb || !action_emb || !out || chunk < 1 || width < 1) return cudaErrorInvalidValue;
+    Op* op = nullptr;
+    int e = new_op(&op, workers);
+    if (e) return e;
+    StageDesc& d = op->desc;
+    d.kind = OP_SUFFIX;
+    finish_desc(d);
+    d.tiles = (chunk + 1 + 7) / 8;
+    d.bands = 1;
+    d.band_div = d.tiles;
+    d.p.suffix = SuffixParams{state_emb, action_emb, out, chunk, width};
+    *handle = op;
+    return cudaSuccess;
+}
+extern "C" int launch_op(void* handle, void* stream) { return launch_solo(handle, stream); }
+extern "C" int destroy_op(void* handle) { return destroy_checked(handle); }
+extern "C" int op_geometry(void* handle, int* tiles, int* bands, int* cost) {
+    Op* op = as_op(handle);
+    if (!op) return cudaErrorInvalidValue;
+    if (tiles) *tiles = op->desc.tiles;
+    if (bands) *bands = op->desc.bands;
+    if (cost) *cost = op->cost;
+    return cudaSuccess;
+}
+
+// =====================================================================================================
+extern "C" int create_native_model(void** handle, int count, const NativeSpec* specs, const int* code, int workers, int length) {
+    if (!handle) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (count < 1 || !specs || !code || workers < 1 || length < 1) return cudaErrorInvalidValue;
+    int device = 0;
+    int e = check_device(&device);
+    if (e) return e;
+    if (workers > sm_count(device)) return cudaErrorInvalidConfiguration;
+    std::vector<StageDesc> stages;
+    stages.reserve(count);
+    for (int i = 0; i < count; i++) {
+        Op* op = as_op(specs[i].handle);
+        if (!op || op->device != device) return cudaErrorInvalidValue;
+        const int want = op->desc.kind == OP_GEMM ? 0 : op->desc.kind == OP_ATTN ? 1 : op->desc.kind == OP_NORM ? 2 : op->desc.kind == OP_MERGE ? 4 : 3;
+        if (specs[i].kind != want) return cudaErrorInvalidValue;
+        StageDesc d = op->desc;
+        for (int s = 0; s < kMaxSources; s++) {
+            d.src[s] = specs[i].sources[s];
+            d.src_mode[s] = specs[i].modes[s] ? SRC_ALL_BANDS : SRC_SAME_BAND;
+            if (d.src[s] >= i || d.src[s] < -1) return cudaErrorInvalidValue;
+        }
+        stages.push_back(d);
+    }
+    std::vector<int> code4(static_cast<size_t>(workers) * length * 4);
+    for (size_t i = 0; i < static_cast<size_t>(workers) * length; i++) {
+        const int* ins = code + i * 32;
+        code4[i * 4 + 0] = ins[0] ? stages[std::min(std::max(ins[1], 0), count - 1)].kind : 0;
+        code4[i * 4 + 1] = ins[1];
+        code4[i * 4 + 2] = ins[2];
+        code4[i * 4 + 3] = ins[3];
+    }
+    Program* prog = nullptr;
+    e = build_program(&prog, device, stages, code4, workers, length);
+    if (e) return e;
+    *handle = prog;
+    return cudaSuccess;
+}
+extern "C" int launch_native_model_range(void* handle, void* stream, const float* images, const float* state, const float* noise,
+                                         const long long* tokens, int begin, int end, int new_epoch) {
+    Program* prog = as_program(handle);
+    if (!prog || begin < 0 || end > static_cast<int>(prog->stages.size()) || begin >= end) return cudaErrorInvalidValue;
+    return launch_program(prog, static_cast<cudaStream_t>(stream), LaunchInputs{images, state, noise, tokens}, begin, end, new_epoch != 0);
+}
+extern "C" int launch_native_model(void* handle, void* stream, const float* images, const float* state, const float* noise,
+                                   const long long* tokens) {
+    Program* prog = as_program(handle);
+    if (!prog) return cudaErrorInvalidValue;
+    return launch_program(prog, static_cast<cudaStream_t>(stream), LaunchInputs{images, state, noise, tokens}, 0,
+                          static_cast<int>(prog->stages.size()), true);
+}
+extern "C" int enable_native_model_timings(void* handle, int enable) {
+    Program* prog = as_program(handle);
+    if (!prog) return cudaErrorInvalidValue;
+    if (enable && !prog->d_timings) {
+        const size_t bytes = sizeof(long long) * 2 * prog->workers * prog->length;
+        cudaError_t e = cudaMalloc(&prog->d_timings, bytes);
+        if (e == cudaSuccess) e = cudaMemset(prog->d_timings, 0, bytes);
+        if (e != cudaSuccess) return e;
+    }
+    prog->timings_on = enable != 0;
+    return cudaSuccess;
+}
+extern "C" int read_native_model_timings(void* handle, long long* out, size_t count) {
+    Program* prog = as_program(handle);
+    if (!prog || !out || !prog->d_timings || count != static_cast<size_t>(2) * prog->workers * prog->length) return cudaErrorInvalidValue;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    return cudaMemcpy(out, prog->d_timings, count * sizeof(long long), cudaMemcpyDeviceToHost);
+}
+static int read_status(Program* prog, int* values, int count) {
+    if (!values || count < 8) return cudaErrorInvalidValue;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    VmStatus st{};
+    e = cudaMemcpy(&st, prog->d_status, sizeof(st), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    values[0] = st.code; values[1] = st.worker; values[2] = st.stage; values[3] = st.band;
+    values[4] = static_cast<int>(st.observed); values[5] = static_cast<int>(st.expected); values[6] = st.abort;
+    values[7] = static_cast<int>(prog->epoch);
+    if (st.abort || st.code) {
+        e = cudaMemset(prog->d_status, 0, sizeof(VmStatus));
+        if (e == cudaSuccess) e = cudaMemset(prog->d_counters, 0, sizeof(unsigned int) * std::max<size_t>(prog->expected.size(), 1));
+        prog->epoch = 0;
+    }
+    return e;
+}
+extern "C" int read_native_model_status(void* handle, int* values, int count) {
+    Program* prog = as_program(handle);
+    if (!prog) {
+        Op* op = as_op(handle);          // operator handles answer for their stand-alone program
+        if (!op || !op->solo) return cudaErrorInvalidValue;
+        prog = op->solo;
+    }
+    return read_status(prog, values, count);
+}
+extern "C" int read_native_model_counters(void* handle, unsigned int* counts, unsigned int* expected, int n, int* total) {
+    Program* prog = as_program(handle);
+    if (!prog) {
+        Op* op = as_op(handle);
+        if (!op || !op->solo) return cudaErrorInvalidValue;
+        prog = op->solo;
+    }
+    const int have = static_cast<int>(prog->expected.size());
+    if (total) *total = have;
+    if (!counts && !expected) return cudaSuccess;
+    if (n < have) return cudaErrorInvalidValue;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    if (counts) {
+        e = cudaMemcpy(counts, prog->d_counters, sizeof(unsigned int) * have, cudaMemcpyDeviceToHost);
+        if (e != cudaSuccess) return e;
+    }
+    if (expected)
+        for (int i = 0; i < have; i++) expected[i] = prog->expected[i] * prog->epoch;
+    return cudaSuccess;
+}
+extern "C" int set_native_model_wait_budget(void* handle, unsigned long long nanoseconds) {
+    Program* prog = as_program(handle);
+    if (!prog) {
+        Op* op = as_op(handle);
+        if (!op) return cudaErrorInvalidValue;
+        int e = solo_program(op);
+        if (e) return e;
+        prog = op->solo;
+    }
+    if (nanoseconds < 1000) return cudaErrorInvalidValue;
+    prog->budget_ns = nanoseconds;
+    return cudaSuccess;
+}
+extern "C" int destroy_native_model(void* handle) {
+    if (!handle) return cudaSuccess;
+    Program* prog = as_program(handle);
+    if (!prog) return cudaErrorInvalidValue;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device != prog->device) return cudaErrorInvalidDevice;
+    prog->magic = 0;
+    delete prog;
+    return cudaSuccess;
+}
+
+// =====================================================================================================
+extern "C" int create_native_linear(void** handle, int count, void* const* stage_handles, const int* parents, const int* code,
+                                    int workers, int length) {
+    if (!handle) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (count < 1 || !stage_handles || !parents) return cudaErrorInvalidValue;
+    std::vector<NativeSpec> specs(count);
+    for (int i = 0; i < count; i++) {
+        Op* op = as_op(stage_handles[i]);
+        if (!op || op->desc.kind != OP_GEMM) return cudaErrorInvalidValue;
+        specs[i].kind = 0;
+        specs[i].handle = stage_handles[i];
+        for (int s = 0; s < 4; s++) { specs[i].sources[s] = -1; specs[i].modes[s] = 0; }
+        if (parents[i] < -1 || parents[i] >= i) return cudaErrorInvalidValue;
+        specs[i].sources[0] = parents[i];
+    }
+    return create_native_model(handle, count, specs.data(), code, workers, length);
+}
+extern "C" int launch_native_linear(void* handle, void* stream) { return launch_native_model(handle, stream, nullptr, nullptr, nullptr, nullptr); }
+extern "C" int read_native_linear(void* handle, unsigned long long* counters, int count, unsigned long long* epoch) {
+    Program* prog = as_program(handle);
+    if (!prog || !counters || !epoch || count != static_cast<int>(prog->expected.size())) return cudaErrorInvalidValue;
+    std::vector<unsigned int> raw(count);
+    int e = read_native_model_counters(handle, raw.data(), nullptr, count, nullptr);
+    if (e) return e;
+    // reported in tiles (a GEMM tile is four warp contributions)
+    for (int i = 0; i < count; i++) counters[i] = raw[i] / 4;
+    *epoch = prog->epoch;
+    return cudaSuccess;
+}
+extern "C" int destroy_native_linear(void* handle) { return destroy_native_model(handle); }
+
+// =====================================================================================================
+extern "C" int quantize_nvfp4(const void* in, void* out, void* scales, int rows, int width, int ld_in, int out_blocks,
+                              float global_scale, int policy, void* stream) {
+    if (!in || !out || !scales || rows < 1 || width < 16 || width % 16 || ld_in < width || ld_in % 8 || out_blocks < width / 16 ||
+        !std::isfinite(global_scale) || global_scale <= 0 || (policy != 0 && policy != 1))
+        return cudaErrorInvalidValue;
+    int device = 0;
+    int e = check_device(&device);
+    if (e) return e;
+    NormParams n{};
+    n.in = in; n.rows = rows; n.width = width; n.mode = 2; n.inv_gs = 1.f / global_scale; n.policy = policy;
+    n.out = static_cast<uint8_t*>(out); n.out_scales = static_cast<uint8_t*>(scales);
+    n.out_blocks = out_blocks; n.ld_in = ld_in; n.ld_out = width / 2;
+    quantize_rows_kernel<<<(rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(n);
+    return cudaGetLastError();
+}

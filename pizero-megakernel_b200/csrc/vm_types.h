@@ -1,0 +1,215 @@
+// Shared host/device description of a pi0 VM program.
+//
+// A program is a list of stages (one operator instance each) plus, per worker
+// CTA, a static stream of instructions {opcode, stage, first_tile, tile_count}.
+// Dependencies between stages are expressed with monotonically growing counters:
+// every finished tile adds 1 to the counter of its 128-row band, and a consumer
+// waits until the bands it reads have reached epoch * expected.
+#pragma once
+#include <stdint.h>
+#include <vector_types.h>
+
+namespace pi0 {
+
+constexpr int kThreads = 256;            // 8 warps per worker CTA
+constexpr int kMaxSources = 4;
+constexpr int kBandRows = 128;
+
+enum OpKind : int {
+    OP_NONE = 0,
+    OP_GEMM = 1,        // NVFP4 block-scaled GEMM on tcgen05, fused epilogue
+    OP_NORM = 2,        // LayerNorm / RMSNorm (or plain copy) -> NVFP4 / BF16
+    OP_ATTN = 3,        // softmax(QK^T)V on tensor cores, optional split-KV partials
+    OP_MERGE = 4,       // split-KV merge (+ NVFP4 quantize)
+    OP_PATCH = 5,       // FP32 patch embedding (14x14x3 conv) + bias + position embedding
+    OP_EMBED = 6,       // token embedding rows * sqrt(width)
+    OP_LINEAR32 = 7,    // small FP32 linear (+bias, SiLU, RMS factor, Euler update)
+    OP_SUFFIX = 8,      // assemble expert input rows: state token + action tokens
+    OP_KINDS
+};
+
+enum SrcMode : int { SRC_SAME_BAND = 0, SRC_ALL_BANDS = 1 };
+
+enum GemmEpilogue : int {
+    EPI_F32 = 0,        // alpha*acc -> FP32
+    EPI_BF16 = 1,       // alpha*acc + bias + residual -> BF16 (one rounding)
+    EPI_FP4 = 2,        // alpha*acc + bias (+residual) [GELU|ReLU^2] -> NVFP4 + swizzled scales
+    EPI_GEGLU_FP4 = 3,  // gelu_tanh(gate)*up on interleaved columns -> NVFP4, width N/2
+    EPI_QKV_ROPE = 4    // BF16, RoPE on Q/K heads, K/V rows appended to the KV cache
+};
+
+struct GemmParams {
+    const void* tmap_a;          // CUtensorMap in global memory: packed A [M_pad, K/2] bytes
+    const void* tmap_b;          // CUtensorMap: packed B [N_pad, K/2] bytes
+    const uint8_t* sfa;          // swizzled E4M3 block scales of A
+    const uint8_t* sfb;
+    int m_tiles, n_tiles;        // 128-row x block_n-column output tiles
+    int k_groups;                // K / 64
+    int block_n;                 // 128 (default), 64 or 32
+    float alpha;                 // global_scale(A) * global_scale(B)
+    int epilogue;
+    int act;                     // EPI_FP4: 0 none, 1 GELU(tanh), 3 ReLU^2
+    int rows;                    // logical rows (rows >= this are written as zero codes / skipped)
+    void* out;                   // FP32 / BF16 / packed FP4
+    int ldo;                     // elements (FP32/BF16) or bytes (FP4) per output row
+    const void* bias;            // BF16 [N] or null
+    const void* residual;        // BF16 [M, ldr] or null
+    int ldr;
+    uint8_t* out_scales;         // swizzled scales of the FP4 output
+    int out_blocks;              // 16-wide blocks per output row (scale layout width)
+    float out_inv_gs;            // 1 / global scale of the FP4 output
+    // EPI_QKV_ROPE
+    const void* rope_cos;        // BF16 [rows, head_dim]
+    const void* rope_sin;
+    void* cache_k;               // BF16 [cache_rows, head_dim]
+    void* cache_v;
+    int q_cols;                  // heads * head_dim (0 when the projection has no Q part)
+    int head_dim;
+    int cache_base;              // first cache row written by this projection
+    uint32_t idesc;              // tcgen05 instruction descriptor
+};
+
+struct NormParams {
+    const void* in;              // BF16 [rows, width]
+    const float* gamma;          // FP32 [width] or null (RMS: already 1+w)
+    const float* beta;           // FP32 [width] or null
+    int rows, width;
+    int mode;                    // 0 = RMSNorm, 1 = LayerNorm, 2 = none (quantize only)
+    int round_norm;              // round normalised value to BF16 before quantisation
+    float eps;
+    float inv_gs;                // 1 / global scale of the FP4 output
+    int policy;                  // 0 nearest (activations), 1 ceil (weights)
+    uint8_t* out;                // packed FP4 [rows_pad, width/2] or null
+    uint8_t* out_scales;         // swizzled scales
+    int out_blocks;              // blocks per row of the scale layout (>= width/16)
+    void* out_bf16;              // optional BF16 copy of the normalised rows
+    int ld_in;                   // input row stride in elements
+    int ld_out;                  // FP4 output row stride in bytes
+};
+
+struct AttnParams {
+    const void* q;               // BF16; element (b, r, h, d) at q + ((b*q_batch_rows + r)*ldq + h*head_dim + d)
+    const void* k;               // BF16; key (b, j, hk, d) at k + ((b*kv_batch_rows + j)*ldkv + hk*head_dim + d)
+    const void* v;
+    void* out;                   // BF16 [.., heads*head_dim] (ldo elements) or null when partial
+    int ldq, ldkv, ldo;
+    int batches, nq, nk;         // queries / keys per batch
+    int q_batch_rows, kv_batch_rows;
+    int heads, kv_heads, head_dim;
+    float scale;
+    int prefix;                  // >= 0: pi0 suffix mask, query 0 sees keys [0, prefix]; -1: no mask
+    int splits;                  // KV splits (1 = none)
+    float* partial_o;            // FP32 [tasks, 128, head_dim] when splits > 1
+    float* partial_ml;           // FP32 [tasks, 128, 2]
+    // fused NVFP4 quantisation of the output (splits == 1)
+    uint8_t* out_fp4;
+    uint8_t* out_scales;
+    int out_blocks;
+    float out_inv_gs;
+    int ld_fp4;
+};
+
+struct MergeParams {
+    const float* partial_o;
+    const float* partial_ml;
+    int heads, nq, head_dim, splits;
+    void* out;                   // BF16 [nq, heads*head_dim] or null
+    int ldo;
+    uint8_t* out_fp4;
+    uint8_t* out_scales;
+    int out_blocks;
+    float out_inv_gs;
+    int ld_fp4;
+};
+
+struct PatchParams {
+    const float* images;         // FP32 [views,224,224,3] (null: bound at launch, slot 1)
+    const float* weight;         // FP32 [588, width]  (k = (py*14+px)*3 + c)
+    const float* bias;           // FP32 [width]
+    const float* pos;            // FP32 [256, width]
+    void* out;                   // BF16 [views*256, width]
+    int views, width;
+};
+
+struct EmbedParams {
+    const long long* tokens;     // null: bound at launch (slot 4)
+    const void* table;           // BF16 [vocab, width]
+    void* out;                   // BF16 rows [row_base, row_base+count)
+    int count, width, row_base, vocab;
+    float scale;
+};
+
+struct Linear32Params {
+    const void* x;               // FP32 or BF16 [rows, ldx]; null: launch slot
+    const float* w;              // FP32 [n, k] row major
+    const float* bias;           // FP32 [n] or null
+    const float* prev;           // Euler: FP32 [rows, n] previous value (null with slot: launch noise)
+    void* out;                   // FP32 [rows, ldo] or BF16
+    int rows, n, k, ldx, ldo;
+    int x_bf16, out_bf16;
+    int silu, rms;               // rms: multiply by rsqrt(mean(x^2)+eps) of the input row
+    int euler;                   // out = prev + dt * value   (separately rounded mul and add)
+    int slot, prev_slot;         // 0 pointer, 2 state, 3 noise
+    int x_row_offset;            // first input row
+    float dt, eps;
+};
+
+struct SuffixParams {
+    const float* state_emb;      // FP32 [1, width]
+    const float* action_emb;     // FP32 [chunk, width]
+    void* out;                   // BF16 [rows_pad, width]
+    int chunk, width;
+};
+
+struct StageDesc {
+    int kind;
+    int tiles;
+    int bands;
+    int counter_base;
+    int band_div;                // band(tile) = min(tile / band_div, bands - 1)
+    int src[kMaxSources];
+    int src_mode[kMaxSources];
+    int units_per_tile;          // counter increments one finished tile contributes (GEMM: one per epilogue warp)
+    union {
+        GemmParams gemm;
+        NormParams norm;
+        AttnParams attn;
+        MergeParams merge;
+        PatchParams patch;
+        EmbedParams embed;
+        Linear32Params lin;
+        SuffixParams suffix;
+    } p;
+};
+
+// Written by the device when a bounded wait expires or a check fails.
+struct VmStatus {
+    int code;                    // 0 ok, 1 dependency wait timed out, 2 pipeline barrier timed out, 3 bad instruction
+    int worker, stage, band;
+    unsigned int observed, expected;
+    int abort;                   // set once; every wait polls it
+    int pad;
+};
+
+struct LaunchInputs {
+    const float* images;
+    const float* state;
+    const float* noise;
+    const long long* tokens;
+};
+
+struct VmProgram {
+    const StageDesc* stages;
+    const int4* code;            // [workers][length] compacted instructions
+    unsigned int* counters;
+    const unsigned int* expected;
+    VmStatus* status;
+    long long* timings;          // optional [workers][length][2] clock stamps
+    int num_stages, length;
+    unsigned int epoch;
+    int stage_begin, stage_end;  // execute stages in [begin, end); sources < begin are treated as complete
+    unsigned long long wait_budget_ns;
+    LaunchInputs in;
+};
+
+}  // namespace pi0

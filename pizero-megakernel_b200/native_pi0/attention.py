@@ -1,0 +1,94 @@
+"""Attention operator: MHA / GQA / MQA over BF16 Q, K, V with FP32 softmax.
+
+Constructor-compatible with the reference ``ResidentAttention`` (``native_pi0/attention.py:8-139``) for
+the pi0 cases: BF16 tensors ``q [B, Nq, H, d]``, ``k, v [B, Nk, Hk, d]`` (views with a common row stride
+are accepted), optional pi0 suffix mask (``prefix``), optional KV cache, optional split-KV with merge.
+Biases, in-kernel RoPE tables and boolean masks are rejected: RoPE is fused into the QKV projection.
+"""
+import ctypes
+
+import torch
+
+from native_pi0 import _native
+
+
+class ResidentAttention:
+    def __init__(self, library, q, k, v, *, workers=16, scale=None, prefix=None, splits=1, kv_cache=None,
+                 cached_prefix_rows=0, output=None, q_bias=None, k_bias=None, v_bias=None, q_rope=None,
+                 k_rope=None, mask=None, fp4_output=None):
+        if any(x is not None for x in (q_bias, k_bias, v_bias, q_rope, k_rope, mask)):
+            raise ValueError("Biases, RoPE tables and boolean masks are fused elsewhere in the NVFP4 engine")
+        for t in (q, k, v):
+            if t.dtype != torch.bfloat16 or t.ndim != 4 or not t.is_cuda or t.stride(-1) != 1:
+                raise ValueError("q, k, v must be CUDA BF16 [batch, rows, heads, dim] with contiguous dim")
+        b, nq, h, d = q.shape
+        bk, nk, hk, dk = k.shape
+        if v.shape != k.shape or bk != b or dk != d or h % hk or d not in (72, 256):
+            raise ValueError("Unsupported attention geometry (head_dim 72 or 256, heads a multiple of kv heads)")
+        if q.stride(2) != d or k.stride(2) != d or v.stride(2) != d or k.stride(1) != v.stride(1):
+            raise ValueError("Heads must be adjacent and K/V must share a row stride")
+        if b > 1 and (q.stride(0) != nq * q.stride(1) or k.stride(0) != nk * k.stride(1) or v.stride(0) != nk * v.stride(1)):
+            raise ValueError("Batches must be stacked rows")
+        self.device = q.device
+        self.scale = float(d ** -0.5 if scale is None else scale)
+        self.q, self.k, self.v = q, k, v
+        self.library = _native.load(library)
+        self.handle = ctypes.c_void_p()
+        self.kv_cache = kv_cache
+        with torch.cuda.device(self.device):
+            if output is None:
+                output = torch.zeros((b, nq, h, d), dtype=torch.bfloat16, device=self.device)
+            if output.dtype != torch.bfloat16 or tuple(output.shape) != (b, nq, h, d) or output.stride(2) != d:
+                raise ValueError("Output must be BF16 [batch, rows, heads, dim]")
+            self.output = output
+            _native.check(self.library.create_attention(
+                ctypes.byref(self.handle), q.data_ptr(), k.data_ptr(), v.data_ptr(), None, None, None, None, None, None, None,
+                output.data_ptr(), None, b, nq, nk, h, hk, d, q.stride(1), k.stride(1), output.stride(1), 0, workers,
+                -1 if prefix is None else int(prefix), self.scale), "Native attention setup")
+            try:
+                if kv_cache is not None:
+                    ck, cv = kv_cache
+                    rows = cached_prefix_rows + nk
+                    _native.check(self.library.configure_attention_cache(self.handle, ck.data_ptr(), cv.data_ptr(), rows,
+                                                                         cached_prefix_rows), "Native attention cache")
+                if fp4_output is not None:
+                    data, scales, gs = fp4_output
+                    _native.check(self.library.configure_attention_fp4_output(
+                        self.handle, data.data_ptr(), scales.data_ptr(), data.stride(0), h * d // 16, float(gs)),
+                        "Native attention FP4 output")
+                if splits != 1:
+                    _native.check(self.library.configure_attention_splits(self.handle, int(splits)), "Native attention splits")
+            except Exception:
+                self.close()
+                raise
+        self.splits = splits
+
+    @property
+    def merge_handle(self):
+        out = ctypes.c_void_p()
+        _native.check(self.library.attention_merge_handle(self.handle, ctypes.byref(out)), "Native attention merge handle")
+        return out
+
+    def forward(self):
+        if not self.handle.value:
+            raise RuntimeError("Attention instance is closed")
+        with torch.cuda.device(self.device):
+            _native.check(self.library.launch_attention(self.handle, torch.cuda.current_stream(self.device).cuda_stream),
+                          "Native attention launch")
+        return self.output
+
+    def status(self):
+        with torch.cuda.device(self.device):
+            return _native.status(self.library, self.handle)
+
+    def close(self):
+        if self.handle.value:
+            with torch.cuda.device(self.device):
+                _native.check(self.library.destroy_attention(self.handle), "Native attention teardown")
+            self.handle = ctypes.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_):
+        self.close()
