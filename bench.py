@@ -1,0 +1,288 @@
+#!/usr/bin/env python
+"""pi0 action-chunk latency benchmark (one JSON line on stdout).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload cfg4|cfg5]
+
+A step is one complete pi0 forward (SigLIP x3 views -> Gemma-2B prefix -> Gemma-300M expert x10 Euler steps)
+as ONE launch of the persistent sm_100a kernel on synthetic inputs with random-initialised weights.
+`value` is the p50 latency in ms with inputs resident in HBM (CUDA events, max over ranks); `e2e` is the same
+call through `NativePi0.sample_actions` with pinned HOST buffers (H2D of images/state/noise and D2H of the
+actions inside the timed region).  With --gpus N (launched under torchrun) every rank runs an independent
+replica on its own GPU: no data-path collective, only a barrier and a MAX reduction of the timings.
+`--impl reference` times the CPU restatement of the reference path (oracle/) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT / "pizero-megakernel_b200"))
+sys.path.insert(0, str(ROOT))
+
+METRIC = "pi0_10step_action_chunk_latency_p50_ms"
+WORKLOADS = {
+    # BASELINE.json configs[3]: full forward, 3 views, no prompt, chunk 50, 10 Euler steps
+    "cfg4": dict(views=3, prompt=0, chunk=50, steps=10, name="configs[3]: full pi0 forward, batch 1, 3 views 224x224, prompt 0, chunk 50, 10 Euler steps"),
+    # BASELINE.json configs[4]: replica sweep shape, 16-token prompt, chunk 63
+    "cfg5": dict(views=3, prompt=16, chunk=63, steps=10, name="configs[4]: pi0 forward, 3 views, 16-token prompt, chunk 63, 10 Euler steps"),
+}
+# Algorithmic work of one forward (GEMM + attention FLOPs) and NVFP4 weight bytes read once.
+WORK = {"cfg4": dict(gflop=3997.0, weight_mb=1461.0), "cfg5": dict(gflop=4136.0, weight_mb=1461.0)}
+
+
+def percentile(values, q):
+    s = sorted(values)
+    if not s:
+        return float("nan")
+    pos = (len(s) - 1) * q
+    lo, hi = int(pos), min(int(pos) + 1, len(s) - 1)
+    return s[lo] + (s[hi] - s[lo]) * (pos - lo)
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.perf_counter(), line.strip()))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [l.split(", ") for t, l in self.lines if t0 <= t <= t1 + 0.2] or [l.split(", ") for _, l in self.lines[-3:]]
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in rows:
+            try:
+                sm.append(float(r[1])), mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for name, flag in zip(names, r[5:9]):
+                if flag.strip().lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        p = json.loads(path.read_text())
+        return p.get("bf16_tflops", 1590.0), p.get("hbm_gbs", 6650.0), "measured (MEASURED_PEAKS.json, burst cuBLAS bf16 / copy)"
+    return 1590.0, 6650.0, "fallback (no MEASURED_PEAKS.json on this box)"
+
+
+def synthetic_inputs(torch, wl, seed, vocab):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    images = torch.rand(wl["views"], 224, 224, 3, generator=g) * 2 - 1          # normalised pixels ~U(-1,1)
+    state = torch.randn(1, 32, generator=g)
+    noise = torch.randn(1, wl["chunk"], 32, generator=g)
+    tokens = torch.randint(0, vocab, (1, wl["prompt"]), generator=g, dtype=torch.int64)
+    return images, state, noise, tokens
+
+
+_CPU_CACHE = {}
+
+
+def cpu_reference_sample(wl, threads):
+    """Time the CPU restatement of the reference path (oracle/pi0_torch.py, FP32 compute) on a bounded sample:
+    2 of 27 vision layers, 2 of 18 prefix layers and 2 of 18 expert layers at full widths with all 10 Euler
+    steps, each phase scaled to its full layer count.  Returns (latency_ms_estimate, description)."""
+    import torch
+    from oracle.pi0_torch import Pi0Dims, Pi0Torch, init_state_dict
+    torch.set_num_threads(threads)
+    k = 2
+    if "model" not in _CPU_CACHE:
+        dims = Pi0Dims(vision_layers=k, prefix_layers=k + 1, expert_layers=k, vocab=1024)   # last prefix layer only writes K/V
+        sd = init_state_dict(dims, seed=0, device="cpu", dtype=torch.float32)
+        _CPU_CACHE["model"] = (dims, sd, Pi0Torch(dims, sd, mode="bf16", compute_dtype=torch.float32))
+        with torch.no_grad():
+            _CPU_CACHE["model"][2].vision(synthetic_inputs(torch, wl, 1, dims.vocab)[0])   # warm-up (thread pool, allocator)
+    dims, sd, model = _CPU_CACHE["model"]
+    images, state, noise, tokens = synthetic_inputs(torch, wl, 1, dims.vocab)
+    with torch.no_grad():
+        t0 = time.perf_counter(); model.vision(images); t_vision = time.perf_counter() - t0
+        t0 = time.perf_counter(); caches = model.prefix(images, tokens); t_prefix = time.perf_counter() - t0 - t_vision
+        state_emb = torch.nn.functional.linear(state, sd["state_proj.weight"], sd["state_proj.bias"])
+        x = noise[0].clone()
+        prefix_rows = caches[0][0].shape[0]
+        t0 = time.perf_counter()
+        for step in range(wl["steps"]):
+            v = model.denoise_step(caches, state_emb, x, 1.0 - step / wl["steps"], prefix_rows)
+            x = x - v / wl["steps"]
+        t_expert = time.perf_counter() - t0
+    full = Pi0Dims()
+    estimate = t_vision * full.vision_layers / k + t_prefix * (full.prefix_layers - 0.5) / (k + 0.5) + t_expert * full.expert_layers / k
+    sample = (f"oracle/pi0_torch.py FP32 on {threads} host threads: {k}/{full.vision_layers} vision, {k}(+KV)/{full.prefix_layers} prefix, "
+              f"{k}/{full.expert_layers} expert layers x {wl['steps']} Euler steps at full widths, measured "
+              f"{t_vision:.2f}+{t_prefix:.2f}+{t_expert:.2f} s, each phase scaled to its full layer count")
+    return estimate * 1e3, sample
+
+
+def run_reference(args, wl, rank):
+    """--impl reference: the CPU restatement of the reference path on all host threads; rank 0 only."""
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    samples, desc = [], ""
+    for i in range(args.warmup + args.steps):
+        ms, desc = cpu_reference_sample(wl, threads)
+        if i >= args.warmup:
+            samples.append(ms)
+    value = percentile(samples, 0.5)
+    line = {"metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": value, "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "impl": "reference",
+            "config": {"workload": wl["name"], "note": "OpenPI is not installable offline; the reference path is represented by the CPU restatement"},
+            "cpu_baseline": {"value": value, "unit": "ms", "cores": threads, "kind": "port", "sample": desc},
+            "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_engine(args, wl, rank, world):
+    import torch
+    import torch.distributed as dist
+    from native_pi0.model import NativePi0
+    from native_pi0.weights import Pi0Config, StateDictModel, random_state_dict
+
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    cfg = Pi0Config()
+    sd = random_state_dict(cfg, seed=1234 + rank, device=device, skip_embedding=(wl["prompt"] == 0))
+    engine = NativePi0(StateDictModel(cfg, sd), num_views=wl["views"], prompt_len=wl["prompt"], chunk_size=wl["chunk"],
+                       flow_steps=wl["steps"])
+    del sd
+    torch.cuda.empty_cache()
+    host = synthetic_inputs(torch, wl, 100 + rank, cfg.vocab)
+    pinned = [t.pin_memory() for t in host]
+    dev = [t.to(device) for t in host]
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- resident-input latency (CUDA events on the launching stream)
+    for _ in range(max(args.warmup, 3)):
+        engine.forward(*dev)
+    status = engine.status()
+    if status["code"]:
+        raise RuntimeError(f"device status {status}")
+    sampler = ClockSampler(torch.cuda.get_device_properties(device).pci_bus_id if False else local)
+    barrier()
+    sampler.start()
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    t_begin = time.perf_counter()
+    events[0].record()
+    for i in range(args.steps):
+        engine.forward(*dev)
+        events[i + 1].record()
+    barrier()
+    t_end = time.perf_counter()
+    per_step = [events[i].elapsed_time(events[i + 1]) for i in range(args.steps)]
+    total_ms = events[0].elapsed_time(events[-1])
+    # ---- end to end through the host-facing call (pinned host inputs, H2D + D2H inside the timed region)
+    for _ in range(2):
+        engine.sample_actions(*pinned)
+    barrier()
+    e2e = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        engine.sample_actions(*pinned)
+        e2e.append((time.perf_counter() - t0) * 1e3)
+    barrier()
+    clocks = sampler.stop(t_begin, t_end)
+    status = engine.status()
+    if status["code"]:
+        raise RuntimeError(f"device status {status}")
+    p50, p90, e2e_p50 = percentile(per_step, 0.5), percentile(per_step, 0.9), percentile(e2e, 0.5)
+    stats = torch.tensor([p50, p90, e2e_p50, total_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    p50, p90, e2e_p50, total_ms = stats.tolist()
+    # ---- per-phase spans of one instrumented launch (rank 0)
+    phases = {}
+    if rank == 0:
+        engine.enable_timings(True)
+        engine.forward(*dev)
+        torch.cuda.synchronize()
+        prof = engine.stage_profile()
+        engine.enable_timings(False)
+        for name in ("vision", "prefix", "expert"):
+            rows = [r for r in prof if r[0].split(".")[0] == name]
+            if rows:
+                phases[name + "_ms"] = (max(r[2] for r in rows) - min(r[1] for r in rows)) / 1e6
+    if rank == 0:
+        tf_peak, hbm_peak, peak_src = measured_peaks()
+        work = WORK[args.workload]
+        achieved = work["gflop"] / p50                      # GFLOP / ms == TFLOP/s
+        h2d = sum(t.numel() * t.element_size() for t in pinned)
+        d2h = engine.output.numel() * 4
+        line = {"metric": METRIC, "value": p50, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+                "ms_per_step": total_ms / args.steps, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+                "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate; bf16 attention, fp32 heads)", "data": "synthetic",
+                "p90_ms": p90, "replica_actions_per_s": world * wl["chunk"] * 1e3 / p50,
+                "config": {"workload": wl["name"], "weights": "random-init N(0,0.02), seeded", "parallelism": f"replicas x{world}, no collective",
+                           "l2": "weights (1.46 GB NVFP4) exceed the 126 MB L2; no explicit flush", "program": engine.plan},
+                "clocks": clocks, "gpu_launches": args.steps,
+                "e2e": {"value": e2e_p50, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak,
+                             "traffic": None, "peak_source": peak_src, "kernel": "pi0_vm_kernel (one launch per step)",
+                             "algorithmic_gflop_per_launch": work["gflop"],
+                             "weight_stream_gbs": work["weight_mb"] / p50, "hbm_peak_gbs": hbm_peak},
+                "phases": phases}
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            ms, desc = cpu_reference_sample(wl, threads)
+            line["cpu_baseline"] = {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": desc}
+        print(json.dumps(line), flush=True)
+    engine.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="native", choices=("native", "reference"))
+    ap.add_argument("--workload", default="cfg4", choices=tuple(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, wl, rank)
+        return
+    run_engine(args, wl, rank, world)
+
+
+if __name__ == "__main__":
+    main()

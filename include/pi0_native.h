@@ -144,7 +144,8 @@ int launch_native_model(void* handle, void* stream, const float* images, const f
  * starts a new forward pass (first range of a pass). */
 int launch_native_model_range(void* handle, void* stream, const float* images, const float* state, const float* noise,
                               const long long* tokens, int begin, int end, int new_epoch);
-/* per-instruction clock stamps, int64 [workers, length, 2] (start, end); enable before the launch to record. */
+/* per-instruction global-timer stamps (ns), int64 [workers, length, 4] = {start, producers ready, end,
+ * GEMM copies issued}; enable before the launch to record. */
 int enable_native_model_timings(void* handle, int enable);
 int read_native_model_timings(void* handle, long long* out, size_t count);
 /* extension: synchronises the device and returns {code, worker, stage, band, observed, expected, aborted, epoch};

@@ -216,12 +216,25 @@ class Pi0Torch:
         self.dt = compute_dtype                 # activation dtype of the bf16 mode (float32 for a fast CPU baseline)
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self._wq = {}
+        self._kv_only = {(f"{LM}layers.{dims.prefix_layers - 1}.self_attn", "kv_only")}
         self.landmarks = {}
 
     # ----- linear layers ---------------------------------------------------------------------------
+    def _fused_scale(self, name, w):
+        """The engine packs q|k|v (k|v for the last prefix layer) and gate|up as ONE NVFP4 tensor, so the members of
+        a fused projection share one tensor scale: amax over the fused matrix / (6*448)."""
+        base, leaf = name.rsplit(".", 1)
+        if leaf in ("q_proj", "k_proj", "v_proj"):
+            members = ["k_proj", "v_proj"] if (base, "kv_only") in self._kv_only else ["q_proj", "k_proj", "v_proj"]
+        elif leaf in ("gate_proj", "up_proj"):
+            members = ["gate_proj", "up_proj"]
+        else:
+            return weight_global_scale(w)
+        return max(weight_global_scale(self.sd[f"{base}.{m}.weight"]) for m in members)
+
     def _qweight(self, name, w):
         if name not in self._wq:
-            gs = weight_global_scale(w)
+            gs = self._fused_scale(name, w)
             self._wq[name] = fake_quant(pad_cols(w.float(), 64), "ceil", gs)
         return self._wq[name]
 

@@ -269,13 +269,7 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
 __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
                                                  int stage_index, int first, int count) {
     const AttnParams& a = st.p.attn;
-    int current_band = -1;
     for (int t = first; t < first + count; ++t) {
-        const int band = tile_band(st, t);
-        if (band != current_band) {
-            if (!cta_wait_sources(prog, ctl, st, stage_index, band)) return;
-            current_band = band;
-        }
         if (a.head_dim > 128) attn_tile<256>(a, t, data);
         else attn_tile<80>(a, t, data);
         cta_publish_tile(prog, st, t);
@@ -332,7 +326,6 @@ __device__ __forceinline__ void merge_tile(const MergeParams& g, int head) {
 
 __device__ __forceinline__ void merge_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage_index,
                                                   int first, int count) {
-    if (!cta_wait_sources(prog, ctl, st, stage_index, 0)) return;
     for (int t = first; t < first + count; ++t) {
         merge_tile(st.p.merge, t);
         cta_publish_tile(prog, st, t);

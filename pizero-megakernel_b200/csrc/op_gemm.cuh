@@ -11,9 +11,11 @@
 
 namespace pi0 {
 
+// Whole warp 0: the dependency wait is lane-parallel, lane 0 issues the copies.
 __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
-                                              int stage_index, int first, int count, PipeState& ps) {
+                                              int stage_index, int first, int count, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
+    const int lane = lane_id();
     const int kstages = (g.k_groups + 3) >> 2;
     const uint32_t b_bytes = static_cast<uint32_t>(g.block_n) * 128u;
     int current_band = -1;
@@ -21,25 +23,33 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
         const int m_tile = t / g.n_tiles, n_tile = t - m_tile * g.n_tiles;
         const int band = tile_band(st, t);
         if (band != current_band) {
-            if (!wait_sources(prog, ctl, st, stage_index, band)) return;
-            fence_proxy_async_global();
+            if (!warp_wait_sources(prog, ctl, st, stage_index, band, band)) return;
+            if (lane == 0) {
+                fence_proxy_async_global();
+                if (stamp && current_band < 0) stamp[1] = static_cast<long long>(global_ns());
+            }
             current_band = band;
         }
-        const int sfb_tile = (n_tile * g.block_n) >> 7;
-        for (int ks = 0; ks < kstages; ++ks) {
-            const uint32_t s = ps.prod_it % kStages, phase = (ps.prod_it / kStages) & 1u;
-            if (!mbar_wait(prog, ctl, &ctl->empty[s], phase ^ 1u, stage_index)) return;
-            const int groups = min(4, g.k_groups - ks * 4);
-            uint8_t* slot = data + s * kStageBytes;
-            mbar_expect_tx(&ctl->full[s], kTileABytes + b_bytes + 2u * groups * 512u);
-            tma_load_2d(slot, g.tmap_a, &ctl->full[s], ks * 128, m_tile * 128);
-            tma_load_2d(slot + kTileABytes, g.tmap_b, &ctl->full[s], ks * 128, n_tile * g.block_n);
-            bulk_load(slot + 2 * kTileABytes, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4) * 512,
-                      groups * 512u, &ctl->full[s]);
-            bulk_load(slot + 2 * kTileABytes + kSfBytes, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4) * 512,
-                      groups * 512u, &ctl->full[s]);
-            ps.prod_it++;
+        int alive = 1;
+        if (lane == 0) {
+            const int sfb_tile = (n_tile * g.block_n) >> 7;
+            for (int ks = 0; ks < kstages; ++ks) {
+                const uint32_t s = ps.prod_it % kStages, phase = (ps.prod_it / kStages) & 1u;
+                if (!mbar_wait(prog, ctl, &ctl->empty[s], phase ^ 1u, stage_index)) { alive = 0; break; }
+                const int groups = min(4, g.k_groups - ks * 4);
+                uint8_t* slot = data + s * kStageBytes;
+                mbar_expect_tx(&ctl->full[s], kTileABytes + b_bytes + 2u * groups * 512u);
+                tma_load_2d(slot, g.tmap_a, &ctl->full[s], ks * 128, m_tile * 128);
+                tma_load_2d(slot + kTileABytes, g.tmap_b, &ctl->full[s], ks * 128, n_tile * g.block_n);
+                bulk_load(slot + 2 * kTileABytes, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4) * 512,
+                          groups * 512u, &ctl->full[s]);
+                bulk_load(slot + 2 * kTileABytes + kSfBytes, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4) * 512,
+                          groups * 512u, &ctl->full[s]);
+                ps.prod_it++;
+            }
         }
+        alive = __shfl_sync(0xffffffffu, alive, 0);
+        if (!alive) return;
     }
 }
 
@@ -254,16 +264,17 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
 // Dispatch of one GEMM instruction onto the warp roles. Warps 2 and 3 have no role and fall through.
 __device__ __forceinline__ void gemm_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem,
                                                  const StageDesc& st, int stage_index, int first, int count,
-                                                 PipeState& ps) {
+                                                 PipeState& ps, long long* stamp) {
     const int warp = threadIdx.x >> 5;
     if (warp == 0) {
-        if (lane_id() == 0) gemm_producer(prog, ctl, data, st, stage_index, first, count, ps);
-        __syncwarp();
+        gemm_producer(prog, ctl, data, st, stage_index, first, count, ps, stamp);
+        if (stamp && threadIdx.x == 0) stamp[3] = static_cast<long long>(global_ns());
     } else if (warp == 1) {
         if (lane_id() == 0) gemm_mma(prog, ctl, data, tmem, st, stage_index, first, count, ps);
         __syncwarp();
     } else if (warp >= 4) {
         gemm_epilogue(prog, ctl, tmem, st, stage_index, first, count, ps);
+        if (stamp && threadIdx.x == 128) stamp[2] = static_cast<long long>(global_ns());
     }
 }
 

@@ -111,13 +111,7 @@ __device__ __forceinline__ void norm_instruction(const VmProgram& prog, Ctl* ctl
                                                  int first, int count) {
     const NormParams& n = st.p.norm;
     const int warp = threadIdx.x >> 5;
-    int current_band = -1;
     for (int t = first; t < first + count; ++t) {
-        const int band = tile_band(st, t);
-        if (band != current_band) {
-            if (!cta_wait_sources(prog, ctl, st, stage_index, band)) return;
-            current_band = band;
-        }
         const int row = t * kNormRowsPerTile + warp;
         if (row < n.rows) norm_row(n, row);
         cta_publish_tile(prog, st, t);

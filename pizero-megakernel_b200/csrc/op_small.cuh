@@ -47,7 +47,6 @@ __device__ __forceinline__ void patch_instruction(const VmProgram& prog, Ctl* ct
                                                   int stage_index, int first, int count) {
     const PatchParams& p = st.p.patch;
     const float* images = p.images ? p.images : prog.in.images;
-    if (!cta_wait_sources(prog, ctl, st, stage_index, 0)) return;
     for (int t = first; t < first + count; ++t) {
         patch_tile(p, images, t, data);
         cta_publish_tile(prog, st, t);
@@ -59,7 +58,6 @@ __device__ __forceinline__ void embed_instruction(const VmProgram& prog, Ctl* ct
                                                   int first, int count) {
     const EmbedParams& e = st.p.embed;
     const long long* tokens = e.tokens ? e.tokens : prog.in.tokens;
-    if (!cta_wait_sources(prog, ctl, st, stage_index, 0)) return;
     const int warp = threadIdx.x >> 5, lane = lane_id();
     for (int t = first; t < first + count; ++t) {
         const int i = t * 8 + warp;
@@ -81,7 +79,6 @@ __device__ __forceinline__ void linear32_instruction(const VmProgram& prog, Ctl*
     const void* xbase = p.slot == 2 ? static_cast<const void*>(prog.in.state)
                         : p.slot == 3 ? static_cast<const void*>(prog.in.noise) : p.x;
     const float* prev = p.prev_slot == 3 ? prog.in.noise : p.prev;
-    if (!cta_wait_sources(prog, ctl, st, stage_index, 0)) return;
     const int warp = threadIdx.x >> 5, lane = lane_id();
     for (int t = first; t < first + count; ++t) {
         const int n = t * 8 + warp;
@@ -136,7 +133,6 @@ __device__ __forceinline__ void linear32_instruction(const VmProgram& prog, Ctl*
 __device__ __forceinline__ void suffix_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage_index,
                                                    int first, int count) {
     const SuffixParams& p = st.p.suffix;
-    if (!cta_wait_sources(prog, ctl, st, stage_index, 0)) return;
     const int warp = threadIdx.x >> 5, lane = lane_id();
     for (int t = first; t < first + count; ++t) {
         const int r = t * 8 + warp;

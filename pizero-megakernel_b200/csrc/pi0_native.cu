@@ -185,6 +185,23 @@ int build_program(Program** out, int device, const std::vector<StageDesc>& stage
     for (auto& c : cover)
         for (int v : c)
             if (v != 1) return cudaErrorInvalidValue;
+    // consumer-side wait lists: counter range and per-launch contribution of each producer
+    for (auto& d : prog->stages) {
+        int polled = 0;
+        for (int i = 0; i < kMaxSources; i++) {
+            d.src_counter_base[i] = 0; d.src_bands[i] = 0; d.src_expected[i] = 0; d.src_expected_last[i] = 0;
+            if (d.src[i] < 0) continue;
+            const StageDesc& src = prog->stages[d.src[i]];
+            d.src_counter_base[i] = src.counter_base;
+            d.src_bands[i] = src.bands;
+            d.src_expected[i] = prog->expected[src.counter_base];
+            d.src_expected_last[i] = prog->expected[src.counter_base + src.bands - 1];
+            for (int b = 0; b + 1 < src.bands; b++)
+                if (prog->expected[src.counter_base + b] != d.src_expected[i]) return cudaErrorInvalidValue;
+            polled += d.src_mode[i] == SRC_SAME_BAND ? std::min(d.bands, src.bands) : src.bands;
+        }
+        if (polled > 32) return cudaErrorInvalidValue;     // one lane per polled counter
+    }
 
     cudaError_t e = cudaMalloc(&prog->d_stages, sizeof(StageDesc) * prog->stages.size());
     if (e == cudaSuccess) e = cudaMalloc(&prog->d_code, sizeof(int4) * static_cast<size_t>(workers) * length);
@@ -812,7 +829,7 @@ extern "C" int enable_native_model_timings(void* handle, int enable) {
     Program* prog = as_program(handle);
     if (!prog) return cudaErrorInvalidValue;
     if (enable && !prog->d_timings) {
-        const size_t bytes = sizeof(long long) * 2 * prog->workers * prog->length;
+        const size_t bytes = sizeof(long long) * 4 * prog->workers * prog->length;
         cudaError_t e = cudaMalloc(&prog->d_timings, bytes);
         if (e == cudaSuccess) e = cudaMemset(prog->d_timings, 0, bytes);
         if (e != cudaSuccess) return e;
@@ -822,7 +839,7 @@ extern "C" int enable_native_model_timings(void* handle, int enable) {
 }
 extern "C" int read_native_model_timings(void* handle, long long* out, size_t count) {
     Program* prog = as_program(handle);
-    if (!prog || !out || !prog->d_timings || count != static_cast<size_t>(2) * prog->workers * prog->length) return cudaErrorInvalidValue;
+    if (!prog || !out || !prog->d_timings || count != static_cast<size_t>(4) * prog->workers * prog->length) return cudaErrorInvalidValue;
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return e;
     return cudaMemcpy(out, prog->d_timings, count * sizeof(long long), cudaMemcpyDeviceToHost);

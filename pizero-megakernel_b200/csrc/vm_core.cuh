@@ -1,4 +1,4 @@
-// Worker-CTA control block, bounded waits and the inter-SM dependency protocol.
+// Worker-CTA control block, instruction prefetch ring, bounded waits and the inter-SM dependency protocol.
 #pragma once
 #include "ptx.cuh"
 #include "vm_types.h"
@@ -9,22 +9,35 @@ constexpr int kStages = 5;                                   // shared-memory ri
 constexpr int kTileABytes = 128 * 128;                       // 128 rows x 128 bytes (256 FP4 along K)
 constexpr int kSfBytes = 4 * 512;                            // four 64-wide K groups of scale atoms
 constexpr int kStageBytes = 2 * kTileABytes + 2 * kSfBytes;  // A | B | SFA | SFB = 36 KiB
-constexpr int kCtlBytes = 1024;
-constexpr int kDataBytes = 216 * 1024;                       // operator scratch behind the control block
+constexpr int kCtlBytes = 3072;
+constexpr int kDataBytes = 214 * 1024;                       // operator scratch behind the control block
 constexpr int kSmemBytes = kCtlBytes + kDataBytes + 1024;    // + slack for 1 KiB alignment
 constexpr int kTmemCols = 512;
 constexpr int kSfCol0 = 256;                                 // accumulators use columns [0,256)
+constexpr int kRing = 4;                                     // instruction slots resident in shared memory
+constexpr int kAhead = 2;                                    // the prefetch warp runs this many instructions ahead
+constexpr int kPrefetchWarp = 2;
 static_assert(kStages * kStageBytes <= kDataBytes, "GEMM ring exceeds the data region");
+static_assert(sizeof(StageDesc) % 16 == 0, "descriptors are copied in 16-byte pieces");
+
+// One decoded instruction: the stream entry and a private copy of its stage descriptor.
+struct alignas(16) Slot {
+    int4 ins;                    // {opcode, stage, first_tile, tile_count}; opcode 0 terminates the stream
+    StageDesc desc;
+};
 
 struct Ctl {
     uint64_t full[kStages];
     uint64_t empty[kStages];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t ready[kRing];       // slot filled (32 asynchronous-copy arrivals of the prefetch warp)
+    uint64_t release[kRing];     // slot no longer read (one arrival per warp)
     uint32_t tmem_base;
     volatile int abort;          // CTA-local copy of the abort decision
     volatile int dep_ok;         // broadcast slot for CTA-wide operators
-    float red[32];               // small reduction scratch
+    int pad;
+    Slot slot[kRing];
 };
 static_assert(sizeof(Ctl) <= kCtlBytes, "control block too large");
 
@@ -67,20 +80,54 @@ __device__ __forceinline__ bool mbar_wait(const VmProgram& prog, Ctl* ctl, uint6
     }
 }
 
-// Single-thread wait until counter >= target.
-__device__ __forceinline__ bool counter_wait(const VmProgram& prog, Ctl* ctl, const unsigned int* counter,
-                                             unsigned int target, int stage, int band) {
-    unsigned int seen = ld_acquire(counter);
-    if (seen >= target) return true;
-    unsigned long long start = global_ns();
+__device__ __forceinline__ int tile_band(const StageDesc& st, int tile) { return min(tile / st.band_div, st.bands - 1); }
+
+// Warp-cooperative dependency wait (all 32 lanes of one warp call it): every counter this tile range reads
+// is polled by its own lane, so a stage with several producers and bands costs one memory round trip, not
+// one per counter.  Bands [band_lo, band_hi] of the consumer are covered.  Returns false on abort / timeout.
+__device__ __forceinline__ bool warp_wait_sources(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage,
+                                                  int band_lo, int band_hi) {
+    const int lane = lane_id();
+    const unsigned int* mine = nullptr;
+    unsigned int target = 0;
+    int my_band = -1, n = 0;
+#pragma unroll
+    for (int i = 0; i < kMaxSources; i++) {
+        const int src = st.src[i];
+        if (src < 0 || src < prog.stage_begin) continue;
+        const int sb = st.src_bands[i];
+        int lo = 0, hi = sb - 1;
+        if (st.src_mode[i] == SRC_SAME_BAND) {
+            lo = min(band_lo, sb - 1);
+            hi = min(band_hi, sb - 1);
+        }
+        for (int b = lo; b <= hi; b++, n++) {
+            if ((n & 31) == lane && mine == nullptr) {
+                mine = prog.counters + st.src_counter_base[i] + b;
+                target = (b == sb - 1 ? st.src_expected_last[i] : st.src_expected[i]) * prog.epoch;
+                my_band = b;
+            }
+        }
+    }
+    // (a consumer never reads more than 32 counters; the host rejects programs that would)
+    unsigned int seen = mine ? ld_acquire(mine) : 0u;
+    bool ok = mine == nullptr || seen >= target;
+    if (__all_sync(0xffffffffu, ok)) return true;
+    const unsigned long long start = global_ns();
     for (uint32_t spin = 1;; ++spin) {
-        __nanosleep(20);
-        seen = ld_acquire(counter);
-        if (seen >= target) return true;
+        if (!ok) {
+            __nanosleep(20);
+            seen = ld_acquire(mine);
+            ok = seen >= target;
+        }
+        if (__all_sync(0xffffffffu, ok)) return true;
         if ((spin & 63u) == 0u) {
-            if (ctl->abort) return false;
-            if (global_ns() - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort)) {
-                report(prog, 1, stage, band, seen, target);
+            bool stop = ctl->abort != 0;
+            if (!stop && (global_ns() - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort))) {
+                if (!ok) report(prog, 1, stage, my_band, seen, target);
+                stop = true;
+            }
+            if (__any_sync(0xffffffffu, stop)) {
                 ctl->abort = 1;
                 return false;
             }
@@ -88,42 +135,24 @@ __device__ __forceinline__ bool counter_wait(const VmProgram& prog, Ctl* ctl, co
     }
 }
 
-// Wait (one thread) for every source of `st` that this tile band reads.
-__device__ __forceinline__ bool wait_sources(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage, int band) {
-#pragma unroll
-    for (int i = 0; i < kMaxSources; i++) {
-        int src = st.src[i];
-        if (src < 0 || src < prog.stage_begin) continue;
-        const StageDesc& ps = prog.stages[src];
-        int lo = 0, hi = ps.bands;
-        if (st.src_mode[i] == SRC_SAME_BAND) {
-            lo = min(band, ps.bands - 1);
-            hi = lo + 1;
-        }
-        for (int b = lo; b < hi; b++) {
-            int c = ps.counter_base + b;
-            if (!counter_wait(prog, ctl, prog.counters + c, prog.expected[c] * prog.epoch, stage, b)) return false;
-        }
-    }
-    return true;
-}
-
-__device__ __forceinline__ int tile_band(const StageDesc& st, int tile) { return min(tile / st.band_div, st.bands - 1); }
-
 // Publish progress of a tile. Call from ONE thread after a barrier (CTA or warp) that covers every
 // writer thread it speaks for. A stage's tile is complete after `units_per_tile` such calls.
 __device__ __forceinline__ void publish_tile(const VmProgram& prog, const StageDesc& st, int tile) {
-    __threadfence();
     red_release_add(prog.counters + st.counter_base + tile_band(st, tile), 1u);
 }
 
-// CTA-wide operators: thread 0 waits, everybody learns the outcome. Returns false on abort.
-__device__ __forceinline__ bool cta_wait_sources(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage, int band) {
-    if (threadIdx.x == 0) ctl->dep_ok = wait_sources(prog, ctl, st, stage, band) ? 1 : 0;
+// CTA-wide operators: warp 0 waits for the bands of the whole tile range, everybody learns the outcome.
+__device__ __forceinline__ bool cta_wait_sources(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage,
+                                                 int first, int count, long long* stamp) {
+    if (threadIdx.x < 32) {
+        const bool ok = warp_wait_sources(prog, ctl, st, stage, tile_band(st, first), tile_band(st, first + count - 1));
+        if (threadIdx.x == 0) {
+            ctl->dep_ok = ok ? 1 : 0;
+            if (stamp) stamp[1] = static_cast<long long>(global_ns());
+        }
+    }
     __syncthreads();
-    bool ok = ctl->dep_ok != 0;
-    __syncthreads();
-    return ok;
+    return ctl->dep_ok != 0;
 }
 __device__ __forceinline__ void cta_publish_tile(const VmProgram& prog, const StageDesc& st, int tile) {
     fence_proxy_async_global();

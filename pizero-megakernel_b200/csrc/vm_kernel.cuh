@@ -1,4 +1,10 @@
 // The persistent worker kernel: every CTA walks its own static instruction stream.
+//
+// Warp 2 runs kAhead instructions ahead of the others and copies each upcoming instruction and its stage
+// descriptor from global memory into a shared-memory slot with asynchronous copies that arrive on the slot's
+// mbarrier, so the working warps never chase pointers through global memory between two dependent stages: they
+// wait on a shared-memory barrier, read the descriptor, poll the (precomputed) producer counters in parallel and
+// start.  A slot is recycled once all eight warps have released it.
 #pragma once
 #include "op_attention.cuh"
 #include "op_gemm.cuh"
@@ -6,6 +12,38 @@
 #include "op_small.cuh"
 
 namespace pi0 {
+
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Instruction `ip` of this worker, or a terminator when the stream (or the requested stage range) is over.
+__device__ __forceinline__ int4 fetch_instruction(const VmProgram& prog, const int4* stream, int ip) {
+    if (ip >= prog.length) return make_int4(0, 0, 0, 0);
+    int4 ins = __ldg(stream + ip);
+    if (ins.x == 0 || ins.y >= prog.stage_end) return make_int4(0, 0, 0, 0);
+    return ins;
+}
+
+// Whole prefetch warp: fill slot (seq % kRing) with instruction `ins`. Returns false on abort.
+__device__ __forceinline__ bool prefetch_slot(const VmProgram& prog, Ctl* ctl, const int4* stream, uint32_t seq, int ip, int4 ins) {
+    const int lane = lane_id();
+    const uint32_t slot = seq % kRing, use = seq / kRing;
+    if (use > 0 && !mbar_wait(prog, ctl, &ctl->release[slot], (use - 1) & 1u, ins.y)) return false;
+    Slot* dst = &ctl->slot[slot];
+    if (ins.x == 0) {
+        if (lane == 0) dst->ins = ins;
+        __syncwarp();
+        mbar_arrive(&ctl->ready[slot]);
+        return true;
+    }
+    const char* src = reinterpret_cast<const char*>(prog.stages + ins.y);
+    char* out = reinterpret_cast<char*>(&dst->desc);
+    for (int off = lane * 16; off < static_cast<int>(sizeof(StageDesc)); off += 32 * 16) cp_async16(out + off, src + off, true);
+    if (lane == 31) cp_async16(&dst->ins, stream + ip, true);
+    cp_async_arrive_noinc(&ctl->ready[slot]);
+    return true;
+}
 
 __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_constant__ VmProgram prog) {
     extern __shared__ uint8_t smem_raw[];
@@ -23,6 +61,10 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
             mbar_init(&ctl->acc_full[b], 1);
             mbar_init(&ctl->acc_empty[b], 4);      // one arrival per epilogue warp
         }
+        for (int r = 0; r < kRing; r++) {
+            mbar_init(&ctl->ready[r], 32);         // every lane of the prefetch warp
+            mbar_init(&ctl->release[r], kThreads / 32);
+        }
         ctl->abort = 0;
         ctl->dep_ok = 1;
         mbar_fence_init();
@@ -36,21 +78,43 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
 
-    PipeState ps;
     const int4* stream = prog.code + static_cast<size_t>(blockIdx.x) * prog.length;
-    for (int ip = 0; ip < prog.length; ++ip) {
-        const int4 ins = stream[ip];
-        if (ins.x == 0 || ins.y >= prog.stage_end) break;
-        if (ins.y < prog.stage_begin) continue;
-        const StageDesc& st = prog.stages[ins.y];
-        if (prog.timings && threadIdx.x == 0) prog.timings[(static_cast<size_t>(blockIdx.x) * prog.length + ip) * 2] = clock64();
+    // first instruction of the requested stage range (streams are sorted by stage)
+    int ip0 = 0;
+    if (prog.stage_begin > 0) {
+        while (ip0 < prog.length) {
+            const int4 ins = __ldg(stream + ip0);
+            if (ins.x == 0 || ins.y >= prog.stage_begin) break;
+            ip0++;
+        }
+    }
+    int4 pending = make_int4(0, 0, 0, 0);
+    if (warp == kPrefetchWarp) {
+        for (int s = 0; s < kAhead; s++) prefetch_slot(prog, ctl, stream, s, ip0 + s, fetch_instruction(prog, stream, ip0 + s));
+        pending = fetch_instruction(prog, stream, ip0 + kAhead);
+    }
+
+    PipeState ps;
+    for (uint32_t seq = 0;; ++seq) {
+        if (warp == kPrefetchWarp) {
+            if (!prefetch_slot(prog, ctl, stream, seq + kAhead, ip0 + seq + kAhead, pending)) break;
+            pending = fetch_instruction(prog, stream, ip0 + seq + kAhead + 1);      // consumed one iteration later
+        }
+        const uint32_t slot = seq % kRing;
+        if (!mbar_wait(prog, ctl, &ctl->ready[slot], (seq / kRing) & 1u, -1)) break;
+        const int4 ins = ctl->slot[slot].ins;
+        if (ins.x == 0) break;
+        const StageDesc& st = ctl->slot[slot].desc;
+        long long* stamp = prog.timings ? prog.timings + (static_cast<size_t>(blockIdx.x) * prog.length + ip0 + seq) * 4 : nullptr;
+        if (stamp && threadIdx.x == 0) stamp[0] = static_cast<long long>(global_ns());
         if (st.kind == OP_GEMM) {
-            gemm_instruction(prog, ctl, data, tmem, st, ins.y, ins.z, ins.w, ps);
+            gemm_instruction(prog, ctl, data, tmem, st, ins.y, ins.z, ins.w, ps, stamp);
             if (ctl->abort) break;
         } else {
             // CTA-wide operator: every warp (including GEMM roles still draining) meets here first.
             __syncthreads();
             if (ctl->abort) break;
+            if (!cta_wait_sources(prog, ctl, st, ins.y, ins.z, ins.w, stamp)) break;
             switch (st.kind) {
                 case OP_NORM: norm_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
                 case OP_ATTN: attn_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
@@ -65,8 +129,10 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
             }
             __syncthreads();
             if (ctl->abort) break;
+            if (stamp && threadIdx.x == 0) stamp[2] = static_cast<long long>(global_ns());
         }
-        if (prog.timings && threadIdx.x == 0) prog.timings[(static_cast<size_t>(blockIdx.x) * prog.length + ip) * 2 + 1] = clock64();
+        __syncwarp();
+        if (lane_id() == 0) mbar_arrive(&ctl->release[slot]);
     }
 
     // Teardown. After an abort, give copies and MMAs that may still be in flight a bounded moment to land.
@@ -74,6 +140,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
+    cp_async_wait<0>();
     tc_fence_before();
     __syncthreads();
     if (warp == 2) {

@@ -161,7 +161,7 @@ struct SuffixParams {
     int chunk, width;
 };
 
-struct StageDesc {
+struct alignas(16) StageDesc {
     int kind;
     int tiles;
     int bands;
@@ -170,6 +170,12 @@ struct StageDesc {
     int src[kMaxSources];
     int src_mode[kMaxSources];
     int units_per_tile;          // counter increments one finished tile contributes (GEMM: one per epilogue warp)
+    // Filled by the host when the program is built, so a consumer polls counters without touching its producers'
+    // descriptors: first counter, band count and the per-launch contribution of a full / of the last band.
+    int src_counter_base[kMaxSources];
+    int src_bands[kMaxSources];
+    unsigned int src_expected[kMaxSources];
+    unsigned int src_expected_last[kMaxSources];
     union {
         GemmParams gemm;
         NormParams norm;
@@ -204,7 +210,7 @@ struct VmProgram {
     unsigned int* counters;
     const unsigned int* expected;
     VmStatus* status;
-    long long* timings;          // optional [workers][length][2] clock stamps
+    long long* timings;          // optional [workers][length][4] global-timer stamps: start, sources ready, end, GEMM drain
     int num_stages, length;
     unsigned int epoch;
     int stage_begin, stage_end;  // execute stages in [begin, end); sources < begin are treated as complete

@@ -1,0 +1,573 @@
+"""NVFP4 pi0 on one B200: the whole forward as one persistent launch over static instruction streams.
+
+``NativePi0`` keeps the surface of the reference class (``native_pi0/model.py:34-348``):
+``from_openpi`` / ``from_model`` constructors, ``forward(images, state, noise, tokens)`` returning the
+reused FP32 action tensor ``[1, chunk, 32]``, ``launch_component``, ``read_timings``, ``close`` and the
+context-manager protocol, with the attributes ``output, plan, stages, landmarks, component_ranges, epoch,
+precision_policy``.  What differs is the engine underneath: every transformer linear is an NVFP4
+block-scaled GEMM on tcgen05 (weights packed on the device at setup with the ``ceil`` scale policy and a
+per-tensor scale of amax/(6*448); activations quantised on the fly with the ``nearest`` policy and tensor
+scale 1), RoPE and the KV-cache write live in the QKV epilogue, GeGLU/GELU + requantisation live in the
+MLP epilogues, and the 51-row action expert uses split-KV attention with a merge stage.
+
+Setup owns all layouts, buffers, weight transforms and the instruction streams; ``forward`` only launches.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from pathlib import Path
+
+import numpy as np
+import torch
+
+from native_pi0 import _native
+from native_pi0._native import NativeSpec
+from native_pi0.program import LinearWork, linear_streams, program_summary, validate_streams
+from native_pi0.quantization import swizzled_size
+from native_pi0.storage import packed_tma_buffer
+from native_pi0.weights import EXPERT, LANGUAGE, PROJECTOR, VISION, Pi0Config, StateDictModel
+
+SAME, ALL = 0, 1
+
+
+def padded(n, a):
+    return (n + a - 1) // a * a
+
+
+class Fp4Matrix:
+    """Device-resident NVFP4 matrix: packed codes [rows_pad, k/2], swizzled E4M3 scales, FP32 tensor scale."""
+
+    def __init__(self, rows_pad, k, device, global_scale=1.0):
+        self.rows_pad, self.k = rows_pad, k
+        self.data = packed_tma_buffer((rows_pad, k // 2), device=device)
+        self.scales = torch.zeros(swizzled_size(rows_pad, k // 16), dtype=torch.uint8, device=device)
+        self.global_scale = float(np.float32(global_scale))
+
+
+class NativePi0:
+    @classmethod
+    def from_openpi(cls, checkpoint_path, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10,
+                    precision="auto", library=None, **kwargs):
+        """Load an OpenPI ``model.safetensors`` (parameter names of ``PI0Pytorch``) straight into the engine."""
+        from safetensors.torch import load_file
+        sd = load_file(str(checkpoint_path), device="cuda")
+        config = Pi0Config(action_dim=sd["action_out_proj.weight"].shape[0])
+        return cls(StateDictModel(config, sd), num_views=num_views, prompt_len=prompt_len, chunk_size=chunk_size,
+                   flow_steps=flow_steps, precision=precision, library=library, **kwargs)
+
+    @classmethod
+    def from_model(cls, model, **kwargs):
+        return cls(model, **kwargs)
+
+    @classmethod
+    def from_state_dict(cls, state_dict, config=None, **kwargs):
+        return cls(StateDictModel(config or Pi0Config(), state_dict), **kwargs)
+
+    def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
+                 library=None, workers=None, partitioned=False, expert_splits=8, expert_block_n=128,
+                 rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False):
+        config = getattr(model, "config", None)
+        if config is None or getattr(config, "pi05", False) or precision not in ("auto", "nvfp4"):
+            raise ValueError("This engine runs ordinary pi0 with NVFP4 transformers (precision 'auto' or 'nvfp4')")
+        if num_views not in (1, 2, 3) or prompt_len < 0 or chunk_size < 1 or chunk_size > 127 or flow_steps < 1:
+            raise ValueError("Invalid fixed inference dimensions")
+        if not isinstance(config, Pi0Config):
+            config = Pi0Config(**{k: getattr(config, k) for k in Pi0Config.__dataclass_fields__ if hasattr(config, k)})
+        self.config = config
+        self.num_views, self.prompt_len, self.chunk_size, self.flow_steps = num_views, prompt_len, chunk_size, flow_steps
+        self.precision_policy = "nvfp4"
+        self.partitioned = partitioned
+        self.expert_splits = expert_splits
+        self.expert_block_n = expert_block_n
+        self.rope_inv_freq_dtype = rope_inv_freq_dtype
+        self.keep_debug_outputs = keep_debug_outputs
+        self.verbose = verbose
+        sd = model.state_dict()
+        self.device = next(iter(sd.values())).device
+        if self.device.type != "cuda":
+            raise ValueError("Supply CUDA-resident parameters")
+        self.library_path = Path(library).resolve() if library is not None else _native.LIBRARY
+        self.lib = _native.load(self.library_path)
+        with torch.cuda.device(self.device):
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.workers = min(sms, 148) if workers is None else workers
+        self.sd = sd
+        self.buffers, self.handles, self._cache = [], [], {}
+        self.stages, self.stage_tiles, self.stage_cost, self.stage_names = [], [], [], []
+        self.landmarks, self.landmark_stage = {}, {}
+        self.handle = C.c_void_p()
+        self.epoch = 0
+        try:
+            with torch.cuda.device(self.device), torch.no_grad():
+                self._build()
+        except Exception:
+            self.close()
+            raise
+        self.sd = None
+
+    # ------------------------------------------------------------------------------------------ buffers
+    def tensor(self, shape, dtype=torch.bfloat16):
+        t = torch.zeros(shape, device=self.device, dtype=dtype)
+        self.buffers.append(t)
+        return t
+
+    def fp4(self, rows_pad, k):
+        m = Fp4Matrix(rows_pad, k, self.device)
+        self.buffers.append(m)
+        return m
+
+    def cached(self, key, make):
+        """Build a derived tensor (quantised weight, folded gamma) once per parameter and share it between stages."""
+        if key not in self._cache:
+            self._cache[key] = make()
+        return self._cache[key]
+
+    def weight(self, w, *, rows_to=128):
+        """BF16/FP32 [N, K] -> NVFP4 on the device (ceil block scales, tensor scale amax/(6*448))."""
+        n, k = w.shape
+        np_, kp = padded(n, rows_to), padded(k, 64)
+        src = torch.zeros((np_, kp), device=self.device, dtype=torch.bfloat16)
+        src[:n, :k] = w.to(torch.bfloat16)
+        gs = max(float(src.float().abs().max()) / (6.0 * 448.0), 1e-30)
+        m = Fp4Matrix(np_, kp, self.device, gs)
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        _native.check(self.lib.quantize_nvfp4(src.data_ptr(), m.data.data_ptr(), m.scales.data_ptr(), np_, kp, kp, kp // 16,
+                                              m.global_scale, 1, stream), "weight quantisation")
+        torch.cuda.current_stream(self.device).synchronize()
+        self.buffers.append(m)
+        return m
+
+    # ------------------------------------------------------------------------------------------ stages
+    def add(self, kind, handle, name, sources=()):
+        tiles, bands, cost = C.c_int(), C.c_int(), C.c_int()
+        _native.check(self.lib.op_geometry(handle, C.byref(tiles), C.byref(bands), C.byref(cost)), "operator geometry")
+        spec = NativeSpec()
+        spec.kind, spec.handle = kind, handle.value if isinstance(handle, C.c_void_p) else handle
+        srcs = [(s, m) for s, m in sources if s is not None and s >= 0]
+        if len(srcs) > 4:
+            raise ValueError("Too many stage sources")
+        for i in range(4):
+            spec.sources[i], spec.modes[i] = srcs[i] if i < len(srcs) else (-1, ALL)
+        self.stages.append(spec)
+        self.stage_tiles.append(tiles.value)
+        self.stage_cost.append(padded(max(cost.value, 64), 64))
+        self.stage_names.append(name)
+        return len(self.stages) - 1
+
+    def mark(self, name, tensor):
+        self.landmarks[name] = tensor
+        self.landmark_stage[name] = len(self.stages)       # valid once stages [0, this) have run
+
+    def _own(self, handle):
+        self.handles.append(handle)
+        return handle
+
+    def gemm(self, name, a: Fp4Matrix, w: Fp4Matrix, *, rows, sources, out=None, bias=None, residual=None,
+             fp4_out: Fp4Matrix = None, activation=0, rope=None, block_n=128):
+        h = C.c_void_p()
+        m, n, k = a.rows_pad, w.rows_pad, w.k
+        if a.k != k:
+            raise ValueError(f"{name}: K mismatch {a.k} vs {k}")
+        dummy = out if out is not None else (fp4_out.data if fp4_out is not None else rope["q"] if rope and rope.get("q") is not None else a.data)
+        _native.check(self.lib.create_resident_fp4(C.byref(h), a.data.data_ptr(), w.data.data_ptr(), a.scales.data_ptr(),
+                                                   w.scales.data_ptr(), dummy.data_ptr(), m, n, k, self.workers,
+                                                   float(np.float32(a.global_scale) * np.float32(w.global_scale))), name)
+        self._own(h)
+        if rope is not None:
+            q = rope.get("q")
+            _native.check(self.lib.configure_resident_fp4_qkv_rope(
+                h, _native.ptr(q), 0 if q is None else q.stride(0), rope["cos"].data_ptr(), rope["sin"].data_ptr(),
+                rope["cache_k"].data_ptr(), rope["cache_v"].data_ptr(), rope["q_cols"], self.config.head_dim, rope["cache_base"]), name)
+        elif fp4_out is not None:
+            _native.check(self.lib.configure_resident_fp4_quantized(h, _native.ptr(bias), _native.ptr(residual), fp4_out.data.data_ptr(),
+                                                                    fp4_out.scales.data_ptr(), fp4_out.global_scale, activation), name)
+        else:
+            _native.check(self.lib.configure_resident_fp4_bf16(h, _native.ptr(bias), _native.ptr(residual), out.data_ptr()), name)
+        _native.check(self.lib.configure_resident_fp4_rows(h, rows), name)
+        if block_n != 128:
+            _native.check(self.lib.configure_resident_fp4_tile(h, block_n), name)
+        return self.add(0, h, name, sources)
+
+    def norm(self, name, x, out: Fp4Matrix, *, rows, sources, kind, gamma=None, beta=None, eps=1e-6, bf16_copy=None):
+        h = C.c_void_p()
+        width = x.shape[1]
+        _native.check(self.lib.create_norm(C.byref(h), x.data_ptr(), None, _native.ptr(gamma), _native.ptr(beta), None, None,
+                                           out.data.data_ptr(), out.scales.data_ptr(), rows, width, self.workers, 0, 4,
+                                           int(kind == "layer"), 1, 1, 0, float(eps), out.global_scale), name)
+        self._own(h)
+        if kind == "none":
+            _native.check(self.lib.configure_norm_quantize_only(h, 0), name)
+        if bf16_copy is not None:
+            _native.check(self.lib.configure_norm_bf16_copy(h, bf16_copy.data_ptr()), name)
+        return self.add(2, h, name, sources)
+
+    def linear32(self, name, x, w, bias, out, *, rows, sources, ldx=None, x_bf16=False, out_bf16=False, silu=False,
+                 rms=False, euler=False, prev=None, slot=0, prev_slot=0, x_row_offset=0, dt=0.0, eps=1e-6):
+        h = C.c_void_p()
+        n, k = w.shape
+        flags = int(x_bf16) | int(out_bf16) << 1 | int(silu) << 2 | int(rms) << 3 | int(euler) << 4
+        _native.check(self.lib.create_linear32(C.byref(h), _native.ptr(x), w.data_ptr(), _native.ptr(bias), _native.ptr(prev),
+                                               out.data_ptr(), rows, n, k, ldx if ldx is not None else k, out.stride(0), flags,
+                                               slot, prev_slot, x_row_offset, float(dt), float(eps), self.workers), name)
+        self._own(h)
+        return self.add(3, h, name, sources)
+
+    # ------------------------------------------------------------------------------------------ tables
+    def rope(self, rows, offset):
+        hd = self.config.head_dim
+        inv = 1.0 / (self.config.rope_base ** (torch.arange(0, hd, 2, dtype=torch.float32, device=self.device) / hd))
+        inv = inv.to(self.rope_inv_freq_dtype).float()
+        pos = torch.arange(offset, offset + rows, device=self.device, dtype=torch.float32)
+        freqs = pos[:, None] * inv[None, :]
+        emb = torch.cat((freqs, freqs), dim=-1)
+        rows_pad = padded(rows, 128)
+        cos = torch.zeros((rows_pad, hd), device=self.device, dtype=torch.bfloat16)
+        sin = torch.zeros_like(cos)
+        cos[:rows] = emb.cos().to(torch.bfloat16)
+        sin[:rows] = emb.sin().to(torch.bfloat16)
+        self.buffers.extend((cos, sin))
+        return cos, sin
+
+    def _interleave_heads(self, w):
+        """Reorder the rows of a Q or K projection so rotate-half partners (i, i + hd/2) become adjacent."""
+        hd = self.config.head_dim
+        idx = torch.stack((torch.arange(hd // 2), torch.arange(hd // 2) + hd // 2), dim=1).reshape(-1).to(w.device)
+        heads = w.shape[0] // hd
+        return w.reshape(heads, hd, -1)[:, idx, :].reshape(w.shape)
+
+    # ------------------------------------------------------------------------------------------ blocks
+    def _vision(self):
+        c, sd, lib = self.config, self.sd, self.lib
+        V, W = self.num_views, c.vision_width
+        M = V * 256
+        hd = W // c.vision_heads
+        patch_w = sd[VISION + "embeddings.patch_embedding.weight"].float().permute(2, 3, 1, 0).reshape(588, W).contiguous()
+        patch_b = sd[VISION + "embeddings.patch_embedding.bias"].float().contiguous()
+        pos = sd[VISION + "embeddings.position_embedding.weight"].float().contiguous()
+        self.buffers.extend((patch_w, patch_b, pos))
+        xa, xb = self.tensor((M, W)), self.tensor((M, W))
+        h = C.c_void_p()
+        _native.check(lib.create_patch_embed(C.byref(h), None, patch_w.data_ptr(), patch_b.data_ptr(), pos.data_ptr(), xa.data_ptr(),
+                                             V, W, self.workers), "patch embedding")
+        self._own(h)
+        s_x = self.add(3, h, "vision.patch")
+        self.mark("patch", xa)
+        a_ln, a_att, a_ln2 = self.fp4(M, W), self.fp4(M, W), self.fp4(M, W)
+        mlp_pad = padded(c.vision_mlp, 128)
+        a_h = self.fp4(M, mlp_pad)
+        qkv = [self.tensor((M, 3 * W)), self.tensor((M, 3 * W))]
+        att = self.tensor((M, W))
+        for i in range(c.vision_layers):
+            p = f"{VISION}encoder.layers.{i}."
+            g1, b1 = sd[p + "layer_norm1.weight"].float().contiguous(), sd[p + "layer_norm1.bias"].float().contiguous()
+            g2, b2 = sd[p + "layer_norm2.weight"].float().contiguous(), sd[p + "layer_norm2.bias"].float().contiguous()
+            wqkv = self.weight(torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"]))
+            bqkv = torch.cat([sd[p + f"self_attn.{n}_proj.bias"] for n in "qkv"]).to(torch.bfloat16).contiguous()
+            wo = self.weight(sd[p + "self_attn.out_proj.weight"])
+            bo = sd[p + "self_attn.out_proj.bias"].to(torch.bfloat16).contiguous()
+            w1 = self.weight(sd[p + "mlp.fc1.weight"])
+            bias1 = torch.zeros(mlp_pad, device=self.device, dtype=torch.bfloat16)
+            bias1[:c.vision_mlp] = sd[p + "mlp.fc1.bias"].to(torch.bfloat16)
+            w2 = self.weight(sd[p + "mlp.fc2.weight"])
+            bias2 = sd[p + "mlp.fc2.bias"].to(torch.bfloat16).contiguous()
+            self.buffers.extend((g1, b1, g2, b2, bqkv, bo, bias1, bias2))
+            buf = qkv[i & 1]
+            s_ln = self.norm(f"vision.{i}.ln1", xa, a_ln, rows=M, sources=[(s_x, SAME)], kind="layer", gamma=g1, beta=b1, eps=c.ln_eps)
+            s_qkv = self.gemm(f"vision.{i}.qkv", a_ln, wqkv, rows=M, sources=[(s_ln, SAME)], out=buf, bias=bqkv)
+            h = C.c_void_p()
+            q, k, v = buf[:, :W], buf[:, W:2 * W], buf[:, 2 * W:]
+            _native.check(lib.create_attention(C.byref(h), q.data_ptr(), k.data_ptr(), v.data_ptr(), None, None, None, None, None,
+                                               None, None, att.data_ptr(), None, V, 256, 256, c.vision_heads, c.vision_heads, hd,
+                                               3 * W, 3 * W, W, 0, self.workers, -1, float(hd ** -0.5)), "vision attention")
+            self._own(h)
+            s_att = self.add(1, h, f"vision.{i}.attention", [(s_qkv, ALL)])
+            s_aq = self.norm(f"vision.{i}.attention_quant", att, a_att, rows=M, sources=[(s_att, SAME)], kind="none")
+            s_o = self.gemm(f"vision.{i}.out", a_att, wo, rows=M, sources=[(s_aq, SAME)], out=xb, bias=bo, residual=xa)
+            s_ln2 = self.norm(f"vision.{i}.ln2", xb, a_ln2, rows=M, sources=[(s_o, SAME)], kind="layer", gamma=g2, beta=b2, eps=c.ln_eps)
+            s_fc1 = self.gemm(f"vision.{i}.fc1", a_ln2, w1, rows=M, sources=[(s_ln2, SAME)], fp4_out=a_h, bias=bias1, activation=1)
+            s_x = self.gemm(f"vision.{i}.fc2", a_h, w2, rows=M, sources=[(s_fc1, SAME)], out=xa, bias=bias2, residual=xb)
+            if i == 0:
+                self.mark("vision.0.qkv", buf), self.mark("vision.0.attention", att)
+            self.mark(f"vision.{i}", xa)
+            if self.verbose and (i + 1) % 9 == 0:
+                print("NativePi0: vision layers", i + 1, flush=True)
+        gp, bp = sd[VISION + "post_layernorm.weight"].float().contiguous(), sd[VISION + "post_layernorm.bias"].float().contiguous()
+        self.buffers.extend((gp, bp))
+        s_pl = self.norm("vision.post_layernorm", xa, a_ln, rows=M, sources=[(s_x, SAME)], kind="layer", gamma=gp, beta=bp, eps=c.ln_eps)
+        return s_pl, a_ln
+
+    def _gemma_layer(self, name, prefix, i, x_in, x_mid, bufs, *, rows, s_x, extra_sources, cos, sin, cache, cache_base,
+                     attention_rows, mask_prefix, splits, kv_only, block_n, prefix_cache_stage=None):
+        c, sd, lib = self.config, self.sd, self.lib
+        p = f"{prefix}layers.{i}."
+        width = x_in.shape[1]
+        H, hd = c.heads, c.head_dim
+        a1, a2, a3, a4, qbuf, attn_out = bufs
+        g1 = self.cached(p + "g1", lambda: (1.0 + sd[p + "input_layernorm.weight"].float()).contiguous())
+        s_n1 = self.norm(f"{name}.norm1", x_in, a1, rows=rows, sources=[(s_x, SAME)] + extra_sources, kind="rms", gamma=g1, eps=c.rms_eps)
+        def make_qkv():
+            wk = self._interleave_heads(sd[p + "self_attn.k_proj.weight"])
+            wv = sd[p + "self_attn.v_proj.weight"]
+            if kv_only:
+                return self.weight(torch.cat((wk, wv)))
+            return self.weight(torch.cat((self._interleave_heads(sd[p + "self_attn.q_proj.weight"]), wk, wv)))
+
+        wqkv = self.cached(p + "qkv", make_qkv)
+        q_cols, q = (0, None) if kv_only else (H * hd, qbuf)
+        s_qkv = self.gemm(f"{name}.qkv", a1, wqkv, rows=rows, sources=[(s_n1, SAME)], block_n=block_n,
+                          rope=dict(q=q, cos=cos, sin=sin, cache_k=cache[0], cache_v=cache[1], q_cols=q_cols, cache_base=cache_base))
+        if kv_only:
+            return s_qkv, s_qkv
+        h = C.c_void_p()
+        _native.check(lib.create_attention(C.byref(h), qbuf.data_ptr(), cache[0].data_ptr(), cache[1].data_ptr(), None, None, None,
+                                           None, None, None, None, attn_out.data_ptr(), None, 1, rows, attention_rows, H, 1, hd,
+                                           H * hd, hd, H * hd, 0, self.workers, mask_prefix, float(hd ** -0.5)), f"{name}.attention")
+        self._own(h)
+        _native.check(lib.configure_attention_fp4_output(h, a2.data.data_ptr(), a2.scales.data_ptr(), a2.data.stride(0),
+                                                         a2.k // 16, a2.global_scale), f"{name}.attention")
+        att_sources = [(s_qkv, ALL)] + ([(prefix_cache_stage, ALL)] if prefix_cache_stage is not None else [])
+        if splits > 1:
+            _native.check(lib.configure_attention_splits(h, splits), f"{name}.attention")
+            s_part = self.add(1, h, f"{name}.attention", att_sources)
+            mh = C.c_void_p()
+            _native.check(lib.attention_merge_handle(h, C.byref(mh)), f"{name}.merge")
+            s_att = self.add(4, mh, f"{name}.merge", [(s_part, ALL)])
+        else:
+            s_att = self.add(1, h, f"{name}.attention", att_sources)
+        wo = self.cached(p + "o", lambda: self.weight(sd[p + "self_attn.o_proj.weight"]))
+        s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=block_n)
+        g2 = self.cached(p + "g2", lambda: (1.0 + sd[p + "post_attention_layernorm.weight"].float()).contiguous())
+        s_n2 = self.norm(f"{name}.norm2", x_mid, a3, rows=rows, sources=[(s_o, SAME)], kind="rms", gamma=g2, eps=c.rms_eps)
+        def make_gate_up():
+            gate, up = sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]
+            return self.weight(torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], gate.shape[1]))
+
+        wgu = self.cached(p + "gate_up", make_gate_up)
+        s_gu = self.gemm(f"{name}.gate_up", a3, wgu, rows=rows, sources=[(s_n2, SAME)], fp4_out=a4, activation=2, block_n=block_n)
+        wd = self.cached(p + "down", lambda: self.weight(sd[p + "mlp.down_proj.weight"]))
+        s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=block_n)
+        return s_dn, s_qkv
+
+    def _build(self):
+        c, sd, lib = self.config, self.sd, self.lib
+        V = self.num_views
+        P = V * 256 + self.prompt_len
+        P_pad = padded(P, 128)
+        S = self.chunk_size + 1
+        S_pad = 128
+        H, hd = c.heads, c.head_dim
+        # ---------------- vision tower + projector -> prefix rows [0, V*256)
+        s_pl, a_post = self._vision()
+        x_a, x_b = self.tensor((P_pad, c.width)), self.tensor((P_pad, c.width))
+        wproj = self.weight(sd[PROJECTOR + "weight"])
+        bproj = sd[PROJECTOR + "bias"].to(torch.bfloat16).contiguous()
+        self.buffers.append(bproj)
+        s_x = self.gemm("vision.projector", a_post, wproj, rows=V * 256, sources=[(s_pl, SAME)], out=x_a, bias=bproj)
+        self.mark("image_tokens", x_a)
+        vision_end = len(self.stages)
+        # ---------------- Gemma-2B prefix: builds the KV cache
+        extra = []
+        if self.prompt_len:
+            table = sd[LANGUAGE + "embed_tokens.weight"]
+            if table.dtype != torch.bfloat16:
+                table = table.to(torch.bfloat16)
+            table = table.contiguous()
+            self.buffers.append(table)
+            h = C.c_void_p()
+            _native.check(lib.create_token_embed(C.byref(h), None, table.data_ptr(), x_a.data_ptr(), self.prompt_len, c.width,
+                                                 V * 256, table.shape[0], float(math.sqrt(c.width)), self.workers), "token embedding")
+            self._own(h)
+            extra = [(self.add(3, h, "prefix.embed"), ALL)]
+        cos_p, sin_p = self.rope(P, 0)
+        self.caches = [(self.tensor((P + S_pad, hd)), self.tensor((P + S_pad, hd))) for _ in range(c.prefix_layers)]
+        bufs = (self.fp4(P_pad, c.width), self.fp4(P_pad, H * hd), self.fp4(P_pad, c.width), self.fp4(P_pad, c.mlp),
+                self.tensor((P_pad, H * hd)), self.tensor((P_pad, H * hd)))
+        cache_stage = []
+        for i in range(c.prefix_layers):
+            s_x, s_kv = self._gemma_layer(f"prefix.{i}", LANGUAGE, i, x_a, x_b, bufs, rows=P, s_x=s_x, extra_sources=extra if i == 0 else [],
+                                          cos=cos_p, sin=sin_p, cache=self.caches[i], cache_base=0, attention_rows=P, mask_prefix=-1,
+                                          splits=1, kv_only=(i == c.prefix_layers - 1), block_n=128)
+            cache_stage.append(s_kv)
+            if i == 0:
+                self.mark("prefix.0.q", bufs[4]), self.mark("prefix.0.attention", bufs[5])
+            self.mark(f"prefix.{i}", x_a)
+            if self.verbose and (i + 1) % 6 == 0:
+                print("NativePi0: prefix layers", i + 1, flush=True)
+        prefix_end = len(self.stages)
+        # ---------------- action expert, flow_steps Euler updates
+        W = c.expert_width
+        f32 = lambda t: t.float().contiguous()
+        w_state, b_state = f32(sd["state_proj.weight"]), f32(sd["state_proj.bias"])
+        w_in, b_in = f32(sd["action_in_proj.weight"]), f32(sd["action_in_proj.bias"])
+        w_t1, b_t1 = f32(sd["action_time_mlp_in.weight"]), f32(sd["action_time_mlp_in.bias"])
+        w_t2, b_t2 = f32(sd["action_time_mlp_out.weight"]), f32(sd["action_time_mlp_out.bias"])
+        # action half of the first time-MLP layer folded into the action projection:
+        # W_a (W_in x + b_in) = (W_a W_in) x + W_a b_in; the time half is a per-step bias.
+        w_fused = (w_t1[:, :W] @ w_in).contiguous()
+        b_fused = w_t1[:, :W] @ b_in
+        final_w = (f32(sd["action_out_proj.weight"]) * (1.0 + f32(sd[EXPERT + "norm.weight"]))[None, :]).contiguous()
+        final_b = f32(sd["action_out_proj.bias"])
+        self.buffers.extend((w_state, b_state, w_fused, w_t2, b_t2, final_w, final_b))
+        state_emb = self.tensor((1, W), torch.float32)
+        s_state = self.linear32("expert.state", None, w_state, b_state, state_emb, rows=1, sources=[], slot=2)
+        h1, h2 = self.tensor((self.chunk_size, W), torch.float32), self.tensor((self.chunk_size, W), torch.float32)
+        actions = self.tensor((self.chunk_size, c.action_dim), torch.float32)
+        xe_a, xe_b = self.tensor((S_pad, W)), self.tensor((S_pad, W))
+        cos_s, sin_s = self.rope(S, P)
+        ebufs = (self.fp4(S_pad, W), self.fp4(S_pad, H * hd), self.fp4(S_pad, W), self.fp4(S_pad, c.expert_mlp),
+                 self.tensor((S_pad, H * hd)), self.tensor((S_pad, H * hd)))
+        time, dt = np.float32(1.0), np.float32(-1.0 / self.flow_steps)
+        s_prev = None
+        for step in range(self.flow_steps):
+            fraction = torch.linspace(0.0, 1.0, W // 2, device=self.device, dtype=torch.float64)
+            period = 0.004 * (4.0 / 0.004) ** fraction
+            angle = float(time) / period * (2.0 * math.pi)
+            t_emb = torch.cat((angle.sin(), angle.cos())).float()
+            step_bias = (b_fused + w_t1[:, W:] @ t_emb + b_t1).contiguous()
+            self.buffers.append(step_bias)
+            first = step == 0
+            s_t1 = self.linear32(f"expert.{step}.time_in", None if first else actions, w_fused, step_bias, h1, rows=self.chunk_size,
+                                 sources=[(s_prev, ALL)], slot=3 if first else 0, silu=True)
+            s_t2 = self.linear32(f"expert.{step}.time_out", h1, w_t2, b_t2, h2, rows=self.chunk_size, sources=[(s_t1, ALL)])
+            h = C.c_void_p()
+            _native.check(lib.create_suffix_assemble(C.byref(h), state_emb.data_ptr(), h2.data_ptr(), xe_a.data_ptr(), self.chunk_size,
+                                                     W, self.workers), "suffix assemble")
+            self._own(h)
+            s_x = self.add(3, h, f"expert.{step}.assemble", [(s_t2, ALL), (s_state, ALL)])
+            for i in range(c.expert_layers):
+                s_x, _ = self._expert_layer(step, i, xe_a, xe_b, ebufs, S, P, s_x, cos_s, sin_s, cache_stage[i])
+            s_prev = self.linear32(f"expert.{step}.euler", xe_a, final_w, final_b, actions, rows=self.chunk_size, sources=[(s_x, ALL)],
+                                   ldx=W, x_bf16=True, rms=True, euler=True, prev=None if first else actions,
+                                   prev_slot=3 if first else 0, x_row_offset=1, dt=float(dt), eps=c.rms_eps)
+            self.mark(f"actions.{step}", actions)
+            time = np.float32(time + dt)
+            if self.verbose:
+                print("NativePi0: expert denoising step", step + 1, "wired", flush=True)
+        self.output = actions.view(1, self.chunk_size, c.action_dim)
+        self.component_ranges = {"vision": (0, vision_end), "prefix": (vision_end, prefix_end), "expert": (prefix_end, len(self.stages))}
+        # ---------------- static instruction streams + program
+        self.code = linear_streams([LinearWork(t, k) for t, k in zip(self.stage_tiles, self.stage_cost)], self.workers)
+        validate_streams(self.code, self.stage_tiles)
+        self.plan = program_summary(self.code)
+        self.plan["stages"] = len(self.stages)
+        specs = (NativeSpec * len(self.stages))(*self.stages)
+        _native.check(lib.create_native_model(C.byref(self.handle), len(specs), C.cast(specs, C.c_void_p), self.code.ctypes.data,
+                                              self.workers, self.code.shape[1]), "Native pi0 setup")
+        if self.verbose:
+            print("NativePi0 static program:", self.plan, flush=True)
+
+    def _expert_layer(self, step, i, x_in, x_mid, bufs, S, P, s_x, cos, sin, prefix_cache_stage):
+        """Every Euler step wires its own stages; the NVFP4 weights are shared through the keyed weight cache."""
+        return self._gemma_layer(f"expert.{step}.{i}", EXPERT, i, x_in, x_mid, bufs, rows=S, s_x=s_x, extra_sources=[], cos=cos, sin=sin,
+                                 cache=self.caches[i], cache_base=P, attention_rows=P + S, mask_prefix=P, splits=self.expert_splits,
+                                 kv_only=False, block_n=self.expert_block_n, prefix_cache_stage=prefix_cache_stage)
+
+    # ------------------------------------------------------------------------------------------ running
+    def _check_inputs(self, images, state, noise, tokens):
+        if not self.handle.value:
+            raise RuntimeError("Native pi0 engine is closed")
+        wanted = ((images, (self.num_views, 224, 224, 3), torch.float32), (state, (1, self.config.action_dim), torch.float32),
+                  (noise, (1, self.chunk_size, self.config.action_dim), torch.float32), (tokens, (1, self.prompt_len), torch.int64))
+        for t, shape, dtype in wanted:
+            if t.device != self.device or t.dtype != dtype or tuple(t.shape) != shape or not t.is_contiguous():
+                raise ValueError(("Resident pi0 input layout", shape, dtype))
+
+    def forward(self, images, state, noise, tokens):
+        """One action chunk.  Inputs are CUDA-resident and contiguous; the returned tensor is reused by the next call."""
+        self._check_inputs(images, state, noise, tokens)
+        if self.partitioned:
+            for n, name in enumerate(("vision", "prefix", "expert")):
+                self.launch_component(name, images, state, noise, tokens, new_epoch=(n == 0))
+        else:
+            self.launch_component(None, images, state, noise, tokens)
+        self.epoch += 1
+        return self.output
+
+    def sample_actions(self, images, state, noise, tokens=None):
+        """Host-facing call: inputs are CPU tensors (pinned memory avoids a staging copy); they are copied to
+        resident device buffers, one forward pass runs, and the action chunk comes back as a CPU FP32 tensor
+        ``[1, chunk, action_dim]``.  Equivalent of OpenPI's ``sample_actions`` with caller-supplied noise."""
+        if tokens is None:
+            tokens = torch.zeros((1, self.prompt_len), dtype=torch.int64)
+        if not hasattr(self, "_resident_inputs"):
+            with torch.cuda.device(self.device):
+                self._resident_inputs = (
+                    torch.zeros((self.num_views, 224, 224, 3), dtype=torch.float32, device=self.device),
+                    torch.zeros((1, self.config.action_dim), dtype=torch.float32, device=self.device),
+                    torch.zeros((1, self.chunk_size, self.config.action_dim), dtype=torch.float32, device=self.device),
+                    torch.zeros((1, self.prompt_len), dtype=torch.int64, device=self.device))
+                self._host_output = torch.zeros((1, self.chunk_size, self.config.action_dim), dtype=torch.float32).pin_memory()
+        for dst, src in zip(self._resident_inputs, (images, state, noise, tokens)):
+            if tuple(src.shape) != tuple(dst.shape) or src.dtype != dst.dtype:
+                raise ValueError(("pi0 input layout", tuple(dst.shape), dst.dtype))
+            dst.copy_(src, non_blocking=True)
+        out = self.forward(*self._resident_inputs)
+        self._host_output.copy_(out, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        return self._host_output
+
+    def launch_component(self, name, images, state, noise, tokens, new_epoch=True):
+        begin, end = (0, len(self.stages)) if name is None else self.component_ranges[name]
+        self.launch_range(begin, end, images, state, noise, tokens, new_epoch)
+
+    def launch_range(self, begin, end, images, state, noise, tokens, new_epoch):
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            code = self.lib.launch_native_model_range(self.handle, stream, images.data_ptr(), state.data_ptr(), noise.data_ptr(),
+                                                      tokens.data_ptr(), begin, end, int(new_epoch))
+        if code:
+            raise RuntimeError(f"Native pi0 launch error {code}")
+
+    def status(self):
+        with torch.cuda.device(self.device):
+            return _native.status(self.lib, self.handle)
+
+    def enable_timings(self, enable=True):
+        _native.check(self.lib.enable_native_model_timings(self.handle, int(enable)), "timing setup")
+
+    def read_timings(self, name=None):
+        """Global-timer stamps (ns) int64 [workers, stream_length, 4] = (start, producers ready, end, GEMM copies
+        issued) of the last launch with timings enabled."""
+        out = np.zeros((self.workers, self.code.shape[1], 4), dtype=np.int64)
+        with torch.cuda.device(self.device):
+            _native.check(self.lib.read_native_model_timings(self.handle, out.ctypes.data, out.size), "timing read")
+        return out
+
+    def stage_profile(self):
+        """Per-stage wall span of the last timed launch: list of (name, ready_ns, end_ns, instructions) where
+        ready is the earliest moment a worker had the stage's producers complete and end the last worker's finish,
+        relative to the earliest stamp (device global timer).  Call ``enable_timings()`` before the launch."""
+        stamps = self.read_timings()
+        live = self.code[:, :, 0] != 0
+        stage_of = self.code[:, :, 1]
+        start, end = stamps[:, :, 1], stamps[:, :, 2]
+        valid = live & (start > 0) & (end > 0)
+        if not valid.any():
+            return []
+        origin = start[valid].min()
+        first = np.full(len(self.stages), np.iinfo(np.int64).max, dtype=np.int64)
+        last = np.zeros(len(self.stages), dtype=np.int64)
+        count = np.zeros(len(self.stages), dtype=np.int64)
+        np.minimum.at(first, stage_of[valid], start[valid] - origin)
+        np.maximum.at(last, stage_of[valid], end[valid] - origin)
+        np.add.at(count, stage_of[valid], 1)
+        return [(self.stage_names[i], int(first[i]), int(last[i]), int(count[i])) for i in range(len(self.stages)) if count[i]]
+
+    def close(self):
+        if getattr(self, "handle", None) is not None and self.handle.value:
+            with torch.cuda.device(self.device):
+                _native.check(self.lib.destroy_native_model(self.handle), "Native pi0 teardown")
+            self.handle = C.c_void_p()
+        for h in getattr(self, "handles", []):
+            if h.value:
+                with torch.cuda.device(self.device):
+                    self.lib.destroy_op(h)
+                h.value = None
+        self.handles = []
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_):
+        self.close()

@@ -19,7 +19,7 @@ class ResidentNVFP4:
     def __init__(self, library, activation, weight, *, workers=16, device="cuda",
                  output_dtype=torch.float32, bias=None, residual=None,
                  output_global_scale=1.0, output_gelu=False, output_geglu=False, output_relu2=False,
-                 block_n=128, rows=None):
+                 block_n=128, rows=None, activation_buffers=None):
         self._handle = ctypes.c_void_p()
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -60,6 +60,12 @@ class ResidentNVFP4:
                               for x in (activation.data, weight.data)]
             self.sa, self.sb = [torch.from_numpy(swizzle_scales(x)).to(self.device)
                                 for x in (activation.scales, weight.scales)]
+            if activation_buffers is not None:
+                # A operand produced on the device by an earlier stage (packed codes + swizzled scales)
+                data, scales = activation_buffers
+                if tuple(data.shape) != tuple(self.a.shape) or data.dtype != torch.uint8 or scales.numel() != self.sa.numel():
+                    raise ValueError("Bound activation buffers must match the packed activation layout")
+                self.a, self.sa = data, scales
             self.bias = None if bias is None else torch.as_tensor(bias, dtype=torch.bfloat16, device=self.device).contiguous()
             self.residual = None if residual is None else torch.as_tensor(residual, dtype=torch.bfloat16, device=self.device).contiguous()
             if self.bias is not None and tuple(self.bias.shape) != (n,):

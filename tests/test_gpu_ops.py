@@ -1,0 +1,374 @@
+"""GPU parity of every operator against the CPU oracles, through the C ABI (ctypes).
+
+Tolerances: NVFP4 packing and scales bit-exact; GEMM / attention outputs <= 1e-2 relative RMS against the
+dequantised-NVFP4 / FP32 oracle (BF16 outputs add one BF16 rounding).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from native_pi0 import _native
+from native_pi0.attention import ResidentAttention
+from native_pi0.normalization import ResidentNorm
+from native_pi0.primitives import ResidentNVFP4
+from native_pi0.quantization import PackedNVFP4, interleave_gate_up, pack_nvfp4, swizzle_scales, unswizzle_scales
+from oracle import nvfp4 as oracle
+from oracle import ops as oracle_ops
+
+
+def bf16(x):
+    return torch.from_numpy(np.asarray(x, dtype=np.float32)).bfloat16()
+
+
+def relrms(a, b):
+    a, b = np.asarray(a, dtype=np.float64), np.asarray(b, dtype=np.float64)
+    return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def config1_inputs(n=4096):
+    rng = np.random.default_rng(0)
+    x = rng.normal(size=(51, 1024)).astype(np.float32)
+    x[rng.random(x.shape) < 0.001] *= 20
+    w = rng.normal(scale=0.02, size=(n, 1024)).astype(np.float32)
+    return bf16(x).float().numpy(), bf16(w).float().numpy()
+
+
+def device_quantize(x, policy, global_scale=1.0, row_alignment=128):
+    lib = _native.load()
+    xt = bf16(x).cuda()
+    rows, width = xt.shape
+    rp = (rows + row_alignment - 1) // row_alignment * row_alignment
+    out = torch.zeros(rp, width // 2, dtype=torch.uint8, device="cuda")
+    sc = torch.zeros(((rp + 127) // 128) * ((width // 16 + 3) // 4) * 512, dtype=torch.uint8, device="cuda")
+    _native.check(lib.quantize_nvfp4(xt.data_ptr(), out.data_ptr(), sc.data_ptr(), rows, width, width, width // 16,
+                                     float(global_scale), int(policy == "ceil"), None), "quantize")
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), unswizzle_scales(sc.cpu().numpy(), rp, width // 16)
+
+
+def test_quantizer_bit_exact_config1_and_golden(golden_dir):
+    x, w = config1_inputs(512)
+    for arr, policy, gs in ((x, "nearest", 1.0), (w, "ceil", 1.0), (w, "ceil", float(np.abs(w).max() / (6 * 448)))):
+        data, scales = device_quantize(arr, policy, gs)
+        ref = pack_nvfp4(arr, scale_policy=policy, global_scale=gs, row_alignment=128)
+        np.testing.assert_array_equal(data, ref.data)
+        np.testing.assert_array_equal(scales, ref.scales)
+        od, osc = oracle.pack(arr[:8], gs, policy)
+        np.testing.assert_array_equal(data[:8], od)
+        np.testing.assert_array_equal(scales[:8], osc)
+    gold = np.load(golden_dir / "nvfp4_pack.npz")          # vectors produced by the reference packer itself
+    for name, policy in (("cfg1_x", "nearest"), ("cfg1_w", "ceil"), ("ties", "nearest"), ("ties_ceil", "ceil"),
+                         ("wide_range", "nearest"), ("wide_range_ceil", "ceil")):
+        arr = gold[name + "_in"]
+        if not np.array_equal(bf16(arr).float().numpy(), arr):
+            continue                                        # the device quantiser consumes BF16 inputs
+        data, scales = device_quantize(arr, policy)
+        rows = arr.shape[0]
+        np.testing.assert_array_equal(data[:rows], gold[name + "_data"][:rows], err_msg=name)
+        np.testing.assert_array_equal(scales[:rows], gold[name + "_scales"][:rows], err_msg=name)
+
+
+def test_quantizer_edge_cases():
+    # zeros, tiny blocks (zero scale -> zero codes), saturation, exact midpoints
+    x = np.zeros((3, 64), np.float32)
+    x[1, :16] = 1e-12
+    x[1, 16:32] = [0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0, -0.25, -0.75, -1.25, -1.75, -2.5, -3.5, -5.0, -6.0]
+    x[2, :] = 3000.0
+    for policy in ("nearest", "ceil"):
+        data, scales = device_quantize(x, policy)
+        ref = pack_nvfp4(bf16(x).float().numpy(), scale_policy=policy, row_alignment=128)
+        np.testing.assert_array_equal(data, ref.data)
+        np.testing.assert_array_equal(scales, ref.scales)
+    assert not data[3:].any() and not scales[3:].any()
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (128, 256, 1152), (256, 384, 4352), (768, 2560, 2048), (128, 1024, 4096)])
+def test_gemm_fp32_matches_dequantised_oracle(m, n, k):
+    rng = np.random.default_rng(23 + m + n + k)
+    a = rng.normal(size=(m, k)).astype(np.float32)
+    b = rng.normal(scale=0.02, size=(n, k)).astype(np.float32)
+    pa, pb = pack_nvfp4(a, global_scale=0.5), pack_nvfp4(b, scale_policy="ceil", global_scale=0.001)
+    ref = oracle.gemm(pa.data, pa.scales, 0.5, pb.data, pb.scales, 0.001, m, n, k)
+    with ResidentNVFP4(None, pa, pb, workers=min(148, (m // 128) * (n // 128))) as op:
+        got = op.forward().cpu().numpy()
+        assert op.status()["code"] == 0
+        again = op.forward().cpu().numpy()
+    np.testing.assert_allclose(got, ref, rtol=3e-5, atol=1e-5 * max(1.0, np.abs(ref).max()))
+    np.testing.assert_array_equal(got, again)               # replay is bit-exact
+
+
+def test_gemm_config1_bf16_output():
+    x, w = config1_inputs()
+    pa, pb = pack_nvfp4(x, row_alignment=128), pack_nvfp4(w, scale_policy="ceil")
+    ref = oracle.gemm(pa.data, pa.scales, 1.0, pb.data, pb.scales, 1.0, 128, 4096, 1024)
+    with ResidentNVFP4(None, pa, pb, workers=32, output_dtype=torch.bfloat16, rows=51) as op:
+        y = op.forward().float().cpu().numpy()
+    assert relrms(y[:51], ref[:51]) <= 1e-2                 # stated tolerance; one BF16 rounding gives ~2e-3
+    assert relrms(y[:51], ref[:51]) <= 3e-3
+    assert not y[51:].any()                                 # rows beyond the logical count are never stored
+    assert relrms(ref[:51], x @ w.T) < 0.2                  # sanity: NVFP4 itself is ~14 % from the BF16 product
+
+
+def test_gemm_bias_residual_and_tiles():
+    rng = np.random.default_rng(47)
+    m, n, k = 256, 512, 1024
+    a, b = rng.normal(size=(m, k)).astype(np.float32), rng.normal(scale=0.05, size=(n, k)).astype(np.float32)
+    bias, res = bf16(rng.normal(size=n)), bf16(rng.normal(size=(m, n)))
+    pa, pb = pack_nvfp4(a), pack_nvfp4(b, scale_policy="ceil")
+    ref = oracle.gemm(pa.data, pa.scales, 1.0, pb.data, pb.scales, 1.0, m, n, k) + bias.float().numpy()[None] + res.float().numpy()
+    expect = bf16(ref).float().numpy()
+    for block_n in (128,):
+        with ResidentNVFP4(None, pa, pb, workers=7, output_dtype=torch.bfloat16, bias=bias, residual=res, block_n=block_n) as op:
+            y = op.forward().float().cpu().numpy()
+        mism = float((y != expect).mean())
+        assert mism < 1e-3, (block_n, mism)                 # BF16 result equal except FP32 summation-order ties
+        assert relrms(y, expect) < 1e-3
+
+
+def _decode(op, rows, width):
+    data = op.output.cpu().numpy()
+    scales = unswizzle_scales(op.output_scales.cpu().numpy(), data.shape[0], width // 16)
+    return PackedNVFP4(data, scales, np.float32(op.output_global_scale), (rows, width))
+
+
+def test_gemm_fp4_epilogues():
+    rng = np.random.default_rng(61)
+    m, n, k = 256, 512, 1152
+    a, b = rng.normal(size=(m, k)).astype(np.float32), rng.normal(scale=0.03, size=(n, k)).astype(np.float32)
+    bias = bf16(rng.normal(scale=0.5, size=n))
+    pa, pb = pack_nvfp4(a), pack_nvfp4(b, scale_policy="ceil")
+    acc = oracle.gemm(pa.data, pa.scales, 1.0, pb.data, pb.scales, 1.0, m, n, k)
+    # GELU(acc + bias) -> NVFP4
+    want = oracle_ops.gelu_tanh(torch.from_numpy(acc + bias.float().numpy()[None])).numpy()
+    ref = pack_nvfp4(want, global_scale=0.5)
+    with ResidentNVFP4(None, pa, pb, workers=8, output_dtype=torch.uint8, bias=bias, output_gelu=True, output_global_scale=0.5) as op:
+        op.forward()
+        got = _decode(op, m, n)
+    assert float((got.scales != ref.scales).mean()) < 2e-3
+    assert float((got.data != ref.data).mean()) < 5e-3      # differences only where FP32 rounding moves a tie
+    assert relrms(got.dequantize(), ref.dequantize()) < 1e-2
+    # compact GeGLU over interleaved gate/up columns -> NVFP4 of width n/2
+    gate, up = b[: n // 2], b[n // 2:]
+    pgu = pack_nvfp4(interleave_gate_up(gate, up), scale_policy="ceil")
+    acc = oracle.gemm(pa.data, pa.scales, 1.0, pgu.data, pgu.scales, 1.0, m, n, k)
+    want = oracle_ops.gelu_tanh(torch.from_numpy(acc[:, 0::2])).numpy() * acc[:, 1::2]
+    ref = pack_nvfp4(want)
+    with ResidentNVFP4(None, pa, pgu, workers=8, output_dtype=torch.uint8, output_geglu=True) as op:
+        op.forward()
+        got = _decode(op, m, n // 2)
+    assert float((got.scales != ref.scales).mean()) < 2e-3
+    assert float((got.data != ref.data).mean()) < 5e-3
+    assert relrms(got.dequantize(), ref.dequantize()) < 1e-2
+    with pytest.raises(ValueError):
+        ResidentNVFP4(None, pa, pgu, output_dtype=torch.uint8, output_geglu=True, bias=bias)
+
+
+def test_gemm_qkv_rope_epilogue():
+    lib = _native.load()
+    rng = np.random.default_rng(71)
+    rows, k, heads, hd = 200, 1024, 2, 256
+    n = (heads + 2) * hd
+    a, w = rng.normal(size=(256, k)).astype(np.float32), rng.normal(scale=0.03, size=(n, k)).astype(np.float32)
+    half = hd // 2
+    idx = np.stack((np.arange(half), np.arange(half) + half), 1).reshape(-1)
+    wperm = w.copy()
+    for h in range(heads + 1):                              # Q heads and the K head are stored pair-interleaved
+        wperm[h * hd:(h + 1) * hd] = w[h * hd:(h + 1) * hd][idx]
+    pa, pb = pack_nvfp4(a), pack_nvfp4(wperm, scale_policy="ceil")
+    acc = oracle.gemm(pa.data, pa.scales, 1.0, pack_nvfp4(w, scale_policy="ceil").data, pack_nvfp4(w, scale_policy="ceil").scales, 1.0, 256, n, k)
+    pos = torch.arange(37, 37 + rows).float()
+    inv = 1.0 / (10000 ** (torch.arange(0, hd, 2).float() / hd))
+    emb = torch.cat((pos[:, None] * inv[None], pos[:, None] * inv[None]), -1)
+    cos, sin = emb.cos().bfloat16(), emb.sin().bfloat16()
+    cosd, sind = torch.zeros(256, hd, dtype=torch.bfloat16), torch.zeros(256, hd, dtype=torch.bfloat16)
+    cosd[:rows], sind[:rows] = cos, sin
+    cosd, sind = cosd.cuda(), sind.cuda()
+    qout = torch.zeros(256, heads * hd, dtype=torch.bfloat16, device="cuda")
+    ck = torch.full((300, hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    cv = torch.full((300, hd), 7.0, dtype=torch.bfloat16, device="cuda")
+    with ResidentNVFP4(None, pa, pb, workers=10, output_dtype=torch.bfloat16, rows=rows) as op:
+        _native.check(lib.configure_resident_fp4_qkv_rope(op.handle, qout.data_ptr(), heads * hd, cosd.data_ptr(), sind.data_ptr(),
+                                                          ck.data_ptr(), cv.data_ptr(), heads * hd, hd, 50), "rope")
+        op.forward()
+        torch.cuda.synchronize()
+        assert op.status()["code"] == 0
+    y = torch.from_numpy(acc[:rows]).bfloat16()
+    for h in range(heads):
+        want = oracle_ops.rope_interleaved(y[:, h * hd:(h + 1) * hd], cos, sin).float().numpy()
+        got = qout[:rows, h * hd:(h + 1) * hd].float().cpu().numpy()
+        assert relrms(got, want) < 4e-3 and float((got != want).mean()) < 0.02
+    want_k = oracle_ops.rope_interleaved(y[:, heads * hd:(heads + 1) * hd], cos, sin).float().numpy()
+    got_k = ck[50:50 + rows].float().cpu().numpy()
+    assert relrms(got_k, want_k) < 4e-3
+    got_v = cv[50:50 + rows].float().cpu().numpy()
+    assert relrms(got_v, y[:, (heads + 1) * hd:].float().numpy()) < 4e-3
+    assert (ck[:50] == 7).all() and (ck[50 + rows:] == 7).all() and not qout[rows:].any()
+
+
+@pytest.mark.parametrize("rows,width,kind", [(51, 1024, "rms"), (768, 2048, "rms"), (256, 1152, "layer"), (7, 64, "layer")])
+def test_norm_to_nvfp4(rows, width, kind):
+    torch.manual_seed(83)
+    x = torch.randn(rows, width).bfloat16()
+    gamma = 1 + torch.randn(width) * 0.05
+    beta = torch.randn(width) * 0.05 if kind == "layer" else None
+    with ResidentNorm(None, x, kind=kind, gamma=gamma, beta=beta, workers=24, global_scale=0.5, row_alignment=128, keep_bf16=True) as op:
+        op.forward()
+        torch.cuda.synchronize()
+        assert op.status()["code"] == 0
+        normalized = op.normalized[:rows].float().cpu()
+        data = op.output.cpu().numpy()
+        scales = unswizzle_scales(op.output_scales.cpu().numpy(), data.shape[0], width // 16)
+        first = data.copy()
+        op.forward()
+        np.testing.assert_array_equal(op.output.cpu().numpy(), first)
+    want = oracle_ops.norm(x, kind, gamma, beta)
+    assert relrms(normalized.numpy(), want.numpy()) < 5e-3
+    assert float((normalized != want).float().mean()) < 0.02        # BF16 values equal except rounding ties
+    ref = pack_nvfp4(normalized.numpy(), global_scale=0.5, row_alignment=128)   # CPU packer == device quantiser
+    np.testing.assert_array_equal(data, ref.data)
+    np.testing.assert_array_equal(scales, ref.scales)
+    assert not data[rows:].any() and not scales[rows:].any()
+
+
+def test_norm_argument_errors():
+    x = torch.randn(4, 64).bfloat16()
+    with pytest.raises(ValueError):
+        ResidentNorm(None, x.float())
+    with pytest.raises(ValueError):
+        ResidentNorm(None, x, kind="rms", beta=torch.zeros(64))
+    with pytest.raises(ValueError):
+        ResidentNorm(None, x, precision="fp8")
+    with pytest.raises(ValueError):
+        ResidentNorm(None, torch.randn(4, 40).bfloat16())
+
+
+ATTENTION_CASES = [
+    # batches, nq, nk, heads, kv_heads, hd, prefix, splits
+    (3, 256, 256, 16, 16, 72, None, 1),      # SigLIP
+    (1, 768, 768, 8, 1, 256, None, 1),       # Gemma prefix, MQA
+    (1, 200, 200, 4, 2, 256, None, 1),       # GQA, ragged rows
+    (1, 51, 819, 8, 1, 256, 768, 1),         # action suffix over the cached prefix, state-row mask
+    (1, 51, 819, 8, 1, 256, 768, 8),         # split-KV 8 + merge
+    (1, 64, 848, 8, 1, 256, 784, 4),
+    (1, 1, 5, 1, 1, 256, 2, 1),
+]
+
+
+@pytest.mark.parametrize("b,nq,nk,h,hk,hd,prefix,splits", ATTENTION_CASES)
+def test_attention(b, nq, nk, h, hk, hd, prefix, splits):
+    torch.manual_seed(419 + nq + nk)
+    q = torch.randn(b, nq, h, hd).bfloat16().cuda()
+    k = torch.randn(b, nk, hk, hd).bfloat16().cuda()
+    v = torch.randn(b, nk, hk, hd).bfloat16().cuda()
+    want = oracle_ops.attention(q, k, v, hd ** -0.5, prefix).numpy()
+    with ResidentAttention(None, q, k, v, workers=64, prefix=prefix, splits=splits) as op:
+        op.output.fill_(float("nan"))
+        got = op.forward().float().cpu().numpy()
+        assert op.status()["code"] == 0
+        again = op.forward().float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert relrms(got, want) <= 1e-2
+    np.testing.assert_array_equal(got, again)
+    if prefix is not None and nq > 1:
+        # the state query must not depend on keys beyond the prefix boundary
+        k2, v2 = k.clone(), v.clone()
+        k2[:, prefix + 1:] = 9.0
+        v2[:, prefix + 1:] = -9.0
+        with ResidentAttention(None, q, k2, v2, workers=64, prefix=prefix, splits=splits) as op:
+            other = op.forward().float().cpu().numpy()
+        np.testing.assert_array_equal(other[:, 0], got[:, 0])
+
+
+def test_attention_fused_fp4_output():
+    torch.manual_seed(5)
+    nq, nk, h, hd = 100, 300, 8, 256
+    q, k, v = [torch.randn(1, n, hh, hd).bfloat16().cuda() for n, hh in ((nq, h), (nk, 1), (nk, 1))]
+    data = torch.zeros(128, h * hd // 2, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros((h * hd // 64) * 512, dtype=torch.uint8, device="cuda")
+    for splits in (1, 3):
+        data.zero_(), scales.zero_()
+        with ResidentAttention(None, q, k, v, workers=32, fp4_output=(data, scales, 0.25), splits=splits) as op:
+            out = op.forward().float().cpu().numpy().reshape(nq, h * hd)
+            assert op.status()["code"] == 0
+        ref = pack_nvfp4(out, global_scale=0.25, row_alignment=128)
+        np.testing.assert_array_equal(data.cpu().numpy(), ref.data)         # quantiser consumed the BF16 rows it stored
+        np.testing.assert_array_equal(unswizzle_scales(scales.cpu().numpy(), 128, h * hd // 16), ref.scales)
+
+
+def test_small_operators():
+    lib = _native.load()
+    torch.manual_seed(11)
+    dev = "cuda"
+    # patch embedding vs conv2d
+    views, width = 2, 1152
+    images = (torch.rand(views, 224, 224, 3, device=dev) * 2 - 1).contiguous()
+    conv_w = torch.randn(width, 3, 14, 14, device=dev) * 0.02
+    conv_b, pos = torch.randn(width, device=dev) * 0.02, torch.randn(256, width, device=dev) * 0.02
+    w = conv_w.permute(2, 3, 1, 0).reshape(588, width).contiguous()
+    out = torch.zeros(views * 256, width, dtype=torch.bfloat16, device=dev)
+    h = C.c_void_p()
+    _native.check(lib.create_patch_embed(C.byref(h), images.data_ptr(), w.data_ptr(), conv_b.data_ptr(), pos.data_ptr(), out.data_ptr(), views, width, 100), "patch")
+    _native.check(lib.launch_op(h, None), "launch")
+    torch.cuda.synchronize()
+    want = torch.nn.functional.conv2d(images.permute(0, 3, 1, 2), conv_w, conv_b, stride=14).flatten(2).transpose(1, 2) + pos[None]
+    assert relrms(out.float().cpu().numpy(), want.reshape(-1, width).bfloat16().float().cpu().numpy()) < 2e-3
+    lib.destroy_op(h)
+    # FP32 linear: bias + SiLU
+    rows, n, k = 50, 1024, 32
+    x, wl, b = torch.randn(rows, k, device=dev), torch.randn(n, k, device=dev) * 0.1, torch.randn(n, device=dev)
+    o = torch.zeros(rows, n, device=dev)
+    h = C.c_void_p()
+    _native.check(lib.create_linear32(C.byref(h), x.data_ptr(), wl.data_ptr(), b.data_ptr(), None, o.data_ptr(), rows, n, k, k, n, 4, 0, 0, 0, 0.0, 1e-6, 64), "lin")
+    _native.check(lib.launch_op(h, None), "launch")
+    torch.cuda.synchronize()
+    torch.testing.assert_close(o, torch.nn.functional.silu(x @ wl.T + b), rtol=1e-5, atol=1e-5)
+    lib.destroy_op(h)
+    # BF16 input with row offset, RMS factor and Euler update
+    rows, n, k = 50, 32, 1024
+    xb = torch.randn(128, k, device=dev).bfloat16()
+    wl, b, prev = torch.randn(n, k, device=dev) * 0.05, torch.randn(n, device=dev), torch.randn(rows, n, device=dev)
+    o = prev.clone()
+    h = C.c_void_p()
+    _native.check(lib.create_linear32(C.byref(h), xb.data_ptr(), wl.data_ptr(), b.data_ptr(), o.data_ptr(), o.data_ptr(), rows, n, k, k, n,
+                                      1 | 8 | 16, 0, 0, 1, -0.1, 1e-6, 4), "lin")
+    _native.check(lib.launch_op(h, None), "launch")
+    torch.cuda.synchronize()
+    xf = xb[1:51].float()
+    val = (xf @ wl.T) * torch.rsqrt(xf.square().mean(-1, keepdim=True) + 1e-6) + b
+    torch.testing.assert_close(o, prev + (-0.1) * val, rtol=2e-5, atol=2e-5)
+    lib.destroy_op(h)
+    # suffix assembly and token embedding
+    state_emb, act = torch.randn(1, 1024, device=dev), torch.randn(50, 1024, device=dev)
+    xs = torch.zeros(128, 1024, dtype=torch.bfloat16, device=dev)
+    h = C.c_void_p()
+    _native.check(lib.create_suffix_assemble(C.byref(h), state_emb.data_ptr(), act.data_ptr(), xs.data_ptr(), 50, 1024, 8), "suffix")
+    _native.check(lib.launch_op(h, None), "launch")
+    torch.cuda.synchronize()
+    assert torch.equal(xs[:51], torch.cat((state_emb, act)).bfloat16()) and not xs[51:].any()
+    lib.destroy_op(h)
+    table = (torch.randn(1000, 2048, device=dev) * 0.02).bfloat16()
+    tokens = torch.randint(0, 1000, (1, 16), device=dev)
+    xt = torch.zeros(896, 2048, dtype=torch.bfloat16, device=dev)
+    h = C.c_void_p()
+    _native.check(lib.create_token_embed(C.byref(h), tokens.data_ptr(), table.data_ptr(), xt.data_ptr(), 16, 2048, 768, 1000, float(2048 ** 0.5), 8), "embed")
+    _native.check(lib.launch_op(h, None), "launch")
+    torch.cuda.synchronize()
+    assert torch.equal(xt[768:784], (table[tokens[0]].float() * torch.tensor(2048 ** 0.5).float()).bfloat16())
+    assert not xt[:768].any() and not xt[784:].any()
+    lib.destroy_op(h)
+
+
+def test_argument_errors_return_codes():
+    lib = _native.load()
+    h = C.c_void_p(123)
+    assert lib.create_resident_fp4(C.byref(h), None, None, None, None, None, 128, 128, 64, 1, 1.0) == 1
+    assert h.value is None
+    buf = torch.zeros(128 * 64, dtype=torch.uint8, device="cuda")
+    assert lib.create_resident_fp4(C.byref(h), buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), 100, 128, 64, 1, 1.0) == 1
+    assert lib.create_resident_fp4(C.byref(h), buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), buf.data_ptr(), 128, 128, 64, 100000, 1.0) == 9
+    assert lib.destroy_resident_fp4(None) == 0 and lib.destroy_native_model(None) == 0 and lib.destroy_norm(None) == 0
+    assert lib.launch_resident_fp4(None, None) == 1
