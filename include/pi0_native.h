@@ -47,7 +47,8 @@ int destroy_resident_fp4(void* handle);
  * Replaces the BF16 path's configure_dense_qkv_rope (native_pi0/dense.cu:231-253). */
 int configure_resident_fp4_qkv_rope(void* handle, void* out_q, int ldq, const void* cos, const void* sin, void* cache_k,
                                     void* cache_v, int q_cols, int head_dim, int cache_base);
-/* extension: logical row count (rows >= this are never stored) and output tile width (128, 64 or 32). */
+/* extension: logical row count (rows >= this are never stored; with at most 64 rows only 64 rows of A are
+ * copied per tile) and output tile width (128 or 64). */
 int configure_resident_fp4_rows(void* handle, int rows);
 int configure_resident_fp4_tile(void* handle, int block_n);
 

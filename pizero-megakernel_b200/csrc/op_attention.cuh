@@ -276,27 +276,36 @@ __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl
     }
 }
 
-// Split-KV merge: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s, one head per tile.
-__device__ __forceinline__ void merge_tile(const MergeParams& g, int head) {
+// Split-KV merge: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s.  A tile is 16 query rows of one head: one
+// (row, 16-column block) per thread, all partial loads of a thread independent of each other.
+constexpr int kMergeRows = 16;
+
+__device__ __forceinline__ void merge_tile(const MergeParams& g, int tile) {
     const int bpr = g.head_dim / 16;
-    for (int i = threadIdx.x; i < g.nq * bpr; i += kThreads) {
-        const int r = i / bpr, b = i - r * bpr;
+    const int chunks = (g.nq + kMergeRows - 1) / kMergeRows;
+    const int head = tile / chunks, r0 = (tile - head * chunks) * kMergeRows;
+    const int rows = min(kMergeRows, g.nq - r0);
+    for (int i = threadIdx.x; i < rows * bpr; i += kThreads) {
+        const int r = r0 + i / bpr, b = i % bpr;
+        const float* ml = g.partial_ml + (static_cast<size_t>(head) * g.splits * kAttnQRows + r) * 2;
+        const float* po = g.partial_o + (static_cast<size_t>(head) * g.splits * kAttnQRows + r) * g.head_dim + b * 16;
         float big = -INFINITY;
-        for (int s = 0; s < g.splits; s++) big = fmaxf(big, __ldcg(g.partial_ml + (static_cast<size_t>(head * g.splits + s) * kAttnQRows + r) * 2));
+#pragma unroll 8
+        for (int s = 0; s < g.splits; s++) big = fmaxf(big, __ldcg(ml + static_cast<size_t>(s) * kAttnQRows * 2));
+        const float ref = big == -INFINITY ? 0.f : big;
         float acc[16];
 #pragma unroll
         for (int e = 0; e < 16; e++) acc[e] = 0.f;
         float denom = 0.f;
+#pragma unroll 4
         for (int s = 0; s < g.splits; s++) {
-            const size_t t = static_cast<size_t>(head * g.splits + s);
-            const float m = __ldcg(g.partial_ml + (t * kAttnQRows + r) * 2), l = __ldcg(g.partial_ml + (t * kAttnQRows + r) * 2 + 1);
-            if (m == -INFINITY) continue;
-            const float w = exp2f(m - big);
-            denom += w * l;
-            const float4* src = reinterpret_cast<const float4*>(g.partial_o + (t * kAttnQRows + r) * g.head_dim + b * 16);
+            const float2 pair = __ldcg(reinterpret_cast<const float2*>(ml + static_cast<size_t>(s) * kAttnQRows * 2));
+            const float w = exp2f(pair.x - ref);                 // 0 for a split whose keys were all masked
+            denom += w * pair.y;
+            const float4* src = reinterpret_cast<const float4*>(po + static_cast<size_t>(s) * kAttnQRows * g.head_dim);
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                float4 x = __ldcg(src + q);
+                const float4 x = __ldcg(src + q);
                 acc[4 * q] += w * x.x; acc[4 * q + 1] += w * x.y; acc[4 * q + 2] += w * x.z; acc[4 * q + 3] += w * x.w;
             }
         }

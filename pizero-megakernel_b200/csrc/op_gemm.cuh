@@ -38,7 +38,9 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
                 if (!mbar_wait(prog, ctl, &ctl->empty[s], phase ^ 1u, stage_index)) { alive = 0; break; }
                 const int groups = min(4, g.k_groups - ks * 4);
                 uint8_t* slot = data + s * kStageBytes;
-                mbar_expect_tx(&ctl->full[s], kTileABytes + b_bytes + 2u * groups * 512u);
+                // a_box_rows < 128 (few logical rows): only the rows that exist are copied; the MMA still reads 128
+                // rows, whatever the remaining rows of the slot hold lands in accumulator rows that are never stored
+                mbar_expect_tx(&ctl->full[s], static_cast<uint32_t>(g.a_box_rows) * 128u + b_bytes + 2u * groups * 512u);
                 tma_load_2d(slot, g.tmap_a, &ctl->full[s], ks * 128, m_tile * 128);
                 tma_load_2d(slot + kTileABytes, g.tmap_b, &ctl->full[s], ks * 128, n_tile * g.block_n);
                 bulk_load(slot + 2 * kTileABytes, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4) * 512,
@@ -54,7 +56,7 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
 }
 
 __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem, const StageDesc& st,
-                                         int stage_index, int first, int count, PipeState& ps) {
+                                         int stage_index, int first, int count, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
     const int kstages = (g.k_groups + 3) >> 2;
     for (int t = first; t < first + count; ++t) {
@@ -69,6 +71,7 @@ __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_
             const uint32_t s = ps.mma_it % kStages, phase = (ps.mma_it / kStages) & 1u;
             if (!mbar_wait(prog, ctl, &ctl->full[s], phase, stage_index)) return;
             tc_fence_after();
+            if (stamp && t == first && ks == 0) stamp[4] = static_cast<long long>(global_ns());
             const int groups = min(4, g.k_groups - ks * 4);
             const uint32_t a_addr = smem_u32(data + s * kStageBytes);
             const uint32_t b_addr = a_addr + kTileABytes;
@@ -90,6 +93,7 @@ __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_
         tc_commit(&ctl->acc_full[buf]);    // accumulator complete
         ps.mma_tile++;
     }
+    if (stamp) stamp[5] = static_cast<long long>(global_ns());
 }
 
 // ---- epilogue helpers ---------------------------------------------------------------------------------------------
@@ -228,15 +232,16 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
 }
 
 __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, uint32_t tmem, const StageDesc& st,
-                                              int stage_index, int first, int count, PipeState& ps) {
+                                              int stage_index, int first, int count, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
     const int quarter = (threadIdx.x >> 5) & 3;          // TMEM lane quarter this warp may read
     const int lane = lane_id();
     for (int t = first; t < first + count; ++t) {
         const int m_tile = t / g.n_tiles, n_tile = t - m_tile * g.n_tiles;
         const uint32_t buf = ps.epi_tile & 1u, phase = (ps.epi_tile >> 1) & 1u;
-        if (!mbar_wait(prog, ctl, &ctl->acc_full[buf], phase, stage_index)) return;
+        if (!mbar_wait_warp(prog, ctl, &ctl->acc_full[buf], phase, stage_index)) return;
         tc_fence_after();
+        if (stamp && t == first && threadIdx.x == 128) stamp[6] = static_cast<long long>(global_ns());
         const int row = m_tile * 128 + quarter * 32 + lane;
         const bool row_ok = row < g.rows;
         const uint32_t taddr = tmem + buf * 128u + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -254,6 +259,7 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
             gemm_epilogue_chunk(g, raw, row, n_tile * g.block_n + c * 32, row_ok);
         }
         // each epilogue warp publishes its own 32 rows (a GEMM tile counts 4 units): no CTA barrier on this path
+        if (stamp && t == first + count - 1 && threadIdx.x == 128) stamp[7] = static_cast<long long>(global_ns());
         fence_proxy_async_global();
         __syncwarp();
         if (lane == 0) publish_tile(prog, st, t);
@@ -270,10 +276,10 @@ __device__ __forceinline__ void gemm_instruction(const VmProgram& prog, Ctl* ctl
         gemm_producer(prog, ctl, data, st, stage_index, first, count, ps, stamp);
         if (stamp && threadIdx.x == 0) stamp[3] = static_cast<long long>(global_ns());
     } else if (warp == 1) {
-        if (lane_id() == 0) gemm_mma(prog, ctl, data, tmem, st, stage_index, first, count, ps);
+        if (lane_id() == 0) gemm_mma(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
         __syncwarp();
     } else if (warp >= 4) {
-        gemm_epilogue(prog, ctl, tmem, st, stage_index, first, count, ps);
+        gemm_epilogue(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         if (stamp && threadIdx.x == 128) stamp[2] = static_cast<long long>(global_ns());
     }
 }

@@ -72,59 +72,83 @@ __device__ __forceinline__ void embed_instruction(const VmProgram& prog, Ctl* ct
     }
 }
 
-// out[r, n] = f(sum_k x[r, k] * W[n, k]); one output column per warp, eight columns per tile, rows in groups of 16.
-__device__ __forceinline__ void linear32_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st,
+// out[r, n] = f(sum_k x[r, k] * W[n, k]) in FP32.  A tile is 16 output columns for all rows: the CTA stages K-chunks
+// of x (up to 64 rows) and of the 16 weight rows in shared memory; thread (col = tid % 16, ty = tid / 16) owns rows
+// ty, ty+16, ty+32, ty+48 of its column, so every shared-memory read is a 16-byte broadcast or conflict-free access.
+constexpr int kLinCols = 16;
+constexpr int kLinRows = 64;
+constexpr int kLinChunk = 128;
+constexpr int kLinLd = kLinChunk + 4;
+
+__device__ __forceinline__ void linear32_tile(const Linear32Params& p, const void* xbase, const float* prev, int tile,
+                                              uint8_t* data) {
+    float4* xs = reinterpret_cast<float4*>(data);                                   // [64][kLinLd] floats
+    float4* ws = xs + kLinRows * kLinLd / 4;                                        // [16][kLinLd] floats
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int n = tile * kLinCols + tx;
+    for (int r0 = 0; r0 < p.rows; r0 += kLinRows) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f}, ss[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int kc = 0; kc < p.k; kc += kLinChunk) {
+            const int kw4 = min(kLinChunk, p.k - kc) >> 2;
+            __syncthreads();
+            for (int i = threadIdx.x; i < kLinRows * kw4; i += kThreads) {
+                const int r = i / kw4, c = i - r * kw4;
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r0 + r < p.rows) {
+                    const size_t off = static_cast<size_t>(r0 + r + p.x_row_offset) * p.ldx + kc + c * 4;
+                    if (p.x_bf16) {
+                        uint2 u = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(xbase) + off));
+                        float2 lo = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.x));
+                        float2 hi = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.y));
+                        v = make_float4(lo.x, lo.y, hi.x, hi.y);
+                    } else {
+                        v = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(xbase) + off));
+                    }
+                }
+                xs[r * (kLinLd / 4) + c] = v;
+            }
+            for (int i = threadIdx.x; i < kLinCols * kw4; i += kThreads) {
+                const int r = i / kw4, c = i - r * kw4;
+                const int col = tile * kLinCols + r;
+                ws[r * (kLinLd / 4) + c] = col < p.n ? __ldg(reinterpret_cast<const float4*>(p.w + static_cast<size_t>(col) * p.k + kc) + c)
+                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            __syncthreads();
+            for (int c = 0; c < kw4; c++) {
+                const float4 w4 = ws[tx * (kLinLd / 4) + c];
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float4 x4 = xs[(ty + 16 * i) * (kLinLd / 4) + c];
+                    acc[i] = fmaf(x4.x, w4.x, fmaf(x4.y, w4.y, fmaf(x4.z, w4.z, fmaf(x4.w, w4.w, acc[i]))));
+                    ss[i] = fmaf(x4.x, x4.x, fmaf(x4.y, x4.y, fmaf(x4.z, x4.z, fmaf(x4.w, x4.w, ss[i]))));
+                }
+            }
+        }
+        if (n < p.n) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int r = r0 + ty + 16 * i;
+                if (r >= p.rows) continue;
+                float v = acc[i];
+                if (p.rms) v *= rsqrtf(ss[i] / static_cast<float>(p.k) + p.eps);
+                if (p.bias) v += p.bias[n];
+                if (p.silu) v = v / (1.f + expf(-v));
+                if (p.euler) v = __fadd_rn(__ldcg(prev + static_cast<size_t>(r) * p.n + n), __fmul_rn(p.dt, v));
+                if (p.out_bf16) static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = __float2bfloat16_rn(v);
+                else static_cast<float*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = v;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void linear32_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
                                                      int stage_index, int first, int count) {
     const Linear32Params& p = st.p.lin;
     const void* xbase = p.slot == 2 ? static_cast<const void*>(prog.in.state)
                         : p.slot == 3 ? static_cast<const void*>(prog.in.noise) : p.x;
     const float* prev = p.prev_slot == 3 ? prog.in.noise : p.prev;
-    const int warp = threadIdx.x >> 5, lane = lane_id();
     for (int t = first; t < first + count; ++t) {
-        const int n = t * 8 + warp;
-        if (n < p.n) {
-            const float* wrow = p.w + static_cast<size_t>(n) * p.k;
-            for (int r0 = 0; r0 < p.rows; r0 += 16) {
-                float acc[16], ss[16];
-#pragma unroll
-                for (int i = 0; i < 16; i++) { acc[i] = 0.f; ss[i] = 0.f; }
-                for (int k0 = lane * 4; k0 < p.k; k0 += 128) {
-                    const float4 w4 = __ldg(reinterpret_cast<const float4*>(wrow + k0));
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const int r = r0 + i;
-                        if (r < p.rows) {
-                            float4 x4;
-                            const size_t off = static_cast<size_t>(r + p.x_row_offset) * p.ldx + k0;
-                            if (p.x_bf16) {
-                                uint2 u = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(xbase) + off));
-                                float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.x));
-                                float2 b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.y));
-                                x4 = make_float4(a.x, a.y, b.x, b.y);
-                            } else {
-                                x4 = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(xbase) + off));
-                            }
-                            acc[i] += x4.x * w4.x + x4.y * w4.y + x4.z * w4.z + x4.w * w4.w;
-                            if (p.rms) ss[i] += x4.x * x4.x + x4.y * x4.y + x4.z * x4.z + x4.w * x4.w;
-                        }
-                    }
-                }
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                    const int r = r0 + i;
-                    if (r >= p.rows) break;
-                    float v = warp_sum(acc[i]);
-                    if (p.rms) v *= rsqrtf(warp_sum(ss[i]) / static_cast<float>(p.k) + p.eps);
-                    if (lane == 0) {
-                        if (p.bias) v += p.bias[n];
-                        if (p.silu) v = v / (1.f + expf(-v));
-                        if (p.euler) v = __fadd_rn(__ldcg(prev + static_cast<size_t>(r) * p.n + n), __fmul_rn(p.dt, v));
-                        if (p.out_bf16) static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = __float2bfloat16_rn(v);
-                        else static_cast<float*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = v;
-                    }
-                }
-            }
-        }
+        linear32_tile(p, xbase, prev, t, data);
         cta_publish_tile(prog, st, t);
     }
 }

@@ -295,7 +295,7 @@ void free_op(Op* op) {
 int gemm_refresh(Op* op) {
     GemmParams& g = op->desc.p.gemm;
     CUtensorMap host[2];
-    int e = encode_operand(&host[0], op->a, op->m, op->k, 128);
+    int e = encode_operand(&host[0], op->a, op->m, op->k, g.a_box_rows);
     if (!e) e = encode_operand(&host[1], op->b, op->n, op->k, g.block_n);
     if (e) return e;
     if (!op->maps) {
@@ -394,6 +394,7 @@ extern "C" int create_resident_fp4(void** handle, const void* a, const void* b, 
     g.sfa = static_cast<const uint8_t*>(sfa);
     g.sfb = static_cast<const uint8_t*>(sfb);
     g.block_n = 128;
+    g.a_box_rows = 128;
     g.alpha = alpha;
     g.epilogue = EPI_F32;
     g.rows = m;
@@ -459,12 +460,12 @@ extern "C" int configure_resident_fp4_rows(void* handle, int rows) {
     Op* op = as_op(handle);
     if (!op || op->desc.kind != OP_GEMM || rows < 1 || rows > op->m) return cudaErrorInvalidValue;
     op->desc.p.gemm.rows = rows;
-    op->solo_dirty = true;
-    return cudaSuccess;
+    op->desc.p.gemm.a_box_rows = (rows <= 64 && op->m == 128) ? 64 : 128;
+    return gemm_refresh(op);
 }
 extern "C" int configure_resident_fp4_tile(void* handle, int block_n) {
     Op* op = as_op(handle);
-    if (!op || op->desc.kind != OP_GEMM || (block_n != 128 && block_n != 64 && block_n != 32)) return cudaErrorInvalidValue;
+    if (!op || op->desc.kind != OP_GEMM || (block_n != 128 && block_n != 64)) return cudaErrorInvalidValue;
     op->desc.p.gemm.block_n = block_n;
     return gemm_refresh(op);
 }
@@ -637,9 +638,9 @@ extern "C" int configure_attention_splits(void* handle, int splits) {
         mg->workers = op->workers;
         mg->desc.kind = OP_MERGE;
         finish_desc(mg->desc);
-        mg->desc.tiles = a.heads;
+        mg->desc.tiles = a.heads * ((a.nq + kMergeRows - 1) / kMergeRows);
         mg->desc.bands = 1;
-        mg->desc.band_div = a.heads;
+        mg->desc.band_div = mg->desc.tiles;
         MergeParams& g = mg->desc.p.merge;
         g.partial_o = op->partial_o; g.partial_ml = op->partial_ml;
         g.heads = a.heads; g.nq = a.nq; g.head_dim = a.head_dim; g.splits = splits;
@@ -733,7 +734,7 @@ extern "C" int create_linear32(void** handle, const void* x, const float* w, con
     StageDesc& d = op->desc;
     d.kind = OP_LINEAR32;
     finish_desc(d);
-    d.tiles = (n + 7) / 8;
+    d.tiles = (n + kLinCols - 1) / kLinCols;
     d.bands = 1;
     d.band_div = d.tiles;
     op->cost = std::max(64, (k * rows / 16 + 63) / 64 * 64);
@@ -829,7 +830,7 @@ extern "C" int enable_native_model_timings(void* handle, int enable) {
     Program* prog = as_program(handle);
     if (!prog) return cudaErrorInvalidValue;
     if (enable && !prog->d_timings) {
-        const size_t bytes = sizeof(long long) * 4 * prog->workers * prog->length;
+        const size_t bytes = sizeof(long long) * 8 * prog->workers * prog->length;
         cudaError_t e = cudaMalloc(&prog->d_timings, bytes);
         if (e == cudaSuccess) e = cudaMemset(prog->d_timings, 0, bytes);
         if (e != cudaSuccess) return e;
@@ -839,7 +840,7 @@ extern "C" int enable_native_model_timings(void* handle, int enable) {
 }
 extern "C" int read_native_model_timings(void* handle, long long* out, size_t count) {
     Program* prog = as_program(handle);
-    if (!prog || !out || !prog->d_timings || count != static_cast<size_t>(4) * prog->workers * prog->length) return cudaErrorInvalidValue;
+    if (!prog || !out || !prog->d_timings || count != static_cast<size_t>(8) * prog->workers * prog->length) return cudaErrorInvalidValue;
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) return e;
     return cudaMemcpy(out, prog->d_timings, count * sizeof(long long), cudaMemcpyDeviceToHost);

@@ -80,6 +80,20 @@ __device__ __forceinline__ bool mbar_wait(const VmProgram& prog, Ctl* ctl, uint6
     }
 }
 
+// The same wait for a whole warp (all 32 lanes call it). Only lane 0 runs the bounded wait and the outcome is
+// broadcast, so a time-out can never split the warp in front of a warp-collective instruction; on success every
+// lane then observes the completed phase itself (it cannot advance again before this warp has consumed it).
+__device__ __forceinline__ bool mbar_wait_warp(const VmProgram& prog, Ctl* ctl, uint64_t* bar, uint32_t parity, int stage) {
+    int ok = 1;
+    if (lane_id() == 0) ok = mbar_wait(prog, ctl, bar, parity, stage) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    if (ok) {
+        while (!mbar_try_wait(bar, parity)) {
+        }
+    }
+    return ok != 0;
+}
+
 __device__ __forceinline__ int tile_band(const StageDesc& st, int tile) { return min(tile / st.band_div, st.bands - 1); }
 
 // Warp-cooperative dependency wait (all 32 lanes of one warp call it): every counter this tile range reads

@@ -29,7 +29,7 @@ __device__ __forceinline__ int4 fetch_instruction(const VmProgram& prog, const i
 __device__ __forceinline__ bool prefetch_slot(const VmProgram& prog, Ctl* ctl, const int4* stream, uint32_t seq, int ip, int4 ins) {
     const int lane = lane_id();
     const uint32_t slot = seq % kRing, use = seq / kRing;
-    if (use > 0 && !mbar_wait(prog, ctl, &ctl->release[slot], (use - 1) & 1u, ins.y)) return false;
+    if (use > 0 && !mbar_wait_warp(prog, ctl, &ctl->release[slot], (use - 1) & 1u, ins.y)) return false;
     Slot* dst = &ctl->slot[slot];
     if (ins.x == 0) {
         if (lane == 0) dst->ins = ins;
@@ -99,13 +99,19 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         if (warp == kPrefetchWarp) {
             if (!prefetch_slot(prog, ctl, stream, seq + kAhead, ip0 + seq + kAhead, pending)) break;
             pending = fetch_instruction(prog, stream, ip0 + seq + kAhead + 1);      // consumed one iteration later
+            // warm the TMA descriptors of the next instruction if its slot has already landed
+            const uint32_t nslot = (seq + 1) % kRing;
+            if (lane_id() < 2 && mbar_try_wait(&ctl->ready[nslot], ((seq + 1) / kRing) & 1u)) {
+                const Slot& nx = ctl->slot[nslot];
+                if (nx.ins.x != 0 && nx.desc.kind == OP_GEMM) prefetch_tmap(lane_id() == 0 ? nx.desc.p.gemm.tmap_a : nx.desc.p.gemm.tmap_b);
+            }
         }
         const uint32_t slot = seq % kRing;
-        if (!mbar_wait(prog, ctl, &ctl->ready[slot], (seq / kRing) & 1u, -1)) break;
+        if (!mbar_wait_warp(prog, ctl, &ctl->ready[slot], (seq / kRing) & 1u, -1)) break;
         const int4 ins = ctl->slot[slot].ins;
         if (ins.x == 0) break;
         const StageDesc& st = ctl->slot[slot].desc;
-        long long* stamp = prog.timings ? prog.timings + (static_cast<size_t>(blockIdx.x) * prog.length + ip0 + seq) * 4 : nullptr;
+        long long* stamp = prog.timings ? prog.timings + (static_cast<size_t>(blockIdx.x) * prog.length + ip0 + seq) * 8 : nullptr;
         if (stamp && threadIdx.x == 0) stamp[0] = static_cast<long long>(global_ns());
         if (st.kind == OP_GEMM) {
             gemm_instruction(prog, ctl, data, tmem, st, ins.y, ins.z, ins.w, ps, stamp);
@@ -121,7 +127,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
                 case OP_MERGE: merge_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
                 case OP_PATCH: patch_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
                 case OP_EMBED: embed_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
-                case OP_LINEAR32: linear32_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
+                case OP_LINEAR32: linear32_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
                 case OP_SUFFIX: suffix_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
                 default:
                     if (threadIdx.x == 0) { report(prog, 3, ins.y, -1, st.kind, 0); ctl->abort = 1; }

@@ -46,6 +46,7 @@ struct GemmParams {
     int m_tiles, n_tiles;        // 128-row x block_n-column output tiles
     int k_groups;                // K / 64
     int block_n;                 // 128 (default), 64 or 32
+    int a_box_rows;              // rows of A copied per tile: 128, or 64 when the logical row count is <= 64
     float alpha;                 // global_scale(A) * global_scale(B)
     int epilogue;
     int act;                     // EPI_FP4: 0 none, 1 GELU(tanh), 3 ReLU^2
@@ -210,7 +211,8 @@ struct VmProgram {
     unsigned int* counters;
     const unsigned int* expected;
     VmStatus* status;
-    long long* timings;          // optional [workers][length][4] global-timer stamps: start, sources ready, end, GEMM drain
+    long long* timings;          // optional [workers][length][8] global-timer stamps (ns): start, sources ready, end, copies issued,
+                                 // first operands landed, MMAs issued, first accumulator ready, last stores done
     int num_stages, length;
     unsigned int epoch;
     int stage_begin, stage_end;  // execute stages in [begin, end); sources < begin are treated as complete

@@ -529,7 +529,7 @@ class NativePi0:
     def read_timings(self, name=None):
         """Global-timer stamps (ns) int64 [workers, stream_length, 4] = (start, producers ready, end, GEMM copies
         issued) of the last launch with timings enabled."""
-        out = np.zeros((self.workers, self.code.shape[1], 4), dtype=np.int64)
+        out = np.zeros((self.workers, self.code.shape[1], 8), dtype=np.int64)
         with torch.cuda.device(self.device):
             _native.check(self.lib.read_native_model_timings(self.handle, out.ctypes.data, out.size), "timing read")
         return out

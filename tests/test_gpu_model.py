@@ -135,11 +135,11 @@ def test_device_wait_timeout_is_reported_not_hung(small_model):
     x = inputs(3, 50, 0, dims.vocab)
     with NativePi0(StateDictModel(cfg, sd)) as engine:
         good = engine.forward(*x).clone()
-        _native.check(engine.lib.set_native_model_wait_budget(engine.handle, 1000), "budget")      # 1 microsecond
+        _native.check(engine.lib.set_native_model_wait_budget(engine.handle, 20_000), "budget")    # 20 microseconds
         engine.forward(*x)
         status = engine.status()
         assert status["code"] in (1, 2) and status["aborted"] == 1
-        assert 0 <= status["stage"] < len(engine.stages)
+        assert -1 <= status["stage"] < len(engine.stages)
         _native.check(engine.lib.set_native_model_wait_budget(engine.handle, 2_000_000_000), "budget")
         assert torch.equal(engine.forward(*x), good)
         assert engine.status()["code"] == 0
