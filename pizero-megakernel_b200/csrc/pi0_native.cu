@@ -98,6 +98,7 @@ struct Program {
     bool timings_on = false;
     unsigned int epoch = 0;
     unsigned long long budget_ns = 2000000000ull;
+    int* h_debug = nullptr;            // host-mapped progress marks (PI0_DEBUG_MARKS=1)
     ~Program() {
         cudaFree(d_stages);
         cudaFree(d_code);
@@ -105,6 +106,7 @@ struct Program {
         cudaFree(d_expected);
         cudaFree(d_status);
         cudaFree(d_timings);
+        if (h_debug) cudaFreeHost(h_debug);
     }
 };
 
@@ -256,6 +258,11 @@ int launch_program(Program* prog, cudaStream_t stream, LaunchInputs in, int begi
     p.stage_end = end;
     p.wait_budget_ns = prog->budget_ns;
     p.in = in;
+    if (!prog->h_debug && getenv("PI0_DEBUG_MARKS")) {
+        if (cudaHostAlloc(&prog->h_debug, sizeof(int) * prog->workers * (kThreads / 32), cudaHostAllocMapped) != cudaSuccess) prog->h_debug = nullptr;
+        else memset(prog->h_debug, 0, sizeof(int) * prog->workers * (kThreads / 32));
+    }
+    p.debug = prog->h_debug;
     pi0_vm_kernel<<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }
@@ -890,6 +897,12 @@ extern "C" int read_native_model_counters(void* handle, unsigned int* counts, un
     }
     if (expected)
         for (int i = 0; i < have; i++) expected[i] = prog->expected[i] * prog->epoch;
+    return cudaSuccess;
+}
+extern "C" int read_native_model_debug(void* handle, int* out, int n) {
+    Program* prog = as_program(handle);
+    if (!prog || !prog->h_debug || !out || n < prog->workers * (kThreads / 32)) return cudaErrorInvalidValue;
+    memcpy(out, prog->h_debug, sizeof(int) * prog->workers * (kThreads / 32));
     return cudaSuccess;
 }
 extern "C" int set_native_model_wait_budget(void* handle, unsigned long long nanoseconds) {

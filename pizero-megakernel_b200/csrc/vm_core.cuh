@@ -33,6 +33,8 @@ struct Ctl {
     uint64_t acc_empty[2];
     uint64_t ready[kRing];       // slot filled (32 asynchronous-copy arrivals of the prefetch warp)
     uint64_t release[kRing];     // slot no longer read (one arrival per warp)
+    uint64_t gather;             // all warps have reached a CTA-wide operator (one arrival per warp)
+    uint64_t done;               // all warps have left the instruction loop
     uint32_t tmem_base;
     volatile int abort;          // CTA-local copy of the abort decision
     volatile int dep_ok;         // broadcast slot for CTA-wide operators
@@ -47,6 +49,13 @@ struct PipeState {
     uint32_t mma_tile = 0;       // accumulator tiles produced
     uint32_t epi_tile = 0;       // accumulator tiles drained
 };
+
+__device__ __forceinline__ void mark(const VmProgram& prog, int code) {
+    if (prog.debug && lane_id() == 0) {
+        volatile int* p = prog.debug + blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+        *p = code;
+    }
+}
 
 __device__ __forceinline__ void report(const VmProgram& prog, int code, int stage, int band, unsigned int observed,
                                        unsigned int expected) {
@@ -68,14 +77,12 @@ __device__ __forceinline__ bool mbar_wait(const VmProgram& prog, Ctl* ctl, uint6
     if (mbar_try_wait(bar, parity)) return true;
     unsigned long long start = global_ns();
     for (uint32_t spin = 1;; ++spin) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((spin & 63u) == 0u) {
-            if (ctl->abort) return false;
-            if (global_ns() - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort)) {
-                report(prog, 2, stage, -1, parity, 0);
-                ctl->abort = 1;
-                return false;
-            }
+        if (mbar_try_wait(bar, parity)) return true;          // each try suspends for at most ~1 us
+        if (ctl->abort) return false;
+        if ((spin & 7u) == 0u && (global_ns() - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort))) {
+            report(prog, 2, stage, -1, parity, 0);
+            ctl->abort = 1;
+            return false;
         }
     }
 }
@@ -85,7 +92,9 @@ __device__ __forceinline__ bool mbar_wait(const VmProgram& prog, Ctl* ctl, uint6
 // lane then observes the completed phase itself (it cannot advance again before this warp has consumed it).
 __device__ __forceinline__ bool mbar_wait_warp(const VmProgram& prog, Ctl* ctl, uint64_t* bar, uint32_t parity, int stage) {
     int ok = 1;
+    mark(prog, 100 + stage);
     if (lane_id() == 0) ok = mbar_wait(prog, ctl, bar, parity, stage) ? 1 : 0;
+    mark(prog, 200000 + stage);
     ok = __shfl_sync(0xffffffffu, ok, 0);
     if (ok) {
         while (!mbar_try_wait(bar, parity)) {
@@ -123,6 +132,7 @@ __device__ __forceinline__ bool warp_wait_sources(const VmProgram& prog, Ctl* ct
             }
         }
     }
+    mark(prog, 300000 + stage);
     // (a consumer never reads more than 32 counters; the host rejects programs that would)
     unsigned int seen = mine ? ld_acquire(mine) : 0u;
     bool ok = mine == nullptr || seen >= target;
@@ -165,7 +175,9 @@ __device__ __forceinline__ bool cta_wait_sources(const VmProgram& prog, Ctl* ctl
             if (stamp) stamp[1] = static_cast<long long>(global_ns());
         }
     }
+    mark(prog, 400000 + stage);
     __syncthreads();
+    mark(prog, 500000 + stage);
     return ctl->dep_ok != 0;
 }
 __device__ __forceinline__ void cta_publish_tile(const VmProgram& prog, const StageDesc& st, int tile) {

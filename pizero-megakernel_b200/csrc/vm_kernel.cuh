@@ -65,6 +65,8 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
             mbar_init(&ctl->ready[r], 32);         // every lane of the prefetch warp
             mbar_init(&ctl->release[r], kThreads / 32);
         }
+        mbar_init(&ctl->gather, kThreads / 32);
+        mbar_init(&ctl->done, kThreads / 32);
         ctl->abort = 0;
         ctl->dep_ok = 1;
         mbar_fence_init();
@@ -95,6 +97,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
     }
 
     PipeState ps;
+    uint32_t gathers = 0;        // CTA-wide operators executed so far (phase of the gather barrier)
     for (uint32_t seq = 0;; ++seq) {
         if (warp == kPrefetchWarp) {
             if (!prefetch_slot(prog, ctl, stream, seq + kAhead, ip0 + seq + kAhead, pending)) break;
@@ -114,11 +117,19 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         long long* stamp = prog.timings ? prog.timings + (static_cast<size_t>(blockIdx.x) * prog.length + ip0 + seq) * 8 : nullptr;
         if (stamp && threadIdx.x == 0) stamp[0] = static_cast<long long>(global_ns());
         if (st.kind == OP_GEMM) {
+            mark(prog, 800000 + ins.y);
             gemm_instruction(prog, ctl, data, tmem, st, ins.y, ins.z, ins.w, ps, stamp);
             if (ctl->abort) break;
         } else {
-            // CTA-wide operator: every warp (including GEMM roles still draining) meets here first.
-            __syncthreads();
+            // CTA-wide operator: every warp (including GEMM roles still draining) meets here first. The meeting
+            // point is an mbarrier with a bounded, abort-aware wait, not bar.sync: a warp that gave up inside a GEMM
+            // role never arrives, and a hardware barrier would then hold the others for ever.
+            mark(prog, 600000 + ins.y);
+            __syncwarp();
+            if (lane_id() == 0) mbar_arrive(&ctl->gather);
+            if (!mbar_wait_warp(prog, ctl, &ctl->gather, gathers & 1u, ins.y)) break;
+            gathers++;
+            mark(prog, 700000 + ins.y);
             if (ctl->abort) break;
             if (!cta_wait_sources(prog, ctl, st, ins.y, ins.z, ins.w, stamp)) break;
             switch (st.kind) {
@@ -141,18 +152,26 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         if (lane_id() == 0) mbar_arrive(&ctl->release[slot]);
     }
 
+    mark(prog, 900001);
     // Teardown. After an abort, give copies and MMAs that may still be in flight a bounded moment to land.
     if (ctl->abort) {
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
+    mark(prog, 900002);
     cp_async_wait<0>();
     tc_fence_before();
-    __syncthreads();
+    __syncwarp();
+    if (lane_id() == 0) mbar_arrive(&ctl->done);
     if (warp == 2) {
+        // the warp that allocated tensor memory frees it once every warp is out of the loop (bounded wait: after
+        // an abort a warp may be late, the memory is still returned)
+        mbar_wait_warp(prog, ctl, &ctl->done, 0u, -1);
+        mark(prog, 900003);
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
+    mark(prog, 900004);
 }
 
 }  // namespace pi0

@@ -218,6 +218,7 @@ struct VmProgram {
     int stage_begin, stage_end;  // execute stages in [begin, end); sources < begin are treated as complete
     unsigned long long wait_budget_ns;
     LaunchInputs in;
+    int* debug;                  // optional host-mapped progress marks, one word per warp (diagnostics)
 };
 
 }  // namespace pi0

@@ -65,7 +65,7 @@ class NativePi0:
         return cls(StateDictModel(config or Pi0Config(), state_dict), **kwargs)
 
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
-                 library=None, workers=None, partitioned=False, expert_splits=8, expert_block_n=128,
+                 library=None, workers=None, partitioned=False, expert_splits=8, expert_block_n=64,
                  rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False):
         config = getattr(model, "config", None)
         if config is None or getattr(config, "pi05", False) or precision not in ("auto", "nvfp4"):
