@@ -51,6 +51,10 @@ int configure_resident_fp4_qkv_rope(void* handle, void* out_q, int ldq, const vo
  * copied per tile) and output tile width (128 or 64). */
 int configure_resident_fp4_rows(void* handle, int rows);
 int configure_resident_fp4_tile(void* handle, int block_n);
+/* extension: tiled = 1 declares that B is stored tile-major (K a multiple of 256): for every output tile n and every
+ * 256-wide K stage s the block_n x 128 bytes of that block are contiguous, at byte offset
+ * ((n * K/256 + s) * block_n) * 128; one TMA box is then one contiguous read.  Set the tile width first. */
+int configure_resident_fp4_weight_layout(void* handle, int tiled);
 
 /* ------------------------------------------------------------------------------------------------------
  * LayerNorm / RMSNorm producer -> NVFP4 (format 4) or BF16 (format 16).

@@ -1,6 +1,6 @@
 // NVFP4 block-scaled GEMM instruction:  out[M,N] = epilogue(alpha * deq(A)[M,K] . deq(B)[N,K]^T)
 //
-//   warp 0 / lane 0 : TMA producer  - operand tiles (128 B swizzled rows) and scale atoms into a 5-stage ring
+//   warp 0 / lane 0 : TMA producer  - operand tiles (128 B swizzled rows) and scale atoms into a ring of 72 KiB slots
 //   warp 1 / lane 0 : MMA issuer    - tcgen05.cp (scales smem->TMEM) + tcgen05.mma kind::mxf4nvf4, K = 64 each
 //   warps 4..7      : epilogue      - tcgen05.ld of a 128xN FP32 accumulator (one row per thread), fused math, stores
 //
@@ -16,8 +16,9 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
                                               int stage_index, int first, int count, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
     const int lane = lane_id();
-    const int kstages = (g.k_groups + 3) >> 2;
-    const uint32_t b_bytes = static_cast<uint32_t>(g.block_n) * 128u;
+    const int chunks = (g.k_groups + 3) >> 2;                        // 256-wide K chunks
+    const int slots = (chunks + kChunks - 1) / kChunks;
+    const uint32_t ab_bytes = static_cast<uint32_t>(kChunks) * 128u * static_cast<uint32_t>(g.a_box_rows + g.block_n);
     int current_band = -1;
     for (int t = first; t < first + count; ++t) {
         const int m_tile = t / g.n_tiles, n_tile = t - m_tile * g.n_tiles;
@@ -33,20 +34,22 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
         int alive = 1;
         if (lane == 0) {
             const int sfb_tile = (n_tile * g.block_n) >> 7;
-            for (int ks = 0; ks < kstages; ++ks) {
+            for (int ks = 0; ks < slots; ++ks) {
                 const uint32_t s = ps.prod_it % kStages, phase = (ps.prod_it / kStages) & 1u;
                 if (!mbar_wait(prog, ctl, &ctl->empty[s], phase ^ 1u, stage_index)) { alive = 0; break; }
-                const int groups = min(4, g.k_groups - ks * 4);
+                const int groups = min(4 * kChunks, g.k_groups - ks * 4 * kChunks);
                 uint8_t* slot = data + s * kStageBytes;
-                // a_box_rows < 128 (few logical rows): only the rows that exist are copied; the MMA still reads 128
-                // rows, whatever the remaining rows of the slot hold lands in accumulator rows that are never stored
-                mbar_expect_tx(&ctl->full[s], static_cast<uint32_t>(g.a_box_rows) * 128u + b_bytes + 2u * groups * 512u);
-                tma_load_2d(slot, g.tmap_a, &ctl->full[s], ks * 128, m_tile * 128);
-                tma_load_2d(slot + kTileABytes, g.tmap_b, &ctl->full[s], ks * 128, n_tile * g.block_n);
-                bulk_load(slot + 2 * kTileABytes, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4) * 512,
-                          groups * 512u, &ctl->full[s]);
-                bulk_load(slot + 2 * kTileABytes + kSfBytes, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4) * 512,
-                          groups * 512u, &ctl->full[s]);
+                // Boxes always deliver kChunks chunks (beyond K the copy engine fills zeros or, inside a padded
+                // allocation, bytes that no MMA reads).  a_box_rows < 128 (few logical rows): only the rows that
+                // exist are copied; the MMA still reads 128 rows, the rest lands in accumulator rows never stored.
+                mbar_expect_tx(&ctl->full[s], ab_bytes + 2u * groups * 512u);
+                tma_load_3d(slot + kSlotA, g.tmap_a, &ctl->full[s], 0, m_tile * 128, ks * kChunks);
+                if (g.b_tiled) tma_load_2d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, (n_tile * chunks + ks * kChunks) * g.block_n);
+                else tma_load_3d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, n_tile * g.block_n, ks * kChunks);
+                bulk_load(slot + kSlotSfa, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4 * kChunks) * 512, groups * 512u,
+                          &ctl->full[s]);
+                bulk_load(slot + kSlotSfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512, groups * 512u,
+                          &ctl->full[s]);
                 ps.prod_it++;
             }
         }
@@ -58,7 +61,9 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
 __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem, const StageDesc& st,
                                          int stage_index, int first, int count, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
-    const int kstages = (g.k_groups + 3) >> 2;
+    const int chunks = (g.k_groups + 3) >> 2;
+    const int slots = (chunks + kChunks - 1) / kChunks;
+    const uint32_t a_chunk = static_cast<uint32_t>(g.a_box_rows) * 128u, b_chunk = static_cast<uint32_t>(g.block_n) * 128u;
     for (int t = first; t < first + count; ++t) {
         const int n_tile = t % g.n_tiles;
         const uint32_t buf = ps.mma_tile & 1u, acc_phase = (ps.mma_tile >> 1) & 1u;
@@ -67,24 +72,22 @@ __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_
         const uint32_t d = tmem + buf * 128u;
         // Scale rows of a narrow B tile sit in the 32-row sub-column of their 128-row atom.
         const uint32_t sfb_sub = static_cast<uint32_t>((n_tile * g.block_n) & 127) >> 5;
-        for (int ks = 0; ks < kstages; ++ks) {
+        for (int ks = 0; ks < slots; ++ks) {
             const uint32_t s = ps.mma_it % kStages, phase = (ps.mma_it / kStages) & 1u;
             if (!mbar_wait(prog, ctl, &ctl->full[s], phase, stage_index)) return;
             tc_fence_after();
             if (stamp && t == first && ks == 0) stamp[4] = static_cast<long long>(global_ns());
-            const int groups = min(4, g.k_groups - ks * 4);
-            const uint32_t a_addr = smem_u32(data + s * kStageBytes);
-            const uint32_t b_addr = a_addr + kTileABytes;
-            const uint32_t sfa_addr = a_addr + 2 * kTileABytes;
-            const uint32_t sfb_addr = sfa_addr + kSfBytes;
-            const uint64_t a_desc = umma_desc_k_sw128(a_addr), b_desc = umma_desc_k_sw128(b_addr);
+            const int groups = min(4 * kChunks, g.k_groups - ks * 4 * kChunks);
+            const uint32_t base = smem_u32(data + s * kStageBytes);
             for (int gi = 0; gi < groups; ++gi) {
-                const uint32_t sfa_t = tmem + kSfCol0 + (s * 4 + gi) * 8;
+                const uint32_t chunk = static_cast<uint32_t>(gi) >> 2, sub = static_cast<uint32_t>(gi) & 3u;
+                const uint32_t sfa_t = tmem + kSfCol0 + (s * 4 * kChunks + gi) * 8;
                 const uint32_t sfb_t = sfa_t + 4;
-                tc_copy_sf(sfa_t, umma_desc_sf(sfa_addr + gi * 512));
-                tc_copy_sf(sfb_t, umma_desc_sf(sfb_addr + gi * 512));
+                tc_copy_sf(sfa_t, umma_desc_sf(base + kSlotSfa + gi * 512));
+                tc_copy_sf(sfb_t, umma_desc_sf(base + kSlotSfb + gi * 512));
                 // 64 FP4 = 32 bytes along K inside the 128-byte swizzled row: advance the start address by 2 units.
-                tc_mma_nvfp4(d, a_desc + 2u * gi, b_desc + 2u * gi, g.idesc, sfa_t, sfb_t + sfb_sub,
+                tc_mma_nvfp4(d, umma_desc_k_sw128(base + kSlotA + chunk * a_chunk) + 2u * sub,
+                             umma_desc_k_sw128(base + kSlotB + chunk * b_chunk) + 2u * sub, g.idesc, sfa_t, sfb_t + sfb_sub,
                              static_cast<uint32_t>((ks | gi) != 0));
             }
             tc_commit(&ctl->empty[s]);     // slot reusable once these MMAs have read it
@@ -210,12 +213,26 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
             // Q and K heads are stored pair-interleaved: column 2i holds original dim i, column 2i+1 holds dim i+hd/2.
             const __nv_bfloat16* cs = static_cast<const __nv_bfloat16*>(g.rope_cos) + static_cast<size_t>(row) * hd;
             const __nv_bfloat16* sn = static_cast<const __nv_bfloat16*>(g.rope_sin) + static_cast<size_t>(row) * hd;
+            // the 16 pairs of this chunk use table entries [dim0, dim0+16) and [dim0+half, dim0+half+16): 8 vector loads
+            const int dim0 = in_head >> 1;
+            uint32_t tc[2][8], ts[2][8];
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const uint4* pc = reinterpret_cast<const uint4*>(cs + dim0 + h * half);
+                const uint4* ps = reinterpret_cast<const uint4*>(sn + dim0 + h * half);
+                const uint4 c0 = __ldg(pc), c1 = __ldg(pc + 1), s0 = __ldg(ps), s1 = __ldg(ps + 1);
+                tc[h][0] = c0.x; tc[h][1] = c0.y; tc[h][2] = c0.z; tc[h][3] = c0.w;
+                tc[h][4] = c1.x; tc[h][5] = c1.y; tc[h][6] = c1.z; tc[h][7] = c1.w;
+                ts[h][0] = s0.x; ts[h][1] = s0.y; ts[h][2] = s0.z; ts[h][3] = s0.w;
+                ts[h][4] = s1.x; ts[h][5] = s1.y; ts[h][6] = s1.z; ts[h][7] = s1.w;
+            }
 #pragma unroll
             for (int i = 0; i < 16; i++) {
-                const int dim = (in_head >> 1) + i;
+                const float2 cl = unpack_bf16x2(tc[0][i >> 1]), ch = unpack_bf16x2(tc[1][i >> 1]);
+                const float2 sl = unpack_bf16x2(ts[0][i >> 1]), sh = unpack_bf16x2(ts[1][i >> 1]);
+                const float c1 = (i & 1) ? cl.y : cl.x, s1 = (i & 1) ? sl.y : sl.x;
+                const float c2 = (i & 1) ? ch.y : ch.x, s2 = (i & 1) ? sh.y : sh.x;
                 float x1 = bf16_round(v[2 * i]), x2 = bf16_round(v[2 * i + 1]);
-                float c1 = __bfloat162float(cs[dim]), s1 = __bfloat162float(sn[dim]);
-                float c2 = __bfloat162float(cs[dim + half]), s2 = __bfloat162float(sn[dim + half]);
                 float o1 = bf16_round(x1 * c1) + bf16_round(-x2 * s1);
                 float o2 = bf16_round(x2 * c2) + bf16_round(x1 * s2);
                 packed[i] = pack_bf16x2(o1, o2);

@@ -94,12 +94,19 @@ __device__ __forceinline__ void norm_row(const NormParams& n, int row) {
     for (int j = 0; j < kNormMaxBlocksPerLane; j++) {
         const int b = lane + 32 * j;
         if (b < blocks) {
-            float v[16];
+            float v[16], gm[16], bt[16];
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float4 g4 = n.gamma ? __ldg(reinterpret_cast<const float4*>(n.gamma + b * 16) + q) : make_float4(1.f, 1.f, 1.f, 1.f);
+                const float4 b4 = n.beta ? __ldg(reinterpret_cast<const float4*>(n.beta + b * 16) + q) : make_float4(0.f, 0.f, 0.f, 0.f);
+                gm[4 * q] = g4.x; gm[4 * q + 1] = g4.y; gm[4 * q + 2] = g4.z; gm[4 * q + 3] = g4.w;
+                bt[4 * q] = b4.x; bt[4 * q + 1] = b4.y; bt[4 * q + 2] = b4.z; bt[4 * q + 3] = b4.w;
+            }
 #pragma unroll
             for (int i = 0; i < 16; i++) {
                 float y = (cache[j][i] - mean) * rstd;
-                if (n.gamma) y *= n.gamma[b * 16 + i];
-                if (n.beta) y += n.beta[b * 16 + i];
+                if (n.gamma) y *= gm[i];
+                if (n.beta) y += bt[i];
                 v[i] = n.round_norm ? bf16_round(y) : y;
             }
             store_block16(n, row, b, v);

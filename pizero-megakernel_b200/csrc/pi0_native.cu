@@ -49,12 +49,27 @@ EncodeTiled encoder() {
     }
     return fn;
 }
-// Packed FP4 matrix [rows, k/2] bytes, boxes of 128 bytes x box_rows with the 128-byte swizzle.
+// Packed FP4 matrix [rows, k/2] bytes seen as [chunk][row][128 bytes]: a box is kChunks consecutive 256-wide K chunks
+// of box_rows rows, each chunk landing as box_rows 128-byte rows with the 128-byte swizzle.
 int encode_operand(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
     EncodeTiled fn = encoder();
     if (!fn) return cudaErrorNotSupported;
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(rows)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(k / 2)};
+    const cuuint64_t row_bytes = static_cast<cuuint64_t>(k / 2);
+    cuuint64_t dims[3] = {128u, static_cast<cuuint64_t>(rows), (row_bytes + 127) / 128};
+    cuuint64_t strides[2] = {row_bytes, 128u};
+    cuuint32_t box[3] = {128u, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(kChunks)};
+    cuuint32_t estr[3] = {1u, 1u, 1u};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+// Tile-major weight: [blocks * block_n rows][128 bytes]; a box is kChunks consecutive blocks of one output tile.
+int encode_tiled(CUtensorMap* map, const void* base, int total_rows, int box_rows) {
+    EncodeTiled fn = encoder();
+    if (!fn) return cudaErrorNotSupported;
+    cuuint64_t dims[2] = {128u, static_cast<cuuint64_t>(total_rows)};
+    cuuint64_t strides[1] = {128u};
     cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
     cuuint32_t estr[2] = {1u, 1u};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
@@ -303,7 +318,8 @@ int gemm_refresh(Op* op) {
     GemmParams& g = op->desc.p.gemm;
     CUtensorMap host[2];
     int e = encode_operand(&host[0], op->a, op->m, op->k, g.a_box_rows);
-    if (!e) e = encode_operand(&host[1], op->b, op->n, op->k, g.block_n);
+    if (!e) e = g.b_tiled ? encode_tiled(&host[1], op->b, op->n * (op->k / 256), kChunks * g.block_n)
+                          : encode_operand(&host[1], op->b, op->n, op->k, g.block_n);
     if (e) return e;
     if (!op->maps) {
         cudaError_t ce = cudaMalloc(&op->maps, 2 * sizeof(CUtensorMap));
@@ -468,6 +484,12 @@ extern "C" int configure_resident_fp4_rows(void* handle, int rows) {
     if (!op || op->desc.kind != OP_GEMM || rows < 1 || rows > op->m) return cudaErrorInvalidValue;
     op->desc.p.gemm.rows = rows;
     op->desc.p.gemm.a_box_rows = (rows <= 64 && op->m == 128) ? 64 : 128;
+    return gemm_refresh(op);
+}
+extern "C" int configure_resident_fp4_weight_layout(void* handle, int tiled) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || (tiled != 0 && tiled != 1) || (tiled && op->k % 256)) return cudaErrorInvalidValue;
+    op->desc.p.gemm.b_tiled = tiled;
     return gemm_refresh(op);
 }
 extern "C" int configure_resident_fp4_tile(void* handle, int block_n) {

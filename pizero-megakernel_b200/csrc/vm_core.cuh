@@ -5,10 +5,18 @@
 
 namespace pi0 {
 
-constexpr int kStages = 5;                                   // shared-memory ring depth of the GEMM pipeline
-constexpr int kTileABytes = 128 * 128;                       // 128 rows x 128 bytes (256 FP4 along K)
-constexpr int kSfBytes = 4 * 512;                            // four 64-wide K groups of scale atoms
-constexpr int kStageBytes = 2 * kTileABytes + 2 * kSfBytes;  // A | B | SFA | SFB = 36 KiB
+// GEMM pipeline: a ring of kStages slots, each holding kChunks consecutive 256-wide K chunks of A and B plus their
+// scale atoms.  One slot is filled by four copies (A, B, SFA, SFB); copies complete at a roughly fixed cost each
+// (about one L2 round trip, whatever their size), so a slot carries as many bytes per copy as shared memory allows.
+constexpr int kStages = 2;                                   // slots in flight
+constexpr int kChunks = 2;                                   // 256-wide K chunks per slot
+constexpr int kTileABytes = 128 * 128;                       // one chunk of one operand: 128 rows x 128 bytes
+constexpr int kSfBytes = kChunks * 4 * 512;                  // scale atoms of one operand: four 64-wide K groups per chunk
+constexpr int kSlotA = 0;
+constexpr int kSlotB = kChunks * kTileABytes;
+constexpr int kSlotSfa = 2 * kChunks * kTileABytes;
+constexpr int kSlotSfb = kSlotSfa + kSfBytes;
+constexpr int kStageBytes = kSlotSfb + kSfBytes;             // 72 KiB
 constexpr int kCtlBytes = 3072;
 constexpr int kDataBytes = 214 * 1024;                       // operator scratch behind the control block
 constexpr int kSmemBytes = kCtlBytes + kDataBytes + 1024;    // + slack for 1 KiB alignment

@@ -46,6 +46,7 @@ struct GemmParams {
     int m_tiles, n_tiles;        // 128-row x block_n-column output tiles
     int k_groups;                // K / 64
     int block_n;                 // 128 (default), 64 or 32
+    int b_tiled;                 // B stored tile-major: block (n_tile, k_stage) is block_n contiguous 128-byte rows
     int a_box_rows;              // rows of A copied per tile: 128, or 64 when the logical row count is <= 64
     float alpha;                 // global_scale(A) * global_scale(B)
     int epilogue;

@@ -52,6 +52,7 @@ _SIGNATURES = {
     "configure_resident_fp4_qkv_rope": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I],
     "configure_resident_fp4_rows": [_P, _I],
     "configure_resident_fp4_tile": [_P, _I],
+    "configure_resident_fp4_weight_layout": [_P, _I],
     "resident_fp4_resources": [_P, C.POINTER(_I), _I],
     "destroy_resident_fp4": [_P],
     "create_norm": [C.POINTER(_P)] + [_P] * 8 + [_I] * 9 + [_F] * 2,

@@ -66,7 +66,7 @@ class NativePi0:
 
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
                  library=None, workers=None, partitioned=False, expert_splits=8, expert_block_n=64,
-                 rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False):
+                 rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True):
         config = getattr(model, "config", None)
         if config is None or getattr(config, "pi05", False) or precision not in ("auto", "nvfp4"):
             raise ValueError("This engine runs ordinary pi0 with NVFP4 transformers (precision 'auto' or 'nvfp4')")
@@ -82,6 +82,7 @@ class NativePi0:
         self.expert_block_n = expert_block_n
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self.keep_debug_outputs = keep_debug_outputs
+        self.tile_weights = tile_weights
         self.verbose = verbose
         sd = model.state_dict()
         self.device = next(iter(sd.values())).device
@@ -123,8 +124,11 @@ class NativePi0:
             self._cache[key] = make()
         return self._cache[key]
 
-    def weight(self, w, *, rows_to=128):
-        """BF16/FP32 [N, K] -> NVFP4 on the device (ceil block scales, tensor scale amax/(6*448))."""
+    def weight(self, w, *, rows_to=128, block_n=128):
+        """BF16/FP32 [N, K] -> NVFP4 on the device (ceil block scales, tensor scale amax/(6*448)).
+
+        When K is a multiple of 256 the packed codes are re-laid tile-major for ``block_n``-wide output tiles
+        (``Fp4Matrix.tiled = block_n``): every TMA box of the weight operand is then one contiguous read."""
         n, k = w.shape
         np_, kp = padded(n, rows_to), padded(k, 64)
         src = torch.zeros((np_, kp), device=self.device, dtype=torch.bfloat16)
@@ -134,6 +138,11 @@ class NativePi0:
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _native.check(self.lib.quantize_nvfp4(src.data_ptr(), m.data.data_ptr(), m.scales.data_ptr(), np_, kp, kp, kp // 16,
                                               m.global_scale, 1, stream), "weight quantisation")
+        m.tiled = 0
+        if self.tile_weights and kp % 256 == 0 and np_ % block_n == 0:
+            tiled = m.data.view(np_ // block_n, block_n, kp // 256, 128).permute(0, 2, 1, 3).contiguous()
+            m.data.copy_(tiled.view(np_, kp // 2))
+            m.tiled = block_n
         torch.cuda.current_stream(self.device).synchronize()
         self.buffers.append(m)
         return m
@@ -187,6 +196,10 @@ class NativePi0:
         _native.check(self.lib.configure_resident_fp4_rows(h, rows), name)
         if block_n != 128:
             _native.check(self.lib.configure_resident_fp4_tile(h, block_n), name)
+        if getattr(w, "tiled", 0):
+            if w.tiled != block_n:
+                raise ValueError(f"{name}: weight tiled for {w.tiled}-wide tiles, used with {block_n}")
+            _native.check(self.lib.configure_resident_fp4_weight_layout(h, 1), name)
         return self.add(0, h, name, sources)
 
     def norm(self, name, x, out: Fp4Matrix, *, rows, sources, kind, gamma=None, beta=None, eps=1e-6, bf16_copy=None):
@@ -310,8 +323,8 @@ class NativePi0:
             wk = self._interleave_heads(sd[p + "self_attn.k_proj.weight"])
             wv = sd[p + "self_attn.v_proj.weight"]
             if kv_only:
-                return self.weight(torch.cat((wk, wv)))
-            return self.weight(torch.cat((self._interleave_heads(sd[p + "self_attn.q_proj.weight"]), wk, wv)))
+                return self.weight(torch.cat((wk, wv)), block_n=block_n)
+            return self.weight(torch.cat((self._interleave_heads(sd[p + "self_attn.q_proj.weight"]), wk, wv)), block_n=block_n)
 
         wqkv = self.cached(p + "qkv", make_qkv)
         q_cols, q = (0, None) if kv_only else (H * hd, qbuf)
@@ -335,17 +348,17 @@ class NativePi0:
             s_att = self.add(4, mh, f"{name}.merge", [(s_part, ALL)])
         else:
             s_att = self.add(1, h, f"{name}.attention", att_sources)
-        wo = self.cached(p + "o", lambda: self.weight(sd[p + "self_attn.o_proj.weight"]))
+        wo = self.cached(p + "o", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=block_n))
         s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=block_n)
         g2 = self.cached(p + "g2", lambda: (1.0 + sd[p + "post_attention_layernorm.weight"].float()).contiguous())
         s_n2 = self.norm(f"{name}.norm2", x_mid, a3, rows=rows, sources=[(s_o, SAME)], kind="rms", gamma=g2, eps=c.rms_eps)
         def make_gate_up():
             gate, up = sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]
-            return self.weight(torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], gate.shape[1]))
+            return self.weight(torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], gate.shape[1]), block_n=block_n)
 
         wgu = self.cached(p + "gate_up", make_gate_up)
         s_gu = self.gemm(f"{name}.gate_up", a3, wgu, rows=rows, sources=[(s_n2, SAME)], fp4_out=a4, activation=2, block_n=block_n)
-        wd = self.cached(p + "down", lambda: self.weight(sd[p + "mlp.down_proj.weight"]))
+        wd = self.cached(p + "down", lambda: self.weight(sd[p + "mlp.down_proj.weight"], block_n=block_n))
         s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=block_n)
         return s_dn, s_qkv
 

@@ -19,7 +19,7 @@ class ResidentNVFP4:
     def __init__(self, library, activation, weight, *, workers=16, device="cuda",
                  output_dtype=torch.float32, bias=None, residual=None,
                  output_global_scale=1.0, output_gelu=False, output_geglu=False, output_relu2=False,
-                 block_n=128, rows=None, activation_buffers=None):
+                 block_n=128, rows=None, activation_buffers=None, tiled_weight=False):
         self._handle = ctypes.c_void_p()
         self.device = torch.device(device)
         if self.device.type != "cuda":
@@ -99,6 +99,11 @@ class ResidentNVFP4:
                     _native.check(lib.configure_resident_fp4_rows(self._handle, int(rows)), "Native FP4 rows")
                 if block_n != 128:
                     _native.check(lib.configure_resident_fp4_tile(self._handle, int(block_n)), "Native FP4 tile")
+                if tiled_weight:
+                    # re-lay the packed weight tile-major: block (n tile, 256-wide K stage) = block_n contiguous 128-byte rows
+                    tiled = self.b.view(n // block_n, block_n, k // 256, 128).permute(0, 2, 1, 3).contiguous()
+                    self.b.copy_(tiled.view(n, k // 2))
+                    _native.check(lib.configure_resident_fp4_weight_layout(self._handle, 1), "Native FP4 weight layout")
                 values = (ctypes.c_int * 8)()
                 _native.check(lib.resident_fp4_resources(self._handle, values, 8), "Native FP4 resource query")
             except Exception:

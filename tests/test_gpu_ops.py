@@ -121,12 +121,20 @@ def test_gemm_bias_residual_and_tiles():
     pa, pb = pack_nvfp4(a), pack_nvfp4(b, scale_policy="ceil")
     ref = oracle.gemm(pa.data, pa.scales, 1.0, pb.data, pb.scales, 1.0, m, n, k) + bias.float().numpy()[None] + res.float().numpy()
     expect = bf16(ref).float().numpy()
-    for block_n in (128,):
-        with ResidentNVFP4(None, pa, pb, workers=7, output_dtype=torch.bfloat16, bias=bias, residual=res, block_n=block_n) as op:
+    results = []
+    for block_n, tiled in ((128, False), (64, False), (128, True), (64, True)):
+        with ResidentNVFP4(None, pa, pb, workers=7, output_dtype=torch.bfloat16, bias=bias, residual=res, block_n=block_n,
+                           tiled_weight=tiled) as op:
             y = op.forward().float().cpu().numpy()
+            assert op.status()["code"] == 0
         mism = float((y != expect).mean())
-        assert mism < 1e-3, (block_n, mism)                 # BF16 result equal except FP32 summation-order ties
+        assert mism < 1e-3, (block_n, tiled, mism)          # BF16 result equal except FP32 summation-order ties
         assert relrms(y, expect) < 1e-3
+        results.append(y)
+    for y in results[1:]:                                   # tile width and weight layout do not change a single bit
+        np.testing.assert_array_equal(y, results[0])
+    with pytest.raises(RuntimeError):
+        ResidentNVFP4(None, pa, pb, block_n=32)             # 32-wide tiles are not offered
 
 
 def _decode(op, rows, width):
