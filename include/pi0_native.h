@@ -103,6 +103,21 @@ int configure_attention_fp4_output(void* handle, void* out_fp4, void* scales, in
 /* extension: handle of the merge stage owned by an attention handle with splits > 1 (NULL otherwise). */
 int attention_merge_handle(void* handle, void** merge);
 
+/* Split-KV attention that allocates nothing.  No counterpart in the reference.
+ * For callers that cannot call cudaMalloc when they need the result - a control loop that must not block on the
+ * driver's allocator, or a process whose device memory all belongs to another runtime's pool.  The split-KV partials
+ * live in a fixed device array inside the library (about 8.1 MiB per GPU that loads it, held until exit) instead of
+ * an allocated buffer; the call makes no cudaMalloc / cudaFree and uses no allocating library routine.
+ * q BF16 [nq, heads*256] (row stride ldq), k and v BF16 [nk, kv_heads*256] (row stride ldkv), out BF16 [nq, heads*256]
+ * (row stride out_ld); prefix >= 0 selects the pi0 suffix mask, < 0 none.  Limits (cudaErrorInvalidValue beyond them):
+ * head_dim == 256, nq <= 128, heads * splits <= 64.  Same arithmetic as create_attention + configure_attention_splits.
+ * The first call on a device looks up the array's device address and raises the kernel's shared-memory limit; make
+ * that first call before any stream capture begins.  All calls on a GPU share the one array, which keeps the last
+ * call's partials: every word read is rewritten first by the same call, but two calls that overlap on the GPU
+ * (different streams) race on it - serialise them. */
+int attention_split_noalloc(const void* q, const void* k, const void* v, void* out, int nq, int nk, int heads, int kv_heads,
+                            int head_dim, int ldq, int ldkv, int out_ld, int prefix, int splits, float scale, void* stream);
+
 /* ------------------------------------------------------------------------------------------------------
  * Small FP32 operators (the reference's NativeTensorOp modes 5, 6, 8, 10: native_pi0/model.cu:95-183,
  * created from native_pi0/model.py:95-104,136-145).  extension: each is an operator handle of its own.

@@ -7,6 +7,7 @@
 #include <cmath>
 #include <cstring>
 #include <memory>
+#include <mutex>
 #include <vector>
 
 #include "../../include/pi0_native.h"
@@ -999,5 +1000,105 @@ extern "C" int quantize_nvfp4(const void* in, void* out, void* scales, int rows,
     n.out = static_cast<uint8_t*>(out); n.out_scales = static_cast<uint8_t*>(scales);
     n.out_blocks = out_blocks; n.ld_in = ld_in; n.ld_out = width / 2;
     quantize_rows_kernel<<<(rows + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(n);
+    return cudaGetLastError();
+}
+
+// =====================================================================================================
+// Allocation-free split-KV attention.
+//
+// Some callers may not allocate device memory at the moment they need attention: a robot control loop that
+// must never block on the driver's allocator (cudaMalloc takes a process-wide lock and synchronises the
+// device, which can cost milliseconds in the middle of a 20 ms control period), or a process that has handed
+// all of its device memory to another runtime's pool at start-up.  For them the split-KV partials live in a
+// file-scope device array of fixed size instead of a buffer obtained from cudaMalloc.  The array exists once
+// per GPU that loads this library (about 8.1 MiB each, held until the process exits), is shared by every
+// call, and keeps the previous call's contents.
+namespace pi0 {
+namespace {
+
+constexpr int kNoAllocMaxParts = 64;                 // heads * splits
+constexpr int kNoAllocHeadDim = 256;
+constexpr size_t kNoAllocPartialO = static_cast<size_t>(kNoAllocMaxParts) * kAttnQRows * kNoAllocHeadDim * sizeof(float);
+constexpr size_t kNoAllocPartialMl = static_cast<size_t>(kNoAllocMaxParts) * kAttnQRows * 2 * sizeof(float);
+constexpr int kNoAllocSmem = kAttnQRows * (kNoAllocHeadDim + 8) * 2 + 4 * kAttnChunk * (kNoAllocHeadDim + 8) * 2 + 1024;
+
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPartialO + kNoAllocPartialMl];
+
+__global__ void __launch_bounds__(kThreads, 1) noalloc_attention_kernel(AttnParams a) {
+    extern __shared__ uint8_t noalloc_smem[];
+    uint8_t* data = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(noalloc_smem) + 1023) & ~static_cast<uintptr_t>(1023));
+    attn_tile<kNoAllocHeadDim>(a, blockIdx.x, data);
+}
+__global__ void __launch_bounds__(kThreads, 1) noalloc_merge_kernel(MergeParams g) { merge_tile(g, blockIdx.x); }
+
+// Device address of the scratch array, looked up once per device.  In host code the array's name is only a
+// handle for the runtime, never an address a kernel could use, so the address must come from
+// cudaGetSymbolAddress with the owning device current.
+struct NoAllocDevice {
+    bool ready = false;
+    unsigned char* scratch = nullptr;
+};
+NoAllocDevice g_noalloc_device[64];
+std::mutex g_noalloc_mutex;
+
+int noalloc_setup(int device, unsigned char** scratch) {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    NoAllocDevice& d = g_noalloc_device[device];
+    if (!d.ready) {
+        void* address = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&address, g_noalloc_scratch);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(noalloc_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kNoAllocSmem);
+        if (e != cudaSuccess) return e;
+        d.scratch = static_cast<unsigned char*>(address);
+        d.ready = true;
+    }
+    *scratch = d.scratch;
+    return cudaSuccess;
+}
+
+}  // namespace
+}  // namespace pi0
+
+extern "C" int attention_split_noalloc(const void* q, const void* k, const void* v, void* out, int nq, int nk, int heads,
+                                       int kv_heads, int head_dim, int ldq, int ldkv, int out_ld, int prefix, int splits,
+                                       float scale, void* stream) {
+    if (!q || !k || !v || !out || nq < 1 || nk < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads || splits < 1 ||
+        ldq < heads * head_dim || ldq % 8 || ldkv < kv_heads * head_dim || ldkv % 8 || out_ld < heads * head_dim || out_ld % 8 ||
+        !std::isfinite(scale) || scale <= 0)
+        return cudaErrorInvalidValue;
+    // limits of the fixed scratch array: 256-wide heads, at most 128 queries, heads * splits <= 64
+    if (head_dim != kNoAllocHeadDim || nq > kAttnQRows || heads * splits > kNoAllocMaxParts) return cudaErrorInvalidValue;
+    int device = 0;
+    int e = check_device(&device);
+    if (e) return e;
+    if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+    unsigned char* scratch = nullptr;
+    e = noalloc_setup(device, &scratch);
+    if (e) return e;
+    float* partial_o = reinterpret_cast<float*>(scratch);
+    float* partial_ml = reinterpret_cast<float*>(scratch + kNoAllocPartialO);
+    AttnParams a{};
+    a.q = q; a.k = k; a.v = v; a.out = nullptr;
+    a.ldq = ldq; a.ldkv = ldkv; a.ldo = out_ld;
+    a.batches = 1; a.nq = nq; a.nk = nk; a.q_batch_rows = nq; a.kv_batch_rows = nk;
+    a.heads = heads; a.kv_heads = kv_heads; a.head_dim = head_dim;
+    a.scale = scale;
+    a.prefix = prefix >= 0 ? prefix : -1;
+    a.splits = splits;
+    a.partial_o = partial_o; a.partial_ml = partial_ml;
+    a.out_inv_gs = 1.f;
+    MergeParams g{};
+    g.partial_o = partial_o; g.partial_ml = partial_ml;
+    g.heads = heads; g.nq = nq; g.head_dim = head_dim; g.splits = splits;
+    g.out = out; g.ldo = out_ld;
+    g.out_inv_gs = 1.f;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Every partial word the merge reads (rows < nq of each head/split) is written by the attention kernel of
+    // this same call first, so nothing in the shared array has to be cleared beforehand.
+    noalloc_attention_kernel<<<heads * splits, kThreads, kNoAllocSmem, s>>>(a);
+    cudaError_t launch = cudaGetLastError();
+    if (launch != cudaSuccess) return launch;
+    noalloc_merge_kernel<<<heads * ((nq + kMergeRows - 1) / kMergeRows), kThreads, 0, s>>>(g);
     return cudaGetLastError();
 }

@@ -90,6 +90,7 @@ _SIGNATURES = {
     "read_native_linear": [_P, _P, _I, _P],
     "destroy_native_linear": [_P],
     "quantize_nvfp4": [_P, _P, _P, _I, _I, _I, _I, _F, _I, _P],
+    "attention_split_noalloc": [_P, _P, _P, _P] + [_I] * 10 + [_F, _P],
 }
 EXPORTS = tuple(_SIGNATURES)
 _cache = {}
