@@ -297,16 +297,28 @@ __device__ __forceinline__ void merge_tile(const MergeParams& g, int tile) {
 #pragma unroll
         for (int e = 0; e < 16; e++) acc[e] = 0.f;
         float denom = 0.f;
-#pragma unroll 4
-        for (int s = 0; s < g.splits; s++) {
-            const float2 pair = __ldcg(reinterpret_cast<const float2*>(ml + static_cast<size_t>(s) * kAttnQRows * 2));
-            const float w = exp2f(pair.x - ref);                 // 0 for a split whose keys were all masked
-            denom += w * pair.y;
-            const float4* src = reinterpret_cast<const float4*>(po + static_cast<size_t>(s) * kAttnQRows * g.head_dim);
+        // four splits at a time: their (m, l) pairs and their 16 output values are requested together, the
+        // weights are computed afterwards, so no load waits for arithmetic
+        for (int s0 = 0; s0 < g.splits; s0 += 4) {
+            float2 pair[4];
+            float4 x[4][4];
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const float4 x = __ldcg(src + q);
-                acc[4 * q] += w * x.x; acc[4 * q + 1] += w * x.y; acc[4 * q + 2] += w * x.z; acc[4 * q + 3] += w * x.w;
+            for (int j = 0; j < 4; j++) {
+                const int s = min(s0 + j, g.splits - 1);
+                pair[j] = __ldcg(reinterpret_cast<const float2*>(ml + static_cast<size_t>(s) * kAttnQRows * 2));
+                const float4* src = reinterpret_cast<const float4*>(po + static_cast<size_t>(s) * kAttnQRows * g.head_dim);
+#pragma unroll
+                for (int q = 0; q < 4; q++) x[j][q] = __ldcg(src + q);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float w = s0 + j < g.splits ? exp2f(pair[j].x - ref) : 0.f;     // 0 for a fully masked split
+                denom += w * pair[j].y;
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    acc[4 * q] += w * x[j][q].x; acc[4 * q + 1] += w * x[j][q].y;
+                    acc[4 * q + 2] += w * x[j][q].z; acc[4 * q + 3] += w * x[j][q].w;
+                }
             }
         }
         const float inv = denom > 0.f ? 1.f / denom : 0.f;

@@ -12,18 +12,45 @@
 namespace pi0 {
 
 // Whole warp 0: the dependency wait is lane-parallel, lane 0 issues the copies.
+//
+// Weights never depend on another stage, so for the first tile of an instruction the B tiles and B scales of the
+// first slots are requested BEFORE the dependency wait (their bytes are announced with expect_tx without an
+// arrival); when the producers are done only the activation half (A, A scales) is still to be fetched.
 __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
                                               int stage_index, int first, int count, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
     const int lane = lane_id();
     const int chunks = (g.k_groups + 3) >> 2;                        // 256-wide K chunks
     const int slots = (chunks + kChunks - 1) / kChunks;
-    const uint32_t ab_bytes = static_cast<uint32_t>(kChunks) * 128u * static_cast<uint32_t>(g.a_box_rows + g.block_n);
+    const uint32_t a_bytes = static_cast<uint32_t>(kChunks) * 128u * static_cast<uint32_t>(g.a_box_rows);
+    const uint32_t b_bytes = static_cast<uint32_t>(kChunks) * 128u * static_cast<uint32_t>(g.block_n);
     int current_band = -1;
     for (int t = first; t < first + count; ++t) {
         const int m_tile = t / g.n_tiles, n_tile = t - m_tile * g.n_tiles;
         const int band = tile_band(st, t);
+        const int sfb_tile = (n_tile * g.block_n) >> 7;
+        int early = 0;                                               // slots whose weight half is already in flight
+        int alive = 1;
         if (band != current_band) {
+            if (t == first) {
+                if (lane == 0) {
+                    early = min(slots, kStages);
+                    for (int ks = 0; ks < early; ++ks) {
+                        const uint32_t it = ps.prod_it + ks, s = it % kStages, phase = (it / kStages) & 1u;
+                        if (!mbar_wait(prog, ctl, &ctl->empty[s], phase ^ 1u, stage_index)) { alive = 0; break; }
+                        const int groups = min(4 * kChunks, g.k_groups - ks * 4 * kChunks);
+                        uint8_t* slot = data + s * kStageBytes;
+                        mbar_expect_tx_only(&ctl->full[s], b_bytes + groups * 512u);
+                        if (g.b_tiled) tma_load_2d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, (n_tile * chunks + ks * kChunks) * g.block_n);
+                        else tma_load_3d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, n_tile * g.block_n, ks * kChunks);
+                        bulk_load(slot + kSlotSfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
+                                  groups * 512u, &ctl->full[s]);
+                    }
+                }
+                early = __shfl_sync(0xffffffffu, early, 0);
+                alive = __shfl_sync(0xffffffffu, alive, 0);
+                if (!alive) return;
+            }
             if (!warp_wait_sources(prog, ctl, st, stage_index, band, band)) return;
             if (lane == 0) {
                 fence_proxy_async_global();
@@ -31,25 +58,26 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
             }
             current_band = band;
         }
-        int alive = 1;
         if (lane == 0) {
-            const int sfb_tile = (n_tile * g.block_n) >> 7;
             for (int ks = 0; ks < slots; ++ks) {
                 const uint32_t s = ps.prod_it % kStages, phase = (ps.prod_it / kStages) & 1u;
-                if (!mbar_wait(prog, ctl, &ctl->empty[s], phase ^ 1u, stage_index)) { alive = 0; break; }
                 const int groups = min(4 * kChunks, g.k_groups - ks * 4 * kChunks);
                 uint8_t* slot = data + s * kStageBytes;
+                const bool weights_issued = ks < early;
+                if (!weights_issued && !mbar_wait(prog, ctl, &ctl->empty[s], phase ^ 1u, stage_index)) { alive = 0; break; }
                 // Boxes always deliver kChunks chunks (beyond K the copy engine fills zeros or, inside a padded
                 // allocation, bytes that no MMA reads).  a_box_rows < 128 (few logical rows): only the rows that
                 // exist are copied; the MMA still reads 128 rows, the rest lands in accumulator rows never stored.
-                mbar_expect_tx(&ctl->full[s], ab_bytes + 2u * groups * 512u);
+                mbar_expect_tx(&ctl->full[s], a_bytes + groups * 512u + (weights_issued ? 0u : b_bytes + groups * 512u));
                 tma_load_3d(slot + kSlotA, g.tmap_a, &ctl->full[s], 0, m_tile * 128, ks * kChunks);
-                if (g.b_tiled) tma_load_2d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, (n_tile * chunks + ks * kChunks) * g.block_n);
-                else tma_load_3d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, n_tile * g.block_n, ks * kChunks);
                 bulk_load(slot + kSlotSfa, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4 * kChunks) * 512, groups * 512u,
                           &ctl->full[s]);
-                bulk_load(slot + kSlotSfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512, groups * 512u,
-                          &ctl->full[s]);
+                if (!weights_issued) {
+                    if (g.b_tiled) tma_load_2d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, (n_tile * chunks + ks * kChunks) * g.block_n);
+                    else tma_load_3d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, n_tile * g.block_n, ks * kChunks);
+                    bulk_load(slot + kSlotSfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
+                              groups * 512u, &ctl->full[s]);
+                }
                 ps.prod_it++;
             }
         }
@@ -111,7 +139,7 @@ __device__ __forceinline__ float2 unpack_bf16x2(uint32_t u) {
 __device__ __forceinline__ float gelu_sigmoid(float x) {
     // x * sigmoid(2u), u = sqrt(2/pi)(x + 0.044715 x^3): identical to the tanh form.
     float z = 1.5957691216057308f * x * (1.f + 0.044715f * x * x);
-    return x / (1.f + __expf(-z));
+    return __fdividef(x, 1.f + __expf(-z));
 }
 
 // One 32-column chunk of one accumulator row (thread == row).
