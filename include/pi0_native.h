@@ -95,6 +95,9 @@ int attention_resources(int* values, int count);
 /* Split the key range into `splits` parts; partial (o, m, l) go to library-owned scratch and a merge stage
  * produces the output. */
 int configure_attention_splits(void* handle, int splits);
+/* extension: with splits > 1, let the tile that finishes last for a head merge the partials itself instead of running
+ * a separate merge stage (call after configure_attention_splits and configure_attention_fp4_output). */
+int configure_attention_fused_merge(void* handle, int enable);
 /* Read keys/values from a KV cache [rows, head_dim] (BF16) instead of k/v; rows = total keys visible. */
 int configure_attention_cache(void* handle, const void* cache_k, const void* cache_v, int rows, int prefix_rows);
 /* extension: also quantise the output rows to NVFP4 (head_dim 256 only). */

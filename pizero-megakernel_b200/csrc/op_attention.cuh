@@ -266,27 +266,13 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
     }
 }
 
-__device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
-                                                 int stage_index, int first, int count) {
-    const AttnParams& a = st.p.attn;
-    for (int t = first; t < first + count; ++t) {
-        if (a.head_dim > 128) attn_tile<256>(a, t, data);
-        else attn_tile<80>(a, t, data);
-        cta_publish_tile(prog, st, t);
-    }
-}
-
 // Split-KV merge: out = sum_s 2^(m_s - M) o_s / sum_s 2^(m_s - M) l_s.  A tile is 16 query rows of one head: one
 // (row, 16-column block) per thread, all partial loads of a thread independent of each other.
 constexpr int kMergeRows = 16;
 
-__device__ __forceinline__ void merge_tile(const MergeParams& g, int tile) {
-    const int bpr = g.head_dim / 16;
-    const int chunks = (g.nq + kMergeRows - 1) / kMergeRows;
-    const int head = tile / chunks, r0 = (tile - head * chunks) * kMergeRows;
-    const int rows = min(kMergeRows, g.nq - r0);
-    for (int i = threadIdx.x; i < rows * bpr; i += kThreads) {
-        const int r = r0 + i / bpr, b = i % bpr;
+// One (query row, 16-column block) of one head.
+__device__ __forceinline__ void merge_item(const MergeParams& g, int head, int r, int b) {
+    {
         const float* ml = g.partial_ml + (static_cast<size_t>(head) * g.splits * kAttnQRows + r) * 2;
         const float* po = g.partial_o + (static_cast<size_t>(head) * g.splits * kAttnQRows + r) * g.head_dim + b * 16;
         float big = -INFINITY;
@@ -345,10 +331,64 @@ __device__ __forceinline__ void merge_tile(const MergeParams& g, int tile) {
     }
 }
 
+__device__ __forceinline__ void merge_tile(const MergeParams& g, int tile) {
+    const int bpr = g.head_dim / 16;
+    const int chunks = (g.nq + kMergeRows - 1) / kMergeRows;
+    const int head = tile / chunks, r0 = (tile - head * chunks) * kMergeRows;
+    const int rows = min(kMergeRows, g.nq - r0);
+    for (int i = threadIdx.x; i < rows * bpr; i += kThreads) merge_item(g, head, r0 + i / bpr, i % bpr);
+}
+
 __device__ __forceinline__ void merge_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage_index,
                                                   int first, int count) {
     for (int t = first; t < first + count; ++t) {
         merge_tile(st.p.merge, t);
+        cta_publish_tile(prog, st, t);
+    }
+}
+
+// One attention instruction.  With a fused split-KV merge the tiles of a head (one per split, resident on different
+// SMs at the same time) meet on a per-head ticket counter that grows by `splits` per launch; once all partials of
+// the head are published, every tile merges its share of the query rows (row % splits == split), so the merge
+// costs neither a stage of its own nor a serial tail on one SM.
+__device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
+                                                 int stage_index, int first, int count) {
+    const AttnParams& a = st.p.attn;
+    for (int t = first; t < first + count; ++t) {
+        if (a.head_dim > 128) attn_tile<256>(a, t, data);
+        else attn_tile<80>(a, t, data);
+        if (a.splits > 1 && a.fused_merge) {
+            const int split = t % a.splits, head = (t / a.splits) % a.heads;
+            __threadfence();                                   // this tile's partials before its ticket
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const unsigned int target = static_cast<unsigned int>(a.splits) * prog.epoch;
+                red_release_add(a.tickets + head, 1u);
+                int ok = 1;
+                const unsigned long long start = global_ns();
+                for (uint32_t spin = 1; ld_acquire(a.tickets + head) < target; ++spin) {
+                    __nanosleep(20);
+                    if ((spin & 63u) == 0u && (ctl->abort || global_ns() - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort))) {
+                        report(prog, 1, stage_index, head, ld_acquire(a.tickets + head), target);
+                        ctl->abort = 1;
+                        ok = 0;
+                        break;
+                    }
+                }
+                ctl->flag = ok;
+            }
+            __syncthreads();
+            if (!ctl->flag) return;                            // uniform: the abort flag is set, the caller leaves the loop
+            MergeParams g;
+            g.partial_o = a.partial_o; g.partial_ml = a.partial_ml;
+            g.heads = a.heads; g.nq = a.nq; g.head_dim = a.head_dim; g.splits = a.splits;
+            g.out = a.out; g.ldo = a.ldo;
+            g.out_fp4 = a.out_fp4; g.out_scales = a.out_scales; g.out_blocks = a.out_blocks;
+            g.out_inv_gs = a.out_inv_gs; g.ld_fp4 = a.ld_fp4;
+            const int bpr = a.head_dim / 16;
+            const int my_rows = (a.nq - split + a.splits - 1) / a.splits;          // rows split, split+splits, ...
+            for (int i = threadIdx.x; i < my_rows * bpr; i += kThreads) merge_item(g, head, split + (i / bpr) * a.splits, i % bpr);
+        }
         cta_publish_tile(prog, st, t);
     }
 }

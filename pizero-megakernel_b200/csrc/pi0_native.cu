@@ -176,6 +176,10 @@ int build_program(Program** out, int device, const std::vector<StageDesc>& stage
         d.counter_base = counters;
         counters += d.bands;
     }
+    for (auto& d : prog->stages) {                     // auxiliary counters (nobody waits on them: expected stays 0)
+        d.aux_base = counters;
+        counters += d.aux_count;
+    }
     prog->expected.assign(counters, 0);
     for (auto& d : prog->stages)
         for (int t = 0; t < d.tiles; t++) prog->expected[d.counter_base + std::min(t / d.band_div, d.bands - 1)] += d.units_per_tile;
@@ -197,6 +201,8 @@ int build_program(Program** out, int device, const std::vector<StageDesc>& stage
             if (s < 0 || s >= static_cast<int>(prog->stages.size()) || s < last) return cudaErrorInvalidValue;
             if (ins[3] < 1 || ins[2] < 0 || ins[2] + ins[3] > prog->stages[s].tiles) return cudaErrorInvalidValue;
             for (int t = ins[2]; t < ins[2] + ins[3]; t++) cover[s][t]++;
+            // tiles of a fused split-KV attention wait for each other: each needs a worker of its own
+            if (prog->stages[s].kind == OP_ATTN && prog->stages[s].p.attn.fused_merge && ins[3] != 1) return cudaErrorInvalidValue;
             last = s;
         }
     }
@@ -226,7 +232,11 @@ int build_program(Program** out, int device, const std::vector<StageDesc>& stage
     if (e == cudaSuccess) e = cudaMalloc(&prog->d_counters, sizeof(unsigned int) * std::max(counters, 1));
     if (e == cudaSuccess) e = cudaMalloc(&prog->d_expected, sizeof(unsigned int) * std::max(counters, 1));
     if (e == cudaSuccess) e = cudaMalloc(&prog->d_status, sizeof(VmStatus));
-    if (e == cudaSuccess) e = cudaMemcpy(prog->d_stages, prog->stages.data(), sizeof(StageDesc) * prog->stages.size(), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) {
+        for (auto& d : prog->stages)
+            if (d.kind == OP_ATTN && d.aux_count) d.p.attn.tickets = prog->d_counters + d.aux_base;
+        e = cudaMemcpy(prog->d_stages, prog->stages.data(), sizeof(StageDesc) * prog->stages.size(), cudaMemcpyHostToDevice);
+    }
     if (e == cudaSuccess) e = cudaMemcpy(prog->d_code, code4.data(), sizeof(int4) * static_cast<size_t>(workers) * length, cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemset(prog->d_counters, 0, sizeof(unsigned int) * std::max(counters, 1));
     if (e == cudaSuccess && counters) e = cudaMemcpy(prog->d_expected, prog->expected.data(), sizeof(unsigned int) * counters, cudaMemcpyHostToDevice);
@@ -351,7 +361,7 @@ int solo_program(Op* op) {
     op->solo = nullptr;
     std::vector<StageDesc> stages{op->desc};
     std::vector<std::pair<int, int>> work{{op->desc.tiles, op->cost}};
-    if (op->merge) {
+    if (op->merge && !op->desc.p.attn.fused_merge) {
         StageDesc m = op->merge->desc;
         m.src[0] = 0;
         m.src_mode[0] = SRC_ALL_BANDS;
@@ -654,8 +664,10 @@ extern "C" int configure_attention_splits(void* handle, int splits) {
     if (op->merge) { free_op(op->merge); op->merge = nullptr; }
     cudaFree(op->partial_o); op->partial_o = nullptr;
     cudaFree(op->partial_ml); op->partial_ml = nullptr;
-    void* final_out = a.splits > 1 && false ? nullptr : a.out;
+    void* final_out = a.out;
     a.splits = splits;
+    a.fused_merge = 0;
+    op->desc.aux_count = 0;
     if (splits > 1) {
         const size_t tasks = static_cast<size_t>(a.heads) * splits;
         cudaError_t e = cudaMalloc(&op->partial_o, tasks * kAttnQRows * a.head_dim * sizeof(float));
@@ -679,6 +691,16 @@ extern "C" int configure_attention_splits(void* handle, int splits) {
         op->merge = mg;
     }
     attention_geometry(op);
+    return cudaSuccess;
+}
+extern "C" int configure_attention_fused_merge(void* handle, int enable) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN || (enable != 0 && enable != 1)) return cudaErrorInvalidValue;
+    AttnParams& a = op->desc.p.attn;
+    if (enable && a.splits < 2) return cudaErrorInvalidValue;
+    a.fused_merge = enable;
+    op->desc.aux_count = enable ? a.heads : 0;
+    op->solo_dirty = true;
     return cudaSuccess;
 }
 extern "C" int configure_attention_cache(void* handle, const void* cache_k, const void* cache_v, int rows, int prefix_rows) {

@@ -46,7 +46,7 @@ struct Ctl {
     uint32_t tmem_base;
     volatile int abort;          // CTA-local copy of the abort decision
     volatile int dep_ok;         // broadcast slot for CTA-wide operators
-    int pad;
+    volatile int flag;           // second broadcast slot (last-arriver decisions)
     Slot slot[kRing];
 };
 static_assert(sizeof(Ctl) <= kCtlBytes, "control block too large");

@@ -109,6 +109,10 @@ struct AttnParams {
     int out_blocks;
     float out_inv_gs;
     int ld_fp4;
+    // splits > 1 with the merge fused into the last-arriving tile of each head: per-head arrival tickets (program
+    // counters, reset with them); 0 / null selects the separate OP_MERGE stage
+    unsigned int* tickets;
+    int fused_merge;
 };
 
 struct MergeParams {
@@ -171,6 +175,7 @@ struct alignas(16) StageDesc {
     int band_div;                // band(tile) = min(tile / band_div, bands - 1)
     int src[kMaxSources];
     int src_mode[kMaxSources];
+    int aux_base, aux_count;     // extra program counters owned by the stage (attention: one ticket per head)
     int units_per_tile;          // counter increments one finished tile contributes (GEMM: one per epilogue warp)
     // Filled by the host when the program is built, so a consumer polls counters without touching its producers'
     // descriptors: first counter, band count and the per-launch contribution of a full / of the last band.

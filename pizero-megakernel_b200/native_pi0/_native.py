@@ -67,6 +67,7 @@ _SIGNATURES = {
     "attention_resources": [C.POINTER(_I), _I],
     "configure_attention_splits": [_P, _I],
     "configure_attention_cache": [_P, _P, _P, _I, _I],
+    "configure_attention_fused_merge": [_P, _I],
     "configure_attention_fp4_output": [_P, _P, _P, _I, _I, _F],
     "attention_merge_handle": [_P, C.POINTER(_P)],
     "create_patch_embed": [C.POINTER(_P)] + [_P] * 5 + [_I] * 3,

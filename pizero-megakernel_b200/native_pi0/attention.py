@@ -15,7 +15,7 @@ from native_pi0 import _native
 class ResidentAttention:
     def __init__(self, library, q, k, v, *, workers=16, scale=None, prefix=None, splits=1, kv_cache=None,
                  cached_prefix_rows=0, output=None, q_bias=None, k_bias=None, v_bias=None, q_rope=None,
-                 k_rope=None, mask=None, fp4_output=None):
+                 k_rope=None, mask=None, fp4_output=None, fused_merge=False):
         if any(x is not None for x in (q_bias, k_bias, v_bias, q_rope, k_rope, mask)):
             raise ValueError("Biases, RoPE tables and boolean masks are fused elsewhere in the NVFP4 engine")
         for t in (q, k, v):
@@ -58,6 +58,8 @@ class ResidentAttention:
                         "Native attention FP4 output")
                 if splits != 1:
                     _native.check(self.library.configure_attention_splits(self.handle, int(splits)), "Native attention splits")
+                    if fused_merge:
+                        _native.check(self.library.configure_attention_fused_merge(self.handle, 1), "Native attention fused merge")
             except Exception:
                 self.close()
                 raise

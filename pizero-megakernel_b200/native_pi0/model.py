@@ -341,13 +341,10 @@ class NativePi0:
                                                          a2.k // 16, a2.global_scale), f"{name}.attention")
         att_sources = [(s_qkv, ALL)] + ([(prefix_cache_stage, ALL)] if prefix_cache_stage is not None else [])
         if splits > 1:
+            # split-KV: the last tile to finish for a head merges the partials (no separate merge stage)
             _native.check(lib.configure_attention_splits(h, splits), f"{name}.attention")
-            s_part = self.add(1, h, f"{name}.attention", att_sources)
-            mh = C.c_void_p()
-            _native.check(lib.attention_merge_handle(h, C.byref(mh)), f"{name}.merge")
-            s_att = self.add(4, mh, f"{name}.merge", [(s_part, ALL)])
-        else:
-            s_att = self.add(1, h, f"{name}.attention", att_sources)
+            _native.check(lib.configure_attention_fused_merge(h, 1), f"{name}.attention")
+        s_att = self.add(1, h, f"{name}.attention", att_sources)
         wo = self.cached(p + "o", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=block_n))
         s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=block_n)
         g2 = self.cached(p + "g2", lambda: (1.0 + sd[p + "post_attention_layernorm.weight"].float()).contiguous())

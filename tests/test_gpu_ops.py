@@ -281,6 +281,14 @@ def test_attention(b, nq, nk, h, hk, hd, prefix, splits):
     assert np.isfinite(got).all()
     assert relrms(got, want) <= 1e-2
     np.testing.assert_array_equal(got, again)
+    if splits > 1:
+        # merge fused into the last-arriving tile of each head: same bits as the separate merge stage, launch after launch
+        with ResidentAttention(None, q, k, v, workers=64, prefix=prefix, splits=splits, fused_merge=True) as op:
+            for _ in range(3):
+                op.output.fill_(float("nan"))
+                fused = op.forward().float().cpu().numpy()
+                assert op.status()["code"] == 0
+                np.testing.assert_array_equal(fused, got)
     if prefix is not None and nq > 1:
         # the state query must not depend on keys beyond the prefix boundary
         k2, v2 = k.clone(), v.clone()
