@@ -53,7 +53,7 @@ __device__ __forceinline__ void attn_load_rows(__nv_bfloat16* dst, const __nv_bf
 }
 
 template <int HD>
-__device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
+__device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data, long long* stamp) {
     constexpr int LD = HD + 8;
     constexpr int KSTEPS = HD / 16;           // along the head dimension
     constexpr int ONT = HD / 8;               // output n-tiles
@@ -91,9 +91,14 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
     for (int j = 0; j < ONT; j++) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const float sl2 = a.scale * 1.4426950408889634f;
-    const bool warp_active = warp * 16 < q_valid;
-    const int row_a = warp * 16 + (lane >> 2);            // local query rows of this thread: row_a, row_a + 8
-    const __nv_bfloat16* q_lane = sQ + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + (lane >> 4) * 8;
+    // At most 64 query rows: warps 0-3 and 4-7 own the same four 16-row blocks and take the first and the second
+    // 32 keys of every chunk; the two halves are combined through shared memory after the last chunk.
+    const bool paired = q_valid <= 64;
+    const int rb = paired ? (warp & 3) : warp;            // 16-row block of this warp
+    const int khalf = paired ? (warp >> 2) : -1;          // the half of each chunk this warp takes (-1: both)
+    const bool warp_active = rb * 16 < q_valid;
+    const int row_a = rb * 16 + (lane >> 2);              // local query rows of this thread: row_a, row_a + 8
+    const __nv_bfloat16* q_lane = sQ + (rb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + (lane >> 4) * 8;
 
     for (int c = 0; c < nchunks; ++c) {
         const int buf = c & 1;
@@ -107,6 +112,7 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
             cp_async_wait<0>();
         }
         __syncthreads();
+        if (stamp && c == 0 && threadIdx.x == 0) stamp[4] = static_cast<long long>(global_ns());
         if (warp_active) {
             const __nv_bfloat16* kbuf = sK + buf * kAttnChunk * LD;
             const __nv_bfloat16* vbuf = sV + buf * kAttnChunk * LD;
@@ -114,6 +120,7 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
 #pragma unroll
             for (int half = 0; half < 2; ++half) {
                 if (key_base + half * 32 >= k_end) break;
+                if (khalf >= 0 && half != khalf) continue;
                 float s[4][4];
 #pragma unroll
                 for (int j = 0; j < 4; j++) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f; }
@@ -189,6 +196,7 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
         __syncthreads();
     }
     if (nchunks == 0) { cp_async_wait<0>(); __syncthreads(); }
+    if (stamp && threadIdx.x == 0) stamp[5] = static_cast<long long>(global_ns());
 
     // quad-reduce the row sums
 #pragma unroll
@@ -197,8 +205,42 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
 
+    bool writer = warp_active;
+    if (paired) {
+        // the loop's last barrier has passed: K and V buffers are free
+        float4* xo = reinterpret_cast<float4*>(sK);                       // [4 blocks][ONT][32 lanes]
+        float4* xml = reinterpret_cast<float4*>(sV);                      // [4 blocks][32 lanes]: m0, m1, l0, l1
+        if (warp_active && khalf == 1) {
+#pragma unroll
+            for (int j = 0; j < ONT; j++) xo[(rb * ONT + j) * 32 + lane] = make_float4(o[j][0], o[j][1], o[j][2], o[j][3]);
+            xml[rb * 32 + lane] = make_float4(m_run[0], m_run[1], l_run[0], l_run[1]);
+        }
+        __syncthreads();
+        writer = warp_active && khalf == 0;
+        if (writer) {
+            const float4 other = xml[rb * 32 + lane];
+            const float om[2] = {other.x, other.y}, ol[2] = {other.z, other.w};
+            float ca[2], cb[2];
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const float m_new = fmaxf(m_run[r], om[r]);
+                const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                ca[r] = exp2f(m_run[r] - m_use);
+                cb[r] = exp2f(om[r] - m_use);
+                l_run[r] = l_run[r] * ca[r] + ol[r] * cb[r];
+                m_run[r] = m_new;
+            }
+#pragma unroll
+            for (int j = 0; j < ONT; j++) {
+                const float4 x = xo[(rb * ONT + j) * 32 + lane];
+                o[j][0] = o[j][0] * ca[0] + x.x * cb[0]; o[j][1] = o[j][1] * ca[0] + x.y * cb[0];
+                o[j][2] = o[j][2] * ca[1] + x.z * cb[1]; o[j][3] = o[j][3] * ca[1] + x.w * cb[1];
+            }
+        }
+    }
+
     if (a.splits > 1) {
-        if (warp_active) {
+        if (writer) {
             float* po = a.partial_o + static_cast<size_t>(tile) * kAttnQRows * a.head_dim;
             float* pml = a.partial_ml + static_cast<size_t>(tile) * kAttnQRows * 2;
 #pragma unroll
@@ -222,7 +264,7 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
     }
 
     // normalise, round to BF16, stage the tile in the (now free) Q rows of this warp
-    if (warp_active) {
+    if (writer) {
 #pragma unroll
         for (int r = 0; r < 2; r++) {
             const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
@@ -270,11 +312,13 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data) {
 // (row, 16-column block) per thread, all partial loads of a thread independent of each other.
 constexpr int kMergeRows = 16;
 
-// One (query row, 16-column block) of one head.
-__device__ __forceinline__ void merge_item(const MergeParams& g, int head, int r, int b) {
+// One (query row, 16-column block) of one group (a head of one 128-query tile); r counts rows inside the query tile.
+__device__ __forceinline__ void merge_item(const MergeParams& g, int group, int r, int b) {
     {
-        const float* ml = g.partial_ml + (static_cast<size_t>(head) * g.splits * kAttnQRows + r) * 2;
-        const float* po = g.partial_o + (static_cast<size_t>(head) * g.splits * kAttnQRows + r) * g.head_dim + b * 16;
+        const int head = group % g.heads;
+        const int grow = (group / g.heads) * kAttnQRows + r;          // row in the output
+        const float* ml = g.partial_ml + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * 2;
+        const float* po = g.partial_o + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * g.head_dim + b * 16;
         float big = -INFINITY;
 #pragma unroll 8
         for (int s = 0; s < g.splits; s++) big = fmaxf(big, __ldcg(ml + static_cast<size_t>(s) * kAttnQRows * 2));
@@ -316,7 +360,7 @@ __device__ __forceinline__ void merge_item(const MergeParams& g, int head, int r
             uint32_t w[8];
 #pragma unroll
             for (int e = 0; e < 8; e++) w[e] = pack2_bf16(v[2 * e], v[2 * e + 1]);
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(r) * g.ldo + col);
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(grow) * g.ldo + col);
             dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
             dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
         }
@@ -325,18 +369,19 @@ __device__ __forceinline__ void merge_item(const MergeParams& g, int head, int r
             for (int e = 0; e < 16; e++) v[e] *= g.out_inv_gs;
             uint32_t code;
             uint2 bytes = quantize_block16(v, 0, code);
-            *reinterpret_cast<uint2*>(g.out_fp4 + static_cast<size_t>(r) * g.ld_fp4 + (col >> 1)) = bytes;
-            g.out_scales[scale_offset(r, col >> 4, g.out_blocks)] = static_cast<uint8_t>(code);
+            *reinterpret_cast<uint2*>(g.out_fp4 + static_cast<size_t>(grow) * g.ld_fp4 + (col >> 1)) = bytes;
+            g.out_scales[scale_offset(grow, col >> 4, g.out_blocks)] = static_cast<uint8_t>(code);
         }
     }
 }
 
 __device__ __forceinline__ void merge_tile(const MergeParams& g, int tile) {
     const int bpr = g.head_dim / 16;
-    const int chunks = (g.nq + kMergeRows - 1) / kMergeRows;
-    const int head = tile / chunks, r0 = (tile - head * chunks) * kMergeRows;
-    const int rows = min(kMergeRows, g.nq - r0);
-    for (int i = threadIdx.x; i < rows * bpr; i += kThreads) merge_item(g, head, r0 + i / bpr, i % bpr);
+    const int chunks = (min(g.nq, kAttnQRows) + kMergeRows - 1) / kMergeRows;
+    const int group = tile / chunks, r0 = (tile - group * chunks) * kMergeRows;
+    const int q_valid = min(kAttnQRows, g.nq - (group / g.heads) * kAttnQRows);
+    const int rows = min(kMergeRows, q_valid - r0);
+    for (int i = threadIdx.x; i < rows * bpr; i += kThreads) merge_item(g, group, r0 + i / bpr, i % bpr);
 }
 
 __device__ __forceinline__ void merge_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage_index,
@@ -347,29 +392,30 @@ __device__ __forceinline__ void merge_instruction(const VmProgram& prog, Ctl* ct
     }
 }
 
-// One attention instruction.  With a fused split-KV merge the tiles of a head (one per split, resident on different
-// SMs at the same time) meet on a per-head ticket counter that grows by `splits` per launch; once all partials of
+// One attention instruction.  With a fused split-KV merge the tiles of a head of one query tile (one per split,
+// resident on different SMs at the same time) meet on a per-group ticket counter that grows by `splits` per launch; once all partials of
 // the head are published, every tile merges its share of the query rows (row % splits == split), so the merge
 // costs neither a stage of its own nor a serial tail on one SM.
 __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
-                                                 int stage_index, int first, int count) {
+                                                 int stage_index, int first, int count, long long* stamp) {
     const AttnParams& a = st.p.attn;
     for (int t = first; t < first + count; ++t) {
-        if (a.head_dim > 128) attn_tile<256>(a, t, data);
-        else attn_tile<80>(a, t, data);
+        long long* stamp_t = t == first ? stamp : nullptr;
+        if (a.head_dim > 128) attn_tile<256>(a, t, data, stamp_t);
+        else attn_tile<80>(a, t, data, stamp_t);
         if (a.splits > 1 && a.fused_merge) {
-            const int split = t % a.splits, head = (t / a.splits) % a.heads;
+            const int split = t % a.splits, group = t / a.splits;         // group: one head of one 128-query tile
             __threadfence();                                   // this tile's partials before its ticket
             __syncthreads();
             if (threadIdx.x == 0) {
                 const unsigned int target = static_cast<unsigned int>(a.splits) * prog.epoch;
-                red_release_add(a.tickets + head, 1u);
+                red_release_add(a.tickets + group, 1u);
                 int ok = 1;
                 const unsigned long long start = global_ns();
-                for (uint32_t spin = 1; ld_acquire(a.tickets + head) < target; ++spin) {
+                for (uint32_t spin = 1; ld_acquire(a.tickets + group) < target; ++spin) {
                     __nanosleep(20);
                     if ((spin & 63u) == 0u && (ctl->abort || global_ns() - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort))) {
-                        report(prog, 1, stage_index, head, ld_acquire(a.tickets + head), target);
+                        report(prog, 1, stage_index, group, ld_acquire(a.tickets + group), target);
                         ctl->abort = 1;
                         ok = 0;
                         break;
@@ -379,6 +425,7 @@ __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl
             }
             __syncthreads();
             if (!ctl->flag) return;                            // uniform: the abort flag is set, the caller leaves the loop
+            if (stamp_t && threadIdx.x == 0) stamp_t[6] = static_cast<long long>(global_ns());
             MergeParams g;
             g.partial_o = a.partial_o; g.partial_ml = a.partial_ml;
             g.heads = a.heads; g.nq = a.nq; g.head_dim = a.head_dim; g.splits = a.splits;
@@ -386,8 +433,10 @@ __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl
             g.out_fp4 = a.out_fp4; g.out_scales = a.out_scales; g.out_blocks = a.out_blocks;
             g.out_inv_gs = a.out_inv_gs; g.ld_fp4 = a.ld_fp4;
             const int bpr = a.head_dim / 16;
-            const int my_rows = (a.nq - split + a.splits - 1) / a.splits;          // rows split, split+splits, ...
-            for (int i = threadIdx.x; i < my_rows * bpr; i += kThreads) merge_item(g, head, split + (i / bpr) * a.splits, i % bpr);
+            const int q_valid = min(kAttnQRows, a.nq - (group / a.heads) * kAttnQRows);
+            const int my_rows = (q_valid - split + a.splits - 1) / a.splits;       // rows split, split+splits, ...
+            for (int i = threadIdx.x; i < my_rows * bpr; i += kThreads) merge_item(g, group, split + (i / bpr) * a.splits, i % bpr);
+            if (stamp_t && threadIdx.x == 0) stamp_t[7] = static_cast<long long>(global_ns());
         }
         cta_publish_tile(prog, st, t);
     }

@@ -15,12 +15,26 @@ __device__ __forceinline__ void patch_tile(const PatchParams& p, const float* im
     float* sp = reinterpret_cast<float*>(data);                    // [16][588]
     const int ntiles = (p.width + kPatchCols - 1) / kPatchCols;
     const int tt = tile / ntiles, nt = tile - tt * ntiles;
-    for (int i = threadIdx.x; i < kPatchTokens * kPatchK; i += kThreads) {
-        const int tok = i / kPatchK, k = i - tok * kPatchK;
-        const int dy = k / 42, rem = k - dy * 42;
-        const int t = tt * kPatchTokens + tok;
-        const int view = t >> 8, pidx = t & 255, py = pidx >> 4, px = pidx & 15;
-        sp[i] = images[((static_cast<size_t>(view) * 224 + py * 14 + dy) * 224 + px * 14) * 3 + rem];
+    // gather the 16 patches: loads are issued in batches of 8 per thread before any is stored
+    for (int base = 0; base < kPatchTokens * kPatchK; base += kThreads * 8) {
+        float v[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int i = base + j * kThreads + threadIdx.x;
+            v[j] = 0.f;
+            if (i < kPatchTokens * kPatchK) {
+                const int tok = i / kPatchK, k = i - tok * kPatchK;
+                const int dy = k / 42, rem = k - dy * 42;
+                const int t = tt * kPatchTokens + tok;
+                const int view = t >> 8, pidx = t & 255, py = pidx >> 4, px = pidx & 15;
+                v[j] = __ldg(images + ((static_cast<size_t>(view) * 224 + py * 14 + dy) * 224 + px * 14) * 3 + rem);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int i = base + j * kThreads + threadIdx.x;
+            if (i < kPatchTokens * kPatchK) sp[i] = v[j];
+        }
     }
     __syncthreads();
     const int n = nt * kPatchCols + threadIdx.x;
@@ -28,10 +42,15 @@ __device__ __forceinline__ void patch_tile(const PatchParams& p, const float* im
         float acc[kPatchTokens];
 #pragma unroll
         for (int i = 0; i < kPatchTokens; i++) acc[i] = 0.f;
-        for (int k = 0; k < kPatchK; k++) {
-            const float w = __ldg(p.weight + static_cast<size_t>(k) * p.width + n);
+        for (int k0 = 0; k0 < kPatchK; k0 += 4) {           // 588 = 4 * 147: four weight loads in flight
+            float w[4];
 #pragma unroll
-            for (int i = 0; i < kPatchTokens; i++) acc[i] = fmaf(sp[i * kPatchK + k], w, acc[i]);
+            for (int j = 0; j < 4; j++) w[j] = __ldg(p.weight + static_cast<size_t>(k0 + j) * p.width + n);
+#pragma unroll
+            for (int i = 0; i < kPatchTokens; i++) {
+                const float4 x = *reinterpret_cast<const float4*>(sp + i * kPatchK + k0);
+                acc[i] = fmaf(x.w, w[3], fmaf(x.z, w[2], fmaf(x.y, w[1], fmaf(x.x, w[0], acc[i]))));
+            }
         }
         const float b = p.bias[n];
 #pragma unroll
@@ -91,36 +110,65 @@ __device__ __forceinline__ void linear32_tile(const Linear32Params& p, const voi
         for (int kc = 0; kc < p.k; kc += kLinChunk) {
             const int kw4 = min(kLinChunk, p.k - kc) >> 2;
             __syncthreads();
-            for (int i = threadIdx.x; i < kLinRows * kw4; i += kThreads) {
+            // stage the chunk: all loads of a thread (8 of x, 2 of w for a full chunk) are issued before any store
+            constexpr int kXLoads = kLinRows * (kLinChunk / 4) / kThreads, kWLoads = kLinCols * (kLinChunk / 4) / kThreads;
+            float4 xv[kXLoads], wv[kWLoads];
+#pragma unroll
+            for (int j = 0; j < kXLoads; j++) {
+                const int i = j * kThreads + threadIdx.x;
                 const int r = i / kw4, c = i - r * kw4;
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (r0 + r < p.rows) {
+                xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < kLinRows * kw4 && r0 + r < p.rows) {
                     const size_t off = static_cast<size_t>(r0 + r + p.x_row_offset) * p.ldx + kc + c * 4;
                     if (p.x_bf16) {
                         uint2 u = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(xbase) + off));
                         float2 lo = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.x));
                         float2 hi = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.y));
-                        v = make_float4(lo.x, lo.y, hi.x, hi.y);
+                        xv[j] = make_float4(lo.x, lo.y, hi.x, hi.y);
                     } else {
-                        v = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(xbase) + off));
+                        xv[j] = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(xbase) + off));
                     }
                 }
-                xs[r * (kLinLd / 4) + c] = v;
             }
-            for (int i = threadIdx.x; i < kLinCols * kw4; i += kThreads) {
+#pragma unroll
+            for (int j = 0; j < kWLoads; j++) {
+                const int i = j * kThreads + threadIdx.x;
                 const int r = i / kw4, c = i - r * kw4;
                 const int col = tile * kLinCols + r;
-                ws[r * (kLinLd / 4) + c] = col < p.n ? __ldg(reinterpret_cast<const float4*>(p.w + static_cast<size_t>(col) * p.k + kc) + c)
-                                                     : make_float4(0.f, 0.f, 0.f, 0.f);
+                wv[j] = (i < kLinCols * kw4 && col < p.n) ? __ldg(reinterpret_cast<const float4*>(p.w + static_cast<size_t>(col) * p.k + kc) + c)
+                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < kXLoads; j++) {
+                const int i = j * kThreads + threadIdx.x;
+                if (i < kLinRows * kw4) xs[(i / kw4) * (kLinLd / 4) + (i % kw4)] = xv[j];
+            }
+#pragma unroll
+            for (int j = 0; j < kWLoads; j++) {
+                const int i = j * kThreads + threadIdx.x;
+                if (i < kLinCols * kw4) ws[(i / kw4) * (kLinLd / 4) + (i % kw4)] = wv[j];
             }
             __syncthreads();
-            for (int c = 0; c < kw4; c++) {
-                const float4 w4 = ws[tx * (kLinLd / 4) + c];
+            if (p.rms) {
+#pragma unroll 4
+                for (int c = 0; c < kw4; c++) {
+                    const float4 w4 = ws[tx * (kLinLd / 4) + c];
 #pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    const float4 x4 = xs[(ty + 16 * i) * (kLinLd / 4) + c];
-                    acc[i] = fmaf(x4.x, w4.x, fmaf(x4.y, w4.y, fmaf(x4.z, w4.z, fmaf(x4.w, w4.w, acc[i]))));
-                    ss[i] = fmaf(x4.x, x4.x, fmaf(x4.y, x4.y, fmaf(x4.z, x4.z, fmaf(x4.w, x4.w, ss[i]))));
+                    for (int i = 0; i < 4; i++) {
+                        const float4 x4 = xs[(ty + 16 * i) * (kLinLd / 4) + c];
+                        acc[i] = fmaf(x4.x, w4.x, fmaf(x4.y, w4.y, fmaf(x4.z, w4.z, fmaf(x4.w, w4.w, acc[i]))));
+                        ss[i] = fmaf(x4.x, x4.x, fmaf(x4.y, x4.y, fmaf(x4.z, x4.z, fmaf(x4.w, x4.w, ss[i]))));
+                    }
+                }
+            } else {
+#pragma unroll 4
+                for (int c = 0; c < kw4; c++) {
+                    const float4 w4 = ws[tx * (kLinLd / 4) + c];
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        const float4 x4 = xs[(ty + 16 * i) * (kLinLd / 4) + c];
+                        acc[i] = fmaf(x4.x, w4.x, fmaf(x4.y, w4.y, fmaf(x4.z, w4.z, fmaf(x4.w, w4.w, acc[i]))));
+                    }
                 }
             }
         }

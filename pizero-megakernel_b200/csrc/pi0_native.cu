@@ -660,7 +660,7 @@ extern "C" int configure_attention_splits(void* handle, int splits) {
     Op* op = as_op(handle);
     if (!op || op->desc.kind != OP_ATTN || splits < 1 || splits > 64) return cudaErrorInvalidValue;
     AttnParams& a = op->desc.p.attn;
-    if (splits > 1 && (a.batches != 1 || a.nq > kAttnQRows || a.head_dim % 16)) return cudaErrorInvalidValue;
+    if (splits > 1 && (a.batches != 1 || a.head_dim % 16)) return cudaErrorInvalidValue;
     if (op->merge) { free_op(op->merge); op->merge = nullptr; }
     cudaFree(op->partial_o); op->partial_o = nullptr;
     cudaFree(op->partial_ml); op->partial_ml = nullptr;
@@ -669,7 +669,8 @@ extern "C" int configure_attention_splits(void* handle, int splits) {
     a.fused_merge = 0;
     op->desc.aux_count = 0;
     if (splits > 1) {
-        const size_t tasks = static_cast<size_t>(a.heads) * splits;
+        const int groups = a.heads * ((a.nq + kAttnQRows - 1) / kAttnQRows);      // heads x 128-query tiles
+        const size_t tasks = static_cast<size_t>(groups) * splits;
         cudaError_t e = cudaMalloc(&op->partial_o, tasks * kAttnQRows * a.head_dim * sizeof(float));
         if (e == cudaSuccess) e = cudaMalloc(&op->partial_ml, tasks * kAttnQRows * 2 * sizeof(float));
         if (e != cudaSuccess) return e;
@@ -680,7 +681,7 @@ extern "C" int configure_attention_splits(void* handle, int splits) {
         mg->workers = op->workers;
         mg->desc.kind = OP_MERGE;
         finish_desc(mg->desc);
-        mg->desc.tiles = a.heads * ((a.nq + kMergeRows - 1) / kMergeRows);
+        mg->desc.tiles = groups * ((std::min(a.nq, kAttnQRows) + kMergeRows - 1) / kMergeRows);
         mg->desc.bands = 1;
         mg->desc.band_div = mg->desc.tiles;
         MergeParams& g = mg->desc.p.merge;
@@ -699,7 +700,7 @@ extern "C" int configure_attention_fused_merge(void* handle, int enable) {
     AttnParams& a = op->desc.p.attn;
     if (enable && a.splits < 2) return cudaErrorInvalidValue;
     a.fused_merge = enable;
-    op->desc.aux_count = enable ? a.heads : 0;
+    op->desc.aux_count = enable ? a.heads * ((a.nq + kAttnQRows - 1) / kAttnQRows) : 0;
     op->solo_dirty = true;
     return cudaSuccess;
 }
@@ -1049,7 +1050,7 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPartial
 __global__ void __launch_bounds__(kThreads, 1) noalloc_attention_kernel(AttnParams a) {
     extern __shared__ uint8_t noalloc_smem[];
     uint8_t* data = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(noalloc_smem) + 1023) & ~static_cast<uintptr_t>(1023));
-    attn_tile<kNoAllocHeadDim>(a, blockIdx.x, data);
+    attn_tile<kNoAllocHeadDim>(a, blockIdx.x, data, nullptr);
 }
 __global__ void __launch_bounds__(kThreads, 1) noalloc_merge_kernel(MergeParams g) { merge_tile(g, blockIdx.x); }
 

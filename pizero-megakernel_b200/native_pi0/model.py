@@ -65,7 +65,7 @@ class NativePi0:
         return cls(StateDictModel(config or Pi0Config(), state_dict), **kwargs)
 
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
-                 library=None, workers=None, partitioned=False, expert_splits=8, expert_block_n=64,
+                 library=None, workers=None, partitioned=False, expert_splits=16, prefix_splits=None, expert_block_n=64,
                  rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True):
         config = getattr(model, "config", None)
         if config is None or getattr(config, "pi05", False) or precision not in ("auto", "nvfp4"):
@@ -79,6 +79,7 @@ class NativePi0:
         self.precision_policy = "nvfp4"
         self.partitioned = partitioned
         self.expert_splits = expert_splits
+        self.prefix_splits = prefix_splits
         self.expert_block_n = expert_block_n
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self.keep_debug_outputs = keep_debug_outputs
@@ -310,6 +311,14 @@ class NativePi0:
         s_pl = self.norm("vision.post_layernorm", xa, a_ln, rows=M, sources=[(s_x, SAME)], kind="layer", gamma=gp, beta=bp, eps=c.ln_eps)
         return s_pl, a_ln
 
+    def _prefix_splits(self, rows):
+        """KV splits of the prefix attention: as many as keep every tile of the stage on a worker of its own (the
+        tiles of a head meet inside the stage to merge their partial results), at most four."""
+        if self.prefix_splits is not None:
+            return int(self.prefix_splits)
+        groups = -(-rows // 128) * self.config.heads
+        return max(1, min(4, self.workers // groups))
+
     def _gemma_layer(self, name, prefix, i, x_in, x_mid, bufs, *, rows, s_x, extra_sources, cos, sin, cache, cache_base,
                      attention_rows, mask_prefix, splits, kv_only, block_n, prefix_cache_stage=None):
         c, sd, lib = self.config, self.sd, self.lib
@@ -397,7 +406,7 @@ class NativePi0:
         for i in range(c.prefix_layers):
             s_x, s_kv = self._gemma_layer(f"prefix.{i}", LANGUAGE, i, x_a, x_b, bufs, rows=P, s_x=s_x, extra_sources=extra if i == 0 else [],
                                           cos=cos_p, sin=sin_p, cache=self.caches[i], cache_base=0, attention_rows=P, mask_prefix=-1,
-                                          splits=1, kv_only=(i == c.prefix_layers - 1), block_n=128)
+                                          splits=self._prefix_splits(P), kv_only=(i == c.prefix_layers - 1), block_n=128)
             cache_stage.append(s_kv)
             if i == 0:
                 self.mark("prefix.0.q", bufs[4]), self.mark("prefix.0.attention", bufs[5])

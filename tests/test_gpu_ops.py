@@ -263,6 +263,10 @@ ATTENTION_CASES = [
     (1, 51, 819, 8, 1, 256, 768, 8),         # split-KV 8 + merge
     (1, 64, 848, 8, 1, 256, 784, 4),
     (1, 1, 5, 1, 1, 256, 2, 1),
+    (1, 300, 500, 4, 1, 256, None, 3),       # split-KV over several 128-query tiles (ragged last tile)
+    (1, 20, 300, 2, 1, 256, None, 1),        # <= 64 queries: the two warp groups share each chunk of keys
+    (2, 40, 100, 4, 4, 72, None, 1),
+    (1, 51, 819, 8, 1, 256, 768, 16),
 ]
 
 
@@ -283,7 +287,7 @@ def test_attention(b, nq, nk, h, hk, hd, prefix, splits):
     np.testing.assert_array_equal(got, again)
     if splits > 1:
         # merge fused into the last-arriving tile of each head: same bits as the separate merge stage, launch after launch
-        with ResidentAttention(None, q, k, v, workers=64, prefix=prefix, splits=splits, fused_merge=True) as op:
+        with ResidentAttention(None, q, k, v, workers=128, prefix=prefix, splits=splits, fused_merge=True) as op:
             for _ in range(3):
                 op.output.fill_(float("nan"))
                 fused = op.forward().float().cpu().numpy()
