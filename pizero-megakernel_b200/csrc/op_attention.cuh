@@ -411,10 +411,13 @@ __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl
                 const unsigned int target = static_cast<unsigned int>(a.splits) * prog.epoch;
                 red_release_add(a.tickets + group, 1u);
                 int ok = 1;
-                const unsigned long long start = global_ns();
+                unsigned long long start = 0;           // the global timer is slow to read: first consulted after 64 polls
                 for (uint32_t spin = 1; ld_acquire(a.tickets + group) < target; ++spin) {
                     __nanosleep(20);
-                    if ((spin & 63u) == 0u && (ctl->abort || global_ns() - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort))) {
+                    if ((spin & 63u) != 0u) continue;
+                    const unsigned long long now = global_ns();
+                    if (start == 0) start = now;
+                    if (ctl->abort || now - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort)) {
                         report(prog, 1, stage_index, group, ld_acquire(a.tickets + group), target);
                         ctl->abort = 1;
                         ok = 0;

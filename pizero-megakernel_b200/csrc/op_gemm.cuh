@@ -1,6 +1,7 @@
 // NVFP4 block-scaled GEMM instruction:  out[M,N] = epilogue(alpha * deq(A)[M,K] . deq(B)[N,K]^T)
 //
-//   warp 0 / lane 0 : TMA producer  - operand tiles (128 B swizzled rows) and scale atoms into a ring of 72 KiB slots
+//   warp 0 / lane 0 : TMA producer  - operand tiles (128 B swizzled rows) and scale atoms into a ring of slots; the ring
+//                                     is laid out per GEMM: 2 slots of 72 KiB for full tiles, up to 5 for narrow ones
 //   warp 1 / lane 0 : MMA issuer    - tcgen05.cp (scales smem->TMEM) + tcgen05.mma kind::mxf4nvf4, K = 64 each
 //   warps 4..7      : epilogue      - tcgen05.ld of a 128xN FP32 accumulator (one row per thread), fused math, stores
 //
@@ -24,6 +25,19 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
     const int slots = (chunks + kChunks - 1) / kChunks;
     const uint32_t a_bytes = static_cast<uint32_t>(kChunks) * 128u * static_cast<uint32_t>(g.a_box_rows);
     const uint32_t b_bytes = static_cast<uint32_t>(kChunks) * 128u * static_cast<uint32_t>(g.block_n);
+    const uint32_t ring = static_cast<uint32_t>(g.ring_stages), stride = static_cast<uint32_t>(g.slot_stride);
+    if (ps.prod_geo != stride) {
+        // Slots of the previous geometry overlap the new ones at other indices: every copy issued so far must have
+        // been read by its MMAs before the first new copy lands (waits for the last release of each slot).
+        int alive0 = 1;
+        if (lane == 0)
+            for (int s = 0; s < kMaxStages && alive0; ++s)
+                alive0 = mbar_wait(prog, ctl, &ctl->empty[s], ((ps.prod_bits >> s) & 1u) ^ 1u, stage_index) ? 1 : 0;
+        alive0 = __shfl_sync(0xffffffffu, alive0, 0);
+        if (!alive0) return;
+        ps.prod_geo = stride;
+        ps.prod_slot = 0;
+    }
     int current_band = -1;
     for (int t = first; t < first + count; ++t) {
         const int m_tile = t / g.n_tiles, n_tile = t - m_tile * g.n_tiles;
@@ -34,16 +48,16 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
         if (band != current_band) {
             if (t == first) {
                 if (lane == 0) {
-                    early = min(slots, kStages);
+                    early = min(slots, g.ring_stages);
                     for (int ks = 0; ks < early; ++ks) {
-                        const uint32_t it = ps.prod_it + ks, s = it % kStages, phase = (it / kStages) & 1u;
-                        if (!mbar_wait(prog, ctl, &ctl->empty[s], phase ^ 1u, stage_index)) { alive = 0; break; }
+                        const uint32_t s = (ps.prod_slot + ks) % ring;
+                        if (!mbar_wait(prog, ctl, &ctl->empty[s], ((ps.prod_bits >> s) & 1u) ^ 1u, stage_index)) { alive = 0; break; }
                         const int groups = min(4 * kChunks, g.k_groups - ks * 4 * kChunks);
-                        uint8_t* slot = data + s * kStageBytes;
+                        uint8_t* slot = data + s * stride;
                         mbar_expect_tx_only(&ctl->full[s], b_bytes + groups * 512u);
-                        if (g.b_tiled) tma_load_2d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, (n_tile * chunks + ks * kChunks) * g.block_n);
-                        else tma_load_3d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, n_tile * g.block_n, ks * kChunks);
-                        bulk_load(slot + kSlotSfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
+                        if (g.b_tiled) tma_load_2d(slot + g.off_b, g.tmap_b, &ctl->full[s], 0, (n_tile * chunks + ks * kChunks) * g.block_n);
+                        else tma_load_3d(slot + g.off_b, g.tmap_b, &ctl->full[s], 0, n_tile * g.block_n, ks * kChunks);
+                        bulk_load(slot + g.off_sfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
                                   groups * 512u, &ctl->full[s]);
                     }
                 }
@@ -60,25 +74,26 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
         }
         if (lane == 0) {
             for (int ks = 0; ks < slots; ++ks) {
-                const uint32_t s = ps.prod_it % kStages, phase = (ps.prod_it / kStages) & 1u;
+                const uint32_t s = ps.prod_slot;
                 const int groups = min(4 * kChunks, g.k_groups - ks * 4 * kChunks);
-                uint8_t* slot = data + s * kStageBytes;
+                uint8_t* slot = data + s * stride;
                 const bool weights_issued = ks < early;
-                if (!weights_issued && !mbar_wait(prog, ctl, &ctl->empty[s], phase ^ 1u, stage_index)) { alive = 0; break; }
+                if (!weights_issued && !mbar_wait(prog, ctl, &ctl->empty[s], ((ps.prod_bits >> s) & 1u) ^ 1u, stage_index)) { alive = 0; break; }
                 // Boxes always deliver kChunks chunks (beyond K the copy engine fills zeros or, inside a padded
                 // allocation, bytes that no MMA reads).  a_box_rows < 128 (few logical rows): only the rows that
                 // exist are copied; the MMA still reads 128 rows, the rest lands in accumulator rows never stored.
                 mbar_expect_tx(&ctl->full[s], a_bytes + groups * 512u + (weights_issued ? 0u : b_bytes + groups * 512u));
-                tma_load_3d(slot + kSlotA, g.tmap_a, &ctl->full[s], 0, m_tile * 128, ks * kChunks);
-                bulk_load(slot + kSlotSfa, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4 * kChunks) * 512, groups * 512u,
+                tma_load_3d(slot, g.tmap_a, &ctl->full[s], 0, m_tile * 128, ks * kChunks);
+                bulk_load(slot + g.off_sfa, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4 * kChunks) * 512, groups * 512u,
                           &ctl->full[s]);
                 if (!weights_issued) {
-                    if (g.b_tiled) tma_load_2d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, (n_tile * chunks + ks * kChunks) * g.block_n);
-                    else tma_load_3d(slot + kSlotB, g.tmap_b, &ctl->full[s], 0, n_tile * g.block_n, ks * kChunks);
-                    bulk_load(slot + kSlotSfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
+                    if (g.b_tiled) tma_load_2d(slot + g.off_b, g.tmap_b, &ctl->full[s], 0, (n_tile * chunks + ks * kChunks) * g.block_n);
+                    else tma_load_3d(slot + g.off_b, g.tmap_b, &ctl->full[s], 0, n_tile * g.block_n, ks * kChunks);
+                    bulk_load(slot + g.off_sfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
                               groups * 512u, &ctl->full[s]);
                 }
-                ps.prod_it++;
+                ps.prod_bits ^= 1u << s;
+                ps.prod_slot = s + 1 == ring ? 0u : s + 1;
             }
         }
         alive = __shfl_sync(0xffffffffu, alive, 0);
@@ -88,42 +103,65 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
 
 __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem, const StageDesc& st,
                                          int stage_index, int first, int count, PipeState& ps, long long* stamp) {
+    // Everything the loop needs is copied out of the descriptor (shared memory) into registers first: the tcgen05
+    // wrappers are memory barriers for the compiler, so any field left behind would be re-read after each of them,
+    // and this single thread's instruction stream is what paces a narrow GEMM.
     const GemmParams& g = st.p.gemm;
-    const int chunks = (g.k_groups + 3) >> 2;
+    const int k_groups = g.k_groups, n_tiles = g.n_tiles, block_n = g.block_n;
+    const int chunks = (k_groups + 3) >> 2;
     const int slots = (chunks + kChunks - 1) / kChunks;
-    const uint32_t a_chunk = static_cast<uint32_t>(g.a_box_rows) * 128u, b_chunk = static_cast<uint32_t>(g.block_n) * 128u;
+    const uint32_t a_chunk16 = static_cast<uint32_t>(g.a_box_rows) * 8u, b_chunk16 = static_cast<uint32_t>(block_n) * 8u;   // 16-byte units
+    const uint32_t ring = static_cast<uint32_t>(g.ring_stages), stride = static_cast<uint32_t>(g.slot_stride);
+    const uint32_t off_b16 = static_cast<uint32_t>(g.off_b) >> 4, off_sfa16 = static_cast<uint32_t>(g.off_sfa) >> 4,
+                   off_sfb16 = static_cast<uint32_t>(g.off_sfb) >> 4;
+    const uint32_t idesc = g.idesc;
+    const uint32_t data16 = (smem_u32(data) & 0x3FFFFu) >> 4, stride16 = stride >> 4;
+    // descriptor high words: K-major 128-byte swizzle (8-row groups 1024 bytes apart, version 1) and the scale atoms
+    // (no swizzle, 8-line groups 128 bytes apart)
+    constexpr uint64_t kOperandHi = (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+    constexpr uint64_t kScaleHi = (1ull << 16) | (8ull << 32) | (1ull << 46);
+    if (ps.mma_geo != stride) { ps.mma_geo = stride; ps.mma_slot = 0; }
+    uint32_t slot = ps.mma_slot, bits = ps.mma_bits, it = ps.mma_it, tile_no = ps.mma_tile;
+    bool first_slot = true;
     for (int t = first; t < first + count; ++t) {
-        const int n_tile = t % g.n_tiles;
-        const uint32_t buf = ps.mma_tile & 1u, acc_phase = (ps.mma_tile >> 1) & 1u;
+        const int n_tile = t % n_tiles;
+        const uint32_t buf = tile_no & 1u, acc_phase = (tile_no >> 1) & 1u;
         if (!mbar_wait(prog, ctl, &ctl->acc_empty[buf], acc_phase ^ 1u, stage_index)) return;
         tc_fence_after();
         const uint32_t d = tmem + buf * 128u;
         // Scale rows of a narrow B tile sit in the 32-row sub-column of their 128-row atom.
-        const uint32_t sfb_sub = static_cast<uint32_t>((n_tile * g.block_n) & 127) >> 5;
+        const uint32_t sfb_sub = static_cast<uint32_t>((n_tile * block_n) & 127) >> 5;
         for (int ks = 0; ks < slots; ++ks) {
-            const uint32_t s = ps.mma_it % kStages, phase = (ps.mma_it / kStages) & 1u;
-            if (!mbar_wait(prog, ctl, &ctl->full[s], phase, stage_index)) return;
+            const uint32_t s = slot;
+            if (!mbar_wait(prog, ctl, &ctl->full[s], (bits >> s) & 1u, stage_index)) return;
             tc_fence_after();
-            if (stamp && t == first && ks == 0) stamp[4] = static_cast<long long>(global_ns());
-            const int groups = min(4 * kChunks, g.k_groups - ks * 4 * kChunks);
-            const uint32_t base = smem_u32(data + s * kStageBytes);
-            for (int gi = 0; gi < groups; ++gi) {
-                const uint32_t chunk = static_cast<uint32_t>(gi) >> 2, sub = static_cast<uint32_t>(gi) & 3u;
-                const uint32_t sfa_t = tmem + kSfCol0 + (s * 4 * kChunks + gi) * 8;
-                const uint32_t sfb_t = sfa_t + 4;
-                tc_copy_sf(sfa_t, umma_desc_sf(base + kSlotSfa + gi * 512));
-                tc_copy_sf(sfb_t, umma_desc_sf(base + kSlotSfb + gi * 512));
-                // 64 FP4 = 32 bytes along K inside the 128-byte swizzled row: advance the start address by 2 units.
-                tc_mma_nvfp4(d, umma_desc_k_sw128(base + kSlotA + chunk * a_chunk) + 2u * sub,
-                             umma_desc_k_sw128(base + kSlotB + chunk * b_chunk) + 2u * sub, g.idesc, sfa_t, sfb_t + sfb_sub,
-                             static_cast<uint32_t>((ks | gi) != 0));
+            if (stamp && first_slot) stamp[4] = static_cast<long long>(global_ns());
+            first_slot = false;
+            const int groups = min(4 * kChunks, k_groups - ks * 4 * kChunks);
+            const uint32_t a16 = data16 + s * stride16;
+            const uint32_t sf_cols = tmem + kSfCol0 + (it & 3u) * (4 * kChunks * 8);
+#pragma unroll
+            for (int gi = 0; gi < 4 * kChunks; ++gi) {
+                if (gi < groups) {
+                    const uint32_t chunk = static_cast<uint32_t>(gi) >> 2, sub = static_cast<uint32_t>(gi) & 3u;
+                    const uint32_t sfa_t = sf_cols + gi * 8, sfb_t = sfa_t + 4;
+                    tc_copy_sf(sfa_t, kScaleHi | static_cast<uint64_t>(a16 + off_sfa16 + gi * 32));
+                    tc_copy_sf(sfb_t, kScaleHi | static_cast<uint64_t>(a16 + off_sfb16 + gi * 32));
+                    // 64 FP4 = 32 bytes along K inside the 128-byte swizzled row: advance the start address by 2 units.
+                    tc_mma_nvfp4(d, kOperandHi | static_cast<uint64_t>(a16 + chunk * a_chunk16 + 2u * sub),
+                                 kOperandHi | static_cast<uint64_t>(a16 + off_b16 + chunk * b_chunk16 + 2u * sub), idesc, sfa_t,
+                                 sfb_t + sfb_sub, gi != 0 ? 1u : static_cast<uint32_t>(ks != 0));
+                }
             }
             tc_commit(&ctl->empty[s]);     // slot reusable once these MMAs have read it
-            ps.mma_it++;
+            bits ^= 1u << s;
+            slot = s + 1 == ring ? 0u : s + 1;
+            it++;
         }
         tc_commit(&ctl->acc_full[buf]);    // accumulator complete
-        ps.mma_tile++;
+        tile_no++;
     }
+    ps.mma_slot = slot; ps.mma_bits = bits; ps.mma_it = it; ps.mma_tile = tile_no;
     if (stamp) stamp[5] = static_cast<long long>(global_ns());
 }
 

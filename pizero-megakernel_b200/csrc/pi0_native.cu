@@ -343,6 +343,20 @@ int gemm_refresh(Op* op) {
     g.m_tiles = op->m / 128;
     g.n_tiles = op->n / g.block_n;
     g.k_groups = op->k / 64;
+    // Operand ring: a slot holds kChunks chunks of the rows that are actually copied (A: a_box_rows, B: block_n) and
+    // 4 KiB of scale atoms per operand. The MMA always reads 128 rows of A; with 64 copied rows the other 64 are
+    // whatever follows in the slot (B, scales) and end in accumulator rows that are never stored, so the read only
+    // has to stay inside shared memory, which the slot's own B and scale regions guarantee.
+    g.off_b = kChunks * 128 * g.a_box_rows;
+    g.off_sfa = g.off_b + kChunks * 128 * g.block_n;
+    g.off_sfb = g.off_sfa + kSfBytes;
+    g.slot_stride = g.off_sfb + kSfBytes;
+    g.ring_stages = std::max(kStages, std::min(kMaxStages, kDataBytes / g.slot_stride));
+    const char* ring_env = getenv("PI0_RING_STAGES");                                   // experiments: cap the ring depth
+    if (ring_env) g.ring_stages = std::max(1, std::min(g.ring_stages, atoi(ring_env)));
+    if (g.slot_stride % 1024 || g.ring_stages * g.slot_stride > kDataBytes ||
+        (kChunks - 1) * 128 * g.a_box_rows + kTileABytes > g.slot_stride)
+        return cudaErrorInvalidValue;
     const char* fmt_env = getenv("PI0_FP4_FORMAT_CODE");
     const uint32_t fmt = fmt_env ? static_cast<uint32_t>(atoi(fmt_env)) & 7u : 1u;    // E2M1 for kind::mxf4nvf4
     g.idesc = (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(g.block_n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);

@@ -8,7 +8,8 @@ namespace pi0 {
 // GEMM pipeline: a ring of kStages slots, each holding kChunks consecutive 256-wide K chunks of A and B plus their
 // scale atoms.  One slot is filled by four copies (A, B, SFA, SFB); copies complete at a roughly fixed cost each
 // (about one L2 round trip, whatever their size), so a slot carries as many bytes per copy as shared memory allows.
-constexpr int kStages = 2;                                   // slots in flight
+constexpr int kStages = 2;                                   // slots in flight with full-size tiles (128 rows of A and of B)
+constexpr int kMaxStages = 5;                                // slots in flight with the narrowest tiles (64 rows of each)
 constexpr int kChunks = 2;                                   // 256-wide K chunks per slot
 constexpr int kTileABytes = 128 * 128;                       // one chunk of one operand: 128 rows x 128 bytes
 constexpr int kSfBytes = kChunks * 4 * 512;                  // scale atoms of one operand: four 64-wide K groups per chunk
@@ -35,8 +36,8 @@ struct alignas(16) Slot {
 };
 
 struct Ctl {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint64_t ready[kRing];       // slot filled (32 asynchronous-copy arrivals of the prefetch warp)
@@ -47,13 +48,18 @@ struct Ctl {
     volatile int abort;          // CTA-local copy of the abort decision
     volatile int dep_ok;         // broadcast slot for CTA-wide operators
     volatile int flag;           // second broadcast slot (last-arriver decisions)
+    int gate;                    // CTA-wide operators entered so far, or -1 once a warp has given up on one (gather_enter)
     Slot slot[kRing];
 };
 static_assert(sizeof(Ctl) <= kCtlBytes, "control block too large");
 
+// The ring geometry (slot count and size) belongs to the GEMM, so positions are kept per barrier: bit s of
+// prod_bits / mma_bits is the parity of the fills / drains slot s has seen. Producer and MMA lane walk the same slot
+// sequence: the cursor continues from one instruction to the next and restarts at 0 when the geometry changes.
 struct PipeState {
-    uint32_t prod_it = 0;        // K stages issued by the TMA lane
-    uint32_t mma_it = 0;         // K stages consumed by the MMA lane
+    uint32_t prod_slot = 0, prod_bits = 0, prod_geo = 0;     // TMA lane
+    uint32_t mma_slot = 0, mma_bits = 0, mma_geo = 0;        // MMA lane
+    uint32_t mma_it = 0;         // K stages consumed by the MMA lane (rotates the scale columns in tensor memory)
     uint32_t mma_tile = 0;       // accumulator tiles produced
     uint32_t epi_tile = 0;       // accumulator tiles drained
 };
@@ -83,14 +89,20 @@ __device__ __forceinline__ void report(const VmProgram& prog, int code, int stag
 // program has been aborted; the caller leaves its loop.
 __device__ __forceinline__ bool mbar_wait(const VmProgram& prog, Ctl* ctl, uint64_t* bar, uint32_t parity, int stage) {
     if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long start = global_ns();
+    // Reading the global timer costs about a microsecond, so the clock is only consulted once a wait has
+    // already lasted for several tries (the budget counts from that first reading).
+    unsigned long long start = 0;
     for (uint32_t spin = 1;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;          // each try suspends for at most ~1 us
         if (ctl->abort) return false;
-        if ((spin & 7u) == 0u && (global_ns() - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort))) {
-            report(prog, 2, stage, -1, parity, 0);
-            ctl->abort = 1;
-            return false;
+        if ((spin & 15u) == 0u) {
+            const unsigned long long now = global_ns();
+            if (start == 0) start = now;
+            if (now - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort)) {
+                report(prog, 2, stage, -1, parity, 0);
+                ctl->abort = 1;
+                return false;
+            }
         }
     }
 }
@@ -109,6 +121,46 @@ __device__ __forceinline__ bool mbar_wait_warp(const VmProgram& prog, Ctl* ctl, 
         }
     }
     return ok != 0;
+}
+
+// Entry of a CTA-wide operator: all eight warps go in, or none does.
+//
+// The operator body synchronises with hardware barriers, which never time out, so a warp may only enter when every
+// other warp is certain to follow. Each warp arrives on the gather barrier and waits with the usual bounds; what it
+// saw (phase complete, or time-out / abort) is turned into one decision per operator by a compare-and-swap on
+// ctl->gate: the first warp to finish its wait moves the gate from k (operators entered so far) to k + 1 ("all
+// arrived, enter") or to -1 ("somebody gave up, leave"), and every other warp adopts that outcome whatever it
+// observed itself. A warp that timed out but finds the gate at k + 1 enters (the phase did complete); a warp that
+// saw the phase complete but finds -1 leaves.
+__device__ __forceinline__ bool gather_enter(const VmProgram& prog, Ctl* ctl, uint32_t k, int stage) {
+    int pass = 0;
+    if (lane_id() == 0) {
+        mbar_arrive(&ctl->gather);
+        const int open = static_cast<int>(k), entered = open + 1;
+        unsigned long long start = 0;
+        for (uint32_t spin = 1;; ++spin) {
+            if (mbar_try_wait(&ctl->gather, k & 1u)) {
+                const int seen = atomicCAS(&ctl->gate, open, entered);
+                pass = (seen == open || seen == entered) ? 1 : 0;
+                break;
+            }
+            bool give_up = ctl->abort != 0;
+            if (!give_up && (spin & 15u) == 0u) {
+                const unsigned long long now = global_ns();
+                if (start == 0) start = now;
+                if (now - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort)) {
+                    report(prog, 2, stage, -2, k, 0);
+                    give_up = true;
+                }
+            }
+            if (give_up) {
+                pass = atomicCAS(&ctl->gate, open, -1) == entered ? 1 : 0;
+                if (!pass) ctl->abort = 1;
+                break;
+            }
+        }
+    }
+    return __shfl_sync(0xffffffffu, pass, 0) != 0;
 }
 
 __device__ __forceinline__ int tile_band(const StageDesc& st, int tile) { return min(tile / st.band_div, st.bands - 1); }
@@ -145,7 +197,7 @@ __device__ __forceinline__ bool warp_wait_sources(const VmProgram& prog, Ctl* ct
     unsigned int seen = mine ? ld_acquire(mine) : 0u;
     bool ok = mine == nullptr || seen >= target;
     if (__all_sync(0xffffffffu, ok)) return true;
-    const unsigned long long start = global_ns();
+    unsigned long long start = 0;                 // the global timer is slow to read: first consulted after 64 polls
     for (uint32_t spin = 1;; ++spin) {
         if (!ok) {
             __nanosleep(20);
@@ -155,7 +207,9 @@ __device__ __forceinline__ bool warp_wait_sources(const VmProgram& prog, Ctl* ct
         if (__all_sync(0xffffffffu, ok)) return true;
         if ((spin & 63u) == 0u) {
             bool stop = ctl->abort != 0;
-            if (!stop && (global_ns() - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort))) {
+            const unsigned long long now = global_ns();
+            if (start == 0) start = now;
+            if (!stop && (now - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort))) {
                 if (!ok) report(prog, 1, stage, my_band, seen, target);
                 stop = true;
             }
@@ -179,7 +233,7 @@ __device__ __forceinline__ bool cta_wait_sources(const VmProgram& prog, Ctl* ctl
     if (threadIdx.x < 32) {
         const bool ok = warp_wait_sources(prog, ctl, st, stage, tile_band(st, first), tile_band(st, first + count - 1));
         if (threadIdx.x == 0) {
-            ctl->dep_ok = ok ? 1 : 0;
+            ctl->dep_ok = (ok && !ctl->abort) ? 1 : 0;       // one decision for the CTA, taken behind the entry gate
             if (stamp) stamp[1] = static_cast<long long>(global_ns());
         }
     }

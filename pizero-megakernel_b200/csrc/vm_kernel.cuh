@@ -53,7 +53,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
     const int warp = threadIdx.x >> 5;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; s++) {
+        for (int s = 0; s < kMaxStages; s++) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
         }
@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         mbar_init(&ctl->done, kThreads / 32);
         ctl->abort = 0;
         ctl->dep_ok = 1;
+        ctl->gate = 0;
         mbar_fence_init();
     }
     if (warp == 2) {
@@ -119,18 +120,18 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         if (st.kind == OP_GEMM) {
             mark(prog, 800000 + ins.y);
             gemm_instruction(prog, ctl, data, tmem, st, ins.y, ins.z, ins.w, ps, stamp);
-            if (ctl->abort) break;
+            // one decision per warp: the lanes with a role return later than the others and must not leave alone
+            if (__any_sync(0xffffffffu, ctl->abort != 0)) break;
         } else {
-            // CTA-wide operator: every warp (including GEMM roles still draining) meets here first. The meeting
-            // point is an mbarrier with a bounded, abort-aware wait, not bar.sync: a warp that gave up inside a GEMM
-            // role never arrives, and a hardware barrier would then hold the others for ever.
+            // CTA-wide operator: every warp (including GEMM roles still draining) meets here first, on an mbarrier
+            // with a bounded, abort-aware wait and an all-or-nothing outcome (gather_enter). Behind the gate all
+            // eight warps are present, so the hardware barriers of the operator body are safe; the next abort
+            // decision is the CTA-wide one of cta_wait_sources.
             mark(prog, 600000 + ins.y);
             __syncwarp();
-            if (lane_id() == 0) mbar_arrive(&ctl->gather);
-            if (!mbar_wait_warp(prog, ctl, &ctl->gather, gathers & 1u, ins.y)) break;
+            if (!gather_enter(prog, ctl, gathers, ins.y)) break;
             gathers++;
             mark(prog, 700000 + ins.y);
-            if (ctl->abort) break;
             if (!cta_wait_sources(prog, ctl, st, ins.y, ins.z, ins.w, stamp)) break;
             switch (st.kind) {
                 case OP_NORM: norm_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;

@@ -48,6 +48,9 @@ struct GemmParams {
     int block_n;                 // 128 (default), 64 or 32
     int b_tiled;                 // B stored tile-major: block (n_tile, k_stage) is block_n contiguous 128-byte rows
     int a_box_rows;              // rows of A copied per tile: 128, or 64 when the logical row count is <= 64
+    int ring_stages;             // operand ring of this GEMM: slots in flight (2..kMaxStages) ...
+    int slot_stride;             // ... bytes from one slot to the next (multiple of 1024) ...
+    int off_b, off_sfa, off_sfb; // ... and where B, the A scales and the B scales start inside a slot (A starts at 0)
     float alpha;                 // global_scale(A) * global_scale(B)
     int epilogue;
     int act;                     // EPI_FP4: 0 none, 1 GELU(tanh), 3 ReLU^2
