@@ -2,7 +2,8 @@
 //
 //   warp 0 / lane 0 : TMA producer  - operand tiles (128 B swizzled rows) and scale atoms into a ring of slots; the ring
 //                                     is laid out per GEMM: 2 slots of 72 KiB for full tiles, up to 5 for narrow ones
-//   warp 1 / lane 0 : MMA issuer    - tcgen05.cp (scales smem->TMEM) + tcgen05.mma kind::mxf4nvf4, K = 64 each
+//   warp 1          : MMA issuer    - warp-uniform loop, one elected lane issues tcgen05.cp (scales smem->TMEM) and
+//                                     tcgen05.mma kind::mxf4nvf4, K = 64 each
 //   warps 4..7      : epilogue      - tcgen05.ld of a 128xN FP32 accumulator (one row per thread), fused math, stores
 //
 // Two TMEM accumulators alternate, so the epilogue of tile t overlaps the MMAs of tile t+1. Pipeline positions live in
@@ -21,6 +22,7 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
                                               int stage_index, int first, int count, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
     const int lane = lane_id();
+    uint32_t p_slot = ps.prod_slot, p_bits = ps.prod_bits;
     const int chunks = (g.k_groups + 3) >> 2;                        // 256-wide K chunks
     const int slots = (chunks + kChunks - 1) / kChunks;
     const uint32_t a_bytes = static_cast<uint32_t>(kChunks) * 128u * static_cast<uint32_t>(g.a_box_rows);
@@ -32,11 +34,11 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
         int alive0 = 1;
         if (lane == 0)
             for (int s = 0; s < kMaxStages && alive0; ++s)
-                alive0 = mbar_wait(prog, ctl, &ctl->empty[s], ((ps.prod_bits >> s) & 1u) ^ 1u, stage_index) ? 1 : 0;
+                alive0 = mbar_wait(prog, ctl, &ctl->empty[s], ((p_bits >> s) & 1u) ^ 1u, stage_index) ? 1 : 0;
         alive0 = __shfl_sync(0xffffffffu, alive0, 0);
         if (!alive0) return;
         ps.prod_geo = stride;
-        ps.prod_slot = 0;
+        p_slot = 0;
     }
     int current_band = -1;
     for (int t = first; t < first + count; ++t) {
@@ -50,8 +52,8 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
                 if (lane == 0) {
                     early = min(slots, g.ring_stages);
                     for (int ks = 0; ks < early; ++ks) {
-                        const uint32_t s = (ps.prod_slot + ks) % ring;
-                        if (!mbar_wait(prog, ctl, &ctl->empty[s], ((ps.prod_bits >> s) & 1u) ^ 1u, stage_index)) { alive = 0; break; }
+                        const uint32_t s = (p_slot + ks) % ring;
+                        if (!mbar_wait(prog, ctl, &ctl->empty[s], ((p_bits >> s) & 1u) ^ 1u, stage_index)) { alive = 0; break; }
                         const int groups = min(4 * kChunks, g.k_groups - ks * 4 * kChunks);
                         uint8_t* slot = data + s * stride;
                         mbar_expect_tx_only(&ctl->full[s], b_bytes + groups * 512u);
@@ -74,11 +76,11 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
         }
         if (lane == 0) {
             for (int ks = 0; ks < slots; ++ks) {
-                const uint32_t s = ps.prod_slot;
+                const uint32_t s = p_slot;
                 const int groups = min(4 * kChunks, g.k_groups - ks * 4 * kChunks);
                 uint8_t* slot = data + s * stride;
                 const bool weights_issued = ks < early;
-                if (!weights_issued && !mbar_wait(prog, ctl, &ctl->empty[s], ((ps.prod_bits >> s) & 1u) ^ 1u, stage_index)) { alive = 0; break; }
+                if (!weights_issued && !mbar_wait(prog, ctl, &ctl->empty[s], ((p_bits >> s) & 1u) ^ 1u, stage_index)) { alive = 0; break; }
                 // Boxes always deliver kChunks chunks (beyond K the copy engine fills zeros or, inside a padded
                 // allocation, bytes that no MMA reads).  a_box_rows < 128 (few logical rows): only the rows that
                 // exist are copied; the MMA still reads 128 rows, the rest lands in accumulator rows never stored.
@@ -92,77 +94,85 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
                     bulk_load(slot + g.off_sfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
                               groups * 512u, &ctl->full[s]);
                 }
-                ps.prod_bits ^= 1u << s;
-                ps.prod_slot = s + 1 == ring ? 0u : s + 1;
+                p_bits ^= 1u << s;
+                p_slot = s + 1 == ring ? 0u : s + 1;
             }
         }
         alive = __shfl_sync(0xffffffffu, alive, 0);
         if (!alive) return;
     }
+    ps.prod_slot = p_slot;
+    ps.prod_bits = p_bits;
 }
 
-__device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem, const StageDesc& st,
-                                         int stage_index, int first, int count, PipeState& ps, long long* stamp) {
-    // Everything the loop needs is copied out of the descriptor (shared memory) into registers first: the tcgen05
-    // wrappers are memory barriers for the compiler, so any field left behind would be re-read after each of them,
-    // and this single thread's instruction stream is what paces a narrow GEMM.
+// Whole warp 1, converged: the loop and all operand arithmetic are warp-uniform and only the tcgen05 instructions are
+// issued by one elected lane. (Run by a single lane inside a divergent branch, every descriptor and address has to be
+// moved from per-thread to uniform registers for each instruction, which measured about 250 cycles per 64-wide K
+// group and made this lane, not the copies or the tensor core, the pace of a narrow GEMM.)
+__device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem_in, const StageDesc& st,
+                                         int stage_index, int first_in, int count_in, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
-    const int k_groups = g.k_groups, n_tiles = g.n_tiles, block_n = g.block_n;
+    const int first = uniform_i32(first_in), count = uniform_i32(count_in);
+    const int k_groups = uniform_i32(g.k_groups), n_tiles = uniform_i32(g.n_tiles), block_n = uniform_i32(g.block_n);
     const int chunks = (k_groups + 3) >> 2;
     const int slots = (chunks + kChunks - 1) / kChunks;
-    const uint32_t a_chunk16 = static_cast<uint32_t>(g.a_box_rows) * 8u, b_chunk16 = static_cast<uint32_t>(block_n) * 8u;   // 16-byte units
-    const uint32_t ring = static_cast<uint32_t>(g.ring_stages), stride = static_cast<uint32_t>(g.slot_stride);
-    const uint32_t off_b16 = static_cast<uint32_t>(g.off_b) >> 4, off_sfa16 = static_cast<uint32_t>(g.off_sfa) >> 4,
-                   off_sfb16 = static_cast<uint32_t>(g.off_sfb) >> 4;
-    const uint32_t idesc = g.idesc;
-    const uint32_t data16 = (smem_u32(data) & 0x3FFFFu) >> 4, stride16 = stride >> 4;
+    const uint32_t a_chunk16 = uniform_u32(static_cast<uint32_t>(g.a_box_rows)) * 8u, b_chunk16 = static_cast<uint32_t>(block_n) * 8u;   // 16-byte units
+    const uint32_t ring = uniform_u32(static_cast<uint32_t>(g.ring_stages)), stride = uniform_u32(static_cast<uint32_t>(g.slot_stride));
+    const uint32_t off_b16 = uniform_u32(static_cast<uint32_t>(g.off_b)) >> 4, off_sfa16 = uniform_u32(static_cast<uint32_t>(g.off_sfa)) >> 4,
+                   off_sfb16 = uniform_u32(static_cast<uint32_t>(g.off_sfb)) >> 4;
+    const uint32_t idesc = uniform_u32(g.idesc);
+    const uint32_t tmem = uniform_u32(tmem_in);
+    const uint32_t data16 = uniform_u32((smem_u32(data) & 0x3FFFFu) >> 4), stride16 = stride >> 4;
     // descriptor high words: K-major 128-byte swizzle (8-row groups 1024 bytes apart, version 1) and the scale atoms
     // (no swizzle, 8-line groups 128 bytes apart)
     constexpr uint64_t kOperandHi = (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
     constexpr uint64_t kScaleHi = (1ull << 16) | (8ull << 32) | (1ull << 46);
     if (ps.mma_geo != stride) { ps.mma_geo = stride; ps.mma_slot = 0; }
-    uint32_t slot = ps.mma_slot, bits = ps.mma_bits, it = ps.mma_it, tile_no = ps.mma_tile;
+    uint32_t slot = uniform_u32(ps.mma_slot), bits = uniform_u32(ps.mma_bits), it = uniform_u32(ps.mma_it), tile_no = uniform_u32(ps.mma_tile);
     bool first_slot = true;
     for (int t = first; t < first + count; ++t) {
         const int n_tile = t % n_tiles;
         const uint32_t buf = tile_no & 1u, acc_phase = (tile_no >> 1) & 1u;
-        if (!mbar_wait(prog, ctl, &ctl->acc_empty[buf], acc_phase ^ 1u, stage_index)) return;
+        if (!mbar_wait_warp(prog, ctl, &ctl->acc_empty[buf], acc_phase ^ 1u, stage_index)) return;
         tc_fence_after();
         const uint32_t d = tmem + buf * 128u;
         // Scale rows of a narrow B tile sit in the 32-row sub-column of their 128-row atom.
         const uint32_t sfb_sub = static_cast<uint32_t>((n_tile * block_n) & 127) >> 5;
         for (int ks = 0; ks < slots; ++ks) {
             const uint32_t s = slot;
-            if (!mbar_wait(prog, ctl, &ctl->full[s], (bits >> s) & 1u, stage_index)) return;
-            tc_fence_after();
-            if (stamp && first_slot) stamp[4] = static_cast<long long>(global_ns());
+            if (!mbar_wait_warp(prog, ctl, &ctl->full[s], (bits >> s) & 1u, stage_index)) return;
+            if (stamp && first_slot && lane_id() == 0) stamp[4] = static_cast<long long>(global_ns());
             first_slot = false;
             const int groups = min(4 * kChunks, k_groups - ks * 4 * kChunks);
             const uint32_t a16 = data16 + s * stride16;
             const uint32_t sf_cols = tmem + kSfCol0 + (it & 3u) * (4 * kChunks * 8);
+            if (elect_one()) {
 #pragma unroll
-            for (int gi = 0; gi < 4 * kChunks; ++gi) {
-                if (gi < groups) {
-                    const uint32_t chunk = static_cast<uint32_t>(gi) >> 2, sub = static_cast<uint32_t>(gi) & 3u;
-                    const uint32_t sfa_t = sf_cols + gi * 8, sfb_t = sfa_t + 4;
-                    tc_copy_sf(sfa_t, kScaleHi | static_cast<uint64_t>(a16 + off_sfa16 + gi * 32));
-                    tc_copy_sf(sfb_t, kScaleHi | static_cast<uint64_t>(a16 + off_sfb16 + gi * 32));
-                    // 64 FP4 = 32 bytes along K inside the 128-byte swizzled row: advance the start address by 2 units.
-                    tc_mma_nvfp4(d, kOperandHi | static_cast<uint64_t>(a16 + chunk * a_chunk16 + 2u * sub),
-                                 kOperandHi | static_cast<uint64_t>(a16 + off_b16 + chunk * b_chunk16 + 2u * sub), idesc, sfa_t,
-                                 sfb_t + sfb_sub, gi != 0 ? 1u : static_cast<uint32_t>(ks != 0));
+                for (int gi = 0; gi < 4 * kChunks; ++gi) {
+                    if (gi < groups) {
+                        const uint32_t chunk = static_cast<uint32_t>(gi) >> 2, sub = static_cast<uint32_t>(gi) & 3u;
+                        const uint32_t sfa_t = sf_cols + gi * 8, sfb_t = sfa_t + 4;
+                        tc_copy_sf(sfa_t, kScaleHi | static_cast<uint64_t>(a16 + off_sfa16 + gi * 32));
+                        tc_copy_sf(sfb_t, kScaleHi | static_cast<uint64_t>(a16 + off_sfb16 + gi * 32));
+                        // 64 FP4 = 32 bytes along K inside the 128-byte swizzled row: advance the start address by 2 units.
+                        tc_mma_nvfp4(d, kOperandHi | static_cast<uint64_t>(a16 + chunk * a_chunk16 + 2u * sub),
+                                     kOperandHi | static_cast<uint64_t>(a16 + off_b16 + chunk * b_chunk16 + 2u * sub), idesc, sfa_t,
+                                     sfb_t + sfb_sub, gi != 0 ? 1u : static_cast<uint32_t>(ks != 0));
+                    }
                 }
+                tc_commit(&ctl->empty[s]);     // slot reusable once these MMAs have read it
             }
-            tc_commit(&ctl->empty[s]);     // slot reusable once these MMAs have read it
+            __syncwarp();
             bits ^= 1u << s;
             slot = s + 1 == ring ? 0u : s + 1;
             it++;
         }
-        tc_commit(&ctl->acc_full[buf]);    // accumulator complete
+        if (elect_one()) tc_commit(&ctl->acc_full[buf]);    // accumulator complete
+        __syncwarp();
         tile_no++;
     }
     ps.mma_slot = slot; ps.mma_bits = bits; ps.mma_it = it; ps.mma_tile = tile_no;
-    if (stamp) stamp[5] = static_cast<long long>(global_ns());
+    if (stamp && lane_id() == 0) stamp[5] = static_cast<long long>(global_ns());
 }
 
 // ---- epilogue helpers ---------------------------------------------------------------------------------------------
@@ -359,8 +369,7 @@ __device__ __forceinline__ void gemm_instruction(const VmProgram& prog, Ctl* ctl
         gemm_producer(prog, ctl, data, st, stage_index, first, count, ps, stamp);
         if (stamp && threadIdx.x == 0) stamp[3] = static_cast<long long>(global_ns());
     } else if (warp == 1) {
-        if (lane_id() == 0) gemm_mma(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
-        __syncwarp();
+        gemm_mma(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
     } else if (warp >= 4) {
         gemm_epilogue(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         if (stamp && threadIdx.x == 128) stamp[2] = static_cast<long long>(global_ns());

@@ -18,6 +18,16 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+// A value every lane of the warp holds, in a form the compiler can see is warp-uniform (broadcast from lane 0), so
+// arithmetic on it runs on the uniform datapath and tcgen05 operands need no per-instruction register transfers.
+__device__ __forceinline__ uint32_t uniform_u32(uint32_t v) { return __shfl_sync(0xffffffffu, v, 0); }
+__device__ __forceinline__ int uniform_i32(int v) { return __shfl_sync(0xffffffffu, v, 0); }
+// One lane of a converged warp (always the same one for the full mask).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t p;
+    asm volatile("{ .reg .pred P; elect.sync _|P, 0xffffffff; selp.u32 %0, 1, 0, P; }" : "=r"(p));
+    return p != 0;
+}
 
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
