@@ -138,6 +138,9 @@ int create_token_embed(void** handle, const long long* tokens, const void* table
 int create_linear32(void** handle, const void* x, const float* w, const float* bias, const float* prev, void* out,
                     int rows, int n, int k, int ldx, int ldo, int flags, int slot, int prev_slot, int x_row_offset,
                     float dt, float eps, int workers);
+/* extension: the tiles of the operator's first row block also store src (FP32 [n]) as BF16 [n] at dst; with the output
+ * pointing one row below dst this makes the state token row 0 of the action-expert input without a stage of its own. */
+int configure_linear32_extra_row(void* handle, const float* src, void* dst);
 /* expert input rows: row 0 = state embedding, rows 1..chunk = action embeddings, BF16 [*, width]. */
 int create_suffix_assemble(void** handle, const float* state_emb, const float* action_emb, void* out, int chunk,
                            int width, int workers);

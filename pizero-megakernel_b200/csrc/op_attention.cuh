@@ -312,6 +312,31 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data, long lon
 // (row, 16-column block) per thread, all partial loads of a thread independent of each other.
 constexpr int kMergeRows = 16;
 
+// Normalise one (row, 16-column block), round to BF16 and store it (BF16 and / or NVFP4 with its block scale).
+__device__ __forceinline__ void merge_store(const MergeParams& g, int head, int grow, int b, const float (&acc)[16], float denom) {
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    float v[16];
+#pragma unroll
+    for (int e = 0; e < 16; e++) v[e] = bf16_round(acc[e] * inv);
+    const int col = head * g.head_dim + b * 16;
+    if (g.out) {
+        uint32_t w[8];
+#pragma unroll
+        for (int e = 0; e < 8; e++) w[e] = pack2_bf16(v[2 * e], v[2 * e + 1]);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(grow) * g.ldo + col);
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    if (g.out_fp4) {
+#pragma unroll
+        for (int e = 0; e < 16; e++) v[e] *= g.out_inv_gs;
+        uint32_t code;
+        uint2 bytes = quantize_block16(v, 0, code);
+        *reinterpret_cast<uint2*>(g.out_fp4 + static_cast<size_t>(grow) * g.ld_fp4 + (col >> 1)) = bytes;
+        g.out_scales[scale_offset(grow, col >> 4, g.out_blocks)] = static_cast<uint8_t>(code);
+    }
+}
+
 // One (query row, 16-column block) of one group (a head of one 128-query tile); r counts rows inside the query tile.
 __device__ __forceinline__ void merge_item(const MergeParams& g, int group, int r, int b) {
     {
@@ -351,37 +376,83 @@ __device__ __forceinline__ void merge_item(const MergeParams& g, int group, int 
                 }
             }
         }
-        const float inv = denom > 0.f ? 1.f / denom : 0.f;
-        float v[16];
+        merge_store(g, head, grow, b, acc, denom);
+    }
+}
+
+// The same for 5..16 splits with four adjacent lanes per (row, block): each lane fetches the partials of splits
+// sub, sub + 4, sub + 8, sub + 12 in one batch of independent loads and the lanes combine with shuffles, so an item
+// costs one round trip to L2 instead of one per four splits. All 32 lanes of a warp must call it together.
+__device__ __forceinline__ void merge_item_wide(const MergeParams& g, int group, int r, int b, bool valid) {
+    const int sub = threadIdx.x & 3;
+    const int head = group % g.heads;
+    const int grow = (group / g.heads) * kAttnQRows + r;
+    const float* ml = g.partial_ml + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * 2;
+    const float* po = g.partial_o + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * g.head_dim + b * 16;
+    float2 pair[4];
+    float4 x[4][4];
 #pragma unroll
-        for (int e = 0; e < 16; e++) v[e] = bf16_round(acc[e] * inv);
-        const int col = head * g.head_dim + b * 16;
-        if (g.out) {
-            uint32_t w[8];
+    for (int j = 0; j < 4; j++) {
+        const int sp = sub + 4 * j;
+        const bool ok = valid && sp < g.splits;
+        pair[j] = make_float2(-INFINITY, 0.f);
 #pragma unroll
-            for (int e = 0; e < 8; e++) w[e] = pack2_bf16(v[2 * e], v[2 * e + 1]);
-            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(grow) * g.ldo + col);
-            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
-            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        for (int q = 0; q < 4; q++) x[j][q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ok) {
+            pair[j] = __ldcg(reinterpret_cast<const float2*>(ml + static_cast<size_t>(sp) * kAttnQRows * 2));
+            const float4* src = reinterpret_cast<const float4*>(po + static_cast<size_t>(sp) * kAttnQRows * g.head_dim);
+#pragma unroll
+            for (int q = 0; q < 4; q++) x[j][q] = __ldcg(src + q);
         }
-        if (g.out_fp4) {
+    }
+    float big = fmaxf(fmaxf(pair[0].x, pair[1].x), fmaxf(pair[2].x, pair[3].x));
+    big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, 1));
+    big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, 2));
+    const float ref = big == -INFINITY ? 0.f : big;
+    float acc[16];
 #pragma unroll
-            for (int e = 0; e < 16; e++) v[e] *= g.out_inv_gs;
-            uint32_t code;
-            uint2 bytes = quantize_block16(v, 0, code);
-            *reinterpret_cast<uint2*>(g.out_fp4 + static_cast<size_t>(grow) * g.ld_fp4 + (col >> 1)) = bytes;
-            g.out_scales[scale_offset(grow, col >> 4, g.out_blocks)] = static_cast<uint8_t>(code);
+    for (int e = 0; e < 16; e++) acc[e] = 0.f;
+    float denom = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float w = exp2f(pair[j].x - ref);               // 0 for an absent or fully masked split
+        denom += w * pair[j].y;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            acc[4 * q] += w * x[j][q].x; acc[4 * q + 1] += w * x[j][q].y;
+            acc[4 * q + 2] += w * x[j][q].z; acc[4 * q + 3] += w * x[j][q].w;
         }
+    }
+#pragma unroll
+    for (int o = 1; o <= 2; o <<= 1) {
+        denom += __shfl_xor_sync(0xffffffffu, denom, o);
+#pragma unroll
+        for (int e = 0; e < 16; e++) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], o);
+    }
+    if (valid && sub == 0) merge_store(g, head, grow, b, acc, denom);
+}
+
+// `rows` rows of one group, starting at `first_row` with stride `row_step`, all 16-column blocks: the whole CTA.
+__device__ __forceinline__ void merge_rows(const MergeParams& g, int group, int first_row, int row_step, int rows) {
+    const int bpr = g.head_dim / 16;
+    const int items = rows * bpr;
+    if (g.splits > 4 && g.splits <= 16) {
+        for (int base = 0; base < items; base += kThreads / 4) {          // warp-uniform trip count
+            const int i = base + (threadIdx.x >> 2);
+            const bool valid = i < items;
+            const int ii = valid ? i : 0;
+            merge_item_wide(g, group, first_row + (ii / bpr) * row_step, ii % bpr, valid);
+        }
+    } else {
+        for (int i = threadIdx.x; i < items; i += kThreads) merge_item(g, group, first_row + (i / bpr) * row_step, i % bpr);
     }
 }
 
 __device__ __forceinline__ void merge_tile(const MergeParams& g, int tile) {
-    const int bpr = g.head_dim / 16;
     const int chunks = (min(g.nq, kAttnQRows) + kMergeRows - 1) / kMergeRows;
     const int group = tile / chunks, r0 = (tile - group * chunks) * kMergeRows;
     const int q_valid = min(kAttnQRows, g.nq - (group / g.heads) * kAttnQRows);
-    const int rows = min(kMergeRows, q_valid - r0);
-    for (int i = threadIdx.x; i < rows * bpr; i += kThreads) merge_item(g, group, r0 + i / bpr, i % bpr);
+    merge_rows(g, group, r0, 1, max(0, min(kMergeRows, q_valid - r0)));
 }
 
 __device__ __forceinline__ void merge_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int stage_index,
@@ -435,10 +506,9 @@ __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl
             g.out = a.out; g.ldo = a.ldo;
             g.out_fp4 = a.out_fp4; g.out_scales = a.out_scales; g.out_blocks = a.out_blocks;
             g.out_inv_gs = a.out_inv_gs; g.ld_fp4 = a.ld_fp4;
-            const int bpr = a.head_dim / 16;
             const int q_valid = min(kAttnQRows, a.nq - (group / a.heads) * kAttnQRows);
             const int my_rows = (q_valid - split + a.splits - 1) / a.splits;       // rows split, split+splits, ...
-            for (int i = threadIdx.x; i < my_rows * bpr; i += kThreads) merge_item(g, group, split + (i / bpr) * a.splits, i % bpr);
+            merge_rows(g, group, split, a.splits, max(0, my_rows));
             if (stamp_t && threadIdx.x == 0) stamp_t[7] = static_cast<long long>(global_ns());
         }
         cta_publish_tile(prog, st, t);

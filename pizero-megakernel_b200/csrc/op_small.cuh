@@ -3,6 +3,7 @@
 #pragma once
 #include "vm_core.cuh"
 #include "op_norm.cuh"
+#include "op_attention.cuh"
 
 namespace pi0 {
 
@@ -91,112 +92,159 @@ __device__ __forceinline__ void embed_instruction(const VmProgram& prog, Ctl* ct
     }
 }
 
-// out[r, n] = f(sum_k x[r, k] * W[n, k]) in FP32.  A tile is 16 output columns for all rows: the CTA stages K-chunks
-// of x (up to 64 rows) and of the 16 weight rows in shared memory; thread (col = tid % 16, ty = tid / 16) owns rows
-// ty, ty+16, ty+32, ty+48 of its column, so every shared-memory read is a 16-byte broadcast or conflict-free access.
+// out[r, n] = f(sum_k x[r, k] * W[n, k]) in FP32.  A tile is 16 output columns for a block of rows (64; 32 or 16 when
+// that still leaves every tile a CTA of its own: each tile stages all of its x rows, so shorter blocks mean fewer
+// bytes per CTA, and an operator with few columns would otherwise occupy one or two CTAs). K runs in chunks of 128 through a four-deep
+// cp.async ring in shared memory (x rows as stored, FP32 or BF16, and the 16 weight rows), so the L2 latency of a
+// chunk is paid once per tile, not once per chunk. Thread (col = tid % 16, ty = tid / 16) owns rows ty, ty + 16, ...
+// of its column; every shared-memory read is a 16-byte broadcast or conflict-free access.
 constexpr int kLinCols = 16;
 constexpr int kLinRows = 64;
 constexpr int kLinChunk = 128;
-constexpr int kLinLd = kLinChunk + 4;
+constexpr int kLinLd = kLinChunk + 4;                                  // floats per staged row (padded)
+constexpr int kLinStages = 4;
+constexpr int kLinStageBytes = (kLinRows + kLinCols) * kLinLd * 4;     // x block + weight rows
+static_assert(kLinStages * kLinStageBytes <= kDataBytes, "linear32 ring exceeds the data region");
 
-__device__ __forceinline__ void linear32_tile(const Linear32Params& p, const void* xbase, const float* prev, int tile,
-                                              uint8_t* data) {
-    float4* xs = reinterpret_cast<float4*>(data);                                   // [64][kLinLd] floats
-    float4* ws = xs + kLinRows * kLinLd / 4;                                        // [16][kLinLd] floats
-    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
-    const int n = tile * kLinCols + tx;
-    for (int r0 = 0; r0 < p.rows; r0 += kLinRows) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f}, ss[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int kc = 0; kc < p.k; kc += kLinChunk) {
-            const int kw4 = min(kLinChunk, p.k - kc) >> 2;
-            __syncthreads();
-            // stage the chunk: all loads of a thread (8 of x, 2 of w for a full chunk) are issued before any store
-            constexpr int kXLoads = kLinRows * (kLinChunk / 4) / kThreads, kWLoads = kLinCols * (kLinChunk / 4) / kThreads;
-            float4 xv[kXLoads], wv[kWLoads];
-#pragma unroll
-            for (int j = 0; j < kXLoads; j++) {
-                const int i = j * kThreads + threadIdx.x;
-                const int r = i / kw4, c = i - r * kw4;
-                xv[j] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (i < kLinRows * kw4 && r0 + r < p.rows) {
-                    const size_t off = static_cast<size_t>(r0 + r + p.x_row_offset) * p.ldx + kc + c * 4;
-                    if (p.x_bf16) {
-                        uint2 u = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(xbase) + off));
-                        float2 lo = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.x));
-                        float2 hi = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u.y));
-                        xv[j] = make_float4(lo.x, lo.y, hi.x, hi.y);
-                    } else {
-                        xv[j] = __ldcg(reinterpret_cast<const float4*>(static_cast<const float*>(xbase) + off));
-                    }
-                }
-            }
-#pragma unroll
-            for (int j = 0; j < kWLoads; j++) {
-                const int i = j * kThreads + threadIdx.x;
-                const int r = i / kw4, c = i - r * kw4;
-                const int col = tile * kLinCols + r;
-                wv[j] = (i < kLinCols * kw4 && col < p.n) ? __ldg(reinterpret_cast<const float4*>(p.w + static_cast<size_t>(col) * p.k + kc) + c)
-                                                          : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int j = 0; j < kXLoads; j++) {
-                const int i = j * kThreads + threadIdx.x;
-                if (i < kLinRows * kw4) xs[(i / kw4) * (kLinLd / 4) + (i % kw4)] = xv[j];
-            }
-#pragma unroll
-            for (int j = 0; j < kWLoads; j++) {
-                const int i = j * kThreads + threadIdx.x;
-                if (i < kLinCols * kw4) ws[(i / kw4) * (kLinLd / 4) + (i % kw4)] = wv[j];
-            }
-            __syncthreads();
-            if (p.rms) {
-#pragma unroll 4
-                for (int c = 0; c < kw4; c++) {
-                    const float4 w4 = ws[tx * (kLinLd / 4) + c];
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const float4 x4 = xs[(ty + 16 * i) * (kLinLd / 4) + c];
-                        acc[i] = fmaf(x4.x, w4.x, fmaf(x4.y, w4.y, fmaf(x4.z, w4.z, fmaf(x4.w, w4.w, acc[i]))));
-                        ss[i] = fmaf(x4.x, x4.x, fmaf(x4.y, x4.y, fmaf(x4.z, x4.z, fmaf(x4.w, x4.w, ss[i]))));
-                    }
-                }
-            } else {
-#pragma unroll 4
-                for (int c = 0; c < kw4; c++) {
-                    const float4 w4 = ws[tx * (kLinLd / 4) + c];
-#pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        const float4 x4 = xs[(ty + 16 * i) * (kLinLd / 4) + c];
-                        acc[i] = fmaf(x4.x, w4.x, fmaf(x4.y, w4.y, fmaf(x4.z, w4.z, fmaf(x4.w, w4.w, acc[i]))));
-                    }
-                }
-            }
+__device__ __forceinline__ void linear32_issue(const Linear32Params& p, const void* xbase, uint8_t* stage, int col0, int r0,
+                                               int row_block, int kc) {
+    const int kw = min(kLinChunk, p.k - kc);
+    float* xs = reinterpret_cast<float*>(stage);
+    float* ws = xs + kLinRows * kLinLd;
+    if (p.x_bf16) {
+        // BF16 rows are staged as stored (8 elements per 16-byte copy) in the first half of each padded row
+        const int per_row = kw >> 3;
+        const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(xbase);
+        for (int i = threadIdx.x; i < row_block * per_row; i += kThreads) {
+            const int r = i / per_row, c = i - r * per_row;
+            const bool ok = r0 + r < p.rows;
+            const __nv_bfloat16* from = ok ? src + static_cast<size_t>(r0 + r + p.x_row_offset) * p.ldx + kc + c * 8 : src;
+            cp_async16(reinterpret_cast<__nv_bfloat16*>(xs + r * kLinLd) + c * 8, from, ok);
         }
-        if (n < p.n) {
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const int r = r0 + ty + 16 * i;
-                if (r >= p.rows) continue;
-                float v = acc[i];
-                if (p.rms) v *= rsqrtf(ss[i] / static_cast<float>(p.k) + p.eps);
-                if (p.bias) v += p.bias[n];
-                if (p.silu) v = v / (1.f + expf(-v));
-                if (p.euler) v = __fadd_rn(__ldcg(prev + static_cast<size_t>(r) * p.n + n), __fmul_rn(p.dt, v));
-                if (p.out_bf16) static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = __float2bfloat16_rn(v);
-                else static_cast<float*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = v;
-            }
+    } else {
+        const int per_row = kw >> 2;
+        const float* src = static_cast<const float*>(xbase);
+        for (int i = threadIdx.x; i < row_block * per_row; i += kThreads) {
+            const int r = i / per_row, c = i - r * per_row;
+            const bool ok = r0 + r < p.rows;
+            const float* from = ok ? src + static_cast<size_t>(r0 + r + p.x_row_offset) * p.ldx + kc + c * 4 : src;
+            cp_async16(xs + r * kLinLd + c * 4, from, ok);
         }
+    }
+    const int per_row = kw >> 2;
+    for (int i = threadIdx.x; i < kLinCols * per_row; i += kThreads) {
+        const int r = i / per_row, c = i - r * per_row;
+        const bool ok = col0 + r < p.n;
+        const float* from = ok ? p.w + static_cast<size_t>(col0 + r) * p.k + kc + c * 4 : p.w;
+        cp_async16(ws + r * kLinLd + c * 4, from, ok);
     }
 }
 
+// Four groups of 64 threads split every K chunk between them; inside a group thread (tx = t % 4, ty = t / 4) owns
+// columns 4 tx .. 4 tx + 3 of rows ty, ty + 16, ... (16 R outputs), so a step of four k values costs 4 + R 16-byte
+// shared-memory reads for 16 R fused multiply-adds (the operator is bound by shared-memory bandwidth, not by the
+// FP32 pipe). The four partial sums of an output meet in shared memory at the end and are added in a fixed order.
+template <int R>
+__device__ __forceinline__ void linear32_tile(const Linear32Params& p, const void* xbase, const float* prev, int tile,
+                                              uint8_t* data, long long* stamp) {
+    constexpr int row_block = 16 * R;
+    const int col_tiles = (p.n + kLinCols - 1) / kLinCols;
+    const int ct = tile % col_tiles, r0 = (tile / col_tiles) * row_block;
+    const int col0 = ct * kLinCols;
+    const int kg = threadIdx.x >> 6, t64 = threadIdx.x & 63;
+    const int tx = t64 & 3, ty = t64 >> 2;
+    const int nchunks = (p.k + kLinChunk - 1) / kLinChunk;
+    const bool rms = p.rms != 0, x_bf16 = p.x_bf16 != 0;
+    float acc[R][4], ss[R];
+#pragma unroll
+    for (int i = 0; i < R; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; ss[i] = 0.f; }
+    __syncthreads();                                   // the previous tile's readers are done with the ring
+    for (int s = 0; s < kLinStages - 1; ++s) {
+        if (s < nchunks) linear32_issue(p, xbase, data + s * kLinStageBytes, col0, r0, row_block, s * kLinChunk);
+        cp_async_commit();
+    }
+    for (int c = 0; c < nchunks; ++c) {
+        cp_async_wait<kLinStages - 2>();               // chunk c has landed (this thread's copies) ...
+        __syncthreads();                               // ... and everybody's; the buffer of chunk c - 1 is free
+        if (stamp && c == 0 && threadIdx.x == 0) stamp[4] = static_cast<long long>(global_ns());
+        const int next = c + kLinStages - 1;
+        if (next < nchunks) linear32_issue(p, xbase, data + (next % kLinStages) * kLinStageBytes, col0, r0, row_block, next * kLinChunk);
+        cp_async_commit();
+        const float* xs = reinterpret_cast<const float*>(data + (c % kLinStages) * kLinStageBytes);
+        const float4* ws4 = reinterpret_cast<const float4*>(xs + kLinRows * kLinLd) + 4 * tx * (kLinLd / 4);
+        const int kw4 = min(kLinChunk, p.k - c * kLinChunk) >> 2;
+        const int q_end = min(kw4, kg * 8 + 8);
+#pragma unroll 2
+        for (int q = kg * 8; q < q_end; q++) {
+            float4 w4[4], x4[R];
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) w4[cc] = ws4[cc * (kLinLd / 4) + q];
+#pragma unroll
+            for (int i = 0; i < R; i++) {
+                if (x_bf16) {
+                    const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(xs + (ty + 16 * i) * kLinLd) + q * 4);
+                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+                    x4[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                } else {
+                    x4[i] = *reinterpret_cast<const float4*>(xs + (ty + 16 * i) * kLinLd + q * 4);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < R; i++) {
+#pragma unroll
+                for (int cc = 0; cc < 4; cc++)
+                    acc[i][cc] = fmaf(x4[i].x, w4[cc].x, fmaf(x4[i].y, w4[cc].y, fmaf(x4[i].z, w4[cc].z, fmaf(x4[i].w, w4[cc].w, acc[i][cc]))));
+                if (rms) ss[i] = fmaf(x4[i].x, x4[i].x, fmaf(x4[i].y, x4[i].y, fmaf(x4[i].z, x4[i].z, fmaf(x4[i].w, x4[i].w, ss[i]))));
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                   // the ring is free: it now holds the partial sums
+    if (stamp && threadIdx.x == 0) stamp[5] = static_cast<long long>(global_ns());
+    float* red = reinterpret_cast<float*>(data);       // [4 groups][row_block][16 columns]
+    float* red_ss = red + 4 * row_block * kLinCols;    // [4 groups][row_block]
+#pragma unroll
+    for (int i = 0; i < R; i++) {
+        *reinterpret_cast<float4*>(red + (kg * row_block + ty + 16 * i) * kLinCols + 4 * tx) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        if (tx == 0) red_ss[kg * row_block + ty + 16 * i] = ss[i];
+    }
+    __syncthreads();
+    for (int o = threadIdx.x; o < row_block * kLinCols; o += kThreads) {
+        const int rl = o >> 4, cl = o & 15;
+        const int r = r0 + rl, n = col0 + cl;
+        if (r >= p.rows || n >= p.n) continue;
+        float v = 0.f, sq = 0.f;
+#pragma unroll
+        for (int k4 = 0; k4 < 4; k4++) {
+            v += red[(k4 * row_block + rl) * kLinCols + cl];
+            sq += red_ss[k4 * row_block + rl];
+        }
+        if (rms) v *= rsqrtf(sq / static_cast<float>(p.k) + p.eps);
+        if (p.bias) v += p.bias[n];
+        if (p.silu) v = v / (1.f + expf(-v));
+        if (p.euler) v = __fadd_rn(__ldcg(prev + static_cast<size_t>(r) * p.n + n), __fmul_rn(p.dt, v));
+        if (p.out_bf16) static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = __float2bfloat16_rn(v);
+        else static_cast<float*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = v;
+    }
+    if (stamp && threadIdx.x == 0) stamp[6] = static_cast<long long>(global_ns());
+    // Optional extra row: FP32 values of this tile's columns copied (as BF16) to the row in front of the output,
+    // which is how the state token joins the action tokens without a stage of its own.
+    if (p.row0_src && r0 == 0 && threadIdx.x < kLinCols && col0 + threadIdx.x < p.n)
+        static_cast<__nv_bfloat16*>(p.row0_dst)[col0 + threadIdx.x] = __float2bfloat16_rn(__ldcg(p.row0_src + col0 + threadIdx.x));
+}
+
 __device__ __forceinline__ void linear32_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
-                                                     int stage_index, int first, int count) {
+                                                     int stage_index, int first, int count, long long* stamp) {
     const Linear32Params& p = st.p.lin;
     const void* xbase = p.slot == 2 ? static_cast<const void*>(prog.in.state)
                         : p.slot == 3 ? static_cast<const void*>(prog.in.noise) : p.x;
     const float* prev = p.prev_slot == 3 ? prog.in.noise : p.prev;
     for (int t = first; t < first + count; ++t) {
-        linear32_tile(p, xbase, prev, t, data);
+        long long* stamp_t = t == first ? stamp : nullptr;
+        if (p.row_block == 16) linear32_tile<1>(p, xbase, prev, t, data, stamp_t);
+        else if (p.row_block == 32) linear32_tile<2>(p, xbase, prev, t, data, stamp_t);
+        else linear32_tile<4>(p, xbase, prev, t, data, stamp_t);
         cta_publish_tile(prog, st, t);
     }
 }

@@ -793,7 +793,8 @@ extern "C" int create_linear32(void** handle, const void* x, const float* w, con
     if (!handle) return cudaErrorInvalidValue;
     *handle = nullptr;
     if (!w || !out || rows < 1 || n < 1 || k < 4 || k % 4 || ldx < k || ldo < n || (slot != 0 && slot != 2 && slot != 3) ||
-        (slot == 0 && !x) || (prev_slot != 0 && prev_slot != 3) || ((flags & 16) && prev_slot == 0 && !prev) || x_row_offset < 0)
+        (slot == 0 && !x) || (prev_slot != 0 && prev_slot != 3) || ((flags & 16) && prev_slot == 0 && !prev) || x_row_offset < 0 ||
+        ldx % 4 || ((flags & 1) && (k % 8 || ldx % 8)))            // rows are staged with 16-byte asynchronous copies
         return cudaErrorInvalidValue;
     Op* op = nullptr;
     int e = new_op(&op, workers);
@@ -801,16 +802,29 @@ extern "C" int create_linear32(void** handle, const void* x, const float* w, con
     StageDesc& d = op->desc;
     d.kind = OP_LINEAR32;
     finish_desc(d);
-    d.tiles = (n + kLinCols - 1) / kLinCols;
+    // few columns (the action head): blocks of 16 rows, so that more than one or two CTAs share the operator
+    const int col_tiles = (n + kLinCols - 1) / kLinCols;
+    const int row_block = (n <= 64 && rows > 16) ? 16 : (rows > 32 && rows <= 64 && 2 * col_tiles <= op->workers) ? 32 : kLinRows;
+    d.tiles = ((n + kLinCols - 1) / kLinCols) * ((rows + row_block - 1) / row_block);
     d.bands = 1;
     d.band_div = d.tiles;
-    op->cost = std::max(64, (k * rows / 16 + 63) / 64 * 64);
+    op->cost = std::max(64, (k * std::min(rows, row_block) / 16 + 63) / 64 * 64);
     Linear32Params& p = d.p.lin;
+    p.row_block = row_block;
     p.x = x; p.w = w; p.bias = bias; p.prev = prev; p.out = out;
     p.rows = rows; p.n = n; p.k = k; p.ldx = ldx; p.ldo = ldo;
     p.x_bf16 = flags & 1; p.out_bf16 = (flags >> 1) & 1; p.silu = (flags >> 2) & 1; p.rms = (flags >> 3) & 1; p.euler = (flags >> 4) & 1;
     p.slot = slot; p.prev_slot = prev_slot; p.x_row_offset = x_row_offset; p.dt = dt; p.eps = eps;
     *handle = op;
+    return cudaSuccess;
+}
+// Extension: the tiles of the first row block also store `src` (FP32 [n]) as BF16 at `dst`.
+extern "C" int configure_linear32_extra_row(void* handle, const float* src, void* dst) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_LINEAR32 || !src || !dst) return cudaErrorInvalidValue;
+    op->desc.p.lin.row0_src = src;
+    op->desc.p.lin.row0_dst = dst;
+    op->solo_dirty = true;
     return cudaSuccess;
 }
 extern "C" int create_suffix_assemble(void** handle, const float* state_emb, const float* action_emb, void* out, int chunk,

@@ -73,6 +73,7 @@ _SIGNATURES = {
     "create_patch_embed": [C.POINTER(_P)] + [_P] * 5 + [_I] * 3,
     "create_token_embed": [C.POINTER(_P), _P, _P, _P, _I, _I, _I, _I, _F, _I],
     "create_linear32": [C.POINTER(_P)] + [_P] * 5 + [_I] * 9 + [_F, _F, _I],
+    "configure_linear32_extra_row": [_P, _P, _P],
     "create_suffix_assemble": [C.POINTER(_P), _P, _P, _P, _I, _I, _I],
     "launch_op": [_P, _P],
     "destroy_op": [_P],

@@ -430,7 +430,7 @@ class NativePi0:
         self.buffers.extend((w_state, b_state, w_fused, w_t2, b_t2, final_w, final_b))
         state_emb = self.tensor((1, W), torch.float32)
         s_state = self.linear32("expert.state", None, w_state, b_state, state_emb, rows=1, sources=[], slot=2)
-        h1, h2 = self.tensor((self.chunk_size, W), torch.float32), self.tensor((self.chunk_size, W), torch.float32)
+        h1 = self.tensor((self.chunk_size, W), torch.float32)
         actions = self.tensor((self.chunk_size, c.action_dim), torch.float32)
         xe_a, xe_b = self.tensor((S_pad, W)), self.tensor((S_pad, W))
         cos_s, sin_s = self.rope(S, P)
@@ -448,12 +448,10 @@ class NativePi0:
             first = step == 0
             s_t1 = self.linear32(f"expert.{step}.time_in", None if first else actions, w_fused, step_bias, h1, rows=self.chunk_size,
                                  sources=[(s_prev, ALL)], slot=3 if first else 0, silu=True)
-            s_t2 = self.linear32(f"expert.{step}.time_out", h1, w_t2, b_t2, h2, rows=self.chunk_size, sources=[(s_t1, ALL)])
-            h = C.c_void_p()
-            _native.check(lib.create_suffix_assemble(C.byref(h), state_emb.data_ptr(), h2.data_ptr(), xe_a.data_ptr(), self.chunk_size,
-                                                     W, self.workers), "suffix assemble")
-            self._own(h)
-            s_x = self.add(3, h, f"expert.{step}.assemble", [(s_t2, ALL), (s_state, ALL)])
+            # time_out writes the action tokens as BF16 rows 1.. of the expert input; its first tiles add row 0 (the state token)
+            s_x = self.linear32(f"expert.{step}.time_out", h1, w_t2, b_t2, xe_a[1:], rows=self.chunk_size,
+                                sources=[(s_t1, ALL), (s_state, ALL)], out_bf16=True)
+            _native.check(lib.configure_linear32_extra_row(self.handles[-1], state_emb.data_ptr(), xe_a.data_ptr()), "state row")
             for i in range(c.expert_layers):
                 s_x, _ = self._expert_layer(step, i, xe_a, xe_b, ebufs, S, P, s_x, cos_s, sin_s, cache_stage[i])
             s_prev = self.linear32(f"expert.{step}.euler", xe_a, final_w, final_b, actions, rows=self.chunk_size, sources=[(s_x, ALL)],

@@ -347,6 +347,22 @@ def test_small_operators():
     torch.cuda.synchronize()
     torch.testing.assert_close(o, torch.nn.functional.silu(x @ wl.T + b), rtol=1e-5, atol=1e-5)
     lib.destroy_op(h)
+    # FP32 1024 -> 1024 with BF16 output one row below an extra row (the state token joining the action tokens)
+    rows, n, k = 50, 1024, 1024
+    x, wl, b = torch.randn(rows, k, device=dev), torch.randn(n, k, device=dev) * 0.03, torch.randn(n, device=dev)
+    row0 = torch.randn(n, device=dev)
+    ob = torch.zeros(128, n, dtype=torch.bfloat16, device=dev)
+    h = C.c_void_p()
+    _native.check(lib.create_linear32(C.byref(h), x.data_ptr(), wl.data_ptr(), b.data_ptr(), None, ob[1:].data_ptr(), rows, n, k, k, n, 2, 0, 0, 0,
+                                      0.0, 1e-6, 64), "lin")
+    _native.check(lib.configure_linear32_extra_row(h, row0.data_ptr(), ob.data_ptr()), "extra row")
+    for _ in range(2):
+        _native.check(lib.launch_op(h, None), "launch")
+    torch.cuda.synchronize()
+    torch.testing.assert_close(ob[1:51].float(), (x.double() @ wl.double().T + b).float().bfloat16().float(), rtol=1e-2, atol=1e-2)
+    assert float((ob[1:51].float() - (x.double() @ wl.double().T + b).float()).abs().max()) < 2e-2
+    assert torch.equal(ob[0], row0.bfloat16()) and not ob[51:].any()
+    lib.destroy_op(h)
     # BF16 input with row offset, RMS factor and Euler update
     rows, n, k = 50, 32, 1024
     xb = torch.randn(128, k, device=dev).bfloat16()
