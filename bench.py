@@ -33,7 +33,10 @@ WORKLOADS = {
     "cfg5": dict(views=3, prompt=16, chunk=63, steps=10, name="configs[4]: pi0 forward, 3 views, 16-token prompt, chunk 63, 10 Euler steps"),
 }
 # Algorithmic work of one forward (GEMM + attention FLOPs) and NVFP4 weight bytes read once.
-WORK = {"cfg4": dict(gflop=3997.0, weight_mb=1461.0), "cfg5": dict(gflop=4136.0, weight_mb=1461.0)}
+# dram_bytes: dram__bytes_read.sum + dram__bytes_write.sum of one launch from an ncu capture of this bench (3.31 GB read: the
+# 1.29 GB of vision/prefix weights once and the 0.17 GB of expert weights in each of the 10 Euler steps; 2.00 GB written:
+# activations and the FP32 split-KV partials leaving the L2 behind the weight stream).  None: not captured.
+WORK = {"cfg4": dict(gflop=3997.0, weight_mb=1461.0, dram_bytes=5.30e9), "cfg5": dict(gflop=4136.0, weight_mb=1461.0, dram_bytes=None)}
 
 
 def percentile(values, q):
@@ -253,7 +256,7 @@ def run_engine(args, wl, rank, world):
                 "clocks": clocks, "gpu_launches": args.steps,
                 "e2e": {"value": e2e_p50, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak,
-                             "traffic": None, "peak_source": peak_src, "kernel": "pi0_vm_kernel (one launch per step)",
+                             "traffic": work["dram_bytes"], "traffic_unit": "bytes per launch (ncu, profiles/)", "peak_source": peak_src, "kernel": "pi0_vm_kernel (one launch per step)",
                              "algorithmic_gflop_per_launch": work["gflop"],
                              "weight_stream_gbs": work["weight_mb"] / p50, "hbm_peak_gbs": hbm_peak},
                 "phases": phases}

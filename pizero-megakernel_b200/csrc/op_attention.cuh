@@ -12,6 +12,11 @@ namespace pi0 {
 
 constexpr int kAttnQRows = 128;
 constexpr int kAttnChunk = 64;
+// Shared memory an attention tile may touch (head dimension 256): Q, two K buffers, two V buffers of 264-element rows,
+// and for split-KV tiles of at most 64 queries the partial-row staging area 4 KiB into the V buffers.
+constexpr int kAttnOperandBytes = 3 * kAttnQRows * (256 + 8) * 2;
+constexpr int kAttnStageEnd = 2 * kAttnQRows * (256 + 8) * 2 + 4096 + 4 * 16 * 264 * 4;
+constexpr int kAttnSmemBytes = kAttnStageEnd > kAttnOperandBytes ? kAttnStageEnd : kAttnOperandBytes;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
     const int bytes = valid ? 16 : 0;       // 0 source bytes: the 16 destination bytes are zero-filled
@@ -241,22 +246,35 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data, long lon
 
     if (a.splits > 1) {
         if (writer) {
+            // The un-normalised rows go through shared memory (each warp's own slice of the now idle K/V buffers,
+            // rows padded to 264 floats) so that they leave as whole 1 KiB rows, 512 contiguous bytes per store
+            // instruction, instead of 8-byte pieces scattered over eight rows.
+            constexpr int SLD = 264;
+            // (paired warps: behind the exchange area, which other warps may still be reading)
+            float* stage = paired ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sV) + 4096) + rb * 16 * SLD
+                                  : reinterpret_cast<float*>(sK) + warp * 16 * SLD;
+            static_assert(kAttnStageEnd <= kDataBytes, "partial staging exceeds the data region");
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                float* srow = stage + ((lane >> 2) + r * 8) * SLD + 2 * (lane & 3);
+#pragma unroll
+                for (int j = 0; j < ONT; j++) *reinterpret_cast<float2*>(srow + j * 8) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+            }
+            __syncwarp();
             float* po = a.partial_o + static_cast<size_t>(tile) * kAttnQRows * a.head_dim;
             float* pml = a.partial_ml + static_cast<size_t>(tile) * kAttnQRows * 2;
+            const int row0 = rb * 16;
+            for (int r = 0; r < 16 && row0 + r < q_valid; ++r) {
+                float* dst = po + static_cast<size_t>(row0 + r) * a.head_dim;
+                for (int c = lane * 4; c < a.head_dim; c += 128)
+                    *reinterpret_cast<float4*>(dst + c) = *reinterpret_cast<const float4*>(stage + r * SLD + c);
+            }
 #pragma unroll
             for (int r = 0; r < 2; r++) {
                 const int row = row_a + r * 8;
-                if (row < q_valid) {
-#pragma unroll
-                    for (int j = 0; j < ONT; j++) {
-                        const int col = j * 8 + 2 * (lane & 3);
-                        if (col < a.head_dim)
-                            *reinterpret_cast<float2*>(po + static_cast<size_t>(row) * a.head_dim + col) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
-                    }
-                    if ((lane & 3) == 0) {
-                        pml[row * 2] = m_run[r];
-                        pml[row * 2 + 1] = l_run[r];
-                    }
+                if (row < q_valid && (lane & 3) == 0) {
+                    pml[row * 2] = m_run[r];
+                    pml[row * 2 + 1] = l_run[r];
                 }
             }
         }

@@ -1071,7 +1071,7 @@ constexpr int kNoAllocMaxParts = 64;                 // heads * splits
 constexpr int kNoAllocHeadDim = 256;
 constexpr size_t kNoAllocPartialO = static_cast<size_t>(kNoAllocMaxParts) * kAttnQRows * kNoAllocHeadDim * sizeof(float);
 constexpr size_t kNoAllocPartialMl = static_cast<size_t>(kNoAllocMaxParts) * kAttnQRows * 2 * sizeof(float);
-constexpr int kNoAllocSmem = kAttnQRows * (kNoAllocHeadDim + 8) * 2 + 4 * kAttnChunk * (kNoAllocHeadDim + 8) * 2 + 1024;
+constexpr int kNoAllocSmem = kAttnSmemBytes + 1024;     // operands and partial-row staging of attn_tile, plus alignment slack
 
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocPartialO + kNoAllocPartialMl];
 
