@@ -494,7 +494,8 @@ __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl
         else attn_tile<80>(a, t, data, stamp_t);
         if (a.splits > 1 && a.fused_merge) {
             const int split = t % a.splits, group = t / a.splits;         // group: one head of one 128-query tile
-            __threadfence();                                   // this tile's partials before its ticket
+            // The barrier orders every thread's partial stores before thread 0's release increment below, which
+            // is cumulative at GPU scope: no per-thread fence is needed.
             __syncthreads();
             if (threadIdx.x == 0) {
                 const unsigned int target = static_cast<unsigned int>(a.splits) * prog.epoch;

@@ -23,7 +23,7 @@ import torch
 
 from native_pi0 import _native
 from native_pi0._native import NativeSpec
-from native_pi0.program import LinearWork, linear_streams, program_summary, validate_streams
+from native_pi0.program import LinearWork, linear_streams, program_summary, spread_streams, validate_streams
 from native_pi0.quantization import swizzled_size
 from native_pi0.storage import packed_tma_buffer
 from native_pi0.weights import EXPERT, LANGUAGE, PROJECTOR, VISION, Pi0Config, StateDictModel
@@ -65,8 +65,8 @@ class NativePi0:
         return cls(StateDictModel(config or Pi0Config(), state_dict), **kwargs)
 
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
-                 library=None, workers=None, partitioned=False, expert_splits=16, prefix_splits=None, expert_block_n=64,
-                 rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True):
+                 library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=64,
+                 rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="spread"):
         config = getattr(model, "config", None)
         if config is None or getattr(config, "pi05", False) or precision not in ("auto", "nvfp4"):
             raise ValueError("This engine runs ordinary pi0 with NVFP4 transformers (precision 'auto' or 'nvfp4')")
@@ -84,6 +84,9 @@ class NativePi0:
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self.keep_debug_outputs = keep_debug_outputs
         self.tile_weights = tile_weights
+        if schedule not in ("spread", "linear"):
+            raise ValueError("schedule must be 'spread' or 'linear'")
+        self.schedule = schedule
         self.verbose = verbose
         sd = model.state_dict()
         self.device = next(iter(sd.values())).device
@@ -311,6 +314,16 @@ class NativePi0:
         s_pl = self.norm("vision.post_layernorm", xa, a_ln, rows=M, sources=[(s_x, SAME)], kind="layer", gamma=gp, beta=bp, eps=c.ln_eps)
         return s_pl, a_ln
 
+    def _expert_splits(self, keys):
+        """KV splits of the expert attention: as many as leave every tile a worker of its own that did NOT run a tile
+        of the QKV projection in front of it (such a worker starts 2-3 microseconds late), at most 16 and at least
+        32 keys per split."""
+        if self.expert_splits is not None:
+            return int(self.expert_splits)
+        c = self.config
+        qkv_tiles = -(-(c.heads + 2) * c.head_dim // self.expert_block_n)
+        return max(1, min(16, (self.workers - qkv_tiles) // c.heads, keys // 32))
+
     def _prefix_splits(self, rows):
         """KV splits of the prefix attention: as many as keep every tile of the stage on a worker of its own (the
         tiles of a head meet inside the stage to merge their partial results), at most four."""
@@ -464,7 +477,11 @@ class NativePi0:
         self.output = actions.view(1, self.chunk_size, c.action_dim)
         self.component_ranges = {"vision": (0, vision_end), "prefix": (vision_end, prefix_end), "expert": (prefix_end, len(self.stages))}
         # ---------------- static instruction streams + program
-        self.code = linear_streams([LinearWork(t, k) for t, k in zip(self.stage_tiles, self.stage_cost)], self.workers)
+        work = [LinearWork(t, k) for t, k in zip(self.stage_tiles, self.stage_cost)]
+        if self.schedule == "spread":
+            self.code = spread_streams(work, self.workers, [[s for s in spec.sources] for spec in self.stages])
+        else:
+            self.code = linear_streams(work, self.workers)
         validate_streams(self.code, self.stage_tiles)
         self.plan = program_summary(self.code)
         self.plan["stages"] = len(self.stages)
@@ -477,7 +494,7 @@ class NativePi0:
     def _expert_layer(self, step, i, x_in, x_mid, bufs, S, P, s_x, cos, sin, prefix_cache_stage):
         """Every Euler step wires its own stages; the NVFP4 weights are shared through the keyed weight cache."""
         return self._gemma_layer(f"expert.{step}.{i}", EXPERT, i, x_in, x_mid, bufs, rows=S, s_x=s_x, extra_sources=[], cos=cos, sin=sin,
-                                 cache=self.caches[i], cache_base=P, attention_rows=P + S, mask_prefix=P, splits=self.expert_splits,
+                                 cache=self.caches[i], cache_base=P, attention_rows=P + S, mask_prefix=P, splits=self._expert_splits(P + S),
                                  kv_only=False, block_n=self.expert_block_n, prefix_cache_stage=prefix_cache_stage)
 
     # ------------------------------------------------------------------------------------------ running

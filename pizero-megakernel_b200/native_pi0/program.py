@@ -52,6 +52,46 @@ def linear_streams(stages, workers):
     return code
 
 
+def spread_streams(stages, workers, sources):
+    """Streams in the layout of ``linear_streams`` for a chain of short, dependent stages.
+
+    ``linear_streams`` hands each stage to the least loaded workers. A worker that has just run a tile of a stage
+    is the last to learn that the next stage may start: it still has to publish, fetch its next instruction and
+    issue its first copies, while an idle worker has done all that in advance and only polls a counter (a
+    difference of 2-3 microseconds per stage on B200). Here the tiles of a stage go first to workers whose previous
+    instruction is NOT one of the stage's sources (``sources[i]``: indices of the stages stage ``i`` waits for);
+    among those, to the least loaded, ties to the lower index. Stages with at least as many tiles as workers
+    are split exactly as in ``linear_streams``."""
+    if not isinstance(workers, int) or workers < 1 or workers > MAX_WORKERS:
+        raise ValueError("Expected 1..148 B200 workers")
+    stages = tuple(stages)
+    if not stages or len(sources) != len(stages) or any(w.tiles < 1 or w.k < 64 or w.k % 64 for w in stages):
+        raise ValueError("Invalid stage geometry")
+    load = np.zeros(workers, dtype=np.int64)
+    last = np.full(workers, -1, dtype=np.int64)          # the stage of each worker's previous instruction
+    rows = [[] for _ in range(workers)]
+    index_of = np.arange(workers)
+    for index, work in enumerate(stages):
+        parts = min(workers, work.tiles)
+        small, extra = divmod(work.tiles, parts)
+        src = [s for s in sources[index] if s is not None and s >= 0]
+        late = np.isin(last, src).astype(np.int64) if src else np.zeros(workers, dtype=np.int64)
+        order = np.lexsort((index_of, load, late))[:parts]            # keys: late first, then load, then index
+        start = 0
+        for rank, worker in enumerate(order.tolist()):
+            count = small + (1 if rank < extra else 0)
+            rows[worker].append((1, index, start, count))
+            load[worker] += count * work.k
+            last[worker] = index
+            start += count
+    length = max(len(r) for r in rows)
+    code = np.zeros((workers, length, WIDTH), dtype=np.int32)
+    for worker, entries in enumerate(rows):
+        if entries:
+            code[worker, :len(entries), :4] = np.asarray(entries, dtype=np.int32)
+    return code
+
+
 def program_summary(code):
     code = np.asarray(code)
     used = code[:, :, 0] != 0

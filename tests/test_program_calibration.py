@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from native_pi0.calibration import ActivationCalibration, cache_key, checkpoint_digest, fp32_descale
-from native_pi0.program import LinearWork, linear_streams, program_summary, validate_streams
+from native_pi0.program import LinearWork, linear_streams, program_summary, spread_streams, validate_streams
 
 
 def test_linear_streams_match_reference(golden_dir):
@@ -30,6 +30,31 @@ def test_linear_streams_errors():
     for bad in ([], [LinearWork(0, 64)], [LinearWork(1, 32)], [LinearWork(1, 96)]):
         with pytest.raises(ValueError):
             linear_streams(bad, 4)
+
+
+def test_spread_streams_avoid_the_workers_of_a_stage_sources():
+    """The latency-oriented scheduler covers every tile exactly once, keeps stage order per worker and never gives a
+    worker two consecutive dependent stages while idle workers exist; wide stages are split as by linear_streams."""
+    tiles = [7, 40, 104, 16, 7, 128, 16] * 4 + [1536, 96, 7]
+    work = [LinearWork(t, 1024) for t in tiles]
+    sources = [[i - 1, -1, -1, -1] for i in range(len(tiles))]
+    code = spread_streams(work, 148, sources)
+    validate_streams(code, tiles)
+    assert code.shape[0] == 148 and code.dtype == np.int32
+    avoidable = 0
+    for worker in range(148):
+        stages = [row[1] for row in code[worker, :, :4].tolist() if row[0]]
+        avoidable += sum(1 for a, b in zip(stages, stages[1:]) if b == a + 1 and tiles[a] + tiles[b] <= 148)
+    assert avoidable == 0
+    wide = tiles.index(1536)
+    counts = sorted(int(row[3]) for worker in range(148) for row in code[worker, :, :4].tolist() if row[0] and row[1] == wide)
+    assert counts[0] == 10 and counts[-1] == 11 and sum(counts) == 1536
+    # a chain without declared sources degenerates to the reference policy
+    np.testing.assert_array_equal(spread_streams(work, 148, [[-1] * 4] * len(tiles)), linear_streams(work, 148))
+    with pytest.raises(ValueError):
+        spread_streams(work, 148, sources[:-1])
+    with pytest.raises(ValueError):
+        spread_streams(work, 0, sources)
 
 
 def test_validator_rejects_corrupt_programs():
