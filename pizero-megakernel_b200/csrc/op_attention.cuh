@@ -15,7 +15,7 @@ constexpr int kAttnChunk = 64;
 // Shared memory an attention tile may touch (head dimension 256): Q, two K buffers, two V buffers of 264-element rows,
 // and for split-KV tiles of at most 64 queries the partial-row staging area 4 KiB into the V buffers.
 constexpr int kAttnOperandBytes = 3 * kAttnQRows * (256 + 8) * 2;
-constexpr int kAttnStageEnd = 2 * kAttnQRows * (256 + 8) * 2 + 4096 + 4 * 16 * 264 * 4;
+constexpr int kAttnStageEnd = 2 * kAttnQRows * (256 + 8) * 2 + 4096 + 8 * 16 * (128 + 8) * 4;
 constexpr int kAttnSmemBytes = kAttnStageEnd > kAttnOperandBytes ? kAttnStageEnd : kAttnOperandBytes;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -210,20 +210,24 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data, long lon
         l_run[r] += __shfl_xor_sync(0xffffffffu, l_run[r], 2);
     }
 
-    bool writer = warp_active;
+    // Columns of the output this warp finishes: all of them, or (paired warps) one half each - the two warps of a
+    // row block swap the halves they do not keep, so the combine, the staging and the stores are shared by all
+    // eight warps instead of falling on four.
+    constexpr int HALF = ONT / 2;
+    const bool upper = paired && khalf == 1;              // keeps n-tiles [HALF, ONT)
     if (paired) {
         // the loop's last barrier has passed: K and V buffers are free
-        float4* xo = reinterpret_cast<float4*>(sK);                       // [4 blocks][ONT][32 lanes]
-        float4* xml = reinterpret_cast<float4*>(sV);                      // [4 blocks][32 lanes]: m0, m1, l0, l1
-        if (warp_active && khalf == 1) {
+        float4* xo = reinterpret_cast<float4*>(sK);                       // [2 senders][4 blocks][HALF][32 lanes]
+        float4* xml = reinterpret_cast<float4*>(sV);                      // [2 senders][4 blocks][32 lanes]: m0, m1, l0, l1
+        if (warp_active) {
 #pragma unroll
-            for (int j = 0; j < ONT; j++) xo[(rb * ONT + j) * 32 + lane] = make_float4(o[j][0], o[j][1], o[j][2], o[j][3]);
-            xml[rb * 32 + lane] = make_float4(m_run[0], m_run[1], l_run[0], l_run[1]);
+            for (int j = 0; j < ONT; j++)
+                if ((j >= HALF) != upper) xo[((khalf * 4 + rb) * HALF + (j % HALF)) * 32 + lane] = make_float4(o[j][0], o[j][1], o[j][2], o[j][3]);
+            xml[(khalf * 4 + rb) * 32 + lane] = make_float4(m_run[0], m_run[1], l_run[0], l_run[1]);
         }
         __syncthreads();
-        writer = warp_active && khalf == 0;
-        if (writer) {
-            const float4 other = xml[rb * 32 + lane];
+        if (warp_active) {
+            const float4 other = xml[((khalf ^ 1) * 4 + rb) * 32 + lane];
             const float om[2] = {other.x, other.y}, ol[2] = {other.z, other.w};
             float ca[2], cb[2];
 #pragma unroll
@@ -232,64 +236,75 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data, long lon
                 const float m_use = m_new == -INFINITY ? 0.f : m_new;
                 ca[r] = exp2f(m_run[r] - m_use);
                 cb[r] = exp2f(om[r] - m_use);
-                l_run[r] = l_run[r] * ca[r] + ol[r] * cb[r];
+                // the same operation order in both warps (first-half warp's term first): identical row sums
+                l_run[r] = upper ? __fmaf_rn(ol[r], cb[r], __fmul_rn(l_run[r], ca[r])) : __fmaf_rn(l_run[r], ca[r], __fmul_rn(ol[r], cb[r]));
                 m_run[r] = m_new;
             }
 #pragma unroll
             for (int j = 0; j < ONT; j++) {
-                const float4 x = xo[(rb * ONT + j) * 32 + lane];
-                o[j][0] = o[j][0] * ca[0] + x.x * cb[0]; o[j][1] = o[j][1] * ca[0] + x.y * cb[0];
-                o[j][2] = o[j][2] * ca[1] + x.z * cb[1]; o[j][3] = o[j][3] * ca[1] + x.w * cb[1];
+                if ((j >= HALF) == upper) {
+                    const float4 x = xo[(((khalf ^ 1) * 4 + rb) * HALF + (j % HALF)) * 32 + lane];
+                    o[j][0] = o[j][0] * ca[0] + x.x * cb[0]; o[j][1] = o[j][1] * ca[0] + x.y * cb[0];
+                    o[j][2] = o[j][2] * ca[1] + x.z * cb[1]; o[j][3] = o[j][3] * ca[1] + x.w * cb[1];
+                }
             }
         }
     }
+    const int col_lo = upper ? HALF * 8 : 0;               // first output column this warp finishes
 
     if (a.splits > 1) {
-        if (writer) {
-            // The un-normalised rows go through shared memory (each warp's own slice of the now idle K/V buffers,
-            // rows padded to 264 floats) so that they leave as whole 1 KiB rows, 512 contiguous bytes per store
-            // instruction, instead of 8-byte pieces scattered over eight rows.
-            constexpr int SLD = 264;
-            // (paired warps: behind the exchange area, which other warps may still be reading)
-            float* stage = paired ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sV) + 4096) + rb * 16 * SLD
+        if (warp_active) {
+            // The un-normalised rows go through shared memory (each warp's own slice of the now idle K/V buffers)
+            // so that they leave as whole row pieces, 512 contiguous bytes per store instruction, instead of
+            // 8-byte pieces scattered over eight rows.
+            constexpr int SLD = 264, SLDH = HALF * 8 + 8;
+            // (paired warps: behind the exchange areas, which other warps may still be reading)
+            float* stage = paired ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sV) + 4096) + warp * 16 * SLDH
                                   : reinterpret_cast<float*>(sK) + warp * 16 * SLD;
+            const int sld = paired ? SLDH : SLD;
             static_assert(kAttnStageEnd <= kDataBytes, "partial staging exceeds the data region");
 #pragma unroll
             for (int r = 0; r < 2; r++) {
-                float* srow = stage + ((lane >> 2) + r * 8) * SLD + 2 * (lane & 3);
+                float* srow = stage + ((lane >> 2) + r * 8) * sld + 2 * (lane & 3);
 #pragma unroll
-                for (int j = 0; j < ONT; j++) *reinterpret_cast<float2*>(srow + j * 8) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+                for (int j = 0; j < ONT; j++)
+                    if (!paired || (j >= HALF) == upper)
+                        *reinterpret_cast<float2*>(srow + (paired ? j % HALF : j) * 8) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
             }
             __syncwarp();
-            float* po = a.partial_o + static_cast<size_t>(tile) * kAttnQRows * a.head_dim;
+            float* po = a.partial_o + static_cast<size_t>(tile) * kAttnQRows * a.head_dim + col_lo;
             float* pml = a.partial_ml + static_cast<size_t>(tile) * kAttnQRows * 2;
             const int row0 = rb * 16;
+            const int width = paired ? a.head_dim / 2 : a.head_dim;
             for (int r = 0; r < 16 && row0 + r < q_valid; ++r) {
                 float* dst = po + static_cast<size_t>(row0 + r) * a.head_dim;
-                for (int c = lane * 4; c < a.head_dim; c += 128)
-                    *reinterpret_cast<float4*>(dst + c) = *reinterpret_cast<const float4*>(stage + r * SLD + c);
+                for (int c = lane * 4; c < width; c += 128)
+                    *reinterpret_cast<float4*>(dst + c) = *reinterpret_cast<const float4*>(stage + r * sld + c);
             }
+            if (!upper) {
 #pragma unroll
-            for (int r = 0; r < 2; r++) {
-                const int row = row_a + r * 8;
-                if (row < q_valid && (lane & 3) == 0) {
-                    pml[row * 2] = m_run[r];
-                    pml[row * 2 + 1] = l_run[r];
+                for (int r = 0; r < 2; r++) {
+                    const int row = row_a + r * 8;
+                    if (row < q_valid && (lane & 3) == 0) {
+                        pml[row * 2] = m_run[r];
+                        pml[row * 2 + 1] = l_run[r];
+                    }
                 }
             }
         }
         return;
     }
 
-    // normalise, round to BF16, stage the tile in the (now free) Q rows of this warp
-    if (writer) {
+    // normalise, round to BF16, stage the tile in the (now free) Q rows of this warp's row block
+    if (warp_active) {
 #pragma unroll
         for (int r = 0; r < 2; r++) {
             const float inv = l_run[r] > 0.f ? 1.f / l_run[r] : 0.f;
             __nv_bfloat16* dst = sQ + (row_a + r * 8) * LD + 2 * (lane & 3);
 #pragma unroll
             for (int j = 0; j < ONT; j++)
-                *reinterpret_cast<uint32_t*>(dst + j * 8) = pack2_bf16(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
+                if (!paired || (j >= HALF) == upper)
+                    *reinterpret_cast<uint32_t*>(dst + j * 8) = pack2_bf16(o[j][2 * r] * inv, o[j][2 * r + 1] * inv);
         }
     }
     __syncthreads();
