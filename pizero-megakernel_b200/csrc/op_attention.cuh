@@ -3,7 +3,7 @@
 // Eight warps, 16 query rows each. K/V stream through shared memory in 64-key chunks (cp.async, double buffered);
 // QK^T and PV run on the tensor cores (mma.sync m16n8k16, BF16 in, FP32 accumulate) with an online softmax in the
 // exp2 domain. MQA/GQA: the KV head is head / (heads / kv_heads). The pi0 suffix mask hides keys beyond `prefix` from
-// query row 0 (the state token). With splits > 1 the tile writes un-normalised FP32 partials (o, m, l) for OP_MERGE;
+// query row 0 (the state token). With splits > 1 the tile writes un-normalised partials (o as BF16; m, l as FP32) for the merge;
 // otherwise it normalises, rounds to BF16, and optionally quantises the rows to NVFP4 in the same pass.
 #pragma once
 #include "vm_core.cuh"
@@ -15,7 +15,7 @@ constexpr int kAttnChunk = 64;
 // Shared memory an attention tile may touch (head dimension 256): Q, two K buffers, two V buffers of 264-element rows,
 // and for split-KV tiles of at most 64 queries the partial-row staging area 4 KiB into the V buffers.
 constexpr int kAttnOperandBytes = 3 * kAttnQRows * (256 + 8) * 2;
-constexpr int kAttnStageEnd = 2 * kAttnQRows * (256 + 8) * 2 + 4096 + 8 * 16 * (128 + 8) * 4;
+constexpr int kAttnStageEnd = 2 * kAttnQRows * (256 + 8) * 2 + 4096 + 8 * 16 * (128 + 16) * 2;
 constexpr int kAttnSmemBytes = kAttnStageEnd > kAttnOperandBytes ? kAttnStageEnd : kAttnOperandBytes;
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -257,30 +257,33 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data, long lon
             // The un-normalised rows go through shared memory (each warp's own slice of the now idle K/V buffers)
             // so that they leave as whole row pieces, 512 contiguous bytes per store instruction, instead of
             // 8-byte pieces scattered over eight rows.
-            constexpr int SLD = 264, SLDH = HALF * 8 + 8;
+            // Partials are kept as BF16: they are combined with FP32 weights and the result is rounded to BF16 (and
+            // then to NVFP4) anyway, while the bytes a tile has to store and its peers have to fetch are what this
+            // stage spends its time on (a CTA moves about 30 GB/s through ordinary loads and stores).
+            constexpr int SLD = HD + 16, SLDH = HALF * 8 + 16;               // staged row lengths in BF16 elements
             // (paired warps: behind the exchange areas, which other warps may still be reading)
-            float* stage = paired ? reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(sV) + 4096) + warp * 16 * SLDH
-                                  : reinterpret_cast<float*>(sK) + warp * 16 * SLD;
+            __nv_bfloat16* stage = paired ? reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uint8_t*>(sV) + 4096) + warp * 16 * SLDH
+                                          : reinterpret_cast<__nv_bfloat16*>(sK) + warp * 16 * SLD;
             const int sld = paired ? SLDH : SLD;
             static_assert(kAttnStageEnd <= kDataBytes, "partial staging exceeds the data region");
 #pragma unroll
             for (int r = 0; r < 2; r++) {
-                float* srow = stage + ((lane >> 2) + r * 8) * sld + 2 * (lane & 3);
+                __nv_bfloat16* srow = stage + ((lane >> 2) + r * 8) * sld + 2 * (lane & 3);
 #pragma unroll
                 for (int j = 0; j < ONT; j++)
                     if (!paired || (j >= HALF) == upper)
-                        *reinterpret_cast<float2*>(srow + (paired ? j % HALF : j) * 8) = make_float2(o[j][2 * r], o[j][2 * r + 1]);
+                        *reinterpret_cast<uint32_t*>(srow + (paired ? j % HALF : j) * 8) = pack2_bf16(o[j][2 * r], o[j][2 * r + 1]);
             }
             __syncwarp();
-            float* po = a.partial_o + static_cast<size_t>(tile) * kAttnQRows * a.head_dim + col_lo;
+            __nv_bfloat16* po = reinterpret_cast<__nv_bfloat16*>(a.partial_o) + static_cast<size_t>(tile) * kAttnQRows * a.head_dim + col_lo;
             float* pml = a.partial_ml + static_cast<size_t>(tile) * kAttnQRows * 2;
             const int row0 = rb * 16;
             const int width = paired ? a.head_dim / 2 : a.head_dim;
-            for (int r = 0; r < 16 && row0 + r < q_valid; ++r) {
-                float* dst = po + static_cast<size_t>(row0 + r) * a.head_dim;
-                for (int c = lane * 4; c < width; c += 128)
-                    *reinterpret_cast<float4*>(dst + c) = *reinterpret_cast<const float4*>(stage + r * sld + c);
-            }
+            // 16-byte pieces: a row piece of `width` elements takes width / 8 lanes; the other lanes take the next row
+            const int lanes_per_row = width >> 3, rows_per_pass = 32 / lanes_per_row;
+            const int lr = lane / lanes_per_row, lc = (lane - lr * lanes_per_row) * 8;
+            for (int r = lr; r < 16 && row0 + r < q_valid; r += rows_per_pass)
+                *reinterpret_cast<uint4*>(po + static_cast<size_t>(row0 + r) * a.head_dim + lc) = *reinterpret_cast<const uint4*>(stage + r * sld + lc);
             if (!upper) {
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
@@ -345,6 +348,17 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data, long lon
 // (row, 16-column block) per thread, all partial loads of a thread independent of each other.
 constexpr int kMergeRows = 16;
 
+// acc += w * (16 BF16 values of one partial row block)
+__device__ __forceinline__ void merge_accumulate(float (&acc)[16], float w, const uint4 (&x)[2]) {
+    const uint32_t u[8] = {x[0].x, x[0].y, x[0].z, x[0].w, x[1].x, x[1].y, x[1].z, x[1].w};
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u[e]));
+        acc[2 * e] += w * f.x;
+        acc[2 * e + 1] += w * f.y;
+    }
+}
+
 // Normalise one (row, 16-column block), round to BF16 and store it (BF16 and / or NVFP4 with its block scale).
 __device__ __forceinline__ void merge_store(const MergeParams& g, int head, int grow, int b, const float (&acc)[16], float denom) {
     const float inv = denom > 0.f ? 1.f / denom : 0.f;
@@ -376,7 +390,7 @@ __device__ __forceinline__ void merge_item(const MergeParams& g, int group, int 
         const int head = group % g.heads;
         const int grow = (group / g.heads) * kAttnQRows + r;          // row in the output
         const float* ml = g.partial_ml + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * 2;
-        const float* po = g.partial_o + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * g.head_dim + b * 16;
+        const __nv_bfloat16* po = reinterpret_cast<const __nv_bfloat16*>(g.partial_o) + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * g.head_dim + b * 16;
         float big = -INFINITY;
 #pragma unroll 8
         for (int s = 0; s < g.splits; s++) big = fmaxf(big, __ldcg(ml + static_cast<size_t>(s) * kAttnQRows * 2));
@@ -389,24 +403,20 @@ __device__ __forceinline__ void merge_item(const MergeParams& g, int group, int 
         // weights are computed afterwards, so no load waits for arithmetic
         for (int s0 = 0; s0 < g.splits; s0 += 4) {
             float2 pair[4];
-            float4 x[4][4];
+            uint4 x[4][2];
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const int s = min(s0 + j, g.splits - 1);
                 pair[j] = __ldcg(reinterpret_cast<const float2*>(ml + static_cast<size_t>(s) * kAttnQRows * 2));
-                const float4* src = reinterpret_cast<const float4*>(po + static_cast<size_t>(s) * kAttnQRows * g.head_dim);
-#pragma unroll
-                for (int q = 0; q < 4; q++) x[j][q] = __ldcg(src + q);
+                const uint4* src = reinterpret_cast<const uint4*>(po + static_cast<size_t>(s) * kAttnQRows * g.head_dim);
+                x[j][0] = __ldcg(src);
+                x[j][1] = __ldcg(src + 1);
             }
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const float w = s0 + j < g.splits ? exp2f(pair[j].x - ref) : 0.f;     // 0 for a fully masked split
                 denom += w * pair[j].y;
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    acc[4 * q] += w * x[j][q].x; acc[4 * q + 1] += w * x[j][q].y;
-                    acc[4 * q + 2] += w * x[j][q].z; acc[4 * q + 3] += w * x[j][q].w;
-                }
+                merge_accumulate(acc, w, x[j]);
             }
         }
         merge_store(g, head, grow, b, acc, denom);
@@ -421,21 +431,20 @@ __device__ __forceinline__ void merge_item_wide(const MergeParams& g, int group,
     const int head = group % g.heads;
     const int grow = (group / g.heads) * kAttnQRows + r;
     const float* ml = g.partial_ml + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * 2;
-    const float* po = g.partial_o + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * g.head_dim + b * 16;
+    const __nv_bfloat16* po = reinterpret_cast<const __nv_bfloat16*>(g.partial_o) + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * g.head_dim + b * 16;
     float2 pair[4];
-    float4 x[4][4];
+    uint4 x[4][2];
 #pragma unroll
     for (int j = 0; j < 4; j++) {
         const int sp = sub + 4 * j;
         const bool ok = valid && sp < g.splits;
         pair[j] = make_float2(-INFINITY, 0.f);
-#pragma unroll
-        for (int q = 0; q < 4; q++) x[j][q] = make_float4(0.f, 0.f, 0.f, 0.f);
+        x[j][0] = x[j][1] = make_uint4(0u, 0u, 0u, 0u);
         if (ok) {
             pair[j] = __ldcg(reinterpret_cast<const float2*>(ml + static_cast<size_t>(sp) * kAttnQRows * 2));
-            const float4* src = reinterpret_cast<const float4*>(po + static_cast<size_t>(sp) * kAttnQRows * g.head_dim);
-#pragma unroll
-            for (int q = 0; q < 4; q++) x[j][q] = __ldcg(src + q);
+            const uint4* src = reinterpret_cast<const uint4*>(po + static_cast<size_t>(sp) * kAttnQRows * g.head_dim);
+            x[j][0] = __ldcg(src);
+            x[j][1] = __ldcg(src + 1);
         }
     }
     float big = fmaxf(fmaxf(pair[0].x, pair[1].x), fmaxf(pair[2].x, pair[3].x));
@@ -450,11 +459,7 @@ __device__ __forceinline__ void merge_item_wide(const MergeParams& g, int group,
     for (int j = 0; j < 4; j++) {
         const float w = exp2f(pair[j].x - ref);               // 0 for an absent or fully masked split
         denom += w * pair[j].y;
-#pragma unroll
-        for (int q = 0; q < 4; q++) {
-            acc[4 * q] += w * x[j][q].x; acc[4 * q + 1] += w * x[j][q].y;
-            acc[4 * q + 2] += w * x[j][q].z; acc[4 * q + 3] += w * x[j][q].w;
-        }
+        merge_accumulate(acc, w, x[j]);
     }
 #pragma unroll
     for (int o = 1; o <= 2; o <<= 1) {

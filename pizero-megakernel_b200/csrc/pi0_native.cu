@@ -93,7 +93,7 @@ struct Op {
     CUtensorMap* maps = nullptr;       // device: [0] = A, [1] = B
     // attention bookkeeping
     Op* merge = nullptr;               // owned merge stage (splits > 1)
-    float* partial_o = nullptr;
+    uint16_t* partial_o = nullptr;
     float* partial_ml = nullptr;
     Program* solo = nullptr;           // lazily built one/two-stage program for stand-alone launches
     bool solo_dirty = true;
@@ -685,7 +685,7 @@ extern "C" int configure_attention_splits(void* handle, int splits) {
     if (splits > 1) {
         const int groups = a.heads * ((a.nq + kAttnQRows - 1) / kAttnQRows);      // heads x 128-query tiles
         const size_t tasks = static_cast<size_t>(groups) * splits;
-        cudaError_t e = cudaMalloc(&op->partial_o, tasks * kAttnQRows * a.head_dim * sizeof(float));
+        cudaError_t e = cudaMalloc(&op->partial_o, tasks * kAttnQRows * a.head_dim * sizeof(uint16_t));
         if (e == cudaSuccess) e = cudaMalloc(&op->partial_ml, tasks * kAttnQRows * 2 * sizeof(float));
         if (e != cudaSuccess) return e;
         a.partial_o = op->partial_o;
@@ -1127,7 +1127,7 @@ extern "C" int attention_split_noalloc(const void* q, const void* k, const void*
     unsigned char* scratch = nullptr;
     e = noalloc_setup(device, &scratch);
     if (e) return e;
-    float* partial_o = reinterpret_cast<float*>(scratch);
+    uint16_t* partial_o = reinterpret_cast<uint16_t*>(scratch);      // (the array is sized for 4-byte elements; half is used)
     float* partial_ml = reinterpret_cast<float*>(scratch + kNoAllocPartialO);
     AttnParams a{};
     a.q = q; a.k = k; a.v = v; a.out = nullptr;

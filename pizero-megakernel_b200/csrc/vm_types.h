@@ -104,7 +104,7 @@ struct AttnParams {
     float scale;
     int prefix;                  // >= 0: pi0 suffix mask, query 0 sees keys [0, prefix]; -1: no mask
     int splits;                  // KV splits (1 = none)
-    float* partial_o;            // FP32 [tasks, 128, head_dim] when splits > 1
+    uint16_t* partial_o;         // BF16 bits [tasks, 128, head_dim] when splits > 1: un-normalised partial rows
     float* partial_ml;           // FP32 [tasks, 128, 2]
     // fused NVFP4 quantisation of the output (splits == 1)
     uint8_t* out_fp4;
@@ -119,7 +119,7 @@ struct AttnParams {
 };
 
 struct MergeParams {
-    const float* partial_o;
+    const uint16_t* partial_o;
     const float* partial_ml;
     int heads, nq, head_dim, splits;
     void* out;                   // BF16 [nq, heads*head_dim] or null
