@@ -332,11 +332,21 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
     for (int t = first; t < first + count; ++t) {
         const int m_tile = t / g.n_tiles, n_tile = t - m_tile * g.n_tiles;
         const uint32_t buf = ps.epi_tile & 1u, phase = (ps.epi_tile >> 1) & 1u;
+        const int row = m_tile * 128 + quarter * 32 + lane;
+        const bool row_ok = row < g.rows;
+        if (g.epilogue == EPI_QKV_ROPE && row_ok) {
+            // while the MMAs run: bring this row's rotary table entries (constant data) close
+            const int hd = g.head_dim, col_a = n_tile * g.block_n;
+            if (col_a < g.q_cols + hd) {                                   // a Q or K tile
+                const int in_head = col_a >= g.q_cols ? col_a - g.q_cols : col_a % hd;
+                const __nv_bfloat16* cs = static_cast<const __nv_bfloat16*>(g.rope_cos) + static_cast<size_t>(row) * hd + (in_head >> 1);
+                const __nv_bfloat16* sn = static_cast<const __nv_bfloat16*>(g.rope_sin) + static_cast<size_t>(row) * hd + (in_head >> 1);
+                prefetch_l1(cs); prefetch_l1(cs + (hd >> 1)); prefetch_l1(sn); prefetch_l1(sn + (hd >> 1));
+            }
+        }
         if (!mbar_wait_warp(prog, ctl, &ctl->acc_full[buf], phase, stage_index)) return;
         tc_fence_after();
         if (stamp && t == first && threadIdx.x == 128) stamp[6] = static_cast<long long>(global_ns());
-        const int row = m_tile * 128 + quarter * 32 + lane;
-        const bool row_ok = row < g.rows;
         const uint32_t taddr = tmem + buf * 128u + (static_cast<uint32_t>(quarter * 32) << 16);
         const int chunks = g.block_n >> 5;
         for (int c = 0; c < chunks; ++c) {

@@ -18,6 +18,8 @@ __device__ __forceinline__ unsigned long long global_ns() {
     return t;
 }
 __device__ __forceinline__ int lane_id() { return threadIdx.x & 31; }
+// Pull a 128-byte line of constant data (tables, norm weights) towards this SM ahead of its use.
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
 // A value every lane of the warp holds, in a form the compiler can see is warp-uniform (broadcast from lane 0), so
 // arithmetic on it runs on the uniform datapath and tcgen05 operands need no per-instruction register transfers.
 __device__ __forceinline__ uint32_t uniform_u32(uint32_t v) { return __shfl_sync(0xffffffffu, v, 0); }

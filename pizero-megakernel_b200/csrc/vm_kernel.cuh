@@ -132,6 +132,15 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
             if (!gather_enter(prog, ctl, gathers, ins.y)) break;
             gathers++;
             mark(prog, 700000 + ins.y);
+            if (st.kind == OP_NORM) {
+                // the norm weights do not depend on any stage: fetch them while the CTA waits for its input rows
+                const NormParams& np = st.p.norm;
+                const int lines = (np.width * 4 + 127) >> 7;
+                for (int i = threadIdx.x; i < lines; i += kThreads) {
+                    if (np.gamma) prefetch_l1(np.gamma + i * 32);
+                    if (np.beta) prefetch_l1(np.beta + i * 32);
+                }
+            }
             if (!cta_wait_sources(prog, ctl, st, ins.y, ins.z, ins.w, stamp)) break;
             switch (st.kind) {
                 case OP_NORM: norm_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;

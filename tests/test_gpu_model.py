@@ -87,6 +87,26 @@ def test_partitioned_and_stage_range_launches_are_bit_exact(small_model):
         assert torch.equal(one.output, a)
 
 
+def test_schedules_and_split_counts_agree(small_model):
+    """Which worker runs which tile never changes a bit of the result: the reference's least-loaded policy and the
+    source-avoiding one give identical actions. The number of KV splits changes the order of the softmax sums (and the
+    BF16 partial rows), so different split counts agree only to the NVFP4 noise gate."""
+    dims, cfg, sd = small_model
+    x = inputs(3, 50, 0, dims.vocab)
+    with NativePi0(StateDictModel(cfg, sd), schedule="spread") as spread, NativePi0(StateDictModel(cfg, sd), schedule="linear") as linear:
+        a = spread.forward(*x).clone()
+        b = linear.forward(*x).clone()
+        assert spread.status()["code"] == 0 and linear.status()["code"] == 0
+        assert not np.array_equal(spread.code, linear.code)
+        assert torch.equal(a, b)
+    with NativePi0(StateDictModel(cfg, sd), expert_splits=4, prefix_splits=1) as other:
+        c = other.forward(*x).clone()
+        assert other.status()["code"] == 0
+        assert nrmse(c, a) <= 0.1
+    with pytest.raises(ValueError):
+        NativePi0(StateDictModel(cfg, sd), schedule="random")
+
+
 def test_single_launch_is_counted_by_cupti(small_model):
     from native_pi0.launch_trace import LaunchTrace
     dims, cfg, sd = small_model
