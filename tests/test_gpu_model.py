@@ -5,7 +5,7 @@ Tolerances.  NVFP4 is not a contraction: a perturbation of 1e-3 ahead of a quant
 by a whole step, so two correct implementations drift apart layer by layer until they differ by about the
 quantisation noise itself.  The per-operator tests (test_gpu_ops.py) are the tight ones; here the gates are
 action NRMSE <= 0.1 against the dequantised-NVFP4 emulation and <= 1.3 x the emulation's own distance from
-the BF16 eager model (stated in DESIGN.md).
+the BF16 eager model.
 """
 import ctypes as C
 
