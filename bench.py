@@ -39,6 +39,16 @@ WORKLOADS = {
 WORK = {"cfg4": dict(gflop=3997.0, weight_mb=1461.0, dram_bytes=4.39e9), "cfg5": dict(gflop=4136.0, weight_mb=1461.0, dram_bytes=None)}
 
 
+# Libraries (NCCL's version banner, for one) write to file descriptor 1 behind Python's back; the contract is ONE JSON
+# line on stdout, so everything else that reaches descriptor 1 is sent to stderr and the line goes out on a saved copy.
+_JSON_FD = os.dup(1)
+os.dup2(2, 1)
+
+
+def emit(line):
+    os.write(_JSON_FD, (json.dumps(line) + "\n").encode())
+
+
 def percentile(values, q):
     s = sorted(values)
     if not s:
@@ -161,7 +171,7 @@ def run_reference(args, wl, rank):
             "cpu_baseline": {"value": value, "unit": "ms", "cores": threads, "kind": "port", "sample": desc},
             "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def run_engine(args, wl, rank, world):
@@ -264,7 +274,7 @@ def run_engine(args, wl, rank, world):
             threads = os.cpu_count() or 1
             ms, desc = cpu_reference_sample(wl, threads)
             line["cpu_baseline"] = {"value": ms, "unit": "ms", "cores": threads, "kind": "port", "sample": desc}
-        print(json.dumps(line), flush=True)
+        emit(line)
     engine.close()
     if world > 1:
         dist.destroy_process_group()
