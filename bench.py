@@ -37,6 +37,9 @@ WORKLOADS = {
 # 1.29 GB of vision/prefix weights once and the 0.17 GB of expert weights in each of the 10 Euler steps; 1.09 GB written:
 # activations and split-KV partials leaving the L2 behind the weight stream).  None: not captured.
 WORK = {"cfg4": dict(gflop=3997.0, weight_mb=1461.0, dram_bytes=4.39e9), "cfg5": dict(gflop=4136.0, weight_mb=1461.0, dram_bytes=None)}
+# Per phase: GEMM + attention GFLOP of one forward, and the NVFP4 weight MB the phase streams (expert: 175.2 MB x 10 steps).
+PHASE_WORK = {"cfg4": dict(vision=(660.5, 232.6), prefix=(2958.7, 1053.4), expert=(379.3, 1752.0)),
+              "cfg5": dict(vision=(660.5, 232.6), prefix=(3022.1, 1053.4), expert=(478.6, 1752.0))}
 
 
 # Libraries (NCCL's version banner, for one) write to file descriptor 1 behind Python's back; the contract is ONE JSON
@@ -269,7 +272,10 @@ def run_engine(args, wl, rank, world):
                              "traffic": work["dram_bytes"], "traffic_unit": "bytes per launch (ncu, profiles/)", "peak_source": peak_src, "kernel": "pi0_vm_kernel (one launch per step)",
                              "algorithmic_gflop_per_launch": work["gflop"],
                              "weight_stream_gbs": work["weight_mb"] / p50, "hbm_peak_gbs": hbm_peak},
-                "phases": phases}
+                "phases": phases,
+                "phase_roofline": {name: {"tflops": gf / phases[name + "_ms"], "frac_of_bf16_peak": gf / phases[name + "_ms"] / tf_peak,
+                                          "weight_gbs": mb / phases[name + "_ms"], "frac_of_hbm_peak": mb / phases[name + "_ms"] / hbm_peak}
+                                   for name, (gf, mb) in PHASE_WORK[args.workload].items() if phases.get(name + "_ms")}}
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             ms, desc = cpu_reference_sample(wl, threads)
