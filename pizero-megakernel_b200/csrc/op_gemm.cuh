@@ -302,16 +302,20 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
                 ts[h][0] = s0.x; ts[h][1] = s0.y; ts[h][2] = s0.z; ts[h][3] = s0.w;
                 ts[h][4] = s1.x; ts[h][5] = s1.y; ts[h][6] = s1.z; ts[h][7] = s1.w;
             }
+            // Packed BF16 arithmetic, two lanes = the two members of a rotation pair: with X = (x1, x2), C = (c1, c2),
+            // S = (s1, s2) and X' = (-x2, x1) the rotated pair is  bf16(X * C) + bf16(X' * S)  lane by lane - every
+            // product rounded to BF16 before the sum, as the reference's rotate-half does.
 #pragma unroll
             for (int i = 0; i < 16; i++) {
-                const float2 cl = unpack_bf16x2(tc[0][i >> 1]), ch = unpack_bf16x2(tc[1][i >> 1]);
-                const float2 sl = unpack_bf16x2(ts[0][i >> 1]), sh = unpack_bf16x2(ts[1][i >> 1]);
-                const float c1 = (i & 1) ? cl.y : cl.x, s1 = (i & 1) ? sl.y : sl.x;
-                const float c2 = (i & 1) ? ch.y : ch.x, s2 = (i & 1) ? sh.y : sh.x;
-                float x1 = bf16_round(v[2 * i]), x2 = bf16_round(v[2 * i + 1]);
-                float o1 = bf16_round(x1 * c1) + bf16_round(-x2 * s1);
-                float o2 = bf16_round(x2 * c2) + bf16_round(x1 * s2);
-                packed[i] = pack_bf16x2(o1, o2);
+                const uint32_t sel = (i & 1) ? 0x7632u : 0x5410u;          // high or low halves of the two table words
+                const uint32_t cw = __byte_perm(tc[0][i >> 1], tc[1][i >> 1], sel);
+                const uint32_t sw = __byte_perm(ts[0][i >> 1], ts[1][i >> 1], sel);
+                const uint32_t xw = pack_bf16x2(v[2 * i], v[2 * i + 1]);   // (x1, x2) rounded to BF16
+                const uint32_t xr = __byte_perm(xw, xw, 0x1032u) ^ 0x00008000u;   // (-x2, x1)
+                const __nv_bfloat162 p = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&xw), *reinterpret_cast<const __nv_bfloat162*>(&cw));
+                const __nv_bfloat162 q = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&xr), *reinterpret_cast<const __nv_bfloat162*>(&sw));
+                const __nv_bfloat162 o = __hadd2_rn(p, q);                  // (_rn: never contracted into a fused multiply-add)
+                packed[i] = *reinterpret_cast<const uint32_t*>(&o);
             }
         }
         __nv_bfloat16* dst;
