@@ -562,10 +562,12 @@ extern "C" int create_norm(void** handle, const void* input, const void* residua
     StageDesc& d = op->desc;
     d.kind = OP_NORM;
     finish_desc(d);
-    d.tiles = (rows + kNormRowsPerTile - 1) / kNormRowsPerTile;
+    const int rows_per_tile = layer ? 2 * kNormPairRows : kNormPairRows;
+    d.tiles = (rows + rows_per_tile - 1) / rows_per_tile;
     d.bands = (rows + kBandRows - 1) / kBandRows;
-    d.band_div = kBandRows / kNormRowsPerTile;
+    d.band_div = kBandRows / rows_per_tile;
     NormParams& n = d.p.norm;
+    n.rows_per_tile = rows_per_tile;
     n.in = input; n.gamma = gamma; n.beta = beta;
     n.rows = rows; n.width = width;
     n.mode = layer ? 1 : 0;
@@ -590,8 +592,12 @@ extern "C" int destroy_norm(void* handle) { return destroy_checked(handle); }
 extern "C" int configure_norm_quantize_only(void* handle, int policy) {
     Op* op = as_op(handle);
     if (!op || op->desc.kind != OP_NORM || (policy != 0 && policy != 1)) return cudaErrorInvalidValue;
-    op->desc.p.norm.mode = 2;
-    op->desc.p.norm.policy = policy;
+    NormParams& n = op->desc.p.norm;
+    n.mode = 2;
+    n.policy = policy;
+    n.rows_per_tile = 2 * kNormPairRows;
+    op->desc.tiles = (n.rows + n.rows_per_tile - 1) / n.rows_per_tile;
+    op->desc.band_div = kBandRows / n.rows_per_tile;
     op->solo_dirty = true;
     return cudaSuccess;
 }

@@ -143,7 +143,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
             }
             if (!cta_wait_sources(prog, ctl, st, ins.y, ins.z, ins.w, stamp)) break;
             switch (st.kind) {
-                case OP_NORM: norm_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
+                case OP_NORM: norm_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
                 case OP_ATTN: attn_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w, stamp); break;
                 case OP_MERGE: merge_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
                 case OP_PATCH: patch_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;

@@ -90,6 +90,7 @@ struct NormParams {
     void* out_bf16;              // optional BF16 copy of the normalised rows
     int ld_in;                   // input row stride in elements
     int ld_out;                  // FP4 output row stride in bytes
+    int rows_per_tile;           // 4 (RMSNorm stages) or 8 (LayerNorm, quantise-only); two warps share a row
 };
 
 struct AttnParams {
