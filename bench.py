@@ -33,10 +33,10 @@ WORKLOADS = {
     "cfg5": dict(views=3, prompt=16, chunk=63, steps=10, name="configs[4]: pi0 forward, 3 views, 16-token prompt, chunk 63, 10 Euler steps"),
 }
 # Algorithmic work of one forward (GEMM + attention FLOPs) and NVFP4 weight bytes read once.
-# dram_bytes: dram__bytes_read.sum + dram__bytes_write.sum of one launch from an ncu capture of this bench (3.30 GB read: the
-# 1.29 GB of vision/prefix weights once and the 0.17 GB of expert weights in each of the 10 Euler steps; 1.09 GB written:
+# dram_bytes: dram__bytes_read.sum + dram__bytes_write.sum of one launch from an ncu capture of this bench (3.29 GB read: the
+# 1.29 GB of vision/prefix weights once and the 0.17 GB of expert weights in each of the 10 Euler steps; 1.01 GB written:
 # activations and split-KV partials leaving the L2 behind the weight stream).  None: not captured.
-WORK = {"cfg4": dict(gflop=3997.0, weight_mb=1461.0, dram_bytes=4.39e9), "cfg5": dict(gflop=4136.0, weight_mb=1461.0, dram_bytes=None)}
+WORK = {"cfg4": dict(gflop=3997.0, weight_mb=1461.0, dram_bytes=4.30e9), "cfg5": dict(gflop=4136.0, weight_mb=1461.0, dram_bytes=None)}
 # Per phase: GEMM + attention GFLOP of one forward, and the NVFP4 weight MB the phase streams (expert: 175.2 MB x 10 steps).
 PHASE_WORK = {"cfg4": dict(vision=(660.5, 232.6), prefix=(2958.7, 1053.4), expert=(379.3, 1752.0)),
               "cfg5": dict(vision=(660.5, 232.6), prefix=(3022.1, 1053.4), expert=(478.6, 1752.0))}
