@@ -44,7 +44,7 @@ struct Ctl {
     uint32_t tmem_base;
     volatile int abort;          // CTA-local copy of the abort decision
     volatile int dep_ok;         // broadcast slot for CTA-wide operators
-    volatile int flag;           // second broadcast slot (last-arriver decisions)
+    volatile int flag;           // second broadcast slot (outcome of the split-KV ticket wait)
     int gate;                    // CTA-wide operators entered so far, or -1 once a warp has given up on one (gather_enter)
     Slot slot[kRing];
 };

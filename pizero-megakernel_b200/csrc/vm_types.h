@@ -113,8 +113,9 @@ struct AttnParams {
     int out_blocks;
     float out_inv_gs;
     int ld_fp4;
-    // splits > 1 with the merge fused into the last-arriving tile of each head: per-head arrival tickets (program
-    // counters, reset with them); 0 / null selects the separate OP_MERGE stage
+    // splits > 1 with the merge inside the attention stage: one arrival ticket per (128-query tile, head); once all
+    // splits of a group have arrived every tile merges its share of the rows. Tickets are program counters (they grow
+    // by `splits` per launch and are reset with them); 0 / null selects the separate OP_MERGE stage
     unsigned int* tickets;
     int fused_merge;
 };

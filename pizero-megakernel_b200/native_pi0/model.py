@@ -363,7 +363,7 @@ class NativePi0:
                                                          a2.k // 16, a2.global_scale), f"{name}.attention")
         att_sources = [(s_qkv, ALL)] + ([(prefix_cache_stage, ALL)] if prefix_cache_stage is not None else [])
         if splits > 1:
-            # split-KV: the last tile to finish for a head merges the partials (no separate merge stage)
+            # split-KV with the merge inside the attention stage: the tiles of a head meet on a ticket and each merges its share of rows
             _native.check(lib.configure_attention_splits(h, splits), f"{name}.attention")
             _native.check(lib.configure_attention_fused_merge(h, 1), f"{name}.attention")
         s_att = self.add(1, h, f"{name}.attention", att_sources)

@@ -286,7 +286,7 @@ def test_attention(b, nq, nk, h, hk, hd, prefix, splits):
     assert relrms(got, want) <= 1e-2
     np.testing.assert_array_equal(got, again)
     if splits > 1:
-        # merge fused into the last-arriving tile of each head: same bits as the separate merge stage, launch after launch
+        # merge inside the attention stage (tiles of a head meet on a ticket): same bits as the separate merge stage, launch after launch
         with ResidentAttention(None, q, k, v, workers=128, prefix=prefix, splits=splits, fused_merge=True) as op:
             for _ in range(3):
                 op.output.fill_(float("nan"))
