@@ -105,3 +105,25 @@ def test_replica_statistics_world_size_2_gloo(tmp_path):
     result = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env)
     assert result.returncode == 0, result.stdout + result.stderr
     assert result.stdout.count("ok") == 2
+
+
+def test_bench_reference_arm_prints_one_contract_line():
+    """`bench.py --impl reference` needs no GPU: it times the CPU restatement on a bounded sample and prints exactly
+    one JSON line on stdout with the keys the benchmark contract names (everything else goes to stderr)."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parents[1]
+    run = subprocess.run([sys.executable, str(root / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=900, cwd=root)
+    assert run.returncode == 0, run.stderr[-2000:]
+    lines = [line for line in run.stdout.splitlines() if line.strip()]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    assert line["impl"] == "reference" and line["metric"] == "pi0_10step_action_chunk_latency_p50_ms" and line["unit"] == "ms"
+    assert line["higher_is_better"] is False and line["n_gpus"] == 1 and line["steps"] == 1 and line["gpu_launches"] == 0
+    assert line["value"] > 0 and line["ms_per_step"] == line["value"]
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1 and line["cpu_baseline"]["value"] == line["value"]
+    assert line["e2e"] == {"value": line["value"], "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in line["config"] and line["data"] == "synthetic"
