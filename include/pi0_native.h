@@ -105,15 +105,26 @@ int configure_attention_fp4_output(void* handle, void* out_fp4, void* scales, in
                                    float global_scale);
 /* extension: handle of the merge stage owned by an attention handle with splits > 1 (NULL otherwise). */
 int attention_merge_handle(void* handle, void** merge);
+/* Development diagnostics of a split attention handle (splits >= 2), never part of a forward pass.
+ * Replaces: native_pi0/attention.cu:629-656 (attention_split_diagnostics, attention_poison_partials).
+ * attention_poison_partials fills the partial rows and their (max, sum) statistics with 0xFF bytes on `stream`, so
+ * that a launch which read a partial it had not written itself would produce NaNs.  attention_split_diagnostics
+ * returns, per (128-query tile, head) group, how many split tiles have arrived over all stand-alone launches so
+ * far (capacity >= number of groups) and the launch count `epoch`; every count equals splits * epoch after a clean
+ * launch. */
+int attention_poison_partials(void* handle, void* stream);
+int attention_split_diagnostics(void* handle, unsigned long long* counts, int capacity, unsigned int* epoch);
 
 /* Split-KV attention that allocates nothing.  No counterpart in the reference.
  * For callers that cannot call cudaMalloc when they need the result - a control loop that must not block on the
  * driver's allocator, or a process whose device memory all belongs to another runtime's pool.  The split-KV partials
- * live in a fixed device array inside the library (about 8.1 MiB per GPU that loads it, held until exit) instead of
+ * live in a fixed device array inside the library (about 4.1 MiB per GPU that loads it, held until exit) instead of
  * an allocated buffer; the call makes no cudaMalloc / cudaFree and uses no allocating library routine.
  * q BF16 [nq, heads*256] (row stride ldq), k and v BF16 [nk, kv_heads*256] (row stride ldkv), out BF16 [nq, heads*256]
  * (row stride out_ld); prefix >= 0 selects the pi0 suffix mask, < 0 none.  Limits (cudaErrorInvalidValue beyond them):
- * head_dim == 256, nq <= 128, heads * splits <= 64.  Same arithmetic as create_attention + configure_attention_splits.
+ * head_dim == 256, nq <= 128, splits >= 1, heads * splits <= 64; all four pointers 16-byte aligned.  Same arithmetic as
+ * create_attention + configure_attention_splits; with splits == 1 every head is one tile that writes `out` directly
+ * and the array is not touched.
  * The first call on a device looks up the array's device address and raises the kernel's shared-memory limit; make
  * that first call before any stream capture begins.  All calls on a GPU share the one array, which keeps the last
  * call's partials: every word read is rewritten first by the same call, but two calls that overlap on the GPU
@@ -170,8 +181,10 @@ int launch_native_model(void* handle, void* stream, const float* images, const f
  * starts a new forward pass (first range of a pass). */
 int launch_native_model_range(void* handle, void* stream, const float* images, const float* state, const float* noise,
                               const long long* tokens, int begin, int end, int new_epoch);
-/* per-instruction global-timer stamps (ns), int64 [workers, length, 4] = {start, producers ready, end,
- * GEMM copies issued}; enable before the launch to record. */
+/* per-instruction global-timer stamps (ns), int64 [workers, length, 8] = {start, producers ready, end, copies
+ * issued, first operands landed, MMAs issued, first accumulator ready, last stores done} (the last five only for
+ * GEMM and attention instructions); enable before the launch to record.  `count` must be 8 * workers * length.
+ * The reference's slots are int32 clock samples (native_pi0/model.cu:292-298); these are 64-bit nanoseconds. */
 int enable_native_model_timings(void* handle, int enable);
 int read_native_model_timings(void* handle, long long* out, size_t count);
 /* extension: synchronises the device and returns {code, worker, stage, band, observed, expected, aborted, epoch};
@@ -180,6 +193,10 @@ int read_native_model_timings(void* handle, long long* out, size_t count);
 int read_native_model_status(void* handle, int* values, int count);
 /* extension: counters uint32 [n] and the expected value per counter for the current epoch. */
 int read_native_model_counters(void* handle, unsigned int* counts, unsigned int* expected, int n, int* total);
+/* extension (debugging): host-mapped progress marks, one word per warp of every worker, written as the warp moves
+ * through its instruction loop; readable while a launch is still running.  Off by default. */
+int enable_native_model_debug(void* handle, int enable);
+int read_native_model_debug(void* handle, int* out, int n);      /* n >= workers * 8 */
 /* extension: time budget of every device-side wait in nanoseconds (default 2e9). */
 int set_native_model_wait_budget(void* handle, unsigned long long nanoseconds);
 int destroy_native_model(void* handle);

@@ -1,8 +1,10 @@
 """Per-operator CPU/PyTorch oracles (TEST INFRASTRUCTURE).
 
 * ``attention`` restates the reference validator's independent FP32 attention
-  (``scripts/validate_attention.py:24-42``): GQA by repeating KV heads, scale, the pi0 suffix mask
-  (query 0 sees keys ``<= prefix``), softmax with fully masked rows -> 0.
+  (``scripts/validate_attention.py:24-42``): optional per-head biases added to Q/K/V, optional rotate-half tables
+  applied to Q and K (only the first half of each table is read), GQA by repeating KV heads, scale, the pi0 suffix
+  mask (query 0 sees keys ``<= prefix``), an optional boolean visibility mask, softmax with fully masked rows -> 0.
+  Pinned by ``tests/golden/attention.npz``, which holds outputs of that reference function itself.
 * ``norm`` restates ``scripts/validate_norm.py:104-111``: optional mean removal, rsqrt(mean square + eps),
   gamma, beta, optional BF16 rounding of the normalised value.
 * ``gelu_tanh`` is ``0.5 x (1 + tanh(0.79788456 (x + 0.044715 x^3)))`` (``native_pi0/dense.cu:53``).
@@ -10,19 +12,36 @@
 import torch
 
 
-def attention(q, k, v, scale, prefix=None):
-    """q [B,Nq,H,d], k/v [B,Nk,Hk,d] -> FP32 [B,Nq,H,d]."""
-    q, k, v = [x.float().cpu() for x in (q, k, v)]
+def _rotate_half(x, tables):
+    """x [B,N,H,d] FP32; tables (cos, sin) [B,N,d]: (lo, hi) -> (lo c - hi s, hi c + lo s) with the first-half angles."""
+    half = x.shape[-1] // 2
+    cos, sin = [t.float().cpu()[..., :half].unsqueeze(2) for t in tables]
+    lo, hi = x[..., :half], x[..., half:]
+    return torch.cat((lo * cos - hi * sin, hi * cos + lo * sin), dim=-1)
+
+
+def attention(q, k, v, scale, prefix=None, *, bias=None, q_rope=None, k_rope=None, mask=None):
+    """q [B,Nq,H,d], k/v [B,Nk,Hk,d] -> FP32 [B,Nq,H,d].  bias: three [heads, d] tensors or Nones (q, k, v);
+    q_rope / k_rope: (cos, sin) tables [B, rows, d]; mask: bool [B, Nq, Nk], True = visible."""
+    q, k, v = [x.float().cpu().clone() for x in (q, k, v)]
+    if bias is not None:
+        q, k, v = [x if b is None else x + b.float().cpu() for x, b in zip((q, k, v), bias)]
+    if q_rope is not None:
+        q = _rotate_half(q, q_rope)
+    if k_rope is not None:
+        k = _rotate_half(k, k_rope)
     groups = q.shape[2] // k.shape[2]
     k = k.repeat_interleave(groups, 2)
     v = v.repeat_interleave(groups, 2)
-    score = (q.transpose(1, 2) @ k.transpose(1, 2).transpose(-1, -2)) * scale
+    score = torch.einsum("bqhd,bkhd->bhqk", q, k) * scale
     visible = torch.ones((q.shape[0], q.shape[1], k.shape[1]), dtype=torch.bool)
     if prefix is not None:
         visible[:, 0, prefix + 1:] = False
-    score.masked_fill_(~visible.unsqueeze(1), float("-inf"))
+    if mask is not None:
+        visible = visible & mask.cpu()
+    score = score.masked_fill(~visible[:, None], float("-inf"))
     prob = torch.softmax(score, dim=-1).nan_to_num(0)
-    return (prob @ v.transpose(1, 2)).transpose(1, 2)
+    return torch.einsum("bhqk,bkhd->bqhd", prob, v)
 
 
 def norm(x, kind, gamma=None, beta=None, eps=1e-6, round_normalized=True):

@@ -19,17 +19,24 @@ namespace {
 constexpr uint32_t kOpMagic = 0x7069304f;       // "pi0O"
 constexpr uint32_t kProgramMagic = 0x70693050;  // "pi0P"
 
+// Current device, checked to be compute capability 10.x. The capability is looked up once per device (one attribute
+// query), so steady-state callers pay only cudaGetDevice.
 int check_device(int* device_out) {
+    static int major_of[64] = {};
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return e;
-    cudaDeviceProp prop{};
-    e = cudaGetDeviceProperties(&prop, device);
-    if (e != cudaSuccess) return e;
-    if (prop.major != 10) return cudaErrorInvalidConfiguration;
+    int major = device >= 0 && device < 64 ? major_of[device] : 0;
+    if (major == 0) {
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+        if (e != cudaSuccess) return e;
+        if (device >= 0 && device < 64) major_of[device] = major;
+    }
+    if (major != 10) return cudaErrorInvalidConfiguration;
     *device_out = device;
     return cudaSuccess;
 }
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 int sm_count(int device) {
     int n = 0;
     cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device);
@@ -95,6 +102,7 @@ struct Op {
     Op* merge = nullptr;               // owned merge stage (splits > 1)
     uint16_t* partial_o = nullptr;
     float* partial_ml = nullptr;
+    size_t partial_bytes = 0, stat_bytes = 0;
     Program* solo = nullptr;           // lazily built one/two-stage program for stand-alone launches
     bool solo_dirty = true;
 };
@@ -114,7 +122,7 @@ struct Program {
     bool timings_on = false;
     unsigned int epoch = 0;
     unsigned long long budget_ns = 2000000000ull;
-    int* h_debug = nullptr;            // host-mapped progress marks (PI0_DEBUG_MARKS=1)
+    int* h_debug = nullptr;            // host-mapped progress marks (enable_native_model_debug)
     ~Program() {
         cudaFree(d_stages);
         cudaFree(d_code);
@@ -284,10 +292,6 @@ int launch_program(Program* prog, cudaStream_t stream, LaunchInputs in, int begi
     p.stage_end = end;
     p.wait_budget_ns = prog->budget_ns;
     p.in = in;
-    if (!prog->h_debug && getenv("PI0_DEBUG_MARKS")) {
-        if (cudaHostAlloc(&prog->h_debug, sizeof(int) * prog->workers * (kThreads / 32), cudaHostAllocMapped) != cudaSuccess) prog->h_debug = nullptr;
-        else memset(prog->h_debug, 0, sizeof(int) * prog->workers * (kThreads / 32));
-    }
     p.debug = prog->h_debug;
     pi0_vm_kernel<<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
     return cudaGetLastError();
@@ -352,13 +356,10 @@ int gemm_refresh(Op* op) {
     g.off_sfb = g.off_sfa + kSfBytes;
     g.slot_stride = g.off_sfb + kSfBytes;
     g.ring_stages = std::max(kStages, std::min(kMaxStages, kDataBytes / g.slot_stride));
-    const char* ring_env = getenv("PI0_RING_STAGES");                                   // experiments: cap the ring depth
-    if (ring_env) g.ring_stages = std::max(1, std::min(g.ring_stages, atoi(ring_env)));
     if (g.slot_stride % 1024 || g.ring_stages * g.slot_stride > kDataBytes ||
         (kChunks - 1) * 128 * g.a_box_rows + kTileABytes > g.slot_stride)
         return cudaErrorInvalidValue;
-    const char* fmt_env = getenv("PI0_FP4_FORMAT_CODE");
-    const uint32_t fmt = fmt_env ? static_cast<uint32_t>(atoi(fmt_env)) & 7u : 1u;    // E2M1 for kind::mxf4nvf4
+    constexpr uint32_t fmt = 1u;                                                       // E2M1, the operand format of kind::mxf4nvf4
     g.idesc = (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(g.block_n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
     op->desc.tiles = g.m_tiles * g.n_tiles;
     op->desc.bands = g.m_tiles;
@@ -637,7 +638,8 @@ extern "C" int create_attention(void** handle, const void* q, const void* k, con
     if (!q || !k || !v || !out || q_bias || k_bias || v_bias || q_cos || q_sin || k_cos || k_sin || mask || fp16 || batches < 1 ||
         nq < 1 || nk < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads || (head_dim != 72 && head_dim != 256) ||
         ldq < heads * head_dim || ldq % 8 || ldkv < kv_heads * head_dim || ldkv % 8 || out_ld < heads * head_dim || out_ld % 8 ||
-        !std::isfinite(scale) || scale <= 0 || (prefix >= 0 && batches != 1))
+        !std::isfinite(scale) || scale <= 0 || (prefix >= 0 && batches != 1) ||
+        !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out))     // rows move in 16-byte pieces
         return cudaErrorInvalidValue;
     Op* op = nullptr;
     int e = new_op(&op, workers);
@@ -681,21 +683,33 @@ extern "C" int configure_attention_splits(void* handle, int splits) {
     if (!op || op->desc.kind != OP_ATTN || splits < 1 || splits > 64) return cudaErrorInvalidValue;
     AttnParams& a = op->desc.p.attn;
     if (splits > 1 && (a.batches != 1 || a.head_dim % 16)) return cudaErrorInvalidValue;
+    // Allocate first; the handle changes only when everything it needs exists (a failed call leaves it as it was).
+    uint16_t* partial_o = nullptr;
+    float* partial_ml = nullptr;
+    const int groups = a.heads * ((a.nq + kAttnQRows - 1) / kAttnQRows);          // heads x 128-query tiles
+    const size_t tasks = static_cast<size_t>(groups) * splits;
+    if (splits > 1) {
+        cudaError_t e = cudaMalloc(&partial_o, tasks * kAttnQRows * a.head_dim * sizeof(uint16_t));
+        if (e == cudaSuccess) e = cudaMalloc(&partial_ml, tasks * kAttnQRows * 2 * sizeof(float));
+        if (e != cudaSuccess) {
+            cudaFree(partial_o);
+            cudaFree(partial_ml);
+            return e;
+        }
+    }
     if (op->merge) { free_op(op->merge); op->merge = nullptr; }
-    cudaFree(op->partial_o); op->partial_o = nullptr;
-    cudaFree(op->partial_ml); op->partial_ml = nullptr;
-    void* final_out = a.out;
+    cudaFree(op->partial_o);
+    cudaFree(op->partial_ml);
+    op->partial_o = partial_o;
+    op->partial_ml = partial_ml;
+    op->partial_bytes = splits > 1 ? tasks * kAttnQRows * a.head_dim * sizeof(uint16_t) : 0;
+    op->stat_bytes = splits > 1 ? tasks * kAttnQRows * 2 * sizeof(float) : 0;
     a.splits = splits;
     a.fused_merge = 0;
+    a.partial_o = partial_o;
+    a.partial_ml = partial_ml;
     op->desc.aux_count = 0;
     if (splits > 1) {
-        const int groups = a.heads * ((a.nq + kAttnQRows - 1) / kAttnQRows);      // heads x 128-query tiles
-        const size_t tasks = static_cast<size_t>(groups) * splits;
-        cudaError_t e = cudaMalloc(&op->partial_o, tasks * kAttnQRows * a.head_dim * sizeof(uint16_t));
-        if (e == cudaSuccess) e = cudaMalloc(&op->partial_ml, tasks * kAttnQRows * 2 * sizeof(float));
-        if (e != cudaSuccess) return e;
-        a.partial_o = op->partial_o;
-        a.partial_ml = op->partial_ml;
         Op* mg = new Op();
         mg->device = op->device;
         mg->workers = op->workers;
@@ -705,13 +719,56 @@ extern "C" int configure_attention_splits(void* handle, int splits) {
         mg->desc.bands = 1;
         mg->desc.band_div = mg->desc.tiles;
         MergeParams& g = mg->desc.p.merge;
-        g.partial_o = op->partial_o; g.partial_ml = op->partial_ml;
+        g.partial_o = partial_o; g.partial_ml = partial_ml;
         g.heads = a.heads; g.nq = a.nq; g.head_dim = a.head_dim; g.splits = splits;
-        g.out = final_out; g.ldo = a.ldo;
+        g.out = a.out; g.ldo = a.ldo;
         g.out_fp4 = a.out_fp4; g.out_scales = a.out_scales; g.out_blocks = a.out_blocks; g.out_inv_gs = a.out_inv_gs; g.ld_fp4 = a.ld_fp4;
         op->merge = mg;
     }
     attention_geometry(op);
+    return cudaSuccess;
+}
+// Fill the split-KV scratch (partial rows and their softmax statistics) with 0xFF bytes - NaN patterns in both
+// formats - so a run that read a partial it had not written in the same launch would show it in its output.
+extern "C" int attention_poison_partials(void* handle, void* stream) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN || op->desc.p.attn.splits < 2) return cudaErrorInvalidValue;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device != op->device) return cudaErrorInvalidDevice;
+    e = cudaMemsetAsync(op->partial_o, 255, op->partial_bytes, static_cast<cudaStream_t>(stream));
+    if (e == cudaSuccess) e = cudaMemsetAsync(op->partial_ml, 255, op->stat_bytes, static_cast<cudaStream_t>(stream));
+    return e;
+}
+// Arrival counts of the split-KV groups (one per head of each 128-query tile) after the launches so far, and the launch
+// count they are measured against: a group is complete when its count equals splits * epoch. With the merge as a stage
+// of its own the counts are those of the attention stage's row bands scaled to tiles per group.
+extern "C" int attention_split_diagnostics(void* handle, unsigned long long* counts, int capacity, unsigned int* epoch) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN || !counts || !epoch) return cudaErrorInvalidValue;
+    const AttnParams& a = op->desc.p.attn;
+    const int groups = a.heads * ((a.nq + kAttnQRows - 1) / kAttnQRows);
+    if (a.splits < 2 || capacity < groups) return cudaErrorInvalidValue;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e;
+    if (device != op->device) return cudaErrorInvalidDevice;
+    *epoch = op->solo ? op->solo->epoch : 0u;
+    for (int g = 0; g < groups; g++) counts[g] = 0;
+    if (!op->solo) return cudaSuccess;
+    e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return e;
+    const StageDesc& d = op->solo->stages[0];
+    std::vector<unsigned int> raw(op->solo->expected.size());
+    e = cudaMemcpy(raw.data(), op->solo->d_counters, raw.size() * sizeof(unsigned int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return e;
+    if (a.fused_merge && d.aux_count == groups) {
+        for (int g = 0; g < groups; g++) counts[g] = raw[d.aux_base + g];
+    } else {
+        // one counter per 128-query tile: heads * splits tiles each, every head of the tile has the same share
+        for (int g = 0; g < groups; g++) counts[g] = raw[d.counter_base + g / a.heads] / static_cast<unsigned int>(a.heads);
+    }
     return cudaSuccess;
 }
 extern "C" int configure_attention_fused_merge(void* handle, int enable) {
@@ -726,7 +783,9 @@ extern "C" int configure_attention_fused_merge(void* handle, int enable) {
 }
 extern "C" int configure_attention_cache(void* handle, const void* cache_k, const void* cache_v, int rows, int prefix_rows) {
     Op* op = as_op(handle);
-    if (!op || op->desc.kind != OP_ATTN || !cache_k || !cache_v || rows < 1 || prefix_rows < 0 || prefix_rows > rows) return cudaErrorInvalidValue;
+    if (!op || op->desc.kind != OP_ATTN || !cache_k || !cache_v || rows < 1 || prefix_rows < 0 || prefix_rows > rows ||
+        !aligned16(cache_k) || !aligned16(cache_v))
+        return cudaErrorInvalidValue;
     AttnParams& a = op->desc.p.attn;
     if (a.batches != 1 || a.kv_heads != 1) return cudaErrorInvalidValue;
     a.k = cache_k; a.v = cache_v; a.ldkv = a.head_dim; a.nk = rows; a.kv_batch_rows = rows;
@@ -979,6 +1038,22 @@ extern "C" int read_native_model_counters(void* handle, unsigned int* counts, un
         for (int i = 0; i < have; i++) expected[i] = prog->expected[i] * prog->epoch;
     return cudaSuccess;
 }
+extern "C" int enable_native_model_debug(void* handle, int enable) {
+    Program* prog = as_program(handle);
+    if (!prog) return cudaErrorInvalidValue;
+    if (enable && !prog->h_debug) {
+        const size_t bytes = sizeof(int) * prog->workers * (kThreads / 32);
+        cudaError_t e = cudaHostAlloc(&prog->h_debug, bytes, cudaHostAllocMapped);
+        if (e != cudaSuccess) { prog->h_debug = nullptr; return e; }
+        memset(prog->h_debug, 0, bytes);
+    } else if (!enable && prog->h_debug) {
+        cudaError_t e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) return e;
+        cudaFreeHost(prog->h_debug);
+        prog->h_debug = nullptr;
+    }
+    return cudaSuccess;
+}
 extern "C" int read_native_model_debug(void* handle, int* out, int n) {
     Program* prog = as_program(handle);
     if (!prog || !prog->h_debug || !out || n < prog->workers * (kThreads / 32)) return cudaErrorInvalidValue;
@@ -1068,14 +1143,14 @@ extern "C" int quantize_nvfp4(const void* in, void* out, void* scales, int rows,
 // device, which can cost milliseconds in the middle of a 20 ms control period), or a process that has handed
 // all of its device memory to another runtime's pool at start-up.  For them the split-KV partials live in a
 // file-scope device array of fixed size instead of a buffer obtained from cudaMalloc.  The array exists once
-// per GPU that loads this library (about 8.1 MiB each, held until the process exits), is shared by every
+// per GPU that loads this library (about 4.1 MiB each, held until the process exits), is shared by every
 // call, and keeps the previous call's contents.
 namespace pi0 {
 namespace {
 
 constexpr int kNoAllocMaxParts = 64;                 // heads * splits
 constexpr int kNoAllocHeadDim = 256;
-constexpr size_t kNoAllocPartialO = static_cast<size_t>(kNoAllocMaxParts) * kAttnQRows * kNoAllocHeadDim * sizeof(float);
+constexpr size_t kNoAllocPartialO = static_cast<size_t>(kNoAllocMaxParts) * kAttnQRows * kNoAllocHeadDim * sizeof(uint16_t);   // BF16 rows
 constexpr size_t kNoAllocPartialMl = static_cast<size_t>(kNoAllocMaxParts) * kAttnQRows * 2 * sizeof(float);
 constexpr int kNoAllocSmem = kAttnSmemBytes + 1024;     // operands and partial-row staging of attn_tile, plus alignment slack
 
@@ -1122,7 +1197,7 @@ extern "C" int attention_split_noalloc(const void* q, const void* k, const void*
                                        float scale, void* stream) {
     if (!q || !k || !v || !out || nq < 1 || nk < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads || splits < 1 ||
         ldq < heads * head_dim || ldq % 8 || ldkv < kv_heads * head_dim || ldkv % 8 || out_ld < heads * head_dim || out_ld % 8 ||
-        !std::isfinite(scale) || scale <= 0)
+        !std::isfinite(scale) || scale <= 0 || !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out))
         return cudaErrorInvalidValue;
     // limits of the fixed scratch array: 256-wide heads, at most 128 queries, heads * splits <= 64
     if (head_dim != kNoAllocHeadDim || nq > kAttnQRows || heads * splits > kNoAllocMaxParts) return cudaErrorInvalidValue;
@@ -1133,24 +1208,31 @@ extern "C" int attention_split_noalloc(const void* q, const void* k, const void*
     unsigned char* scratch = nullptr;
     e = noalloc_setup(device, &scratch);
     if (e) return e;
-    uint16_t* partial_o = reinterpret_cast<uint16_t*>(scratch);      // (the array is sized for 4-byte elements; half is used)
+    uint16_t* partial_o = reinterpret_cast<uint16_t*>(scratch);
     float* partial_ml = reinterpret_cast<float*>(scratch + kNoAllocPartialO);
     AttnParams a{};
-    a.q = q; a.k = k; a.v = v; a.out = nullptr;
+    a.q = q; a.k = k; a.v = v;
     a.ldq = ldq; a.ldkv = ldkv; a.ldo = out_ld;
     a.batches = 1; a.nq = nq; a.nk = nk; a.q_batch_rows = nq; a.kv_batch_rows = nk;
     a.heads = heads; a.kv_heads = kv_heads; a.head_dim = head_dim;
     a.scale = scale;
     a.prefix = prefix >= 0 ? prefix : -1;
     a.splits = splits;
-    a.partial_o = partial_o; a.partial_ml = partial_ml;
     a.out_inv_gs = 1.f;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (splits == 1) {
+        // One part per head: the tile normalises and stores its rows itself; no partials, no merge, the array is unused.
+        a.out = out;
+        noalloc_attention_kernel<<<heads, kThreads, kNoAllocSmem, s>>>(a);
+        return cudaGetLastError();
+    }
+    a.out = nullptr;
+    a.partial_o = partial_o; a.partial_ml = partial_ml;
     MergeParams g{};
     g.partial_o = partial_o; g.partial_ml = partial_ml;
     g.heads = heads; g.nq = nq; g.head_dim = head_dim; g.splits = splits;
     g.out = out; g.ldo = out_ld;
     g.out_inv_gs = 1.f;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Every partial word the merge reads (rows < nq of each head/split) is written by the attention kernel of
     // this same call first, so nothing in the shared array has to be cleared beforehand.
     noalloc_attention_kernel<<<heads * splits, kThreads, kNoAllocSmem, s>>>(a);

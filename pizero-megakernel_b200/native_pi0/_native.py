@@ -70,6 +70,8 @@ _SIGNATURES = {
     "configure_attention_fused_merge": [_P, _I],
     "configure_attention_fp4_output": [_P, _P, _P, _I, _I, _F],
     "attention_merge_handle": [_P, C.POINTER(_P)],
+    "attention_poison_partials": [_P, _P],
+    "attention_split_diagnostics": [_P, _P, _I, C.POINTER(C.c_uint)],
     "create_patch_embed": [C.POINTER(_P)] + [_P] * 5 + [_I] * 3,
     "create_token_embed": [C.POINTER(_P), _P, _P, _P, _I, _I, _I, _I, _F, _I],
     "create_linear32": [C.POINTER(_P)] + [_P] * 5 + [_I] * 9 + [_F, _F, _I],
@@ -85,6 +87,8 @@ _SIGNATURES = {
     "read_native_model_timings": [_P, _P, C.c_size_t],
     "read_native_model_status": [_P, C.POINTER(_I), _I],
     "read_native_model_counters": [_P, _P, _P, _I, C.POINTER(_I)],
+    "enable_native_model_debug": [_P, _I],
+    "read_native_model_debug": [_P, C.POINTER(_I), _I],
     "set_native_model_wait_budget": [_P, C.c_ulonglong],
     "destroy_native_model": [_P],
     "create_native_linear": [C.POINTER(_P), _I, _P, _P, _P, _I, _I],
@@ -96,6 +100,28 @@ _SIGNATURES = {
 }
 EXPORTS = tuple(_SIGNATURES)
 _cache = {}
+
+# libpi0_trace.so: (argument types, result type); these return CUptiResult, not cudaError_t
+_TRACE_SIGNATURES = {
+    "begin_launch_trace": ([C.POINTER(_P)], _I),
+    "end_launch_trace": ([_P, C.POINTER(_I), C.c_char_p, _I], _I),
+    "launch_trace_error": ([_I], C.c_char_p),
+}
+
+
+def load_trace(path=None):
+    """The CUPTI launch counter, a library of its own so that the engine does not link CUPTI."""
+    path = Path(path) if path is not None else TRACE_LIBRARY
+    key = "trace:" + str(path)
+    if key not in _cache:
+        if not path.exists():
+            raise RuntimeError(f"{path} is missing: run native_pi0._native.build() first")
+        lib = C.CDLL(str(path))
+        for name, (argtypes, restype) in _TRACE_SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes, fn.restype = argtypes, restype
+        _cache[key] = lib
+    return _cache[key]
 
 
 def load(path=None):

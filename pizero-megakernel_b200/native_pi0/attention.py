@@ -83,6 +83,30 @@ class ResidentAttention:
         with torch.cuda.device(self.device):
             return _native.status(self.library, self.handle)
 
+    def _split_only(self):
+        if not self.handle.value or self.splits == 1:
+            raise RuntimeError("A live split attention instance is required")
+
+    def poison_partials(self):
+        """Development aid (``native_pi0/attention.py:131-137``): overwrite the split-KV scratch with NaN patterns on
+        the current stream, so that a following launch which read a stale partial would show it."""
+        self._split_only()
+        with torch.cuda.device(self.device):
+            _native.check(self.library.attention_poison_partials(self.handle, torch.cuda.current_stream(self.device).cuda_stream),
+                          "Attention scratch poisoning")
+
+    def read_split_counts(self):
+        """Development aid (``native_pi0/attention.py:120-129``): synchronise and return the launch count and, per
+        (128-query tile, head) group, the number of split tiles that have arrived so far; after clean launches every
+        count is ``splits * epoch``."""
+        self._split_only()
+        groups = self.q.shape[2] * ((self.q.shape[1] + 127) // 128)
+        counts, epoch = (ctypes.c_ulonglong * groups)(), ctypes.c_uint()
+        with torch.cuda.device(self.device):
+            _native.check(self.library.attention_split_diagnostics(self.handle, counts, groups, ctypes.byref(epoch)),
+                          "Attention diagnostics")
+        return {"epoch": epoch.value, "counts": list(counts)}
+
     def close(self):
         if self.handle.value:
             with torch.cuda.device(self.device):

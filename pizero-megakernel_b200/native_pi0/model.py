@@ -561,8 +561,9 @@ class NativePi0:
         _native.check(self.lib.enable_native_model_timings(self.handle, int(enable)), "timing setup")
 
     def read_timings(self, name=None):
-        """Global-timer stamps (ns) int64 [workers, stream_length, 4] = (start, producers ready, end, GEMM copies
-        issued) of the last launch with timings enabled."""
+        """Global-timer stamps (ns) int64 [workers, stream_length, 8] of the last launch with timings enabled: start,
+        producers ready, end, copies issued, first operands landed, MMAs issued, first accumulator ready, last stores
+        done (the last five only for GEMM and attention instructions)."""
         out = np.zeros((self.workers, self.code.shape[1], 8), dtype=np.int64)
         with torch.cuda.device(self.device):
             _native.check(self.lib.read_native_model_timings(self.handle, out.ctypes.data, out.size), "timing read")

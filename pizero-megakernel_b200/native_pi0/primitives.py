@@ -15,86 +15,87 @@ from native_pi0.quantization import swizzle_scales
 from native_pi0.storage import packed_tma_buffer
 
 
+_OUTPUT_KINDS = {torch.float32: "f32", torch.bfloat16: "bf16", torch.uint8: "fp4"}
+_ACTIVATION_CODES = {"none": 0, "gelu": 1, "geglu": 2, "relu2": 3}          # configure_resident_fp4_quantized
+_RESOURCE_KEYS = ("registers_per_thread", "static_shared_bytes", "dynamic_shared_bytes", "local_bytes_per_thread",
+                  "predicted_max_ctas_per_sm", "threads_per_cta", "max_threads_per_sm", "sm_count")
+
+
+def _operand_geometry(name, packed):
+    """(rows, K) of a ``PackedNVFP4`` operand after checking its arrays are what the kernel consumes."""
+    data, scales = packed.data, packed.scales
+    if data.dtype != np.uint8 or scales.dtype != np.uint8 or data.ndim != 2 or scales.ndim != 2 or data.size == 0:
+        raise ValueError(f"{name}: packed E2M1 codes and E4M3 scale codes must be non-empty 2-D uint8 arrays")
+    if int(scales.max(initial=0)) > 126:
+        raise ValueError(f"{name}: scale codes above 126 are not finite unsigned E4M3 values")
+    rows, k = data.shape[0], 2 * data.shape[1]
+    if rows % 128 or k % 64:
+        raise ValueError(f"{name}: rows must be padded to 128 and K to 64 (got {rows} x {k})")
+    if scales.shape != (rows, k // 16):
+        raise ValueError(f"{name}: expected one scale per 16 K-elements, shape {(rows, k // 16)}, got {scales.shape}")
+    return rows, k
+
+
+def _epilogue_kind(output_dtype, gelu, geglu, relu2, global_scale, bias, residual):
+    """Validate the requested epilogue and return (output kind, activation name)."""
+    kind = _OUTPUT_KINDS.get(output_dtype)
+    if kind is None:
+        raise ValueError("output_dtype must be torch.float32, torch.bfloat16 or torch.uint8 (packed NVFP4)")
+    chosen = [name for name, on in (("gelu", gelu), ("geglu", geglu), ("relu2", relu2)) if on]
+    if len(chosen) > 1:
+        raise ValueError(f"At most one output activation can be fused, got {chosen}")
+    activation = chosen[0] if chosen else "none"
+    fused_add = bias is not None or residual is not None
+    if not np.isfinite(global_scale) or global_scale <= 0:
+        raise ValueError("output_global_scale must be a positive finite number")
+    if kind == "f32" and fused_add:
+        raise ValueError("The FP32 epilogue stores the raw product: bias and residual need a BF16 or NVFP4 output")
+    if kind != "fp4" and (activation != "none" or global_scale != 1):
+        raise ValueError("Activations and an output tensor scale belong to the NVFP4 (uint8) output")
+    if activation == "geglu" and fused_add:
+        raise ValueError("GeGLU halves the width over interleaved gate/up columns and takes neither bias nor residual")
+    return kind, activation
+
+
 class ResidentNVFP4:
     def __init__(self, library, activation, weight, *, workers=16, device="cuda",
                  output_dtype=torch.float32, bias=None, residual=None,
                  output_global_scale=1.0, output_gelu=False, output_geglu=False, output_relu2=False,
                  block_n=128, rows=None, activation_buffers=None, tiled_weight=False):
         self._handle = ctypes.c_void_p()
-        self.device = torch.device(device)
-        if self.device.type != "cuda":
-            raise ValueError("CUDA device required")
-        if self.device.index is None:
-            self.device = torch.device("cuda", torch.cuda.current_device())
-        for operand in (activation, weight):
-            if (operand.data.dtype != np.uint8 or operand.data.ndim != 2 or 0 in operand.data.shape
-                    or operand.scales.dtype != np.uint8 or operand.scales.ndim != 2
-                    or np.any(operand.scales > 126)):
-                raise ValueError("Expected packed uint8 E2M1 data and finite unsigned E4M3 scales")
-        m, half_k = activation.data.shape
-        n, weight_half_k = weight.data.shape
-        k = 2 * half_k
-        if weight_half_k != half_k or m % 128 or n % 128 or k % 64:
-            raise ValueError("Packed M/N must be multiples of 128 and K a multiple of 64")
-        if activation.scales.shape != (m, k // 16) or weight.scales.shape != (n, k // 16):
-            raise ValueError("Scale dimensions do not match operands")
-        if output_dtype not in (torch.float32, torch.bfloat16, torch.uint8):
-            raise ValueError("Output must be FP32, BF16, or packed FP4 (uint8)")
-        if output_dtype == torch.float32 and (bias is not None or residual is not None):
-            raise ValueError("Bias/residual fusion requires BF16 or FP4 output")
+        device = torch.device(device)
+        if device.type != "cuda":
+            raise ValueError("ResidentNVFP4 runs on a CUDA device")
+        self.device = device if device.index is not None else torch.device("cuda", torch.cuda.current_device())
+        m, k = _operand_geometry("activation", activation)
+        n, weight_k = _operand_geometry("weight", weight)
+        if weight_k != k:
+            raise ValueError(f"activation K ({k}) and weight K ({weight_k}) differ")
         self.output_global_scale = np.float32(output_global_scale)
-        self.activation_global_scale = np.float32(activation.global_scale)
-        self.weight_global_scale = np.float32(weight.global_scale)
-        if not np.isfinite(self.output_global_scale) or self.output_global_scale <= 0:
-            raise ValueError("Output global scale must be finite and positive")
-        if sum(map(bool, (output_gelu, output_geglu, output_relu2))) > 1:
-            raise ValueError("Select only one output activation")
-        if output_geglu and (output_gelu or bias is not None or residual is not None):
-            raise ValueError("Compact GeGLU requires interleaved gate/up weights without bias/residual")
-        if output_dtype != torch.uint8 and (output_gelu or output_geglu or output_relu2 or self.output_global_scale != 1):
-            raise ValueError("Output activation/global scaling requires packed FP4 output")
-        self._library = _native.load(library)
-        alpha = np.float32(activation.global_scale * weight.global_scale)
+        kind, act = _epilogue_kind(output_dtype, output_gelu, output_geglu, output_relu2, self.output_global_scale, bias, residual)
+        self.activation_global_scale, self.weight_global_scale = np.float32(activation.global_scale), np.float32(weight.global_scale)
+        self.output_width = n // 2 if act == "geglu" else n
+        self._library = lib = _native.load(library)
         with torch.cuda.device(self.device):
-            self.a, self.b = [packed_tma_buffer(x.shape, device=self.device).copy_(torch.from_numpy(np.ascontiguousarray(x)))
-                              for x in (activation.data, weight.data)]
-            self.sa, self.sb = [torch.from_numpy(swizzle_scales(x)).to(self.device)
-                                for x in (activation.scales, weight.scales)]
-            if activation_buffers is not None:
-                # A operand produced on the device by an earlier stage (packed codes + swizzled scales)
-                data, scales = activation_buffers
-                if tuple(data.shape) != tuple(self.a.shape) or data.dtype != torch.uint8 or scales.numel() != self.sa.numel():
-                    raise ValueError("Bound activation buffers must match the packed activation layout")
-                self.a, self.sa = data, scales
-            self.bias = None if bias is None else torch.as_tensor(bias, dtype=torch.bfloat16, device=self.device).contiguous()
-            self.residual = None if residual is None else torch.as_tensor(residual, dtype=torch.bfloat16, device=self.device).contiguous()
-            if self.bias is not None and tuple(self.bias.shape) != (n,):
-                raise ValueError("Bias must have shape (N,)")
-            if self.residual is not None and tuple(self.residual.shape) != (m, n):
-                raise ValueError("Residual must have padded shape (M,N)")
-            self.output_width = n // 2 if output_geglu else n
-            if output_dtype == torch.uint8:
+            self._upload(activation, weight, activation_buffers, bias, residual, m, n)
+            if kind == "fp4":
                 self.output = packed_tma_buffer((m, self.output_width // 2), device=self.device)
-                self.output_scales = torch.zeros(((m + 127) // 128) * ((self.output_width // 16 + 3) // 4) * 512,
-                                                 dtype=torch.uint8, device=self.device)
+                atoms = ((m + 127) // 128) * ((self.output_width // 16 + 3) // 4)
+                self.output_scales = torch.zeros(atoms * 512, dtype=torch.uint8, device=self.device)
             else:
-                self.output = torch.zeros((m, n), dtype=output_dtype, device=self.device)
-                self.output_scales = None
-            lib = self._library
-            _native.check(lib.create_resident_fp4(ctypes.byref(self._handle), self.a.data_ptr(), self.b.data_ptr(),
-                                                  self.sa.data_ptr(), self.sb.data_ptr(), self.output.data_ptr(),
-                                                  m, n, k, workers, float(alpha)), "Native FP4 setup")
+                self.output, self.output_scales = torch.zeros((m, n), dtype=output_dtype, device=self.device), None
+            alpha = float(self.activation_global_scale * self.weight_global_scale)
+            _native.check(lib.create_resident_fp4(ctypes.byref(self._handle), self.a.data_ptr(), self.b.data_ptr(), self.sa.data_ptr(),
+                                                  self.sb.data_ptr(), self.output.data_ptr(), m, n, k, workers, alpha), "Native FP4 setup")
             try:
-                if output_dtype == torch.uint8:
-                    activation_code = 3 if output_relu2 else 2 if output_geglu else int(bool(output_gelu))
+                if kind == "fp4":
                     _native.check(lib.configure_resident_fp4_quantized(
                         self._handle, _native.ptr(self.bias), _native.ptr(self.residual), self.output.data_ptr(),
-                        self.output_scales.data_ptr(), float(self.output_global_scale), activation_code),
+                        self.output_scales.data_ptr(), float(self.output_global_scale), _ACTIVATION_CODES[act]),
                         "Native FP4 quantized-output setup")
-                elif output_dtype == torch.bfloat16:
-                    _native.check(lib.configure_resident_fp4_bf16(
-                        self._handle, _native.ptr(self.bias), _native.ptr(self.residual), self.output.data_ptr()),
-                        "Native FP4 epilogue setup")
+                elif kind == "bf16":
+                    _native.check(lib.configure_resident_fp4_bf16(self._handle, _native.ptr(self.bias), _native.ptr(self.residual),
+                                                                  self.output.data_ptr()), "Native FP4 epilogue setup")
                 if rows is not None:
                     _native.check(lib.configure_resident_fp4_rows(self._handle, int(rows)), "Native FP4 rows")
                 if block_n != 128:
@@ -104,14 +105,42 @@ class ResidentNVFP4:
                     tiled = self.b.view(n // block_n, block_n, k // 256, 128).permute(0, 2, 1, 3).contiguous()
                     self.b.copy_(tiled.view(n, k // 2))
                     _native.check(lib.configure_resident_fp4_weight_layout(self._handle, 1), "Native FP4 weight layout")
-                values = (ctypes.c_int * 8)()
-                _native.check(lib.resident_fp4_resources(self._handle, values, 8), "Native FP4 resource query")
+                values = (ctypes.c_int * len(_RESOURCE_KEYS))()
+                _native.check(lib.resident_fp4_resources(self._handle, values, len(values)), "Native FP4 resource query")
             except Exception:
                 self.close()
                 raise
-        self.resources = dict(zip(("registers_per_thread", "static_shared_bytes", "dynamic_shared_bytes",
-                                   "local_bytes_per_thread", "predicted_max_ctas_per_sm", "threads_per_cta",
-                                   "max_threads_per_sm", "sm_count"), values))
+        self.resources = dict(zip(_RESOURCE_KEYS, values))
+
+    def _upload(self, activation, weight, activation_buffers, bias, residual, m, n):
+        """Device copies of the operands: codes in TMA-safe storage, scales in the 128x4 atom order."""
+        def codes(packed):
+            buffer = packed_tma_buffer(packed.data.shape, device=self.device)
+            buffer.copy_(torch.from_numpy(np.ascontiguousarray(packed.data)))
+            return buffer
+
+        def scales(packed):
+            return torch.from_numpy(swizzle_scales(packed.scales)).to(self.device)
+
+        self.b, self.sb = codes(weight), scales(weight)
+        if activation_buffers is None:
+            self.a, self.sa = codes(activation), scales(activation)
+        else:
+            # A operand produced on the device by an earlier stage (packed codes + swizzled scales)
+            data, swizzled = activation_buffers
+            atoms = ((m + 127) // 128) * ((activation.scales.shape[1] + 3) // 4) * 512
+            if tuple(data.shape) != tuple(activation.data.shape) or data.dtype != torch.uint8 or swizzled.numel() != atoms:
+                raise ValueError("Bound activation buffers must match the packed activation layout")
+            self.a, self.sa = data, swizzled
+        self.bias = self.residual = None
+        if bias is not None:
+            self.bias = torch.as_tensor(bias, dtype=torch.bfloat16, device=self.device).contiguous()
+            if tuple(self.bias.shape) != (n,):
+                raise ValueError(f"bias must have shape ({n},)")
+        if residual is not None:
+            self.residual = torch.as_tensor(residual, dtype=torch.bfloat16, device=self.device).contiguous()
+            if tuple(self.residual.shape) != (m, n):
+                raise ValueError(f"residual must have the padded output shape ({m}, {n})")
 
     @property
     def handle(self):

@@ -10,6 +10,9 @@ Outputs (all small):
                       reference validator uses
   program.npz         linear_streams outputs for a few stage lists
   calibration.json    ActivationCalibration.finalize / cache_key / fp32_descale
+  attention.npz       inputs and outputs of the reference validator's own CPU FP32 attention
+                      (scripts/validate_attention.py `reference`): GQA, pi0 suffix mask, bias,
+                      rotate-half tables, boolean mask with a fully masked row
 """
 import importlib.util
 import json
@@ -119,7 +122,61 @@ def main():
         "fp32_descale": float(cal.fp32_descale(.0123, .0456)),
     }
     (HERE / "calibration.json").write_text(json.dumps(gold, indent=1, sort_keys=True))
+    attention_fixtures()
     print("golden vectors written to", HERE)
+
+
+def attention_fixtures():
+    """Call the reference validator's `reference(operation)` on small seeded cases.  The validator module imports the
+    reference's ctypes wrappers (no CUDA needed to import them); `operation` is any object with the attributes the
+    function reads."""
+    import types
+
+    import torch
+    sys.path.insert(0, str(REF))
+    spec = importlib.util.spec_from_file_location("ref_validate_attention", REF / "scripts" / "validate_attention.py")
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    out = {}
+    cases = {
+        # name: (batch, nq, nk, heads, kv_heads, head_dim, prefix, bias, rope, mask)
+        "mqa_suffix": (1, 7, 19, 8, 1, 64, 12, False, False, False),
+        "gqa_plain": (2, 9, 9, 4, 2, 72, None, False, False, False),
+        "bias_rope": (1, 6, 6, 2, 2, 64, None, True, True, False),
+        "masked": (1, 5, 11, 2, 1, 128, None, False, False, True),
+    }
+    for name, (b, nq, nk, h, hk, d, prefix, bias, rope, masked) in cases.items():
+        g = torch.Generator().manual_seed(sum(map(ord, name)))
+        q = torch.randn(b, nq, h, d, generator=g).bfloat16()
+        k = torch.randn(b, nk, hk, d, generator=g).bfloat16()
+        v = torch.randn(b, nk, hk, d, generator=g).bfloat16()
+        biases = [(torch.randn(heads, d, generator=g) * .1).bfloat16() for heads in (h, hk, hk)] if bias else [None, None, None]
+
+        def tables(rows):
+            angle = torch.randn(b, rows, d, generator=g)
+            return angle.cos().bfloat16(), angle.sin().bfloat16()
+
+        q_rope = tables(nq) if rope else None
+        k_rope = (q_rope if nq == nk else tables(nk)) if rope else None
+        mask = None
+        if masked:
+            mask = torch.rand(b, nq, nk, generator=g) > .2
+            mask[:, 0] = False                                   # a fully masked row must come out as zeros
+        op = types.SimpleNamespace(q=q, k=k, v=v, bias=biases, q_rope=q_rope, k_rope=k_rope, scale=float(d ** -0.5),
+                                   prefix=prefix, mask=mask)
+        want = mod.reference(op)
+        out[name + "_q"], out[name + "_k"], out[name + "_v"] = [t.float().numpy() for t in (q, k, v)]
+        out[name + "_out"] = want.numpy()
+        out[name + "_prefix"] = np.int64(-1 if prefix is None else prefix)
+        if bias:
+            for tag, t in zip(("qb", "kb", "vb"), biases):
+                out[f"{name}_{tag}"] = t.float().numpy()
+        if rope:
+            out[name + "_qcos"], out[name + "_qsin"] = [t.float().numpy() for t in q_rope]
+            out[name + "_kcos"], out[name + "_ksin"] = [t.float().numpy() for t in k_rope]
+        if masked:
+            out[name + "_mask"] = mask.numpy()
+    np.savez_compressed(HERE / "attention.npz", **out)
 
 
 if __name__ == "__main__":

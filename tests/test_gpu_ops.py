@@ -279,20 +279,30 @@ def test_attention(b, nq, nk, h, hk, hd, prefix, splits):
     want = oracle_ops.attention(q, k, v, hd ** -0.5, prefix).numpy()
     with ResidentAttention(None, q, k, v, workers=64, prefix=prefix, splits=splits) as op:
         op.output.fill_(float("nan"))
+        if splits > 1:
+            op.poison_partials()          # a partial read before it is written in this launch would surface as NaN
         got = op.forward().float().cpu().numpy()
         assert op.status()["code"] == 0
+        if splits > 1:
+            op.poison_partials()
         again = op.forward().float().cpu().numpy()
+        if splits > 1:
+            state = op.read_split_counts()
+            assert state["epoch"] == 2 and all(c == 2 * splits for c in state["counts"]), state
     assert np.isfinite(got).all()
     assert relrms(got, want) <= 1e-2
     np.testing.assert_array_equal(got, again)
     if splits > 1:
         # merge inside the attention stage (tiles of a head meet on a ticket): same bits as the separate merge stage, launch after launch
         with ResidentAttention(None, q, k, v, workers=128, prefix=prefix, splits=splits, fused_merge=True) as op:
-            for _ in range(3):
+            for launch in range(3):
                 op.output.fill_(float("nan"))
+                op.poison_partials()
                 fused = op.forward().float().cpu().numpy()
                 assert op.status()["code"] == 0
                 np.testing.assert_array_equal(fused, got)
+                state = op.read_split_counts()
+                assert state["epoch"] == launch + 1 and all(c == (launch + 1) * splits for c in state["counts"]), state
     if prefix is not None and nq > 1:
         # the state query must not depend on keys beyond the prefix boundary
         k2, v2 = k.clone(), v.clone()

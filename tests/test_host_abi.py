@@ -35,6 +35,22 @@ def test_header_symbols_are_exported(libraries):
         assert hasattr(owner, name), f"{name} declared in include/pi0_native.h but not exported"
 
 
+def test_every_exported_entry_point_is_declared():
+    """The other direction: nothing is exported behind the header's back."""
+    declared = set(declared_functions())
+    for source in ("pi0_native.cu", "launch_trace.cpp"):
+        text = (ROOT / "pizero-megakernel_b200" / "csrc" / source).read_text()
+        exported = set(re.findall(r'extern "C"\s+(?:int|const char\*)\s+(\w+)\s*\(', text))
+        assert exported and not exported - declared, sorted(exported - declared)
+
+
+def test_timing_record_width_matches_the_header():
+    header = (ROOT / "include" / "pi0_native.h").read_text()
+    source = (ROOT / "pizero-megakernel_b200" / "csrc" / "pi0_native.cu").read_text()
+    assert "int64 [workers, length, 8]" in header
+    assert "static_cast<size_t>(8) * prog->workers * prog->length" in source
+
+
 def test_loader_signatures_cover_the_header():
     from native_pi0 import _native
     missing = set(declared_functions()) - set(_native.EXPORTS) - {"begin_launch_trace", "end_launch_trace", "launch_trace_error"}

@@ -5,7 +5,9 @@ test.  Some callers - a control loop that must not block on the driver's allocat
 is owned by another pool - cannot obtain scratch memory when they need attention; ``attention_split_noalloc`` keeps
 its split-KV partials in a fixed device array inside the library instead.  The check: two calls in a row through
 the C ABI (different inputs, so stale partials of the first call would show in the second) reproduce the output of
-``create_attention`` + ``configure_attention_splits`` bit for bit, and sizes beyond the array are rejected.
+``create_attention`` + ``configure_attention_splits`` bit for bit - with at most 64 queries (the two warp groups
+share every key chunk), with 65..128 queries (each warp owns its rows) and with one part per head (no partials at
+all) - stay within 1e-2 NRMSE of the FP32 attention oracle, and sizes beyond the array are rejected.
 """
 import ctypes as C
 
@@ -16,6 +18,7 @@ pytestmark = pytest.mark.gpu
 
 from native_pi0 import _native
 from native_pi0.attention import ResidentAttention
+from oracle import ops as oracle_ops
 
 
 def run_reference(q, k, v, prefix, splits):
@@ -23,6 +26,10 @@ def run_reference(q, k, v, prefix, splits):
         out = op.forward().clone()
         assert op.status()["code"] == 0
     return out
+
+
+def hd_scale(hd):
+    return float(hd ** -0.5)
 
 
 def run_noalloc(lib, q, k, v, prefix, splits):
@@ -40,7 +47,8 @@ def run_noalloc(lib, q, k, v, prefix, splits):
 def test_noalloc_attention_matches_operator_twice():
     lib = _native.load()
     torch.manual_seed(2024)
-    cases = [(51, 819, 8, 768, 8), (64, 300, 4, None, 5)]      # second call: fewer parts, leaves stale partials behind
+    # second call: fewer parts, leaves stale partials behind; third: more than 64 queries; fourth: one part per head
+    cases = [(51, 819, 8, 768, 8), (64, 300, 4, None, 5), (100, 420, 8, None, 3), (51, 819, 8, 768, 1)]
     for nq, nk, heads, prefix, splits in cases:
         q = torch.randn(1, nq, heads, 256, device="cuda").bfloat16()
         k = torch.randn(1, nk, 1, 256, device="cuda").bfloat16()
@@ -49,6 +57,9 @@ def test_noalloc_attention_matches_operator_twice():
         got = run_noalloc(lib, q, k, v, prefix, splits)
         assert torch.isfinite(got.float()).all()
         assert torch.equal(got, want)                          # same kernels' arithmetic, same order: bit-exact
+        ref = oracle_ops.attention(q, k, v, hd_scale(256), prefix)
+        err = float((got.float().cpu() - ref).norm() / ref.norm())
+        assert err <= 1e-2, (nq, nk, splits, err)
     # the same inputs again after other data went through the shared array
     again = run_noalloc(lib, q, k, v, prefix, splits)
     assert torch.equal(again, want)
@@ -64,4 +75,7 @@ def test_noalloc_attention_rejects_sizes_beyond_the_array():
     assert lib.attention_split_noalloc(*args(16, 8, 256, 9)) == 1       # heads * splits > 64
     assert lib.attention_split_noalloc(*args(129, 8, 256, 2)) == 1      # more than 128 queries
     assert lib.attention_split_noalloc(*args(16, 8, 128, 2)) == 1       # head_dim other than 256
+    assert lib.attention_split_noalloc(*args(16, 8, 256, 0)) == 1       # no parts at all
+    assert lib.attention_split_noalloc(q.data_ptr() + 2, k.data_ptr(), k.data_ptr(), out.data_ptr(), 16, 32, 8, 1, 256, 2048, 256, 2048, -1, 2,
+                                       0.0625, None) == 1               # rows move in 16-byte pieces: unaligned pointers are refused
     assert lib.attention_split_noalloc(None, k.data_ptr(), k.data_ptr(), out.data_ptr(), 16, 32, 8, 1, 256, 2048, 256, 2048, -1, 2, 0.0625, None) == 1
