@@ -348,6 +348,7 @@ class Pi0Torch:
             emb = (emb.to(x.dtype) * math.sqrt(d.width)).to(x.dtype)
             x = torch.cat((x, emb))
         rows = x.shape[0]
+        self.landmarks["prefix.input"] = x
         cos, sin = rope_tables(torch.arange(rows, device=x.device), d.head_dim, d.rope_base, torch.bfloat16 if self.mode == "nvfp4" else x.dtype, self.rope_inv_freq_dtype)
         caches = []
         for i in range(d.prefix_layers):
@@ -356,7 +357,9 @@ class Pi0Torch:
             self.landmarks[f"prefix.{i}"] = x
         return caches
 
-    def denoise_step(self, caches, state_emb, actions, t, prefix_rows):
+    def denoise_step(self, caches, state_emb, actions, t, prefix_rows, tag=None):
+        """One velocity evaluation.  ``tag`` (the Euler step index) makes the expert's rows observable: the assembled
+        input as ``expert.<tag>.input`` and every layer's output as ``expert.<tag>.<layer>``."""
         d, sd = self.d, self.sd
         w = d.expert_width
         chunk = actions.shape[0]
@@ -371,8 +374,12 @@ class Pi0Torch:
         cos, sin = rope_tables(torch.arange(prefix_rows, prefix_rows + rows, device=x.device), d.head_dim, d.rope_base, adt, self.rope_inv_freq_dtype)
         mask = torch.ones(rows, prefix_rows + rows, dtype=torch.bool, device=x.device)
         mask[0, prefix_rows + 1:] = False
+        if tag is not None:
+            self.landmarks[f"expert.{tag}.input"] = x
         for i in range(d.expert_layers):
             x, _ = self.gemma_layer(x, EX, i, cos, sin, caches[i], mask)
+            if tag is not None:
+                self.landmarks[f"expert.{tag}.{i}"] = x
         xf = x[1:].float()
         if self.mode == "nvfp4":
             # engine: FP32 projection of the BF16 rows with (1+w) folded, times the row's 1/rms
@@ -386,13 +393,14 @@ class Pi0Torch:
         """images [views,224,224,3], state [1,32], noise [1,chunk,32], tokens [1,T] -> actions FP32 [1,chunk,32]."""
         self.landmarks = {}
         caches = self.prefix(images, tokens)
+        self.caches = caches
         prefix_rows = caches[0][0].shape[0]
         state_emb = F.linear(state.float(), self.sd["state_proj.weight"].float(), self.sd["state_proj.bias"].float())
         x = noise[0].float().clone()
         t = torch.tensor(1.0, dtype=torch.float32)
         dt = torch.tensor(-1.0 / steps, dtype=torch.float32)
         for step in range(steps):
-            v = self.denoise_step(caches, state_emb, x, float(t), prefix_rows)
+            v = self.denoise_step(caches, state_emb, x, float(t), prefix_rows, tag=step)
             x = x + dt.to(x.device) * v
             self.landmarks[f"actions.{step}"] = x.clone()
             t = t + dt

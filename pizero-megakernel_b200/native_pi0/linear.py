@@ -90,3 +90,74 @@ class NativeLinearProgram:
 
     def __exit__(self, *_):
         self.close()
+
+
+class NativeStageProgram:
+    """Any operator handles as one persistent launch (extension; the reference chains only dense projections).
+
+    ``stages`` is a list of ``(operator, sources)``: ``operator`` is a wrapper object (``ResidentNVFP4``,
+    ``ResidentNorm``, ``ResidentAttention``) and ``sources`` a list of ``(producer_index, mode)`` with mode 0 = wait
+    for the producer's tiles of the same 128-row band, 1 = wait for all of them.  The caller binds the buffers
+    (a consumer reads what its producer writes); the program only adds the ordering.
+    """
+    _KIND = {"ResidentNVFP4": 0, "ResidentDense": 0, "ResidentAttention": 1, "ResidentNorm": 2}
+
+    def __init__(self, library, stages, *, workers=148, schedule="linear"):
+        from native_pi0.program import spread_streams, validate_streams
+        self.library = _native.load(library)
+        self.handle = C.c_void_p()
+        self.operators = [op for op, _ in stages]
+        if not self.operators:
+            raise ValueError("At least one stage is required")
+        self.device = self.operators[0].device
+        specs, tiles, work = [], [], []
+        for index, (op, sources) in enumerate(stages):
+            kind = self._KIND.get(type(op).__name__)
+            if kind is None or not op.handle.value:
+                raise ValueError("Stages must be live operator wrappers")
+            sources = list(sources)
+            if len(sources) > 4 or any(not (0 <= s < index) or m not in (0, 1) for s, m in sources):
+                raise ValueError("Sources must be (earlier stage, mode 0|1), at most four")
+            spec = _native.NativeSpec()
+            spec.kind, spec.handle = kind, op.handle.value
+            for slot in range(4):
+                spec.sources[slot], spec.modes[slot] = sources[slot] if slot < len(sources) else (-1, 1)
+            specs.append(spec)
+            t, b, k = C.c_int(), C.c_int(), C.c_int()
+            _native.check(self.library.op_geometry(op.handle, C.byref(t), C.byref(b), C.byref(k)), "geometry")
+            tiles.append(t.value)
+            work.append(LinearWork(t.value, max(64, (k.value + 63) // 64 * 64)))
+        if schedule == "spread":
+            self.code = spread_streams(work, workers, [[s for s in spec.sources] for spec in specs])
+        else:
+            self.code = linear_streams(work, workers)
+        validate_streams(self.code, tiles)
+        self.plan = program_summary(self.code)
+        array = (_native.NativeSpec * len(specs))(*specs)
+        with torch.cuda.device(self.device):
+            _native.check(self.library.create_native_model(C.byref(self.handle), len(specs), C.cast(array, C.c_void_p),
+                                                           self.code.ctypes.data, workers, self.code.shape[1]), "Native stage program setup")
+
+    def forward(self):
+        if not self.handle.value:
+            raise RuntimeError("Native stage program is closed")
+        with torch.cuda.device(self.device):
+            _native.check(self.library.launch_native_model(self.handle, torch.cuda.current_stream(self.device).cuda_stream,
+                                                           None, None, None, None), "Native stage program launch")
+        return self.operators[-1].output
+
+    def status(self):
+        with torch.cuda.device(self.device):
+            return _native.status(self.library, self.handle)
+
+    def close(self):
+        if self.handle.value:
+            with torch.cuda.device(self.device):
+                _native.check(self.library.destroy_native_model(self.handle), "Native stage program teardown")
+            self.handle = C.c_void_p()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_):
+        self.close()

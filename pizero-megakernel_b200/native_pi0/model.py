@@ -411,6 +411,7 @@ class NativePi0:
                                                  V * 256, table.shape[0], float(math.sqrt(c.width)), self.workers), "token embedding")
             self._own(h)
             extra = [(self.add(3, h, "prefix.embed"), ALL)]
+        self.mark("prefix.input", x_a)
         cos_p, sin_p = self.rope(P, 0)
         self.caches = [(self.tensor((P + S_pad, hd)), self.tensor((P + S_pad, hd))) for _ in range(c.prefix_layers)]
         bufs = (self.fp4(P_pad, c.width), self.fp4(P_pad, H * hd), self.fp4(P_pad, c.width), self.fp4(P_pad, c.mlp),
@@ -465,8 +466,10 @@ class NativePi0:
             s_x = self.linear32(f"expert.{step}.time_out", h1, w_t2, b_t2, xe_a[1:], rows=self.chunk_size,
                                 sources=[(s_t1, ALL), (s_state, ALL)], out_bf16=True)
             _native.check(lib.configure_linear32_extra_row(self.handles[-1], state_emb.data_ptr(), xe_a.data_ptr()), "state row")
+            self.mark(f"expert.{step}.input", xe_a)
             for i in range(c.expert_layers):
                 s_x, _ = self._expert_layer(step, i, xe_a, xe_b, ebufs, S, P, s_x, cos_s, sin_s, cache_stage[i])
+                self.mark(f"expert.{step}.{i}", xe_a)
             s_prev = self.linear32(f"expert.{step}.euler", xe_a, final_w, final_b, actions, rows=self.chunk_size, sources=[(s_x, ALL)],
                                    ldx=W, x_bf16=True, rms=True, euler=True, prev=None if first else actions,
                                    prev_slot=3 if first else 0, x_row_offset=1, dt=float(dt), eps=c.rms_eps)

@@ -175,6 +175,80 @@ def test_gemm_fp4_epilogues():
         ResidentNVFP4(None, pa, pgu, output_dtype=torch.uint8, output_geglu=True, bias=bias)
 
 
+def _device_packed(x, policy, global_scale=1.0):
+    """NVFP4 operand packed on the device (bit-exact with pack_nvfp4, see test_quantizer_*): large weights in seconds."""
+    data, scales = device_quantize(x, policy, global_scale)
+    return PackedNVFP4(data, scales, np.float32(global_scale), x.shape)
+
+
+def _oracle_product(pa, pb):
+    """deq(A) . deq(B)^T: the oracle's dequantisation, the product in FP64 on the GPU (exact operands, so only the
+    summation differs from the CPU oracle's; used where the CPU product would take minutes)."""
+    a = torch.from_numpy(oracle.dequantize(pa.data, pa.scales, pa.global_scale, pa.data.shape[0:1] + (pa.data.shape[1] * 2,))).cuda().double()
+    b = torch.from_numpy(oracle.dequantize(pb.data, pb.scales, pb.global_scale, pb.data.shape[0:1] + (pb.data.shape[1] * 2,))).cuda().double()
+    return (a @ b.T).float().cpu().numpy()
+
+
+def test_gemma_mlp_block_at_full_shape():
+    """The Gemma-2B MLP block at its real size: X[768, 2048] -> RMSNorm -> NVFP4 -> gate/up 2048 -> 2 x 16384 with the
+    GeGLU epilogue -> NVFP4 -> down 16384 -> 2048 + residual (BF16).  Every stage is checked against the oracle fed
+    with the stage's actual input (N = 32768 output columns, K = 16384 = 256 K-groups through the operand ring), then
+    the three stages run as one program and must reproduce the separate launches bit for bit."""
+    from native_pi0.linear import NativeStageProgram
+    rng = np.random.default_rng(2)
+    m, width, mlp = 768, 2048, 16384
+    x = bf16(rng.normal(size=(m, width)))
+    gamma = torch.from_numpy((1 + rng.normal(scale=0.02, size=width)).astype(np.float32))
+    gate = bf16(rng.normal(scale=0.02, size=(mlp, width))).float().numpy()
+    up = bf16(rng.normal(scale=0.02, size=(mlp, width))).float().numpy()
+    down = bf16(rng.normal(scale=0.02, size=(width, mlp))).float().numpy()
+    gs_gu = float(max(np.abs(gate).max(), np.abs(up).max()) / (6 * 448))
+    gs_dn = float(np.abs(down).max() / (6 * 448))
+    p_gu = _device_packed(interleave_gate_up(gate, up), "ceil", gs_gu)
+    p_dn = _device_packed(down, "ceil", gs_dn)
+    placeholder_a = PackedNVFP4(np.zeros((m, width // 2), np.uint8), np.zeros((m, width // 16), np.uint8), np.float32(1), (m, width))
+    placeholder_h = PackedNVFP4(np.zeros((m, mlp // 2), np.uint8), np.zeros((m, mlp // 16), np.uint8), np.float32(1), (m, mlp))
+    with ResidentNorm(None, x, kind="rms", gamma=gamma, workers=148, row_alignment=128, keep_bf16=True) as norm, \
+            ResidentNVFP4(None, placeholder_a, p_gu, workers=148, output_dtype=torch.uint8, output_geglu=True,
+                          activation_buffers=(norm.output, norm.output_scales), tiled_weight=True) as gu, \
+            ResidentNVFP4(None, placeholder_h, p_dn, workers=148, output_dtype=torch.bfloat16, residual=x,
+                          activation_buffers=(gu.output, gu.output_scales), tiled_weight=True) as dn:
+        norm.forward(); gu.forward(); y = dn.forward().float().cpu().numpy()
+        for op in (norm, gu, dn):
+            assert op.status()["code"] == 0
+        # stage 1: normalised rows against the norm oracle, codes against the packer
+        normalized = norm.normalized[:m].float().cpu()
+        want = oracle_ops.norm(x, "rms", gamma, None)
+        assert relrms(normalized.numpy(), want.numpy()) < 5e-3
+        a_data = norm.output.cpu().numpy()
+        a_scales = unswizzle_scales(norm.output_scales.cpu().numpy(), m, width // 16)
+        ref = pack_nvfp4(normalized.numpy(), row_alignment=128)
+        np.testing.assert_array_equal(a_data, ref.data)
+        np.testing.assert_array_equal(a_scales, ref.scales)
+        ideal = pack_nvfp4(want.numpy(), row_alignment=128)
+        assert float((a_data != ideal.data).mean()) < 1e-2              # BF16 rounding ties of the normalised value
+        # stage 2: GeGLU(gate, up) of the device's own stage-1 codes
+        pa = PackedNVFP4(a_data, a_scales, np.float32(1), (m, width))
+        acc = _oracle_product(pa, p_gu)
+        hidden = oracle_ops.gelu_tanh(torch.from_numpy(acc[:, 0::2])).numpy() * acc[:, 1::2]
+        ref_h = pack_nvfp4(hidden)
+        got_h = _decode(gu, m, mlp)
+        assert float((got_h.scales != ref_h.scales).mean()) < 2e-3
+        assert float((got_h.data != ref_h.data).mean()) < 5e-3
+        assert relrms(got_h.dequantize(), ref_h.dequantize()) < 1e-2
+        # stage 3: down projection of the device's own stage-2 codes, + residual, one BF16 rounding
+        out = _oracle_product(got_h, p_dn) + x.float().numpy()
+        assert relrms(y, out) < 1e-2
+        assert relrms(y, bf16(out).float().numpy()) < 3e-3
+        # the same three stages as ONE launch with row-band dependencies
+        for schedule in ("linear", "spread"):
+            with NativeStageProgram(None, [(norm, []), (gu, [(0, 0)]), (dn, [(1, 0)])], workers=148, schedule=schedule) as program:
+                dn.output.fill_(float("nan"))
+                z = program.forward().float().cpu().numpy()
+                assert program.status()["code"] == 0
+                np.testing.assert_array_equal(z, y)
+
+
 def test_gemm_qkv_rope_epilogue():
     lib = _native.load()
     rng = np.random.default_rng(71)
