@@ -57,6 +57,45 @@ int configure_resident_fp4_tile(void* handle, int block_n);
 int configure_resident_fp4_weight_layout(void* handle, int tiled);
 
 /* ------------------------------------------------------------------------------------------------------
+ * Dense projection:  out[M,N] = epilogue(alpha * A[M,K] . B[N,K]^T), A and B both BF16 (fp8 == 0) or both FP8 E4M3
+ * (fp8 == 1), row-major with K contiguous, FP32 accumulation on tcgen05 (kind::f16 / kind::f8f6f4) through the same
+ * TMA ring and tensor-memory accumulators as the NVFP4 GEMM.  M, N multiples of 128; K a multiple of 64 (BF16) or 128
+ * (FP8); all pointers 16-byte aligned.  bf16 == 1: BF16 output, else FP32; bias BF16 [N] and residual BF16 [M, N]
+ * are added in FP32 (residual first, then bias) before the single rounding.
+ * Replaces: native_pi0/dense.cu:142-253 (create_dense, launch_dense, destroy_dense and the six configure_dense_*),
+ * bound in native_pi0/dense.py:8-129; the GEMM itself replaces native_pi0/tcgen_probe.cu:35-125.
+ */
+int create_dense(void** handle, const void* a, const void* b, void* out, const void* bias, const void* residual,
+                 int m, int n, int k, int workers, int fp8, int bf16, float alpha);
+int launch_dense(void* handle, void* stream);
+int destroy_dense(void* handle);
+/* The configure calls below need BF16 operands and BF16 output, as in the reference. */
+/* (+bias) is rounded to BF16 first, then the residual is added and the sum rounded again (needs a residual). */
+int configure_dense_round_before_residual(void* handle);
+/* Interleaved (gate, up) column pairs -> compact BF16 [M, N/2] = bf16(bf16(gelu_tanh(bf16 gate)) * bf16 up); no bias,
+ * no residual, N a multiple of 256. */
+int configure_dense_geglu(void* handle, void* compact_output);
+/* GELU(tanh) of the BF16-rounded value in columns < logical_columns, zeros beyond (no residual). */
+int configure_dense_gelu(void* handle, int logical_columns);
+/* Every accumulator row r is multiplied by factors[r] (FP32 [M]): the 1/rms of an un-normalised input row whose
+ * norm weight has been folded into B (no bias, no residual). */
+int configure_dense_rms_factor(void* handle, const float* factors);
+/* At most 64 logical rows (M == 128): only 64 rows of A are copied per tile and rows >= 64 are never stored. */
+int configure_dense_skinny(void* handle);
+/* Fused QKV epilogue of a [M, key_offset + 512] projection: Q heads (columns < key_offset) stay in `out`, rotated;
+ * the K head (columns key_offset..+256) is rotated and written to cache_k row cache_base + r; the V head to cache_v.
+ * cos/sin BF16 [rows, 256].  Layout note: the rotation is done on ADJACENT column pairs, so the rows of the Q and K
+ * heads of B must be ordered (0, 128, 1, 129, ...) inside each head (the Python wrapper does this); Q in `out` and K in
+ * the cache are then in that same pair order, which attention over them does not see. */
+int configure_dense_qkv_rope(void* handle, const void* cos, const void* sin, void* cache_k, void* cache_v, int logical_rows,
+                             int key_offset, int cache_base);
+/* extension: logical row count and output tile width (128 or 64) of a dense projection.  The NVFP4 GEMM's
+ * configure_resident_fp4_{bf16, quantized, qkv_rope, rows, tile} calls accept dense handles too (a dense projection
+ * may emit NVFP4 for an NVFP4 consumer); configure_resident_fp4_weight_layout does not. */
+int configure_dense_rows(void* handle, int rows);
+int configure_dense_tile(void* handle, int block_n);
+
+/* ------------------------------------------------------------------------------------------------------
  * LayerNorm / RMSNorm producer -> NVFP4 (format 4) or BF16 (format 16).
  * Replaces: native_pi0/norm.cu:138-176 (create_norm, launch_norm, destroy_norm), bound in
  * native_pi0/normalization.py:43-66.  Supported subset: BF16 input (fp16 == 0), no fused residual

@@ -218,6 +218,12 @@ class Pi0Torch:
         self._wq = {}
         self._kv_only = {(f"{LM}layers.{dims.prefix_layers - 1}.self_attn", "kv_only")}
         self.landmarks = {}
+        self.record_ops = False                 # also keep every operator's output (``ops``), named like the engine's stages
+        self.ops = {}
+
+    def rec(self, name, tensor):
+        if self.record_ops:
+            self.ops[name] = tensor
 
     # ----- linear layers ---------------------------------------------------------------------------
     def _fused_scale(self, name, w):
@@ -286,25 +292,35 @@ class Pi0Torch:
         for i in range(d.vision_layers):
             p = f"{VP}encoder.layers.{i}."
             y = F.layer_norm(x.float(), (d.vision_width,), sd[p + "layer_norm1.weight"].float(), sd[p + "layer_norm1.bias"].float(), d.ln_eps).to(x.dtype)
+            self.rec(f"vision.{i}.ln1", y)
             q = self.act(self.linear(y, p + "self_attn.q_proj"))
             k = self.act(self.linear(y, p + "self_attn.k_proj"))
             v = self.act(self.linear(y, p + "self_attn.v_proj"))
+            self.rec(f"vision.{i}.qkv", torch.cat((q, k, v), dim=-1))
             outs = []
             for b in range(views):
                 sl = slice(b * 256, (b + 1) * 256)
                 outs.append(self.attention(q[sl].reshape(256, d.vision_heads, hd), k[sl].reshape(256, d.vision_heads, hd),
                                            v[sl].reshape(256, d.vision_heads, hd), hd ** -0.5))
             a = torch.cat(outs).reshape(-1, d.vision_width)
+            self.rec(f"vision.{i}.attention", a)
             o = self.linear(a, p + "self_attn.out_proj")
             x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+            self.rec(f"vision.{i}.out", x)
             y = F.layer_norm(x.float(), (d.vision_width,), sd[p + "layer_norm2.weight"].float(), sd[p + "layer_norm2.bias"].float(), d.ln_eps).to(x.dtype)
+            self.rec(f"vision.{i}.ln2", y)
             h = self.linear(y, p + "mlp.fc1")
             h = F.gelu(h.float(), approximate="tanh") if self.mode == "nvfp4" else F.gelu(h, approximate="tanh")
+            self.rec(f"vision.{i}.fc1", h)
             o = self.linear(h, p + "mlp.fc2")
             x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+            self.rec(f"vision.{i}.fc2", x)
             self.landmarks[f"vision.{i}"] = x
         y = F.layer_norm(x.float(), (d.vision_width,), sd[VP + "post_layernorm.weight"].float(), sd[VP + "post_layernorm.bias"].float(), d.ln_eps).to(x.dtype)
-        return self.act(self.linear(y, PJ[:-1]))
+        self.rec("vision.post_layernorm", y)
+        out = self.act(self.linear(y, PJ[:-1]))
+        self.rec("vision.projector", out)
+        return out
 
     # ----- Gemma -----------------------------------------------------------------------------------
     def rms(self, x, w):
@@ -312,14 +328,18 @@ class Pi0Torch:
         y = xf * torch.rsqrt(xf.square().mean(-1, keepdim=True) + self.d.rms_eps) * (1.0 + w.float())
         return y.to(x.dtype)
 
-    def gemma_layer(self, x, prefix, i, cos, sin, cache, mask, kv_only=False):
-        """One decoder layer on rows x [N, width].  ``cache`` = (K, V) of earlier rows or None.  Returns (x, (K, V))."""
+    def gemma_layer(self, x, prefix, i, cos, sin, cache, mask, kv_only=False, name=None):
+        """One decoder layer on rows x [N, width].  ``cache`` = (K, V) of earlier rows or None.  Returns (x, (K, V)).
+        ``name`` (the engine's stage prefix, e.g. ``prefix.3`` or ``expert.0.3``) labels the operator outputs kept by ``rec``."""
         d, sd = self.d, self.sd
         p = f"{prefix}layers.{i}."
         y = self.rms(x, sd[p + "input_layernorm.weight"])
+        self.rec(f"{name}.norm1", y)
         k = self.act(self.linear(y, p + "self_attn.k_proj", bias=False)).reshape(-1, 1, d.head_dim)
         v = self.act(self.linear(y, p + "self_attn.v_proj", bias=False)).reshape(-1, 1, d.head_dim)
         k = apply_rope(k, cos, sin)
+        self.rec(f"{name}.qkv.k", k)
+        self.rec(f"{name}.qkv.v", v)
         if cache is not None:
             k_all, v_all = torch.cat((cache[0], k)), torch.cat((cache[1], v))
         else:
@@ -328,15 +348,21 @@ class Pi0Torch:
             return x, (k, v)
         q = self.act(self.linear(y, p + "self_attn.q_proj", bias=False)).reshape(-1, d.heads, d.head_dim)
         q = apply_rope(q, cos, sin)
+        self.rec(f"{name}.qkv.q", q)
         a = self.attention(q, k_all, v_all, d.head_dim ** -0.5, mask).reshape(x.shape[0], -1)
+        self.rec(f"{name}.attention", a)
         o = self.linear(a, p + "self_attn.o_proj", bias=False)
         x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+        self.rec(f"{name}.o_proj", x)
         y = self.rms(x, sd[p + "post_attention_layernorm.weight"])
+        self.rec(f"{name}.norm2", y)
         gate = self.linear(y, p + "mlp.gate_proj", bias=False)
         up = self.linear(y, p + "mlp.up_proj", bias=False)
         h = F.gelu(gate.float(), approximate="tanh") * up.float() if self.mode == "nvfp4" else F.gelu(gate, approximate="tanh") * up
+        self.rec(f"{name}.gate_up", h)
         o = self.linear(h, p + "mlp.down_proj", bias=False)
         x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+        self.rec(f"{name}.down", x)
         return x, (k, v)
 
     def prefix(self, images, tokens):
@@ -352,7 +378,7 @@ class Pi0Torch:
         cos, sin = rope_tables(torch.arange(rows, device=x.device), d.head_dim, d.rope_base, torch.bfloat16 if self.mode == "nvfp4" else x.dtype, self.rope_inv_freq_dtype)
         caches = []
         for i in range(d.prefix_layers):
-            x, kv = self.gemma_layer(x, LM, i, cos, sin, None, None, kv_only=(i == d.prefix_layers - 1))
+            x, kv = self.gemma_layer(x, LM, i, cos, sin, None, None, kv_only=(i == d.prefix_layers - 1), name=f"prefix.{i}")
             caches.append(kv)
             self.landmarks[f"prefix.{i}"] = x
         return caches
@@ -367,6 +393,7 @@ class Pi0Torch:
         t_emb = time_embedding(t, w, actions.device)[None].expand(chunk, -1)
         h = F.linear(torch.cat((a_emb, t_emb), dim=-1), sd["action_time_mlp_in.weight"].float(), sd["action_time_mlp_in.bias"].float())
         h = F.silu(h)
+        self.rec(f"expert.{tag}.time_in", h)
         h = F.linear(h, sd["action_time_mlp_out.weight"].float(), sd["action_time_mlp_out.bias"].float())
         adt = torch.bfloat16 if self.mode == "nvfp4" else self.dt
         x = torch.cat((state_emb, h)).to(adt)
@@ -377,7 +404,7 @@ class Pi0Torch:
         if tag is not None:
             self.landmarks[f"expert.{tag}.input"] = x
         for i in range(d.expert_layers):
-            x, _ = self.gemma_layer(x, EX, i, cos, sin, caches[i], mask)
+            x, _ = self.gemma_layer(x, EX, i, cos, sin, caches[i], mask, name=f"expert.{tag}.{i}")
             if tag is not None:
                 self.landmarks[f"expert.{tag}.{i}"] = x
         xf = x[1:].float()

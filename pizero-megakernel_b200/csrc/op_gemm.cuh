@@ -1,9 +1,12 @@
-// NVFP4 block-scaled GEMM instruction:  out[M,N] = epilogue(alpha * deq(A)[M,K] . deq(B)[N,K]^T)
+// GEMM instruction:  out[M,N] = epilogue(alpha * A[M,K] . B[N,K]^T), FP32 accumulation in tensor memory.
+// Operands: NVFP4 (packed E2M1 with E4M3 block scales, tcgen05.mma kind::mxf4nvf4.block_scale), BF16 (kind::f16) or
+// FP8 E4M3 (kind::f8f6f4).  In every format a row of K is cut into 128-byte chunks and one MMA consumes 32 bytes of
+// each operand row (64 FP4, 16 BF16 or 32 FP8 elements), so the copy ring and the issue loop are the same code.
 //
 //   warp 0 / lane 0 : TMA producer  - operand tiles (128 B swizzled rows) and scale atoms into a ring of slots; the ring
-//                                     is laid out per GEMM: 2 slots of 72 KiB for full tiles, up to 5 for narrow ones
-//   warp 1          : MMA issuer    - warp-uniform loop, one elected lane issues tcgen05.cp (scales smem->TMEM) and
-//                                     tcgen05.mma kind::mxf4nvf4, K = 64 each
+//                                     is laid out per GEMM: 2 slots of 72 KiB for full NVFP4 tiles, up to 5 for narrow ones
+//   warp 1          : MMA issuer    - warp-uniform loop, one elected lane issues tcgen05.cp (scales smem->TMEM, NVFP4
+//                                     only) and tcgen05.mma, 32 operand bytes of K each
 //   warps 4..7      : epilogue      - tcgen05.ld of a 128xN FP32 accumulator (one row per thread), fused math, stores
 //
 // Two TMEM accumulators alternate, so the epilogue of tile t overlaps the MMAs of tile t+1. Pipeline positions live in
@@ -28,6 +31,7 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
     const uint32_t a_bytes = static_cast<uint32_t>(kChunks) * 128u * static_cast<uint32_t>(g.a_box_rows);
     const uint32_t b_bytes = static_cast<uint32_t>(kChunks) * 128u * static_cast<uint32_t>(g.block_n);
     const uint32_t ring = static_cast<uint32_t>(g.ring_stages), stride = static_cast<uint32_t>(g.slot_stride);
+    const uint32_t sf_unit = g.operands == GEMM_NVFP4 ? 512u : 0u;      // scale-atom bytes per MMA group and operand
     if (ps.prod_geo != stride) {
         // Slots of the previous geometry overlap the new ones at other indices: every copy issued so far must have
         // been read by its MMAs before the first new copy lands (waits for the last release of each slot).
@@ -56,11 +60,12 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
                         if (!mbar_wait(prog, ctl, &ctl->empty[s], ((p_bits >> s) & 1u) ^ 1u, stage_index)) { alive = 0; break; }
                         const int groups = min(4 * kChunks, g.k_groups - ks * 4 * kChunks);
                         uint8_t* slot = data + s * stride;
-                        mbar_expect_tx_only(&ctl->full[s], b_bytes + groups * 512u);
+                        mbar_expect_tx_only(&ctl->full[s], b_bytes + groups * sf_unit);
                         if (g.b_tiled) tma_load_2d(slot + g.off_b, g.tmap_b, &ctl->full[s], 0, (n_tile * chunks + ks * kChunks) * g.block_n);
                         else tma_load_3d(slot + g.off_b, g.tmap_b, &ctl->full[s], 0, n_tile * g.block_n, ks * kChunks);
-                        bulk_load(slot + g.off_sfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
-                                  groups * 512u, &ctl->full[s]);
+                        if (sf_unit)
+                            bulk_load(slot + g.off_sfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
+                                      groups * 512u, &ctl->full[s]);
                     }
                 }
                 early = __shfl_sync(0xffffffffu, early, 0);
@@ -84,15 +89,17 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
                 // Boxes always deliver kChunks chunks (beyond K the copy engine fills zeros or, inside a padded
                 // allocation, bytes that no MMA reads).  a_box_rows < 128 (few logical rows): only the rows that
                 // exist are copied; the MMA still reads 128 rows, the rest lands in accumulator rows never stored.
-                mbar_expect_tx(&ctl->full[s], a_bytes + groups * 512u + (weights_issued ? 0u : b_bytes + groups * 512u));
+                mbar_expect_tx(&ctl->full[s], a_bytes + groups * sf_unit + (weights_issued ? 0u : b_bytes + groups * sf_unit));
                 tma_load_3d(slot, g.tmap_a, &ctl->full[s], 0, m_tile * 128, ks * kChunks);
-                bulk_load(slot + g.off_sfa, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4 * kChunks) * 512, groups * 512u,
-                          &ctl->full[s]);
+                if (sf_unit)
+                    bulk_load(slot + g.off_sfa, g.sfa + (static_cast<size_t>(m_tile) * g.k_groups + ks * 4 * kChunks) * 512, groups * 512u,
+                              &ctl->full[s]);
                 if (!weights_issued) {
                     if (g.b_tiled) tma_load_2d(slot + g.off_b, g.tmap_b, &ctl->full[s], 0, (n_tile * chunks + ks * kChunks) * g.block_n);
                     else tma_load_3d(slot + g.off_b, g.tmap_b, &ctl->full[s], 0, n_tile * g.block_n, ks * kChunks);
-                    bulk_load(slot + g.off_sfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
-                              groups * 512u, &ctl->full[s]);
+                    if (sf_unit)
+                        bulk_load(slot + g.off_sfb, g.sfb + (static_cast<size_t>(sfb_tile) * g.k_groups + ks * 4 * kChunks) * 512,
+                                  groups * 512u, &ctl->full[s]);
                 }
                 p_bits ^= 1u << s;
                 p_slot = s + 1 == ring ? 0u : s + 1;
@@ -121,6 +128,7 @@ __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_
     const uint32_t off_b16 = uniform_u32(static_cast<uint32_t>(g.off_b)) >> 4, off_sfa16 = uniform_u32(static_cast<uint32_t>(g.off_sfa)) >> 4,
                    off_sfb16 = uniform_u32(static_cast<uint32_t>(g.off_sfb)) >> 4;
     const uint32_t idesc = uniform_u32(g.idesc);
+    const int operands = uniform_i32(g.operands);
     const uint32_t tmem = uniform_u32(tmem_in);
     const uint32_t data16 = uniform_u32((smem_u32(data) & 0x3FFFFu) >> 4), stride16 = stride >> 4;
     // descriptor high words: K-major 128-byte swizzle (8-row groups 1024 bytes apart, version 1) and the scale atoms
@@ -146,7 +154,23 @@ __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_
             const int groups = min(4 * kChunks, k_groups - ks * 4 * kChunks);
             const uint32_t a16 = data16 + s * stride16;
             const uint32_t sf_cols = tmem + kSfCol0 + (it & 3u) * (4 * kChunks * 8);
-            if (elect_one()) {
+            if (operands != GEMM_NVFP4) {
+                // BF16 / FP8 rows: the same descriptors and the same 32-byte advance along K, no scale factors
+                if (elect_one()) {
+#pragma unroll
+                    for (int gi = 0; gi < 4 * kChunks; ++gi) {
+                        if (gi < groups) {
+                            const uint32_t chunk = static_cast<uint32_t>(gi) >> 2, sub = static_cast<uint32_t>(gi) & 3u;
+                            const uint64_t da = kOperandHi | static_cast<uint64_t>(a16 + chunk * a_chunk16 + 2u * sub);
+                            const uint64_t db = kOperandHi | static_cast<uint64_t>(a16 + off_b16 + chunk * b_chunk16 + 2u * sub);
+                            const uint32_t acc = gi != 0 ? 1u : static_cast<uint32_t>(ks != 0);
+                            if (operands == GEMM_BF16) tc_mma_f16(d, da, db, idesc, acc);
+                            else tc_mma_f8(d, da, db, idesc, acc);
+                        }
+                    }
+                    tc_commit(&ctl->empty[s]);
+                }
+            } else if (elect_one()) {
 #pragma unroll
                 for (int gi = 0; gi < 4 * kChunks; ++gi) {
                     if (gi < groups) {
@@ -194,15 +218,11 @@ __device__ __forceinline__ float gelu_sigmoid(float x) {
 __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const uint32_t (&raw)[32], int row, int col0,
                                                     bool row_ok) {
     float v[32];
-#pragma unroll
-    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(raw[i]) * g.alpha;
     if (!row_ok) return;
-    if (g.epilogue == EPI_F32) {
-        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + static_cast<size_t>(row) * g.ldo + col0);
+    // alpha, and for a projection of un-normalised rows the row's 1/rms (the norm weight is folded into B)
+    const float row_scale = g.row_factor ? g.alpha * __ldcg(g.row_factor + row) : g.alpha;
 #pragma unroll
-        for (int i = 0; i < 8; i++) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        return;
-    }
+    for (int i = 0; i < 32; i++) v[i] = __uint_as_float(raw[i]) * row_scale;
     if (g.epilogue == EPI_GEGLU_FP4) {
         // interleaved (gate, up) column pairs -> 16 outputs = one scale block
         float h[16];
@@ -215,7 +235,22 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         g.out_scales[scale_offset(row, out_col >> 4, g.out_blocks)] = static_cast<uint8_t>(code);
         return;
     }
-    if (g.bias) {
+    if (g.epilogue == EPI_GEGLU_BF16) {
+        // bf16(gelu(bf16 gate)) * bf16(up), rounded once more: the BF16 model's GeGLU on interleaved (gate, up) columns
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float h0 = bf16_round(gelu_tanh(bf16_round(v[4 * i]))) * bf16_round(v[4 * i + 1]);
+            const float h1 = bf16_round(gelu_tanh(bf16_round(v[4 * i + 2]))) * bf16_round(v[4 * i + 3]);
+            w[i] = pack_bf16x2(h0, h1);
+        }
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(row) * g.ldo + (col0 >> 1));
+        dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+        dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        return;
+    }
+    const bool early_bias = g.bias && g.residual && g.round_before_residual;
+    if (early_bias) {
         const uint4* b = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(g.bias) + col0);
 #pragma unroll
         for (int i = 0; i < 4; i++) {
@@ -228,6 +263,10 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         }
     }
     if (g.residual) {
+        if (g.round_before_residual) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = bf16_round(v[i]);
+        }
         const uint4* r = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(g.residual) +
                                                         static_cast<size_t>(row) * g.ldr + col0);
 #pragma unroll
@@ -240,7 +279,30 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
             f = unpack_bf16x2(u.w); v[8 * i + 6] += f.x; v[8 * i + 7] += f.y;
         }
     }
+    if (g.bias && !early_bias) {
+        // (residual first, bias second: the order of the reference epilogue, whose BF16 result the tests reproduce bit for bit)
+        const uint4* b = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(g.bias) + col0);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            uint4 u = __ldg(b + i);
+            float2 f;
+            f = unpack_bf16x2(u.x); v[8 * i + 0] += f.x; v[8 * i + 1] += f.y;
+            f = unpack_bf16x2(u.y); v[8 * i + 2] += f.x; v[8 * i + 3] += f.y;
+            f = unpack_bf16x2(u.z); v[8 * i + 4] += f.x; v[8 * i + 5] += f.y;
+            f = unpack_bf16x2(u.w); v[8 * i + 6] += f.x; v[8 * i + 7] += f.y;
+        }
+    }
+    if (g.epilogue == EPI_F32) {
+        float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + static_cast<size_t>(row) * g.ldo + col0);
+#pragma unroll
+        for (int i = 0; i < 8; i++) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        return;
+    }
     if (g.epilogue == EPI_BF16) {
+        if (g.gelu_cols > 0) {
+#pragma unroll
+            for (int i = 0; i < 32; i++) v[i] = col0 + i < g.gelu_cols ? gelu_tanh(bf16_round(v[i])) : 0.f;
+        }
         uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(row) * g.ldo + col0);
 #pragma unroll
         for (int i = 0; i < 4; i++)

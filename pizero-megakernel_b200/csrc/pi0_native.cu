@@ -57,12 +57,13 @@ EncodeTiled encoder() {
     }
     return fn;
 }
-// Packed FP4 matrix [rows, k/2] bytes seen as [chunk][row][128 bytes]: a box is kChunks consecutive 256-wide K chunks
-// of box_rows rows, each chunk landing as box_rows 128-byte rows with the 128-byte swizzle.
-int encode_operand(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+// Operand matrix [rows, row_bytes] seen as [chunk][row][128 bytes]: a box is kChunks consecutive 128-byte chunks of K
+// (256 FP4, 64 BF16 or 128 FP8 elements each) of box_rows rows, each chunk landing as box_rows 128-byte rows with the
+// 128-byte swizzle.
+int encode_operand(CUtensorMap* map, const void* base, int rows, size_t row_bytes_in, int box_rows) {
     EncodeTiled fn = encoder();
     if (!fn) return cudaErrorNotSupported;
-    const cuuint64_t row_bytes = static_cast<cuuint64_t>(k / 2);
+    const cuuint64_t row_bytes = static_cast<cuuint64_t>(row_bytes_in);
     cuuint64_t dims[3] = {128u, static_cast<cuuint64_t>(rows), (row_bytes + 127) / 128};
     cuuint64_t strides[2] = {row_bytes, 128u};
     cuuint32_t box[3] = {128u, static_cast<cuuint32_t>(box_rows), static_cast<cuuint32_t>(kChunks)};
@@ -97,6 +98,7 @@ struct Op {
     // GEMM bookkeeping (tensor maps are rebuilt when the tile width changes)
     const void *a = nullptr, *b = nullptr;
     int m = 0, n = 0, k = 0;
+    int operands = GEMM_NVFP4;
     CUtensorMap* maps = nullptr;       // device: [0] = A, [1] = B
     // attention bookkeeping
     Op* merge = nullptr;               // owned merge stage (splits > 1)
@@ -329,12 +331,18 @@ void free_op(Op* op) {
     delete op;
 }
 
+// Bytes of one operand row: K elements of 4, 16 or 8 bits.
+size_t operand_row_bytes(int operands, int k) {
+    return operands == GEMM_NVFP4 ? static_cast<size_t>(k) / 2 : operands == GEMM_BF16 ? static_cast<size_t>(k) * 2 : static_cast<size_t>(k);
+}
+
 int gemm_refresh(Op* op) {
     GemmParams& g = op->desc.p.gemm;
     CUtensorMap host[2];
-    int e = encode_operand(&host[0], op->a, op->m, op->k, g.a_box_rows);
+    const size_t row_bytes = operand_row_bytes(op->operands, op->k);
+    int e = encode_operand(&host[0], op->a, op->m, row_bytes, g.a_box_rows);
     if (!e) e = g.b_tiled ? encode_tiled(&host[1], op->b, op->n * (op->k / 256), kChunks * g.block_n)
-                          : encode_operand(&host[1], op->b, op->n, op->k, g.block_n);
+                          : encode_operand(&host[1], op->b, op->n, row_bytes, g.block_n);
     if (e) return e;
     if (!op->maps) {
         cudaError_t ce = cudaMalloc(&op->maps, 2 * sizeof(CUtensorMap));
@@ -346,21 +354,27 @@ int gemm_refresh(Op* op) {
     g.tmap_b = op->maps + 1;
     g.m_tiles = op->m / 128;
     g.n_tiles = op->n / g.block_n;
-    g.k_groups = op->k / 64;
-    // Operand ring: a slot holds kChunks chunks of the rows that are actually copied (A: a_box_rows, B: block_n) and
-    // 4 KiB of scale atoms per operand. The MMA always reads 128 rows of A; with 64 copied rows the other 64 are
+    g.operands = op->operands;
+    g.k_groups = static_cast<int>(row_bytes / 32);
+    // Operand ring: a slot holds kChunks chunks of the rows that are actually copied (A: a_box_rows, B: block_n) and,
+    // for NVFP4, 4 KiB of scale atoms per operand. The MMA always reads 128 rows of A; with 64 copied rows the other 64 are
     // whatever follows in the slot (B, scales) and end in accumulator rows that are never stored, so the read only
     // has to stay inside shared memory, which the slot's own B and scale regions guarantee.
     g.off_b = kChunks * 128 * g.a_box_rows;
+    const int sf_bytes = op->operands == GEMM_NVFP4 ? kSfBytes : 0;
     g.off_sfa = g.off_b + kChunks * 128 * g.block_n;
-    g.off_sfb = g.off_sfa + kSfBytes;
-    g.slot_stride = g.off_sfb + kSfBytes;
+    g.off_sfb = g.off_sfa + sf_bytes;
+    g.slot_stride = g.off_sfb + sf_bytes;
     g.ring_stages = std::max(kStages, std::min(kMaxStages, kDataBytes / g.slot_stride));
     if (g.slot_stride % 1024 || g.ring_stages * g.slot_stride > kDataBytes ||
         (kChunks - 1) * 128 * g.a_box_rows + kTileABytes > g.slot_stride)
         return cudaErrorInvalidValue;
-    constexpr uint32_t fmt = 1u;                                                       // E2M1, the operand format of kind::mxf4nvf4
-    g.idesc = (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(g.block_n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
+    // tcgen05 instruction descriptor: operand formats at bits 7 and 10 (block-scaled kind: 1 = E2M1; kind::f16: 1 = BF16;
+    // kind::f8f6f4: 0 = E4M3), FP32 accumulator (bit 4) for the dense kinds, N / 8 at bit 17, M / 16 at bit 24; both
+    // operands K-major.
+    const uint32_t fmt = op->operands == GEMM_FP8 ? 0u : 1u;
+    const uint32_t acc_f32 = op->operands == GEMM_NVFP4 ? 0u : (1u << 4);
+    g.idesc = acc_f32 | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(g.block_n >> 3) << 17) | (static_cast<uint32_t>(128 >> 4) << 24);
     op->desc.tiles = g.m_tiles * g.n_tiles;
     op->desc.bands = g.m_tiles;
     op->desc.band_div = g.n_tiles;
@@ -514,7 +528,8 @@ extern "C" int configure_resident_fp4_rows(void* handle, int rows) {
 }
 extern "C" int configure_resident_fp4_weight_layout(void* handle, int tiled) {
     Op* op = as_op(handle);
-    if (!op || op->desc.kind != OP_GEMM || (tiled != 0 && tiled != 1) || (tiled && op->k % 256)) return cudaErrorInvalidValue;
+    if (!op || op->desc.kind != OP_GEMM || (tiled != 0 && tiled != 1) || (tiled && (op->k % 256 || op->operands != GEMM_NVFP4)))
+        return cudaErrorInvalidValue;
     op->desc.p.gemm.b_tiled = tiled;
     return gemm_refresh(op);
 }
@@ -544,6 +559,132 @@ extern "C" int resident_fp4_resources(void* handle, int* values, int count) {
     return cudaSuccess;
 }
 extern "C" int destroy_resident_fp4(void* handle) { return destroy_checked(handle); }
+
+// =====================================================================================================
+// Dense (BF16 / FP8 E4M3) projections on the same tcgen05 pipeline, with the BF16 model's epilogues.
+extern "C" int create_dense(void** handle, const void* a, const void* b, void* out, const void* bias, const void* residual,
+                            int m, int n, int k, int workers, int fp8, int bf16, float alpha) {
+    if (!handle) return cudaErrorInvalidValue;
+    *handle = nullptr;
+    if (!a || !b || !out || m < 128 || m % 128 || n < 128 || n % 128 || k < 64 || k % 64 || (fp8 != 0 && fp8 != 1) ||
+        (bf16 != 0 && bf16 != 1) || !std::isfinite(alpha) || alpha <= 0 || (fp8 && k % 128) ||
+        !aligned16(a) || !aligned16(b) || !aligned16(out) || !aligned16(bias) || !aligned16(residual))
+        return cudaErrorInvalidValue;
+    Op* op = nullptr;
+    int e = new_op(&op, workers);
+    if (e) return e;
+    op->a = a; op->b = b; op->m = m; op->n = n; op->k = k;
+    op->operands = fp8 ? GEMM_FP8 : GEMM_BF16;
+    StageDesc& d = op->desc;
+    d.kind = OP_GEMM;
+    finish_desc(d);
+    GemmParams& g = d.p.gemm;
+    g.block_n = 128;
+    g.a_box_rows = 128;
+    g.alpha = alpha;
+    g.epilogue = bf16 ? EPI_BF16 : EPI_F32;
+    g.rows = m;
+    g.out = out;
+    g.ldo = n;
+    g.bias = bias;
+    g.residual = residual;
+    g.ldr = n;
+    g.out_inv_gs = 1.f;
+    e = gemm_refresh(op);
+    if (e) { free_op(op); return e; }
+    *handle = op;
+    return cudaSuccess;
+}
+namespace {
+// A dense handle whose operands are BF16 and whose output is BF16: what every configure_dense_* call requires.
+Op* dense_bf16(void* handle) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || op->operands != GEMM_BF16) return nullptr;
+    const int epilogue = op->desc.p.gemm.epilogue;
+    return epilogue == EPI_BF16 || epilogue == EPI_GEGLU_BF16 || epilogue == EPI_QKV_ROPE ? op : nullptr;
+}
+}  // namespace
+extern "C" int launch_dense(void* handle, void* stream) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || op->operands == GEMM_NVFP4) return cudaErrorInvalidValue;
+    return launch_solo(handle, stream);
+}
+extern "C" int destroy_dense(void* handle) { return destroy_checked(handle); }
+extern "C" int configure_dense_round_before_residual(void* handle) {
+    Op* op = dense_bf16(handle);
+    if (!op || !op->desc.p.gemm.residual || op->desc.p.gemm.epilogue != EPI_BF16) return cudaErrorInvalidValue;
+    op->desc.p.gemm.round_before_residual = 1;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_dense_geglu(void* handle, void* compact_output) {
+    Op* op = dense_bf16(handle);
+    if (!op || !compact_output || !aligned16(compact_output)) return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    if (g.epilogue != EPI_BF16 || g.bias || g.residual || g.gelu_cols || op->n % 256) return cudaErrorInvalidValue;
+    g.epilogue = EPI_GEGLU_BF16;
+    g.out = compact_output;
+    g.ldo = op->n / 2;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_dense_gelu(void* handle, int logical_columns) {
+    Op* op = dense_bf16(handle);
+    if (!op) return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    if (g.epilogue != EPI_BF16 || g.residual || logical_columns < 1 || logical_columns > op->n) return cudaErrorInvalidValue;
+    g.gelu_cols = logical_columns;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_dense_rms_factor(void* handle, const float* factors) {
+    Op* op = dense_bf16(handle);
+    if (!op || !factors) return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    if (g.bias || g.residual) return cudaErrorInvalidValue;
+    g.row_factor = factors;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_dense_skinny(void* handle) {
+    Op* op = dense_bf16(handle);
+    if (!op || op->m != 128) return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    g.a_box_rows = 64;                      // only 64 rows of A are copied per tile ...
+    g.rows = std::min(g.rows, 64);          // ... and only those rows are ever stored
+    return gemm_refresh(op);
+}
+extern "C" int configure_dense_qkv_rope(void* handle, const void* cos, const void* sin, void* cache_k, void* cache_v,
+                                        int logical_rows, int key_offset, int cache_base) {
+    Op* op = dense_bf16(handle);
+    if (!op || !cos || !sin || !cache_k || !cache_v || logical_rows < 1 || key_offset < 0 || key_offset % 256 || cache_base < 0 ||
+        !aligned16(cos) || !aligned16(sin) || !aligned16(cache_k) || !aligned16(cache_v))
+        return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    if (g.epilogue != EPI_BF16 || g.bias || g.residual || g.gelu_cols || logical_rows > op->m || key_offset + 512 != op->n)
+        return cudaErrorInvalidValue;
+    g.epilogue = EPI_QKV_ROPE;
+    g.rope_cos = cos; g.rope_sin = sin;
+    g.cache_k = cache_k; g.cache_v = cache_v;
+    g.q_cols = key_offset; g.head_dim = 256; g.cache_base = cache_base;
+    g.rows = std::min(g.rows, logical_rows);
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+// extension: logical rows (as configure_resident_fp4_rows) and output tile width of a dense projection.
+extern "C" int configure_dense_rows(void* handle, int rows) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || op->operands == GEMM_NVFP4 || rows < 1 || rows > op->m) return cudaErrorInvalidValue;
+    op->desc.p.gemm.rows = rows;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+extern "C" int configure_dense_tile(void* handle, int block_n) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || op->operands == GEMM_NVFP4 || (block_n != 128 && block_n != 64)) return cudaErrorInvalidValue;
+    op->desc.p.gemm.block_n = block_n;
+    return gemm_refresh(op);
+}
 
 // =====================================================================================================
 extern "C" int create_norm(void** handle, const void* input, const void* residual, const float* gamma, const float* beta,

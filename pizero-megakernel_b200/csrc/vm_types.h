@@ -17,7 +17,7 @@ constexpr int kBandRows = 128;
 
 enum OpKind : int {
     OP_NONE = 0,
-    OP_GEMM = 1,        // NVFP4 block-scaled GEMM on tcgen05, fused epilogue
+    OP_GEMM = 1,        // tcgen05 GEMM (NVFP4 block-scaled, BF16 or FP8 operands), fused epilogue
     OP_NORM = 2,        // LayerNorm / RMSNorm (or plain copy) -> NVFP4 / BF16
     OP_ATTN = 3,        // softmax(QK^T)V on tensor cores, optional split-KV partials
     OP_MERGE = 4,       // split-KV merge (+ NVFP4 quantize)
@@ -35,16 +35,24 @@ enum GemmEpilogue : int {
     EPI_BF16 = 1,       // alpha*acc + bias + residual -> BF16 (one rounding)
     EPI_FP4 = 2,        // alpha*acc + bias (+residual) [GELU|ReLU^2] -> NVFP4 + swizzled scales
     EPI_GEGLU_FP4 = 3,  // gelu_tanh(gate)*up on interleaved columns -> NVFP4, width N/2
-    EPI_QKV_ROPE = 4    // BF16, RoPE on Q/K heads, K/V rows appended to the KV cache
+    EPI_QKV_ROPE = 4,   // BF16, RoPE on Q/K heads, K/V rows appended to the KV cache
+    EPI_GEGLU_BF16 = 5  // bf16(gelu_tanh(bf16 gate)) * bf16(up) on interleaved columns -> BF16, width N/2
+};
+
+enum GemmOperands : int {
+    GEMM_NVFP4 = 0,     // packed E2M1 + E4M3 block scales, kind::mxf4nvf4, 64 K-elements per MMA
+    GEMM_BF16 = 1,      // BF16 rows, kind::f16, 16 K-elements per MMA
+    GEMM_FP8 = 2        // E4M3 rows, kind::f8f6f4, 32 K-elements per MMA
 };
 
 struct GemmParams {
-    const void* tmap_a;          // CUtensorMap in global memory: packed A [M_pad, K/2] bytes
-    const void* tmap_b;          // CUtensorMap: packed B [N_pad, K/2] bytes
-    const uint8_t* sfa;          // swizzled E4M3 block scales of A
+    const void* tmap_a;          // CUtensorMap in global memory: A rows as bytes [M_pad, row_bytes] (NVFP4: K/2, BF16: 2K, FP8: K)
+    const void* tmap_b;          // CUtensorMap: B rows [N_pad, row_bytes]
+    const uint8_t* sfa;          // swizzled E4M3 block scales of A (NVFP4 only)
     const uint8_t* sfb;
+    int operands;                // GemmOperands
     int m_tiles, n_tiles;        // 128-row x block_n-column output tiles
-    int k_groups;                // K / 64
+    int k_groups;                // row_bytes / 32: one MMA each (64 FP4, 16 BF16 or 32 FP8 elements of K)
     int block_n;                 // 128 (default), 64 or 32
     int b_tiled;                 // B stored tile-major: block (n_tile, k_stage) is block_n contiguous 128-byte rows
     int a_box_rows;              // rows of A copied per tile: 128, or 64 when the logical row count is <= 64
@@ -54,6 +62,9 @@ struct GemmParams {
     float alpha;                 // global_scale(A) * global_scale(B)
     int epilogue;
     int act;                     // EPI_FP4: 0 none, 1 GELU(tanh), 3 ReLU^2
+    const float* row_factor;     // FP32 [M] multiplied into every accumulator row (1/rms of the input row) or null
+    int round_before_residual;   // EPI_BF16: (+bias) round to BF16, then add the residual and round again
+    int gelu_cols;               // EPI_BF16: > 0 applies GELU(tanh) to bf16(value) in columns < gelu_cols and stores 0 beyond
     int rows;                    // logical rows (rows >= this are written as zero codes / skipped)
     void* out;                   // FP32 / BF16 / packed FP4
     int ldo;                     // elements (FP32/BF16) or bytes (FP4) per output row

@@ -55,6 +55,17 @@ _SIGNATURES = {
     "configure_resident_fp4_weight_layout": [_P, _I],
     "resident_fp4_resources": [_P, C.POINTER(_I), _I],
     "destroy_resident_fp4": [_P],
+    "create_dense": [C.POINTER(_P)] + [_P] * 5 + [_I] * 6 + [_F],
+    "launch_dense": [_P, _P],
+    "destroy_dense": [_P],
+    "configure_dense_round_before_residual": [_P],
+    "configure_dense_geglu": [_P, _P],
+    "configure_dense_gelu": [_P, _I],
+    "configure_dense_rms_factor": [_P, _P],
+    "configure_dense_skinny": [_P],
+    "configure_dense_qkv_rope": [_P] * 5 + [_I] * 3,
+    "configure_dense_rows": [_P, _I],
+    "configure_dense_tile": [_P, _I],
     "create_norm": [C.POINTER(_P)] + [_P] * 8 + [_I] * 9 + [_F] * 2,
     "launch_norm": [_P, _P],
     "destroy_norm": [_P],

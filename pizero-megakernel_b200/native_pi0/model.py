@@ -45,6 +45,17 @@ class Fp4Matrix:
         self.global_scale = float(np.float32(global_scale))
 
 
+class StageOutput:
+    """What one stage writes, for validators that compare or replace a stage's result: ``name`` is the stage name
+    (suffixed ``.q`` / ``.k`` / ``.v`` for the three parts of a fused QKV projection), ``kind`` one of ``bf16``,
+    ``f32``, ``fp4`` (an ``Fp4Matrix``), ``q_rope`` (BF16 query heads, rotation partners adjacent), ``k_cache`` (the
+    same layout, rows ``base..base+rows`` of the layer's key cache) and ``v_cache``; ``rows`` x ``cols`` is the
+    logical extent inside the padded buffer."""
+
+    def __init__(self, name, kind, buffer, rows, cols, base=0):
+        self.name, self.kind, self.buffer, self.rows, self.cols, self.base = name, kind, buffer, rows, cols, base
+
+
 class NativePi0:
     @classmethod
     def from_openpi(cls, checkpoint_path, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10,
@@ -99,7 +110,7 @@ class NativePi0:
         self.workers = min(sms, 148) if workers is None else workers
         self.sd = sd
         self.buffers, self.handles, self._cache = [], [], {}
-        self.stages, self.stage_tiles, self.stage_cost, self.stage_names = [], [], [], []
+        self.stages, self.stage_tiles, self.stage_cost, self.stage_names, self.stage_outputs = [], [], [], [], []
         self.landmarks, self.landmark_stage = {}, {}
         self.handle = C.c_void_p()
         self.epoch = 0
@@ -139,6 +150,7 @@ class NativePi0:
         src[:n, :k] = w.to(torch.bfloat16)
         gs = max(float(src.float().abs().max()) / (6.0 * 448.0), 1e-30)
         m = Fp4Matrix(np_, kp, self.device, gs)
+        m.logical_rows = n
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _native.check(self.lib.quantize_nvfp4(src.data_ptr(), m.data.data_ptr(), m.scales.data_ptr(), np_, kp, kp, kp // 16,
                                               m.global_scale, 1, stream), "weight quantisation")
@@ -152,7 +164,7 @@ class NativePi0:
         return m
 
     # ------------------------------------------------------------------------------------------ stages
-    def add(self, kind, handle, name, sources=()):
+    def add(self, kind, handle, name, sources=(), outputs=()):
         tiles, bands, cost = C.c_int(), C.c_int(), C.c_int()
         _native.check(self.lib.op_geometry(handle, C.byref(tiles), C.byref(bands), C.byref(cost)), "operator geometry")
         spec = NativeSpec()
@@ -166,6 +178,7 @@ class NativePi0:
         self.stage_tiles.append(tiles.value)
         self.stage_cost.append(padded(max(cost.value, 64), 64))
         self.stage_names.append(name)
+        self.stage_outputs.append(list(outputs))
         return len(self.stages) - 1
 
     def mark(self, name, tensor):
@@ -204,7 +217,18 @@ class NativePi0:
             if w.tiled != block_n:
                 raise ValueError(f"{name}: weight tiled for {w.tiled}-wide tiles, used with {block_n}")
             _native.check(self.lib.configure_resident_fp4_weight_layout(h, 1), name)
-        return self.add(0, h, name, sources)
+        cols = getattr(w, "logical_rows", n)
+        if rope is not None:
+            hd = self.config.head_dim
+            outs = [StageOutput(name + ".k", "k_cache", rope["cache_k"], rows, hd, rope["cache_base"]),
+                    StageOutput(name + ".v", "v_cache", rope["cache_v"], rows, hd, rope["cache_base"])]
+            if rope.get("q") is not None:
+                outs.append(StageOutput(name + ".q", "q_rope", rope["q"], rows, rope["q_cols"]))
+        elif fp4_out is not None:
+            outs = [StageOutput(name, "fp4", fp4_out, rows, cols // 2 if activation == 2 else cols)]
+        else:
+            outs = [StageOutput(name, "bf16", out, rows, cols)]
+        return self.add(0, h, name, sources, outs)
 
     def norm(self, name, x, out: Fp4Matrix, *, rows, sources, kind, gamma=None, beta=None, eps=1e-6, bf16_copy=None):
         h = C.c_void_p()
@@ -217,7 +241,7 @@ class NativePi0:
             _native.check(self.lib.configure_norm_quantize_only(h, 0), name)
         if bf16_copy is not None:
             _native.check(self.lib.configure_norm_bf16_copy(h, bf16_copy.data_ptr()), name)
-        return self.add(2, h, name, sources)
+        return self.add(2, h, name, sources, [StageOutput(name, "fp4", out, rows, width)])
 
     def linear32(self, name, x, w, bias, out, *, rows, sources, ldx=None, x_bf16=False, out_bf16=False, silu=False,
                  rms=False, euler=False, prev=None, slot=0, prev_slot=0, x_row_offset=0, dt=0.0, eps=1e-6):
@@ -228,7 +252,7 @@ class NativePi0:
                                                out.data_ptr(), rows, n, k, ldx if ldx is not None else k, out.stride(0), flags,
                                                slot, prev_slot, x_row_offset, float(dt), float(eps), self.workers), name)
         self._own(h)
-        return self.add(3, h, name, sources)
+        return self.add(3, h, name, sources, [StageOutput(name, "bf16" if out_bf16 else "f32", out, rows, n)])
 
     # ------------------------------------------------------------------------------------------ tables
     def rope(self, rows, offset):
@@ -268,7 +292,7 @@ class NativePi0:
         _native.check(lib.create_patch_embed(C.byref(h), None, patch_w.data_ptr(), patch_b.data_ptr(), pos.data_ptr(), xa.data_ptr(),
                                              V, W, self.workers), "patch embedding")
         self._own(h)
-        s_x = self.add(3, h, "vision.patch")
+        s_x = self.add(3, h, "vision.patch", (), [StageOutput("vision.patch", "bf16", xa, M, W)])
         self.mark("patch", xa)
         a_ln, a_att, a_ln2 = self.fp4(M, W), self.fp4(M, W), self.fp4(M, W)
         mlp_pad = padded(c.vision_mlp, 128)
@@ -298,7 +322,7 @@ class NativePi0:
                                                None, None, att.data_ptr(), None, V, 256, 256, c.vision_heads, c.vision_heads, hd,
                                                3 * W, 3 * W, W, 0, self.workers, -1, float(hd ** -0.5)), "vision attention")
             self._own(h)
-            s_att = self.add(1, h, f"vision.{i}.attention", [(s_qkv, ALL)])
+            s_att = self.add(1, h, f"vision.{i}.attention", [(s_qkv, ALL)], [StageOutput(f"vision.{i}.attention", "bf16", att, M, W)])
             s_aq = self.norm(f"vision.{i}.attention_quant", att, a_att, rows=M, sources=[(s_att, SAME)], kind="none")
             s_o = self.gemm(f"vision.{i}.out", a_att, wo, rows=M, sources=[(s_aq, SAME)], out=xb, bias=bo, residual=xa)
             s_ln2 = self.norm(f"vision.{i}.ln2", xb, a_ln2, rows=M, sources=[(s_o, SAME)], kind="layer", gamma=g2, beta=b2, eps=c.ln_eps)
@@ -366,7 +390,8 @@ class NativePi0:
             # split-KV with the merge inside the attention stage: the tiles of a head meet on a ticket and each merges its share of rows
             _native.check(lib.configure_attention_splits(h, splits), f"{name}.attention")
             _native.check(lib.configure_attention_fused_merge(h, 1), f"{name}.attention")
-        s_att = self.add(1, h, f"{name}.attention", att_sources)
+        s_att = self.add(1, h, f"{name}.attention", att_sources, [StageOutput(f"{name}.attention", "bf16", attn_out, rows, H * hd),
+                                                                  StageOutput(f"{name}.attention", "fp4", a2, rows, H * hd)])
         wo = self.cached(p + "o", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=block_n))
         s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=block_n)
         g2 = self.cached(p + "g2", lambda: (1.0 + sd[p + "post_attention_layernorm.weight"].float()).contiguous())

@@ -1,8 +1,20 @@
 """The benchmarked model - 27 SigLIP / 18 Gemma-2B / 18 expert layers at full widths - against the NVFP4 oracle,
-landmark by landmark, for the two benchmark shapes (3 views, prompt 0, chunk 50) and (3 views, prompt 16, chunk 63).
+landmark by landmark and operator by operator, for the two benchmark shapes (3 views, prompt 0, chunk 50) and
+(3 views, prompt 16, chunk 63).
 
-Two passes over one forward, both cut into one launch per landmark interval (``launch_range``; the intervals of a pass
-share one epoch, so every stage runs exactly once, as in a single launch):
+Three passes over one forward, each cut into several launches (``launch_range``; the launches of a pass share one
+epoch, so every stage runs exactly once, as in a single launch):
+
+* operator by operator - one launch per stage (about 1 800).  After each stage its output is compared with the
+  oracle's value of the same operator and then REPLACED by the oracle's (NVFP4 outputs by the oracle's exact codes and
+  block scales), so every operator of the full model is checked in isolation on the oracle's own input.  Gates
+  (measured worst case over all stages of both shapes in brackets): GEMM outputs in BF16 / FP32, rotated Q and the
+  KV-cache rows <= 1e-3 relative RMS [1.4e-4]; NVFP4 outputs of norms and GEMM epilogues <= 0.1 % of the E2M1 codes
+  [0.002 %] and of the block scales [0.02 %] different, <= 1e-2 relative RMS after dequantisation [5.5e-3];
+  attention in BF16 <= 1e-2 [2.4e-3: the kernel rounds the probabilities to BF16 for the PV product, the oracle
+  keeps FP32]; the NVFP4 copy of the attention rows - the same rows, whose 2e-3 differences move values across
+  quantiser boundaries - <= 1 % of the codes [0.5 %], <= 2.5 % of the scales [1.5 %], <= 4e-2 after dequantisation
+  [2.4e-2].  A mis-indexed head, a wrong mask column, a bad scale or a wrong weight in any single stage fails here.
 
 * free running  - the engine consumes its own activations; every landmark both sides record (``patch``,
   ``vision.i``, ``image_tokens``, ``prefix.i``, the prefix KV caches, ``expert.s.i``, ``actions.s``) is compared with
@@ -10,18 +22,21 @@ share one epoch, so every stage runs exactly once, as in a single launch):
   gated loosely.
 * teacher forced - before an interval runs, the engine's buffer is overwritten with the ORACLE's value of that
   landmark (the layer's input), so the interval's output differs from the oracle's only by what one layer adds:
-  FP32 summation order, BF16 rounding of attention probabilities and the few E2M1 codes those flip.  This is the
-  reference's layer-landmark comparison (``scripts/validate_native_pi0.py:46-68,135-144``) made independent of
-  depth, and it is the tight gate: a mis-indexed head, a wrong mask column or a bad scale in any one of the 63
-  layers (or 180 expert layer evaluations) shows up as an outlier here.
+  FP32 summation order, BF16 rounding of attention probabilities and the E2M1 codes those flip in the three to four
+  quantisers of a layer.  This is the reference's layer-landmark comparison
+  (``scripts/validate_native_pi0.py:46-68,135-144``) made independent of depth.  The flipped codes are a roughly
+  constant absolute error per layer, so relative to the residual stream it is largest where that is still small:
+  measured 0.08-0.11 after the first layer of a tower and 0.01-0.02 from the tenth on.
 
-Tolerances (relative RMS of the difference over the oracle's RMS, whole landmark tensor): teacher forced
-<= 2e-2 per transformer layer (three to four NVFP4 quantisers in a row; a single operator is held to 1e-2 in
-test_gpu_ops.py), <= 1e-2 for the patch embedding and the FP32 action head; free running <= 0.35 anywhere and
-<= 0.15 on the action chunk; the engine may be at most 1.3 x as far from BF16 eager as the oracle itself is.
+Tolerances of the layer passes (relative RMS of the difference over the oracle's RMS, whole landmark tensor):
+teacher forced <= 0.15 per transformer layer with a median <= 0.03, <= 1e-2 for the patch embedding, the projector
+and the FP32 action head; free running <= 0.9 anywhere (the prefix reaches 0.74 after 17 layers of random-init
+weights) and <= 0.15 on the action chunk; the engine may be at most 1.3 x as far from BF16 eager as the oracle
+itself is.
 """
 import json
 import os
+from collections import defaultdict
 
 import pytest
 import torch
@@ -30,10 +45,10 @@ pytestmark = pytest.mark.gpu
 
 from native_pi0.model import NativePi0
 from native_pi0.weights import Pi0Config, StateDictModel
-from oracle.pi0_torch import Pi0Dims, Pi0Torch, init_state_dict
+from oracle.pi0_torch import Pi0Dims, Pi0Torch, fake_quant, init_state_dict, quantize_codes
 
 FULL = dict(vocab=1024)                       # every other dimension is the model's own (27/18/18 layers, 16384 / 4096 MLPs)
-LAYER_TOL, HEAD_TOL, FREE_TOL, ACTION_TOL = 2e-2, 1e-2, 0.35, 0.15
+LAYER_TOL, LAYER_MEDIAN_TOL, HEAD_TOL, FREE_TOL, ACTION_TOL = 0.15, 0.03, 1e-2, 0.9, 0.15
 
 
 def nrmse(a, b):
@@ -46,6 +61,114 @@ def engine_k_layout(k):
     hd = k.shape[-1]
     idx = torch.stack((torch.arange(hd // 2), torch.arange(hd // 2) + hd // 2), dim=1).reshape(-1).to(k.device)
     return k[..., idx]
+
+
+def scale_positions(rows, blocks_used, blocks_total, device):
+    """Byte offsets of the block scales (row r, block b) in the 128 x 4 atom layout (``quantization.py:104-115``)."""
+    r = torch.arange(rows, device=device)[:, None]
+    b = torch.arange(blocks_used, device=device)[None, :]
+    return ((r // 128) * ((blocks_total + 3) // 4) + b // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4
+
+
+def read_fp4(matrix, rows, cols):
+    """E2M1 codes uint8 [rows, cols] (sign in bit 3) and scale codes uint8 [rows, cols/16] of an engine NVFP4 buffer."""
+    data = matrix.data[:rows, :cols // 2]
+    codes = torch.stack((data & 15, data >> 4), dim=-1).reshape(rows, cols)
+    scales = matrix.scales[scale_positions(rows, cols // 16, matrix.k // 16, data.device)]
+    return codes, scales
+
+
+def write_fp4(matrix, rows, cols, codes, scales):
+    pairs = codes.reshape(rows, cols // 2, 2)
+    matrix.data[:rows, :cols // 2] = pairs[..., 0] | (pairs[..., 1] << 4)
+    matrix.scales[scale_positions(rows, cols // 16, matrix.k // 16, codes.device)] = scales
+
+
+_E2M1 = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+
+
+def decode(codes, scales):
+    table = torch.arange(127, device=codes.device)
+    mant, expo = (table & 7).double(), (table >> 3).double()
+    ue4m3 = torch.where(expo == 0, mant * 2.0 ** -9, (1 + mant / 8) * 2.0 ** (expo - 7)).float()
+    mag = _E2M1.to(codes.device)[(codes & 7).long()]
+    val = torch.where((codes & 8) != 0, -mag, mag)
+    return (val.reshape(*scales.shape, 16) * ue4m3[scales.long()].unsqueeze(-1)).reshape(codes.shape)
+
+
+class OperatorWalker:
+    """One launch per stage; every stage output the oracle also has is compared and then replaced by the oracle's."""
+
+    def __init__(self, engine, oracle, inputs):
+        self.engine, self.oracle, self.inputs = engine, oracle, inputs
+        self.at_stage = defaultdict(list)                   # landmarks valid once stages [0, s) have run
+        for name, stage in engine.landmark_stage.items():
+            if name in oracle.landmarks:
+                self.at_stage[stage].append(name)
+
+    def reference(self, out):
+        name = out.name.replace(".attention_quant", ".attention")
+        return self.oracle.ops.get(name)
+
+    def check(self, out, want, stats):
+        rows, cols = out.rows, out.cols
+        if out.kind in ("bf16", "f32"):
+            got = out.buffer[:rows, :cols]
+            want = want.reshape(rows, cols)
+            stats[(out.kind, out.name.rsplit(".", 1)[-1])].append((nrmse(got, want), out.name))
+            got.copy_(want.to(got.dtype))
+        elif out.kind == "fp4":
+            want = want.reshape(rows, cols).float()
+            codes, scales = read_fp4(out.buffer, rows, cols)
+            ref_codes, ref_scales = quantize_codes(want, "nearest", out.buffer.global_scale)
+            key = out.name.rsplit(".", 1)[-1]
+            stats[("fp4_deq", key)].append((nrmse(decode(codes, scales), decode(ref_codes, ref_scales)), out.name))
+            stats[("fp4_codes", key)].append((float((codes != ref_codes).float().mean()), out.name))
+            stats[("fp4_scales", key)].append((float((scales != ref_scales).float().mean()), out.name))
+            write_fp4(out.buffer, rows, cols, ref_codes, ref_scales)
+        else:
+            hd = self.engine.config.head_dim
+            if out.kind == "q_rope":
+                got = out.buffer[:rows, :cols]
+                want = engine_k_layout(want.reshape(rows, cols // hd, hd)).reshape(rows, cols)
+            else:
+                got = out.buffer[out.base:out.base + rows]
+                want = want.reshape(rows, hd)
+                if out.kind == "k_cache":
+                    want = engine_k_layout(want)
+            stats[(out.kind, "qkv")].append((nrmse(got, want), out.name))
+            got.copy_(want.to(got.dtype))
+
+    def run(self):
+        engine, oracle = self.engine, self.oracle
+        stats = defaultdict(list)
+        for s in range(len(engine.stages)):
+            for name in self.at_stage.get(s, ()):
+                want = oracle.landmarks[name]
+                got = engine.landmarks[name]
+                got = got if name.startswith("actions.") else got[:want.shape[0]]
+                stats[("landmark", name.split(".")[0])].append((nrmse(got, want.reshape(got.shape)), name))
+                got.copy_(want.reshape(got.shape).to(got.dtype))
+            engine.launch_range(s, s + 1, *self.inputs, new_epoch=(s == 0))
+            for out in engine.stage_outputs[s]:
+                want = self.reference(out)
+                if want is not None:
+                    self.check(out, want, stats)
+        status = engine.status()
+        assert status["code"] == 0, status
+        final = nrmse(engine.output, oracle.landmarks[f"actions.{engine.flow_steps - 1}"].reshape(engine.output.shape))
+        return stats, final
+
+
+# per-operator gates: (kind, operator) -> largest allowed value over all stages of that operator
+def operator_gate(kind, op):
+    if op == "attention":                                   # BF16 probabilities in the PV product; see the module docstring
+        return {"fp4_codes": 1e-2, "fp4_scales": 2.5e-2, "fp4_deq": 4e-2}.get(kind, 1e-2)
+    if kind in ("fp4_codes", "fp4_scales"):
+        return 1e-3
+    if kind in ("fp4_deq", "landmark"):
+        return 1e-2
+    return 1e-3                                             # GEMM epilogues in BF16 / FP32, RoPE, KV-cache rows
 
 
 @pytest.fixture(scope="module")
@@ -126,6 +249,7 @@ def test_full_depth_model_layer_by_layer(full_model, views, chunk, prompt):
     dims, cfg, sd = full_model
     x = make_inputs(views, chunk, prompt, dims.vocab)
     oracle = Pi0Torch(dims, sd, mode="nvfp4")
+    oracle.record_ops = True
     emulation = oracle.sample_actions(*x)
     eager = Pi0Torch(dims, sd, mode="bf16").sample_actions(*x)
     with NativePi0.from_model(StateDictModel(cfg, sd), num_views=views, prompt_len=prompt, chunk_size=chunk) as engine:
@@ -138,23 +262,37 @@ def test_full_depth_model_layer_by_layer(full_model, views, chunk, prompt):
         free, cut = walker.run(teacher_forced=False)
         assert torch.equal(single, cut)
         forced, _ = walker.run(teacher_forced=True)
+        op_stats, op_final = OperatorWalker(engine, oracle, x).run()
         again = engine.forward(*x).clone()              # the handle is back to free running: same bits as before
         assert torch.equal(single, again)
+    compared = sum(len(v) for v in op_stats.values())
+    assert compared > 2 * len(engine.stages), compared      # (NVFP4 outputs count three times: values, codes, scales)
+    op_table = {f"{kind}:{op}": {"worst": max(v)[0], "at": max(v)[1], "median": sorted(v)[len(v) // 2][0], "count": len(v)}
+                for (kind, op), v in sorted(op_stats.items())}
+    layers = sorted(v for k, v in forced.items() if k.startswith(("vision.", "prefix.", "expert.")) and not k.endswith("input"))
+    layer_median = layers[len(layers) // 2]
     report = {"config": [views, chunk, prompt],
               "action_nrmse_vs_emulation": nrmse(single, emulation), "action_nrmse_vs_bf16_eager": nrmse(single, eager),
               "emulation_nrmse_vs_bf16_eager": nrmse(emulation, eager),
               "teacher_forced_worst": {p: worst(forced, p) for p in ("patch", "vision.", "image_tokens", "prefix.", "cache.", "expert.", "actions.")},
               "free_running_worst": {p: worst(free, p) for p in ("vision.", "prefix.", "cache.", "expert.", "actions.")},
-              "teacher_forced_median_layer": sorted(v for k, v in forced.items() if k.startswith(("vision.", "prefix.", "expert.")) and not k.endswith("input"))[len(forced) // 3]}
+              "teacher_forced_median_layer": layer_median}
+    report["operator_pass_final_action_nrmse"] = op_final
     print("\nFULL-MODEL-PARITY " + json.dumps(report))
+    print("FULL-MODEL-OPERATORS " + json.dumps(op_table))
     out_dir = os.environ.get("PI0_PARITY_REPORT_DIR")
     if out_dir:
         with open(os.path.join(out_dir, f"full_model_parity_{views}_{chunk}_{prompt}.json"), "w") as f:
-            json.dump({"report": report, "teacher_forced": forced, "free_running": free}, f, indent=1)
+            json.dump({"report": report, "operators": op_table, "teacher_forced": forced, "free_running": free}, f, indent=1)
+    # ---- operator by operator: every stage on the oracle's own input
+    for (kind, op), values in op_stats.items():
+        value, where = max(values)
+        assert value <= operator_gate(kind, op), (kind, op, where, value)
+    assert op_final <= 1e-2
     # ---- teacher forced: every layer on its own
-    assert forced["patch"] <= HEAD_TOL
+    assert forced["patch"] <= HEAD_TOL and layer_median <= LAYER_MEDIAN_TOL
     for name, err in forced.items():
-        if name.startswith("actions."):
+        if name.startswith(("actions.", "image_tokens", "cache.")) or name.endswith(".input"):
             assert err <= HEAD_TOL, (name, err)
         else:
             assert err <= LAYER_TOL, (name, err)
