@@ -69,7 +69,8 @@ int create_dense(void** handle, const void* a, const void* b, void* out, const v
                  int m, int n, int k, int workers, int fp8, int bf16, float alpha);
 int launch_dense(void* handle, void* stream);
 int destroy_dense(void* handle);
-/* The configure calls below need BF16 operands and BF16 output, as in the reference. */
+/* The configure calls below need a BF16 output.  (The reference also demands BF16 operands; these epilogues do not
+ * depend on the operand format, so they accept FP8 and NVFP4 projection handles as well.) */
 /* (+bias) is rounded to BF16 first, then the residual is added and the sum rounded again (needs a residual). */
 int configure_dense_round_before_residual(void* handle);
 /* Interleaved (gate, up) column pairs -> compact BF16 [M, N/2] = bf16(bf16(gelu_tanh(bf16 gate)) * bf16 up); no bias,

@@ -209,10 +209,34 @@ def time_embedding(t, width, device):
     return torch.cat((angle.sin(), angle.cos())).float()
 
 
+_SITE_OF_LEAF = {"q_proj": "qkv", "k_proj": "qkv", "v_proj": "qkv", "out_proj": "out", "o_proj": "o_proj", "fc1": "fc1", "fc2": "fc2",
+                 "gate_proj": "gate_up", "up_proj": "gate_up", "down_proj": "down"}
+
+
+def site_of(parameter):
+    """Engine site name of a linear's parameter prefix: ``vision.<i>.{qkv,out,fc1,fc2}``, ``vision.projector``,
+    ``prefix.<i>.{qkv,o_proj,gate_up,down}``, ``expert.<i>.{...}``."""
+    if parameter.startswith(PJ[:-1]):
+        return "vision.projector"
+    tower = "vision" if parameter.startswith(VP) else "prefix" if parameter.startswith(LM) else "expert"
+    layer = parameter.split("layers.")[1].split(".")[0]
+    return f"{tower}.{layer}.{_SITE_OF_LEAF[parameter.rsplit('.', 1)[1]]}"
+
+
 class Pi0Torch:
-    def __init__(self, dims: Pi0Dims, state_dict, mode="bf16", compute_dtype=torch.bfloat16, rope_inv_freq_dtype=torch.float32):
+    def __init__(self, dims: Pi0Dims, state_dict, mode="bf16", compute_dtype=torch.bfloat16, rope_inv_freq_dtype=torch.float32,
+                 precision=None):
+        """``precision`` (mode "nvfp4" only): dict of fnmatch patterns over site names -> "nvfp4" | "bf16" with an optional
+        "default", as the engine takes it; BF16 sites multiply BF16 operands with FP32 accumulation and round the way the
+        engine's BF16 epilogues do."""
         assert mode in ("bf16", "nvfp4")
         self.d, self.sd, self.mode = dims, state_dict, mode
+        precision = precision or {}
+        if isinstance(precision, str):
+            precision = {"default": precision}
+        self._precision_map = [(k, v) for k, v in precision.items() if k != "default"]
+        self._precision_default = precision.get("default", "nvfp4")
+        self._site_cache = {}
         self.dt = compute_dtype                 # activation dtype of the bf16 mode (float32 for a fast CPU baseline)
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self._wq = {}
@@ -226,6 +250,26 @@ class Pi0Torch:
             self.ops[name] = tensor
 
     # ----- linear layers ---------------------------------------------------------------------------
+    def bf16_site(self, parameter):
+        """True when the linear at ``parameter`` runs on BF16 operands in the engine configuration being emulated."""
+        if self.mode != "nvfp4":
+            return False
+        if parameter not in self._site_cache:
+            import fnmatch
+            site = site_of(parameter)
+            chosen = next((v for k, v in self._precision_map if fnmatch.fnmatchcase(site, k)), self._precision_default)
+            self._site_cache[parameter] = chosen == "bf16"
+        return self._site_cache[parameter]
+
+    def add_residual(self, o, x, parameter):
+        """Residual add of a projection ``o`` (FP32 accumulator incl. bias).  NVFP4 sites round once after the sum; BF16
+        sites round the projection first (OpenPI's eager ``x + o`` on BF16 tensors), then the sum."""
+        if self.mode != "nvfp4":
+            return x + o
+        if self.bf16_site(parameter):
+            return (o.to(torch.bfloat16).float() + x.float()).to(torch.bfloat16)
+        return (o + x.float()).to(torch.bfloat16)
+
     def _fused_scale(self, name, w):
         """The engine packs q|k|v (k|v for the last prefix layer) and gate|up as ONE NVFP4 tensor, so the members of
         a fused projection share one tensor scale: amax over the fused matrix / (6*448)."""
@@ -251,6 +295,9 @@ class Pi0Torch:
         b = self.sd.get(name + ".bias") if bias else None
         if self.mode == "bf16":
             return F.linear(x.to(self.dt), w.to(self.dt), None if b is None else b.to(self.dt))
+        if self.bf16_site(name):
+            y = x.to(torch.bfloat16).float() @ w.to(torch.bfloat16).float().T
+            return y if b is None else y + b.to(torch.bfloat16).float()
         wq = self._qweight(name, w)
         xq = fake_quant(pad_cols(x.float(), 64), "nearest", 1.0)
         y = xq @ wq.T
@@ -305,15 +352,20 @@ class Pi0Torch:
             a = torch.cat(outs).reshape(-1, d.vision_width)
             self.rec(f"vision.{i}.attention", a)
             o = self.linear(a, p + "self_attn.out_proj")
-            x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+            x = self.add_residual(o, x, p + "self_attn.out_proj")
             self.rec(f"vision.{i}.out", x)
             y = F.layer_norm(x.float(), (d.vision_width,), sd[p + "layer_norm2.weight"].float(), sd[p + "layer_norm2.bias"].float(), d.ln_eps).to(x.dtype)
             self.rec(f"vision.{i}.ln2", y)
             h = self.linear(y, p + "mlp.fc1")
-            h = F.gelu(h.float(), approximate="tanh") if self.mode == "nvfp4" else F.gelu(h, approximate="tanh")
+            if self.mode != "nvfp4":
+                h = F.gelu(h, approximate="tanh")
+            elif self.bf16_site(p + "mlp.fc2"):
+                h = F.gelu(h.to(torch.bfloat16).float(), approximate="tanh").to(torch.bfloat16)     # BF16 hidden rows for a BF16 consumer
+            else:
+                h = F.gelu(h.float(), approximate="tanh")
             self.rec(f"vision.{i}.fc1", h)
             o = self.linear(h, p + "mlp.fc2")
-            x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+            x = self.add_residual(o, x, p + "mlp.fc2")
             self.rec(f"vision.{i}.fc2", x)
             self.landmarks[f"vision.{i}"] = x
         y = F.layer_norm(x.float(), (d.vision_width,), sd[VP + "post_layernorm.weight"].float(), sd[VP + "post_layernorm.bias"].float(), d.ln_eps).to(x.dtype)
@@ -352,16 +404,22 @@ class Pi0Torch:
         a = self.attention(q, k_all, v_all, d.head_dim ** -0.5, mask).reshape(x.shape[0], -1)
         self.rec(f"{name}.attention", a)
         o = self.linear(a, p + "self_attn.o_proj", bias=False)
-        x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+        x = self.add_residual(o, x, p + "self_attn.o_proj")
         self.rec(f"{name}.o_proj", x)
         y = self.rms(x, sd[p + "post_attention_layernorm.weight"])
         self.rec(f"{name}.norm2", y)
         gate = self.linear(y, p + "mlp.gate_proj", bias=False)
         up = self.linear(y, p + "mlp.up_proj", bias=False)
-        h = F.gelu(gate.float(), approximate="tanh") * up.float() if self.mode == "nvfp4" else F.gelu(gate, approximate="tanh") * up
+        if self.mode != "nvfp4":
+            h = F.gelu(gate, approximate="tanh") * up
+        elif self.bf16_site(p + "mlp.down_proj"):
+            bf = torch.bfloat16
+            h = (F.gelu(gate.to(bf).float(), approximate="tanh").to(bf).float() * up.to(bf).float()).to(bf)
+        else:
+            h = F.gelu(gate.float(), approximate="tanh") * up.float()
         self.rec(f"{name}.gate_up", h)
         o = self.linear(h, p + "mlp.down_proj", bias=False)
-        x = self.act(o + x.float()) if self.mode == "nvfp4" else x + o
+        x = self.add_residual(o, x, p + "mlp.down_proj")
         self.rec(f"{name}.down", x)
         return x, (k, v)
 

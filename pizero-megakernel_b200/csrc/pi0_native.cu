@@ -596,10 +596,11 @@ extern "C" int create_dense(void** handle, const void* a, const void* b, void* o
     return cudaSuccess;
 }
 namespace {
-// A dense handle whose operands are BF16 and whose output is BF16: what every configure_dense_* call requires.
+// A GEMM handle whose output is BF16: what every configure_dense_* call requires. (The reference also demands BF16
+// operands; here the epilogues are independent of the operand format, so an NVFP4 or FP8 projection may use them.)
 Op* dense_bf16(void* handle) {
     Op* op = as_op(handle);
-    if (!op || op->desc.kind != OP_GEMM || op->operands != GEMM_BF16) return nullptr;
+    if (!op || op->desc.kind != OP_GEMM) return nullptr;
     const int epilogue = op->desc.p.gemm.epilogue;
     return epilogue == EPI_BF16 || epilogue == EPI_GEGLU_BF16 || epilogue == EPI_QKV_ROPE ? op : nullptr;
 }

@@ -10,11 +10,21 @@ per-tensor scale of amax/(6*448); activations quantised on the fly with the ``ne
 scale 1), RoPE and the KV-cache write live in the QKV epilogue, GeGLU/GELU + requantisation live in the
 MLP epilogues, and the 51-row action expert uses split-KV attention with a merge stage.
 
+``precision`` selects the operand format of the transformer linears site by site: ``"nvfp4"`` (or ``"auto"``) for
+all of them, ``"bf16"`` for all of them (the reference's ``bf16_reference`` policy: BF16 weights and activations on
+``tcgen05.mma kind::f16``, projections rounded to BF16 before the residual add as OpenPI's eager model does), or a
+dict of ``fnmatch`` patterns over site names -> ``"nvfp4" | "bf16"`` with an optional ``"default"``; the first
+matching pattern wins.  Sites are ``vision.<layer>.{qkv,out,fc1,fc2}``, ``vision.projector``,
+``prefix.<layer>.{qkv,o_proj,gate_up,down}`` and ``expert.<layer>.{qkv,o_proj,gate_up,down}`` (an expert site covers
+all Euler steps: they share the weight).  A producer writes its output in the format its consumer reads, so a
+BF16 site costs its own weight traffic and nothing else.
+
 Setup owns all layouts, buffers, weight transforms and the instruction streams; ``forward`` only launches.
 """
 from __future__ import annotations
 
 import ctypes as C
+import fnmatch
 import math
 from pathlib import Path
 
@@ -43,6 +53,37 @@ class Fp4Matrix:
         self.data = packed_tma_buffer((rows_pad, k // 2), device=device)
         self.scales = torch.zeros(swizzled_size(rows_pad, k // 16), dtype=torch.uint8, device=device)
         self.global_scale = float(np.float32(global_scale))
+
+
+class DenseMatrix:
+    """Device-resident BF16 weight [rows_pad, k] (K contiguous, padded to 64) of a BF16 site."""
+
+    def __init__(self, data, logical_rows):
+        self.data, self.rows_pad, self.k, self.logical_rows = data, data.shape[0], data.shape[1], logical_rows
+        self.tiled = 0
+
+
+class Activation:
+    """A GEMM input that one producer stage writes: NVFP4 (codes + block scales) and / or BF16 rows, whichever its
+    consumers read.  The buffers are created on first demand and shared by every layer that uses this slot."""
+
+    def __init__(self, engine, rows_pad, width):
+        self.engine, self.rows_pad, self.width = engine, rows_pad, width
+        self.fp4 = self.bf16 = None
+
+    def require(self, precision):
+        if precision == "nvfp4" and self.fp4 is None:
+            self.fp4 = self.engine.fp4(self.rows_pad, self.width)
+        if precision == "bf16" and self.bf16 is None:
+            self.bf16 = self.engine.tensor((self.rows_pad, self.width))
+        return self
+
+    def only(self, precision):
+        """This slot restricted to one form (what a producer should write for one particular consumer)."""
+        view = Activation(self.engine, self.rows_pad, self.width)
+        self.require(precision)
+        view.fp4, view.bf16 = (self.fp4, None) if precision == "nvfp4" else (None, self.bf16)
+        return view
 
 
 class StageOutput:
@@ -79,15 +120,24 @@ class NativePi0:
                  library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=64,
                  rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="spread"):
         config = getattr(model, "config", None)
-        if config is None or getattr(config, "pi05", False) or precision not in ("auto", "nvfp4"):
-            raise ValueError("This engine runs ordinary pi0 with NVFP4 transformers (precision 'auto' or 'nvfp4')")
+        if config is None or getattr(config, "pi05", False):
+            raise ValueError("This engine runs ordinary pi0 (not pi0.5)")
+        if isinstance(precision, dict):
+            self.precision_map = [(k, v) for k, v in precision.items() if k != "default"]
+            self.default_precision = precision.get("default", "nvfp4")
+        elif precision in ("auto", "nvfp4", "bf16"):
+            self.precision_map, self.default_precision = [], "bf16" if precision == "bf16" else "nvfp4"
+        else:
+            raise ValueError("precision must be 'auto', 'nvfp4', 'bf16' or a dict of site patterns")
+        if any(v not in ("nvfp4", "bf16") for _, v in self.precision_map) or self.default_precision not in ("nvfp4", "bf16"):
+            raise ValueError("site precisions are 'nvfp4' or 'bf16'")
         if num_views not in (1, 2, 3) or prompt_len < 0 or chunk_size < 1 or chunk_size > 127 or flow_steps < 1:
             raise ValueError("Invalid fixed inference dimensions")
         if not isinstance(config, Pi0Config):
             config = Pi0Config(**{k: getattr(config, k) for k in Pi0Config.__dataclass_fields__ if hasattr(config, k)})
         self.config = config
         self.num_views, self.prompt_len, self.chunk_size, self.flow_steps = num_views, prompt_len, chunk_size, flow_steps
-        self.precision_policy = "nvfp4"
+        self.site_precisions = {}
         self.partitioned = partitioned
         self.expert_splits = expert_splits
         self.prefix_splits = prefix_splits
@@ -121,6 +171,15 @@ class NativePi0:
             self.close()
             raise
         self.sd = None
+        used = set(self.site_precisions.values())
+        self.precision_policy = "nvfp4" if used == {"nvfp4"} else "bf16_reference" if used == {"bf16"} else "mixed"
+
+    def site(self, name):
+        """Operand format of the linear at ``name``: first matching pattern of the precision dict, else the default."""
+        if name not in self.site_precisions:
+            chosen = next((v for k, v in self.precision_map if fnmatch.fnmatchcase(name, k)), self.default_precision)
+            self.site_precisions[name] = chosen
+        return self.site_precisions[name]
 
     # ------------------------------------------------------------------------------------------ buffers
     def tensor(self, shape, dtype=torch.bfloat16):
@@ -139,15 +198,20 @@ class NativePi0:
             self._cache[key] = make()
         return self._cache[key]
 
-    def weight(self, w, *, rows_to=128, block_n=128):
-        """BF16/FP32 [N, K] -> NVFP4 on the device (ceil block scales, tensor scale amax/(6*448)).
+    def weight(self, w, *, rows_to=128, block_n=128, precision="nvfp4"):
+        """BF16/FP32 [N, K] -> the site's operand format on the device: NVFP4 (ceil block scales, tensor scale
+        amax/(6*448)) or zero-padded BF16.
 
-        When K is a multiple of 256 the packed codes are re-laid tile-major for ``block_n``-wide output tiles
+        When K is a multiple of 256 the packed NVFP4 codes are re-laid tile-major for ``block_n``-wide output tiles
         (``Fp4Matrix.tiled = block_n``): every TMA box of the weight operand is then one contiguous read."""
         n, k = w.shape
         np_, kp = padded(n, rows_to), padded(k, 64)
         src = torch.zeros((np_, kp), device=self.device, dtype=torch.bfloat16)
         src[:n, :k] = w.to(torch.bfloat16)
+        if precision == "bf16":
+            m = DenseMatrix(src, n)
+            self.buffers.append(m)
+            return m
         gs = max(float(src.float().abs().max()) / (6.0 * 448.0), 1e-30)
         m = Fp4Matrix(np_, kp, self.device, gs)
         m.logical_rows = n
@@ -189,27 +253,61 @@ class NativePi0:
         self.handles.append(handle)
         return handle
 
-    def gemm(self, name, a: Fp4Matrix, w: Fp4Matrix, *, rows, sources, out=None, bias=None, residual=None,
-             fp4_out: Fp4Matrix = None, activation=0, rope=None, block_n=128):
+    def gemm(self, name, a: Activation, w, *, rows, sources, out=None, bias=None, residual=None,
+             out_act: Activation = None, out_precision=None, activation=0, act_cols=None, rope=None, block_n=128):
+        """One projection stage.  ``w`` decides the operand format (``Fp4Matrix``: NVFP4 on ``a.fp4``; ``DenseMatrix``:
+        BF16 on ``a.bf16``).  The result goes to ``out`` (BF16, + bias + residual), to the fused QKV destinations
+        (``rope``), or to ``out_act`` in the format ``out_precision`` of the consuming site with ``activation``
+        0 none / 1 GELU / 2 GeGLU over interleaved gate/up columns (``act_cols``: logical width for the GELU)."""
         h = C.c_void_p()
+        dense = isinstance(w, DenseMatrix)
+        src = a.bf16 if dense else a.fp4
+        if src is None:
+            raise ValueError(f"{name}: the producer of this activation does not write the {'BF16' if dense else 'NVFP4'} form")
         m, n, k = a.rows_pad, w.rows_pad, w.k
-        if a.k != k:
-            raise ValueError(f"{name}: K mismatch {a.k} vs {k}")
-        dummy = out if out is not None else (fp4_out.data if fp4_out is not None else rope["q"] if rope and rope.get("q") is not None else a.data)
-        _native.check(self.lib.create_resident_fp4(C.byref(h), a.data.data_ptr(), w.data.data_ptr(), a.scales.data_ptr(),
-                                                   w.scales.data_ptr(), dummy.data_ptr(), m, n, k, self.workers,
-                                                   float(np.float32(a.global_scale) * np.float32(w.global_scale))), name)
+        if (src.shape[1] if dense else src.k) != k:
+            raise ValueError(f"{name}: K mismatch")
+        target = None if out_act is None else (out_act.bf16 if out_precision == "bf16" else out_act.fp4)
+        placeholder = src if dense else src.data            # every path below binds the real destination
+        if dense:
+            _native.check(self.lib.create_dense(C.byref(h), src.data_ptr(), w.data.data_ptr(), placeholder.data_ptr(), None, None,
+                                                m, n, k, self.workers, 0, 1, 1.0), name)
+        else:
+            _native.check(self.lib.create_resident_fp4(C.byref(h), src.data.data_ptr(), w.data.data_ptr(), src.scales.data_ptr(),
+                                                       w.scales.data_ptr(), placeholder.data_ptr(), m, n, k, self.workers,
+                                                       float(np.float32(src.global_scale) * np.float32(w.global_scale))), name)
         self._own(h)
+        cols = getattr(w, "logical_rows", n)
         if rope is not None:
             q = rope.get("q")
             _native.check(self.lib.configure_resident_fp4_qkv_rope(
                 h, _native.ptr(q), 0 if q is None else q.stride(0), rope["cos"].data_ptr(), rope["sin"].data_ptr(),
                 rope["cache_k"].data_ptr(), rope["cache_v"].data_ptr(), rope["q_cols"], self.config.head_dim, rope["cache_base"]), name)
-        elif fp4_out is not None:
-            _native.check(self.lib.configure_resident_fp4_quantized(h, _native.ptr(bias), _native.ptr(residual), fp4_out.data.data_ptr(),
-                                                                    fp4_out.scales.data_ptr(), fp4_out.global_scale, activation), name)
+            hd = self.config.head_dim
+            outs = [StageOutput(name + ".k", "k_cache", rope["cache_k"], rows, hd, rope["cache_base"]),
+                    StageOutput(name + ".v", "v_cache", rope["cache_v"], rows, hd, rope["cache_base"])]
+            if q is not None:
+                outs.append(StageOutput(name + ".q", "q_rope", q, rows, rope["q_cols"]))
+        elif out_act is not None and out_precision == "nvfp4":
+            _native.check(self.lib.configure_resident_fp4_quantized(h, _native.ptr(bias), _native.ptr(residual), target.data.data_ptr(),
+                                                                    target.scales.data_ptr(), target.global_scale, activation), name)
+            outs = [StageOutput(name, "fp4", target, rows, cols // 2 if activation == 2 else cols)]
+        elif out_act is not None:
+            # BF16 activation for a BF16 consumer: GELU of the BF16-rounded projection, or the compact GeGLU
+            if activation == 2:
+                _native.check(self.lib.configure_resident_fp4_bf16(h, None, None, placeholder.data_ptr()), name)
+                _native.check(self.lib.configure_dense_geglu(h, target.data_ptr()), name)
+            else:
+                _native.check(self.lib.configure_resident_fp4_bf16(h, _native.ptr(bias), _native.ptr(residual), target.data_ptr()), name)
+                if activation == 1:
+                    _native.check(self.lib.configure_dense_gelu(h, act_cols if act_cols is not None else cols), name)
+            outs = [StageOutput(name, "bf16", target, rows, cols // 2 if activation == 2 else cols)]
         else:
             _native.check(self.lib.configure_resident_fp4_bf16(h, _native.ptr(bias), _native.ptr(residual), out.data_ptr()), name)
+            if dense and residual is not None:
+                # the BF16 model rounds the projection before the residual add (OpenPI eager: x + o in BF16)
+                _native.check(self.lib.configure_dense_round_before_residual(h), name)
+            outs = [StageOutput(name, "bf16", out, rows, cols)]
         _native.check(self.lib.configure_resident_fp4_rows(h, rows), name)
         if block_n != 128:
             _native.check(self.lib.configure_resident_fp4_tile(h, block_n), name)
@@ -217,31 +315,29 @@ class NativePi0:
             if w.tiled != block_n:
                 raise ValueError(f"{name}: weight tiled for {w.tiled}-wide tiles, used with {block_n}")
             _native.check(self.lib.configure_resident_fp4_weight_layout(h, 1), name)
-        cols = getattr(w, "logical_rows", n)
-        if rope is not None:
-            hd = self.config.head_dim
-            outs = [StageOutput(name + ".k", "k_cache", rope["cache_k"], rows, hd, rope["cache_base"]),
-                    StageOutput(name + ".v", "v_cache", rope["cache_v"], rows, hd, rope["cache_base"])]
-            if rope.get("q") is not None:
-                outs.append(StageOutput(name + ".q", "q_rope", rope["q"], rows, rope["q_cols"]))
-        elif fp4_out is not None:
-            outs = [StageOutput(name, "fp4", fp4_out, rows, cols // 2 if activation == 2 else cols)]
-        else:
-            outs = [StageOutput(name, "bf16", out, rows, cols)]
         return self.add(0, h, name, sources, outs)
 
-    def norm(self, name, x, out: Fp4Matrix, *, rows, sources, kind, gamma=None, beta=None, eps=1e-6, bf16_copy=None):
+    def norm(self, name, x, out: Activation, *, rows, sources, kind, gamma=None, beta=None, eps=1e-6):
+        """LayerNorm / RMSNorm / plain quantiser stage writing every form of ``out`` that exists (NVFP4 and / or BF16)."""
         h = C.c_void_p()
         width = x.shape[1]
-        _native.check(self.lib.create_norm(C.byref(h), x.data_ptr(), None, _native.ptr(gamma), _native.ptr(beta), None, None,
-                                           out.data.data_ptr(), out.scales.data_ptr(), rows, width, self.workers, 0, 4,
-                                           int(kind == "layer"), 1, 1, 0, float(eps), out.global_scale), name)
+        if out.fp4 is not None:
+            _native.check(self.lib.create_norm(C.byref(h), x.data_ptr(), None, _native.ptr(gamma), _native.ptr(beta), None, None,
+                                               out.fp4.data.data_ptr(), out.fp4.scales.data_ptr(), rows, width, self.workers, 0, 4,
+                                               int(kind == "layer"), 1, 1, 0, float(eps), out.fp4.global_scale), name)
+            outs = [StageOutput(name, "fp4", out.fp4, rows, width)]
+        else:
+            _native.check(self.lib.create_norm(C.byref(h), x.data_ptr(), None, _native.ptr(gamma), _native.ptr(beta), None, None,
+                                               out.bf16.data_ptr(), None, rows, width, self.workers, 0, 16,
+                                               int(kind == "layer"), 1, 1, 0, float(eps), 1.0), name)
+            outs = [StageOutput(name, "bf16", out.bf16, rows, width)]
         self._own(h)
         if kind == "none":
             _native.check(self.lib.configure_norm_quantize_only(h, 0), name)
-        if bf16_copy is not None:
-            _native.check(self.lib.configure_norm_bf16_copy(h, bf16_copy.data_ptr()), name)
-        return self.add(2, h, name, sources, [StageOutput(name, "fp4", out, rows, width)])
+        if out.fp4 is not None and out.bf16 is not None:
+            _native.check(self.lib.configure_norm_bf16_copy(h, out.bf16.data_ptr()), name)
+            outs.append(StageOutput(name, "bf16", out.bf16, rows, width))
+        return self.add(2, h, name, sources, outs)
 
     def linear32(self, name, x, w, bias, out, *, rows, sources, ldx=None, x_bf16=False, out_bf16=False, silu=False,
                  rms=False, euler=False, prev=None, slot=0, prev_slot=0, x_row_offset=0, dt=0.0, eps=1e-6):
@@ -294,27 +390,28 @@ class NativePi0:
         self._own(h)
         s_x = self.add(3, h, "vision.patch", (), [StageOutput("vision.patch", "bf16", xa, M, W)])
         self.mark("patch", xa)
-        a_ln, a_att, a_ln2 = self.fp4(M, W), self.fp4(M, W), self.fp4(M, W)
         mlp_pad = padded(c.vision_mlp, 128)
-        a_h = self.fp4(M, mlp_pad)
+        a_ln, a_att, a_ln2, a_h = Activation(self, M, W), Activation(self, M, W), Activation(self, M, W), Activation(self, M, mlp_pad)
         qkv = [self.tensor((M, 3 * W)), self.tensor((M, 3 * W))]
-        att = self.tensor((M, W))
+        a_att.bf16 = self.tensor((M, W))                    # the attention stage always writes BF16 rows
+        att = a_att.bf16
         for i in range(c.vision_layers):
             p = f"{VISION}encoder.layers.{i}."
+            p_qkv, p_out, p_fc1, p_fc2 = [self.site(f"vision.{i}.{n}") for n in ("qkv", "out", "fc1", "fc2")]
             g1, b1 = sd[p + "layer_norm1.weight"].float().contiguous(), sd[p + "layer_norm1.bias"].float().contiguous()
             g2, b2 = sd[p + "layer_norm2.weight"].float().contiguous(), sd[p + "layer_norm2.bias"].float().contiguous()
-            wqkv = self.weight(torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"]))
+            wqkv = self.weight(torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"]), precision=p_qkv)
             bqkv = torch.cat([sd[p + f"self_attn.{n}_proj.bias"] for n in "qkv"]).to(torch.bfloat16).contiguous()
-            wo = self.weight(sd[p + "self_attn.out_proj.weight"])
+            wo = self.weight(sd[p + "self_attn.out_proj.weight"], precision=p_out)
             bo = sd[p + "self_attn.out_proj.bias"].to(torch.bfloat16).contiguous()
-            w1 = self.weight(sd[p + "mlp.fc1.weight"])
+            w1 = self.weight(sd[p + "mlp.fc1.weight"], precision=p_fc1)
             bias1 = torch.zeros(mlp_pad, device=self.device, dtype=torch.bfloat16)
             bias1[:c.vision_mlp] = sd[p + "mlp.fc1.bias"].to(torch.bfloat16)
-            w2 = self.weight(sd[p + "mlp.fc2.weight"])
+            w2 = self.weight(sd[p + "mlp.fc2.weight"], precision=p_fc2)
             bias2 = sd[p + "mlp.fc2.bias"].to(torch.bfloat16).contiguous()
             self.buffers.extend((g1, b1, g2, b2, bqkv, bo, bias1, bias2))
             buf = qkv[i & 1]
-            s_ln = self.norm(f"vision.{i}.ln1", xa, a_ln, rows=M, sources=[(s_x, SAME)], kind="layer", gamma=g1, beta=b1, eps=c.ln_eps)
+            s_ln = self.norm(f"vision.{i}.ln1", xa, a_ln.only(p_qkv), rows=M, sources=[(s_x, SAME)], kind="layer", gamma=g1, beta=b1, eps=c.ln_eps)
             s_qkv = self.gemm(f"vision.{i}.qkv", a_ln, wqkv, rows=M, sources=[(s_ln, SAME)], out=buf, bias=bqkv)
             h = C.c_void_p()
             q, k, v = buf[:, :W], buf[:, W:2 * W], buf[:, 2 * W:]
@@ -323,10 +420,13 @@ class NativePi0:
                                                3 * W, 3 * W, W, 0, self.workers, -1, float(hd ** -0.5)), "vision attention")
             self._own(h)
             s_att = self.add(1, h, f"vision.{i}.attention", [(s_qkv, ALL)], [StageOutput(f"vision.{i}.attention", "bf16", att, M, W)])
-            s_aq = self.norm(f"vision.{i}.attention_quant", att, a_att, rows=M, sources=[(s_att, SAME)], kind="none")
-            s_o = self.gemm(f"vision.{i}.out", a_att, wo, rows=M, sources=[(s_aq, SAME)], out=xb, bias=bo, residual=xa)
-            s_ln2 = self.norm(f"vision.{i}.ln2", xb, a_ln2, rows=M, sources=[(s_o, SAME)], kind="layer", gamma=g2, beta=b2, eps=c.ln_eps)
-            s_fc1 = self.gemm(f"vision.{i}.fc1", a_ln2, w1, rows=M, sources=[(s_ln2, SAME)], fp4_out=a_h, bias=bias1, activation=1)
+            if p_out == "nvfp4":
+                # the 72-wide heads do not quantise inside the attention stage: a quantiser stage of its own
+                s_att = self.norm(f"vision.{i}.attention_quant", att, a_att.only("nvfp4"), rows=M, sources=[(s_att, SAME)], kind="none")
+            s_o = self.gemm(f"vision.{i}.out", a_att, wo, rows=M, sources=[(s_att, SAME)], out=xb, bias=bo, residual=xa)
+            s_ln2 = self.norm(f"vision.{i}.ln2", xb, a_ln2.only(p_fc1), rows=M, sources=[(s_o, SAME)], kind="layer", gamma=g2, beta=b2, eps=c.ln_eps)
+            s_fc1 = self.gemm(f"vision.{i}.fc1", a_ln2, w1, rows=M, sources=[(s_ln2, SAME)], out_act=a_h.require(p_fc2), out_precision=p_fc2,
+                              bias=bias1, activation=1, act_cols=c.vision_mlp)
             s_x = self.gemm(f"vision.{i}.fc2", a_h, w2, rows=M, sources=[(s_fc1, SAME)], out=xa, bias=bias2, residual=xb)
             if i == 0:
                 self.mark("vision.0.qkv", buf), self.mark("vision.0.attention", att)
@@ -335,8 +435,10 @@ class NativePi0:
                 print("NativePi0: vision layers", i + 1, flush=True)
         gp, bp = sd[VISION + "post_layernorm.weight"].float().contiguous(), sd[VISION + "post_layernorm.bias"].float().contiguous()
         self.buffers.extend((gp, bp))
-        s_pl = self.norm("vision.post_layernorm", xa, a_ln, rows=M, sources=[(s_x, SAME)], kind="layer", gamma=gp, beta=bp, eps=c.ln_eps)
-        return s_pl, a_ln
+        p_proj = self.site("vision.projector")
+        a_post = a_ln.only(p_proj)
+        s_pl = self.norm("vision.post_layernorm", xa, a_post, rows=M, sources=[(s_x, SAME)], kind="layer", gamma=gp, beta=bp, eps=c.ln_eps)
+        return s_pl, a_post
 
     def _expert_splits(self, keys):
         """KV splits of the expert attention: as many as leave every tile a worker of its own that did NOT run a tile
@@ -356,54 +458,62 @@ class NativePi0:
         groups = -(-rows // 128) * self.config.heads
         return max(1, min(4, self.workers // groups))
 
-    def _gemma_layer(self, name, prefix, i, x_in, x_mid, bufs, *, rows, s_x, extra_sources, cos, sin, cache, cache_base,
+    def _gemma_layer(self, name, site, prefix, i, x_in, x_mid, bufs, *, rows, s_x, extra_sources, cos, sin, cache, cache_base,
                      attention_rows, mask_prefix, splits, kv_only, block_n, prefix_cache_stage=None):
+        """One Gemma decoder layer.  ``name`` labels the stages (``expert.<step>.<layer>``), ``site`` the weights
+        (``expert.<layer>``: one operand format for all Euler steps)."""
         c, sd, lib = self.config, self.sd, self.lib
         p = f"{prefix}layers.{i}."
-        width = x_in.shape[1]
         H, hd = c.heads, c.head_dim
-        a1, a2, a3, a4, qbuf, attn_out = bufs
+        a1, a2, a3, a4, qbuf = bufs
+        p_qkv, p_o, p_gu, p_dn = [self.site(f"{site}.{n}") for n in ("qkv", "o_proj", "gate_up", "down")]
+        tile = lambda precision: block_n if precision == "nvfp4" else 128       # BF16 sites use full-width tiles
         g1 = self.cached(p + "g1", lambda: (1.0 + sd[p + "input_layernorm.weight"].float()).contiguous())
-        s_n1 = self.norm(f"{name}.norm1", x_in, a1, rows=rows, sources=[(s_x, SAME)] + extra_sources, kind="rms", gamma=g1, eps=c.rms_eps)
+        s_n1 = self.norm(f"{name}.norm1", x_in, a1.only(p_qkv), rows=rows, sources=[(s_x, SAME)] + extra_sources, kind="rms", gamma=g1, eps=c.rms_eps)
         def make_qkv():
             wk = self._interleave_heads(sd[p + "self_attn.k_proj.weight"])
             wv = sd[p + "self_attn.v_proj.weight"]
             if kv_only:
-                return self.weight(torch.cat((wk, wv)), block_n=block_n)
-            return self.weight(torch.cat((self._interleave_heads(sd[p + "self_attn.q_proj.weight"]), wk, wv)), block_n=block_n)
+                return self.weight(torch.cat((wk, wv)), block_n=tile(p_qkv), precision=p_qkv)
+            return self.weight(torch.cat((self._interleave_heads(sd[p + "self_attn.q_proj.weight"]), wk, wv)), block_n=tile(p_qkv), precision=p_qkv)
 
         wqkv = self.cached(p + "qkv", make_qkv)
         q_cols, q = (0, None) if kv_only else (H * hd, qbuf)
-        s_qkv = self.gemm(f"{name}.qkv", a1, wqkv, rows=rows, sources=[(s_n1, SAME)], block_n=block_n,
+        s_qkv = self.gemm(f"{name}.qkv", a1, wqkv, rows=rows, sources=[(s_n1, SAME)], block_n=tile(p_qkv),
                           rope=dict(q=q, cos=cos, sin=sin, cache_k=cache[0], cache_v=cache[1], q_cols=q_cols, cache_base=cache_base))
         if kv_only:
             return s_qkv, s_qkv
+        attn_out = a2.bf16
         h = C.c_void_p()
         _native.check(lib.create_attention(C.byref(h), qbuf.data_ptr(), cache[0].data_ptr(), cache[1].data_ptr(), None, None, None,
                                            None, None, None, None, attn_out.data_ptr(), None, 1, rows, attention_rows, H, 1, hd,
                                            H * hd, hd, H * hd, 0, self.workers, mask_prefix, float(hd ** -0.5)), f"{name}.attention")
         self._own(h)
-        _native.check(lib.configure_attention_fp4_output(h, a2.data.data_ptr(), a2.scales.data_ptr(), a2.data.stride(0),
-                                                         a2.k // 16, a2.global_scale), f"{name}.attention")
+        outs = [StageOutput(f"{name}.attention", "bf16", attn_out, rows, H * hd)]
+        if p_o == "nvfp4":
+            fp4 = a2.require("nvfp4").fp4
+            _native.check(lib.configure_attention_fp4_output(h, fp4.data.data_ptr(), fp4.scales.data_ptr(), fp4.data.stride(0),
+                                                             fp4.k // 16, fp4.global_scale), f"{name}.attention")
+            outs.append(StageOutput(f"{name}.attention", "fp4", fp4, rows, H * hd))
         att_sources = [(s_qkv, ALL)] + ([(prefix_cache_stage, ALL)] if prefix_cache_stage is not None else [])
         if splits > 1:
             # split-KV with the merge inside the attention stage: the tiles of a head meet on a ticket and each merges its share of rows
             _native.check(lib.configure_attention_splits(h, splits), f"{name}.attention")
             _native.check(lib.configure_attention_fused_merge(h, 1), f"{name}.attention")
-        s_att = self.add(1, h, f"{name}.attention", att_sources, [StageOutput(f"{name}.attention", "bf16", attn_out, rows, H * hd),
-                                                                  StageOutput(f"{name}.attention", "fp4", a2, rows, H * hd)])
-        wo = self.cached(p + "o", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=block_n))
-        s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=block_n)
+        s_att = self.add(1, h, f"{name}.attention", att_sources, outs)
+        wo = self.cached(p + "o", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=tile(p_o), precision=p_o))
+        s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=tile(p_o))
         g2 = self.cached(p + "g2", lambda: (1.0 + sd[p + "post_attention_layernorm.weight"].float()).contiguous())
-        s_n2 = self.norm(f"{name}.norm2", x_mid, a3, rows=rows, sources=[(s_o, SAME)], kind="rms", gamma=g2, eps=c.rms_eps)
+        s_n2 = self.norm(f"{name}.norm2", x_mid, a3.only(p_gu), rows=rows, sources=[(s_o, SAME)], kind="rms", gamma=g2, eps=c.rms_eps)
         def make_gate_up():
             gate, up = sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]
-            return self.weight(torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], gate.shape[1]), block_n=block_n)
+            return self.weight(torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], gate.shape[1]), block_n=tile(p_gu), precision=p_gu)
 
         wgu = self.cached(p + "gate_up", make_gate_up)
-        s_gu = self.gemm(f"{name}.gate_up", a3, wgu, rows=rows, sources=[(s_n2, SAME)], fp4_out=a4, activation=2, block_n=block_n)
-        wd = self.cached(p + "down", lambda: self.weight(sd[p + "mlp.down_proj.weight"], block_n=block_n))
-        s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=block_n)
+        s_gu = self.gemm(f"{name}.gate_up", a3, wgu, rows=rows, sources=[(s_n2, SAME)], out_act=a4.require(p_dn), out_precision=p_dn,
+                         activation=2, block_n=tile(p_gu))
+        wd = self.cached(p + "down", lambda: self.weight(sd[p + "mlp.down_proj.weight"], block_n=tile(p_dn), precision=p_dn))
+        s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=tile(p_dn))
         return s_dn, s_qkv
 
     def _build(self):
@@ -417,7 +527,7 @@ class NativePi0:
         # ---------------- vision tower + projector -> prefix rows [0, V*256)
         s_pl, a_post = self._vision()
         x_a, x_b = self.tensor((P_pad, c.width)), self.tensor((P_pad, c.width))
-        wproj = self.weight(sd[PROJECTOR + "weight"])
+        wproj = self.weight(sd[PROJECTOR + "weight"], precision=self.site("vision.projector"))
         bproj = sd[PROJECTOR + "bias"].to(torch.bfloat16).contiguous()
         self.buffers.append(bproj)
         s_x = self.gemm("vision.projector", a_post, wproj, rows=V * 256, sources=[(s_pl, SAME)], out=x_a, bias=bproj)
@@ -439,16 +549,17 @@ class NativePi0:
         self.mark("prefix.input", x_a)
         cos_p, sin_p = self.rope(P, 0)
         self.caches = [(self.tensor((P + S_pad, hd)), self.tensor((P + S_pad, hd))) for _ in range(c.prefix_layers)]
-        bufs = (self.fp4(P_pad, c.width), self.fp4(P_pad, H * hd), self.fp4(P_pad, c.width), self.fp4(P_pad, c.mlp),
-                self.tensor((P_pad, H * hd)), self.tensor((P_pad, H * hd)))
+        bufs = (Activation(self, P_pad, c.width), Activation(self, P_pad, H * hd), Activation(self, P_pad, c.width),
+                Activation(self, P_pad, c.mlp), self.tensor((P_pad, H * hd)))
+        bufs[1].bf16 = self.tensor((P_pad, H * hd))          # attention output rows (BF16), always written
         cache_stage = []
         for i in range(c.prefix_layers):
-            s_x, s_kv = self._gemma_layer(f"prefix.{i}", LANGUAGE, i, x_a, x_b, bufs, rows=P, s_x=s_x, extra_sources=extra if i == 0 else [],
+            s_x, s_kv = self._gemma_layer(f"prefix.{i}", f"prefix.{i}", LANGUAGE, i, x_a, x_b, bufs, rows=P, s_x=s_x, extra_sources=extra if i == 0 else [],
                                           cos=cos_p, sin=sin_p, cache=self.caches[i], cache_base=0, attention_rows=P, mask_prefix=-1,
                                           splits=self._prefix_splits(P), kv_only=(i == c.prefix_layers - 1), block_n=128)
             cache_stage.append(s_kv)
             if i == 0:
-                self.mark("prefix.0.q", bufs[4]), self.mark("prefix.0.attention", bufs[5])
+                self.mark("prefix.0.q", bufs[4]), self.mark("prefix.0.attention", bufs[1].bf16)
             self.mark(f"prefix.{i}", x_a)
             if self.verbose and (i + 1) % 6 == 0:
                 print("NativePi0: prefix layers", i + 1, flush=True)
@@ -473,8 +584,9 @@ class NativePi0:
         actions = self.tensor((self.chunk_size, c.action_dim), torch.float32)
         xe_a, xe_b = self.tensor((S_pad, W)), self.tensor((S_pad, W))
         cos_s, sin_s = self.rope(S, P)
-        ebufs = (self.fp4(S_pad, W), self.fp4(S_pad, H * hd), self.fp4(S_pad, W), self.fp4(S_pad, c.expert_mlp),
-                 self.tensor((S_pad, H * hd)), self.tensor((S_pad, H * hd)))
+        ebufs = (Activation(self, S_pad, W), Activation(self, S_pad, H * hd), Activation(self, S_pad, W),
+                 Activation(self, S_pad, c.expert_mlp), self.tensor((S_pad, H * hd)))
+        ebufs[1].bf16 = self.tensor((S_pad, H * hd))
         time, dt = np.float32(1.0), np.float32(-1.0 / self.flow_steps)
         s_prev = None
         for step in range(self.flow_steps):
@@ -521,7 +633,7 @@ class NativePi0:
 
     def _expert_layer(self, step, i, x_in, x_mid, bufs, S, P, s_x, cos, sin, prefix_cache_stage):
         """Every Euler step wires its own stages; the NVFP4 weights are shared through the keyed weight cache."""
-        return self._gemma_layer(f"expert.{step}.{i}", EXPERT, i, x_in, x_mid, bufs, rows=S, s_x=s_x, extra_sources=[], cos=cos, sin=sin,
+        return self._gemma_layer(f"expert.{step}.{i}", f"expert.{i}", EXPERT, i, x_in, x_mid, bufs, rows=S, s_x=s_x, extra_sources=[], cos=cos, sin=sin,
                                  cache=self.caches[i], cache_base=P, attention_rows=P + S, mask_prefix=P, splits=self._expert_splits(P + S),
                                  kv_only=False, block_n=self.expert_block_n, prefix_cache_stage=prefix_cache_stage)
 

@@ -244,15 +244,15 @@ def worst(errors, prefix):
     return name, picked[name]
 
 
-@pytest.mark.parametrize("views,chunk,prompt", [(3, 50, 0), (3, 63, 16)])
-def test_full_depth_model_layer_by_layer(full_model, views, chunk, prompt):
+@pytest.mark.parametrize("views,chunk,prompt,precision", [(3, 50, 0, "nvfp4"), (3, 63, 16, "nvfp4"), (3, 50, 0, "bf16")])
+def test_full_depth_model_layer_by_layer(full_model, views, chunk, prompt, precision):
     dims, cfg, sd = full_model
     x = make_inputs(views, chunk, prompt, dims.vocab)
-    oracle = Pi0Torch(dims, sd, mode="nvfp4")
+    oracle = Pi0Torch(dims, sd, mode="nvfp4", precision=precision)
     oracle.record_ops = True
     emulation = oracle.sample_actions(*x)
     eager = Pi0Torch(dims, sd, mode="bf16").sample_actions(*x)
-    with NativePi0.from_model(StateDictModel(cfg, sd), num_views=views, prompt_len=prompt, chunk_size=chunk) as engine:
+    with NativePi0.from_model(StateDictModel(cfg, sd), num_views=views, prompt_len=prompt, chunk_size=chunk, precision=precision) as engine:
         assert len(engine.stages) > 1500 and engine.plan["stages"] == len(engine.stages)
         walker = Walker(engine, oracle, x, chunk + 1)
         expected = 1 + dims.vision_layers + 2 + dims.prefix_layers + 10 * (dims.expert_layers + 2)
@@ -266,12 +266,12 @@ def test_full_depth_model_layer_by_layer(full_model, views, chunk, prompt):
         again = engine.forward(*x).clone()              # the handle is back to free running: same bits as before
         assert torch.equal(single, again)
     compared = sum(len(v) for v in op_stats.values())
-    assert compared > 2 * len(engine.stages), compared      # (NVFP4 outputs count three times: values, codes, scales)
+    assert compared > len(engine.stages), compared          # (NVFP4 outputs count three times: values, codes, scales)
     op_table = {f"{kind}:{op}": {"worst": max(v)[0], "at": max(v)[1], "median": sorted(v)[len(v) // 2][0], "count": len(v)}
                 for (kind, op), v in sorted(op_stats.items())}
     layers = sorted(v for k, v in forced.items() if k.startswith(("vision.", "prefix.", "expert.")) and not k.endswith("input"))
     layer_median = layers[len(layers) // 2]
-    report = {"config": [views, chunk, prompt],
+    report = {"config": [views, chunk, prompt, precision],
               "action_nrmse_vs_emulation": nrmse(single, emulation), "action_nrmse_vs_bf16_eager": nrmse(single, eager),
               "emulation_nrmse_vs_bf16_eager": nrmse(emulation, eager),
               "teacher_forced_worst": {p: worst(forced, p) for p in ("patch", "vision.", "image_tokens", "prefix.", "cache.", "expert.", "actions.")},
@@ -282,13 +282,18 @@ def test_full_depth_model_layer_by_layer(full_model, views, chunk, prompt):
     print("FULL-MODEL-OPERATORS " + json.dumps(op_table))
     out_dir = os.environ.get("PI0_PARITY_REPORT_DIR")
     if out_dir:
-        with open(os.path.join(out_dir, f"full_model_parity_{views}_{chunk}_{prompt}.json"), "w") as f:
+        with open(os.path.join(out_dir, f"full_model_parity_{views}_{chunk}_{prompt}_{precision}.json"), "w") as f:
             json.dump({"report": report, "operators": op_table, "teacher_forced": forced, "free_running": free}, f, indent=1)
     # ---- operator by operator: every stage on the oracle's own input
     for (kind, op), values in op_stats.items():
         value, where = max(values)
         assert value <= operator_gate(kind, op), (kind, op, where, value)
     assert op_final <= 1e-2
+    if precision == "bf16":
+        # every site in BF16: the reference's own action gate against BF16 eager (scripts/validate_native_pi0.py:149-150)
+        assert nrmse(single, eager) <= 0.015625
+        assert float((single - eager).abs().max() / eager.square().mean().sqrt()) <= 0.0625
+        assert float(torch.nn.functional.cosine_similarity(single.flatten(), eager.flatten(), dim=0)) >= 0.999
     # ---- teacher forced: every layer on its own
     assert forced["patch"] <= HEAD_TOL and layer_median <= LAYER_MEDIAN_TOL
     for name, err in forced.items():

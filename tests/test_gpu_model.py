@@ -73,6 +73,32 @@ def test_forward_matches_oracle(small_model, views, chunk, prompt):
         assert set(engine.component_ranges) == {"vision", "prefix", "expert"}
 
 
+@pytest.mark.parametrize("precision,policy", [("bf16", "bf16_reference"), ({"*.qkv": "bf16"}, "mixed"),
+                                              ({"default": "bf16", "vision.*": "nvfp4", "expert.*.down": "nvfp4"}, "mixed")])
+def test_site_precisions(small_model, precision, policy):
+    """Operand format chosen site by site: the engine against the oracle emulating the same choice.  With every site in
+    BF16 the engine has to meet the reference's own action gate against BF16 eager (``scripts/validate_native_pi0.py
+    :149-150``: NRMSE <= 2 BF16 eps, max error <= 0.0625 RMS, cosine >= 0.999)."""
+    dims, cfg, sd = small_model
+    x = inputs(3, 50, 16, dims.vocab)
+    emulation = Pi0Torch(dims, sd, mode="nvfp4", precision=precision).sample_actions(*x)
+    eager = Pi0Torch(dims, sd, mode="bf16").sample_actions(*x)
+    with NativePi0(StateDictModel(cfg, sd), prompt_len=16, precision=precision) as engine:
+        out = engine.forward(*x).clone()
+        assert engine.status()["code"] == 0 and engine.precision_policy == policy
+        assert torch.equal(engine.forward(*x), out)
+        formats = set(engine.site_precisions.values())
+    assert formats == ({"bf16"} if policy == "bf16_reference" else {"bf16", "nvfp4"})
+    if policy == "bf16_reference":
+        assert nrmse(out, emulation) <= 0.0156
+        assert nrmse(out, eager) <= 0.015625
+        assert float((out - eager).abs().max() / eager.square().mean().sqrt()) <= 0.0625
+        assert float(torch.nn.functional.cosine_similarity(out.flatten(), eager.flatten(), dim=0)) >= 0.999
+    else:
+        assert nrmse(out, emulation) <= 0.1
+        assert nrmse(out, eager) <= 1.3 * max(nrmse(emulation, eager), 0.05)
+
+
 def test_partitioned_and_stage_range_launches_are_bit_exact(small_model):
     dims, cfg, sd = small_model
     x = inputs(3, 50, 0, dims.vocab)
@@ -128,7 +154,9 @@ def test_input_validation_and_capture_rejection(small_model):
     dims, cfg, sd = small_model
     x = inputs(3, 50, 0, dims.vocab)
     with pytest.raises(ValueError):
-        NativePi0(StateDictModel(cfg, sd), precision="bf16")
+        NativePi0(StateDictModel(cfg, sd), precision="fp8")
+    with pytest.raises(ValueError):
+        NativePi0(StateDictModel(cfg, sd), precision={"*.qkv": "int4"})
     with pytest.raises(ValueError):
         NativePi0(StateDictModel(cfg, sd), num_views=4)
     with NativePi0(StateDictModel(cfg, sd)) as engine:
