@@ -33,6 +33,15 @@ sys.path.insert(0, str(ROOT / "pizero-megakernel_b200"))
 sys.path.insert(0, str(ROOT))
 
 METRIC = "pi0_10step_action_chunk_latency_p50_ms"
+# Operand-format presets for --precision (site patterns of NativePi0's `precision` argument)
+PRECISIONS = {
+    "nvfp4": "nvfp4",
+    "qkv_bf16": {"*.qkv": "bf16"},
+    "attention_bf16": {"*.qkv": "bf16", "*.o_proj": "bf16", "*.out": "bf16"},
+    "expert_bf16": {"expert.*": "bf16"},
+    "attention_expert_bf16": {"*.qkv": "bf16", "*.o_proj": "bf16", "*.out": "bf16", "expert.*": "bf16"},
+    "bf16": "bf16",
+}
 WORKLOADS = {
     # BASELINE.json configs[3]: full forward, 3 views, no prompt, chunk 50, 10 Euler steps
     "cfg4": dict(views=3, prompt=0, chunk=50, steps=10, name="configs[3]: full pi0 forward, batch 1, 3 views 224x224, prompt 0, chunk 50, 10 Euler steps"),
@@ -303,7 +312,8 @@ def run_engine(args, wl, rank, world):
     need_table = wl["prompt"] > 0 or replica_wl is not None
     sd = random_state_dict(cfg, seed=1234 + rank, device=device, skip_embedding=not need_table)
     model = StateDictModel(cfg, sd)
-    engine = NativePi0(model, num_views=wl["views"], prompt_len=wl["prompt"], chunk_size=wl["chunk"], flow_steps=wl["steps"])
+    engine = NativePi0(model, num_views=wl["views"], prompt_len=wl["prompt"], chunk_size=wl["chunk"], flow_steps=wl["steps"],
+                       precision=PRECISIONS[args.precision])
     host = synthetic_inputs(torch, wl, 100 + rank, cfg.vocab)
     pinned = [t.pin_memory() for t in host]
     dev = [t.to(device) for t in host]
@@ -330,6 +340,7 @@ def run_engine(args, wl, rank, world):
                 phases[name + "_ms"] = (max(r[2] for r in rows) - min(r[1] for r in rows)) / 1e6
     actions = engine.forward(*dev).clone()
     plan = engine.plan
+    policy = engine.precision_policy
     engine.close()
     # ---- BF16 baselines on the same GPU, same weights, same inputs (rank 0, one GPU)
     baselines, accuracy = None, None
@@ -342,7 +353,7 @@ def run_engine(args, wl, rank, world):
     replica = None
     if replica_wl is not None:
         engine5 = NativePi0(model, num_views=replica_wl["views"], prompt_len=replica_wl["prompt"], chunk_size=replica_wl["chunk"],
-                            flow_steps=replica_wl["steps"])
+                            flow_steps=replica_wl["steps"], precision=PRECISIONS[args.precision])
         host5 = synthetic_inputs(torch, replica_wl, 200 + rank, cfg.vocab)
         t5 = time_engine(torch, dist, engine5, [t.to(device) for t in host5], [t.pin_memory() for t in host5], args.steps, args.warmup, world)
         engine5.close()
@@ -366,10 +377,13 @@ def run_engine(args, wl, rank, world):
         d2h = actions.numel() * 4
         line = {"metric": METRIC, "value": p50, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
                 "ms_per_step": total_ms / args.steps, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-                "dtype": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate; bf16 attention, fp32 heads)", "data": "synthetic",
+                "dtype": {"nvfp4": "nvfp4 (e2m1 x ue4m3 block scales, fp32 accumulate; bf16 attention, fp32 heads)",
+                          "bf16_reference": "bf16 (fp32 accumulate; fp32 heads)"}.get(policy, f"mixed nvfp4 / bf16 sites ({args.precision})"),
+                "data": "synthetic",
                 "p90_ms": p90, "replica_actions_per_s": world * wl["chunk"] * 1e3 / p50,
                 "config": {"workload": wl["name"], "weights": "random-init N(0,0.02), seeded", "parallelism": f"replicas x{world}, no collective",
-                           "l2": "weights (1.46 GB NVFP4) exceed the 126 MB L2; no explicit flush", "program": plan},
+                           "l2": "weights (1.46 GB NVFP4) exceed the 126 MB L2; no explicit flush", "program": plan,
+                           "precision": args.precision},
                 "clocks": clocks, "gpu_launches": args.steps,
                 "e2e": {"value": e2e_p50, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
                 "roofline": {"bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s", "frac": achieved / tf_peak,
@@ -407,6 +421,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=("native", "reference"))
     ap.add_argument("--workload", default="cfg4", choices=tuple(WORKLOADS))
+    ap.add_argument("--precision", default="nvfp4", choices=tuple(PRECISIONS), help="operand format of the transformer linears")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-replica-shape", action="store_true", help="skip the configs[4] (prompt 16, chunk 63) block")
     ap.add_argument("--gpu-baselines", default="eager,graph", help="comma list of eager, graph, compiled; empty string: none")

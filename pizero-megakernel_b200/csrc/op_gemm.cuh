@@ -116,6 +116,8 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
 // issued by one elected lane. (Run by a single lane inside a divergent branch, every descriptor and address has to be
 // moved from per-thread to uniform registers for each instruction, which measured about 250 cycles per 64-wide K
 // group and made this lane, not the copies or the tensor core, the pace of a narrow GEMM.)
+// (One instantiation per operand format, so each issue loop carries only its own instructions.)
+template <int OPERANDS>
 __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem_in, const StageDesc& st,
                                          int stage_index, int first_in, int count_in, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
@@ -128,7 +130,6 @@ __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_
     const uint32_t off_b16 = uniform_u32(static_cast<uint32_t>(g.off_b)) >> 4, off_sfa16 = uniform_u32(static_cast<uint32_t>(g.off_sfa)) >> 4,
                    off_sfb16 = uniform_u32(static_cast<uint32_t>(g.off_sfb)) >> 4;
     const uint32_t idesc = uniform_u32(g.idesc);
-    const int operands = uniform_i32(g.operands);
     const uint32_t tmem = uniform_u32(tmem_in);
     const uint32_t data16 = uniform_u32((smem_u32(data) & 0x3FFFFu) >> 4), stride16 = stride >> 4;
     // descriptor high words: K-major 128-byte swizzle (8-row groups 1024 bytes apart, version 1) and the scale atoms
@@ -154,7 +155,7 @@ __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_
             const int groups = min(4 * kChunks, k_groups - ks * 4 * kChunks);
             const uint32_t a16 = data16 + s * stride16;
             const uint32_t sf_cols = tmem + kSfCol0 + (it & 3u) * (4 * kChunks * 8);
-            if (operands != GEMM_NVFP4) {
+            if constexpr (OPERANDS != GEMM_NVFP4) {
                 // BF16 / FP8 rows: the same descriptors and the same 32-byte advance along K, no scale factors
                 if (elect_one()) {
 #pragma unroll
@@ -164,7 +165,7 @@ __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_
                             const uint64_t da = kOperandHi | static_cast<uint64_t>(a16 + chunk * a_chunk16 + 2u * sub);
                             const uint64_t db = kOperandHi | static_cast<uint64_t>(a16 + off_b16 + chunk * b_chunk16 + 2u * sub);
                             const uint32_t acc = gi != 0 ? 1u : static_cast<uint32_t>(ks != 0);
-                            if (operands == GEMM_BF16) tc_mma_f16(d, da, db, idesc, acc);
+                            if constexpr (OPERANDS == GEMM_BF16) tc_mma_f16(d, da, db, idesc, acc);
                             else tc_mma_f8(d, da, db, idesc, acc);
                         }
                     }
@@ -215,6 +216,8 @@ __device__ __forceinline__ float gelu_sigmoid(float x) {
 }
 
 // One 32-column chunk of one accumulator row (thread == row).
+// (Instantiated per epilogue kind: each accumulator drain carries only its own arithmetic and registers.)
+template <int EPI>
 __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const uint32_t (&raw)[32], int row, int col0,
                                                     bool row_ok) {
     float v[32];
@@ -223,7 +226,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
     const float row_scale = g.row_factor ? g.alpha * __ldcg(g.row_factor + row) : g.alpha;
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(raw[i]) * row_scale;
-    if (g.epilogue == EPI_GEGLU_FP4) {
+    if constexpr (EPI == EPI_GEGLU_FP4) {
         // interleaved (gate, up) column pairs -> 16 outputs = one scale block
         float h[16];
 #pragma unroll
@@ -235,7 +238,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         g.out_scales[scale_offset(row, out_col >> 4, g.out_blocks)] = static_cast<uint8_t>(code);
         return;
     }
-    if (g.epilogue == EPI_GEGLU_BF16) {
+    if constexpr (EPI == EPI_GEGLU_BF16) {
         // bf16(gelu(bf16 gate)) * bf16(up), rounded once more: the BF16 model's GeGLU on interleaved (gate, up) columns
         uint32_t w[8];
 #pragma unroll
@@ -249,7 +252,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
         return;
     }
-    const bool early_bias = g.bias && g.residual && g.round_before_residual;
+    const bool early_bias = EPI == EPI_BF16_EXT && g.bias && g.residual && g.round_before_residual;
     if (early_bias) {
         const uint4* b = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(g.bias) + col0);
 #pragma unroll
@@ -263,7 +266,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         }
     }
     if (g.residual) {
-        if (g.round_before_residual) {
+        if (EPI == EPI_BF16_EXT && g.round_before_residual) {
 #pragma unroll
             for (int i = 0; i < 32; i++) v[i] = bf16_round(v[i]);
         }
@@ -292,14 +295,14 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
             f = unpack_bf16x2(u.w); v[8 * i + 6] += f.x; v[8 * i + 7] += f.y;
         }
     }
-    if (g.epilogue == EPI_F32) {
+    if constexpr (EPI == EPI_F32) {
         float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + static_cast<size_t>(row) * g.ldo + col0);
 #pragma unroll
         for (int i = 0; i < 8; i++) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
         return;
     }
-    if (g.epilogue == EPI_BF16) {
-        if (g.gelu_cols > 0) {
+    if constexpr (EPI == EPI_BF16 || EPI == EPI_BF16_EXT) {
+        if (EPI == EPI_BF16_EXT && g.gelu_cols > 0) {
 #pragma unroll
             for (int i = 0; i < 32; i++) v[i] = col0 + i < g.gelu_cols ? gelu_tanh(bf16_round(v[i])) : 0.f;
         }
@@ -310,7 +313,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
                                 pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
         return;
     }
-    if (g.epilogue == EPI_FP4) {
+    if constexpr (EPI == EPI_FP4) {
         if (g.act == 1) {
 #pragma unroll
             for (int i = 0; i < 32; i++) v[i] = gelu_sigmoid(v[i]);
@@ -337,7 +340,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         return;
     }
     // EPI_QKV_ROPE: values are first rounded to BF16 (the projection output), then rotated.
-    {
+    if constexpr (EPI == EPI_QKV_ROPE) {
         const int hd = g.head_dim, half = hd >> 1;
         const int kv0 = g.q_cols;                      // K columns [kv0, kv0+hd), V columns [kv0+hd, kv0+2hd)
         const bool is_v = col0 >= kv0 + hd;
@@ -390,6 +393,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
     }
 }
 
+template <int EPI>
 __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, uint32_t tmem, const StageDesc& st,
                                               int stage_index, int first, int count, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
@@ -400,7 +404,7 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
         const uint32_t buf = ps.epi_tile & 1u, phase = (ps.epi_tile >> 1) & 1u;
         const int row = m_tile * 128 + quarter * 32 + lane;
         const bool row_ok = row < g.rows;
-        if (g.epilogue == EPI_QKV_ROPE && row_ok) {
+        if (EPI == EPI_QKV_ROPE && row_ok) {
             // while the MMAs run: bring this row's rotary table entries (constant data) close
             const int hd = g.head_dim, col_a = n_tile * g.block_n;
             if (col_a < g.q_cols + hd) {                                   // a Q or K tile
@@ -425,7 +429,7 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
             }
-            gemm_epilogue_chunk(g, raw, row, n_tile * g.block_n + c * 32, row_ok);
+            gemm_epilogue_chunk<EPI>(g, raw, row, n_tile * g.block_n + c * 32, row_ok);
         }
         // each epilogue warp publishes its own 32 rows (a GEMM tile counts 4 units): no CTA barrier on this path
         if (stamp && t == first + count - 1 && threadIdx.x == 128) stamp[7] = static_cast<long long>(global_ns());
@@ -445,9 +449,20 @@ __device__ __forceinline__ void gemm_instruction(const VmProgram& prog, Ctl* ctl
         gemm_producer(prog, ctl, data, st, stage_index, first, count, ps, stamp);
         if (stamp && threadIdx.x == 0) stamp[3] = static_cast<long long>(global_ns());
     } else if (warp == 1) {
-        gemm_mma(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
+        const int operands = st.p.gemm.operands;
+        if (operands == GEMM_NVFP4) gemm_mma<GEMM_NVFP4>(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
+        else if (operands == GEMM_BF16) gemm_mma<GEMM_BF16>(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
+        else gemm_mma<GEMM_FP8>(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
     } else if (warp >= 4) {
-        gemm_epilogue(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        switch (st.p.gemm.epilogue) {                   // one drain loop per epilogue kind: only its own arithmetic and registers
+            case EPI_F32: gemm_epilogue<EPI_F32>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
+            case EPI_BF16: gemm_epilogue<EPI_BF16>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
+            case EPI_BF16_EXT: gemm_epilogue<EPI_BF16_EXT>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
+            case EPI_FP4: gemm_epilogue<EPI_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
+            case EPI_GEGLU_FP4: gemm_epilogue<EPI_GEGLU_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
+            case EPI_GEGLU_BF16: gemm_epilogue<EPI_GEGLU_BF16>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
+            default: gemm_epilogue<EPI_QKV_ROPE>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
+        }
         if (stamp && threadIdx.x == 128) stamp[2] = static_cast<long long>(global_ns());
     }
 }

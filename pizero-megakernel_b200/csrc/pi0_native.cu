@@ -479,6 +479,7 @@ extern "C" int configure_resident_fp4_bf16(void* handle, const void* bias, const
     if (!op || op->desc.kind != OP_GEMM || !out) return cudaErrorInvalidValue;
     GemmParams& g = op->desc.p.gemm;
     g.epilogue = EPI_BF16;
+    g.round_before_residual = 0; g.gelu_cols = 0;
     g.bias = bias; g.residual = residual; g.ldr = op->n;
     g.out = out; g.ldo = op->n;
     op->solo_dirty = true;
@@ -602,7 +603,7 @@ Op* dense_bf16(void* handle) {
     Op* op = as_op(handle);
     if (!op || op->desc.kind != OP_GEMM) return nullptr;
     const int epilogue = op->desc.p.gemm.epilogue;
-    return epilogue == EPI_BF16 || epilogue == EPI_GEGLU_BF16 || epilogue == EPI_QKV_ROPE ? op : nullptr;
+    return epilogue == EPI_BF16 || epilogue == EPI_BF16_EXT || epilogue == EPI_GEGLU_BF16 || epilogue == EPI_QKV_ROPE ? op : nullptr;
 }
 }  // namespace
 extern "C" int launch_dense(void* handle, void* stream) {
@@ -613,7 +614,9 @@ extern "C" int launch_dense(void* handle, void* stream) {
 extern "C" int destroy_dense(void* handle) { return destroy_checked(handle); }
 extern "C" int configure_dense_round_before_residual(void* handle) {
     Op* op = dense_bf16(handle);
-    if (!op || !op->desc.p.gemm.residual || op->desc.p.gemm.epilogue != EPI_BF16) return cudaErrorInvalidValue;
+    const bool plain = op && (op->desc.p.gemm.epilogue == EPI_BF16 || op->desc.p.gemm.epilogue == EPI_BF16_EXT);
+    if (!plain || !op->desc.p.gemm.residual) return cudaErrorInvalidValue;
+    op->desc.p.gemm.epilogue = EPI_BF16_EXT;
     op->desc.p.gemm.round_before_residual = 1;
     op->solo_dirty = true;
     return cudaSuccess;
@@ -622,7 +625,7 @@ extern "C" int configure_dense_geglu(void* handle, void* compact_output) {
     Op* op = dense_bf16(handle);
     if (!op || !compact_output || !aligned16(compact_output)) return cudaErrorInvalidValue;
     GemmParams& g = op->desc.p.gemm;
-    if (g.epilogue != EPI_BF16 || g.bias || g.residual || g.gelu_cols || op->n % 256) return cudaErrorInvalidValue;
+    if (g.epilogue != EPI_BF16 || g.bias || g.residual || op->n % 256) return cudaErrorInvalidValue;
     g.epilogue = EPI_GEGLU_BF16;
     g.out = compact_output;
     g.ldo = op->n / 2;
@@ -633,7 +636,9 @@ extern "C" int configure_dense_gelu(void* handle, int logical_columns) {
     Op* op = dense_bf16(handle);
     if (!op) return cudaErrorInvalidValue;
     GemmParams& g = op->desc.p.gemm;
-    if (g.epilogue != EPI_BF16 || g.residual || logical_columns < 1 || logical_columns > op->n) return cudaErrorInvalidValue;
+    if ((g.epilogue != EPI_BF16 && g.epilogue != EPI_BF16_EXT) || g.residual || logical_columns < 1 || logical_columns > op->n)
+        return cudaErrorInvalidValue;
+    g.epilogue = EPI_BF16_EXT;
     g.gelu_cols = logical_columns;
     op->solo_dirty = true;
     return cudaSuccess;
@@ -662,7 +667,7 @@ extern "C" int configure_dense_qkv_rope(void* handle, const void* cos, const voi
         !aligned16(cos) || !aligned16(sin) || !aligned16(cache_k) || !aligned16(cache_v))
         return cudaErrorInvalidValue;
     GemmParams& g = op->desc.p.gemm;
-    if (g.epilogue != EPI_BF16 || g.bias || g.residual || g.gelu_cols || logical_rows > op->m || key_offset + 512 != op->n)
+    if (g.epilogue != EPI_BF16 || g.bias || g.residual || logical_rows > op->m || key_offset + 512 != op->n)
         return cudaErrorInvalidValue;
     g.epilogue = EPI_QKV_ROPE;
     g.rope_cos = cos; g.rope_sin = sin;

@@ -36,7 +36,8 @@ enum GemmEpilogue : int {
     EPI_FP4 = 2,        // alpha*acc + bias (+residual) [GELU|ReLU^2] -> NVFP4 + swizzled scales
     EPI_GEGLU_FP4 = 3,  // gelu_tanh(gate)*up on interleaved columns -> NVFP4, width N/2
     EPI_QKV_ROPE = 4,   // BF16, RoPE on Q/K heads, K/V rows appended to the KV cache
-    EPI_GEGLU_BF16 = 5  // bf16(gelu_tanh(bf16 gate)) * bf16(up) on interleaved columns -> BF16, width N/2
+    EPI_GEGLU_BF16 = 5, // bf16(gelu_tanh(bf16 gate)) * bf16(up) on interleaved columns -> BF16, width N/2
+    EPI_BF16_EXT = 6    // EPI_BF16 with the BF16 model's options: round before the residual add, GELU with a column limit
 };
 
 enum GemmOperands : int {
