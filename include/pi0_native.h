@@ -47,6 +47,18 @@ int destroy_resident_fp4(void* handle);
  * Replaces the BF16 path's configure_dense_qkv_rope (native_pi0/dense.cu:231-253). */
 int configure_resident_fp4_qkv_rope(void* handle, void* out_q, int ldq, const void* cos, const void* sin, void* cache_k,
                                     void* cache_v, int q_cols, int head_dim, int cache_base);
+/* extension: residual-stream epilogue.  out BF16 [M, N] = alpha*acc + residual + bias as configure_resident_fp4_bf16;
+ * the rounded rows are also quantised, un-normalised, to NVFP4 (copy_fp4 packed [M, N/2], copy_scales swizzled with
+ * N/16 blocks per row, tensor scale copy_global_scale), and sumsq FP32 [M, N / tile width] receives, per output tile,
+ * the sum of squares of its part of each row.  With configure_resident_fp4_row_rms on the projection that reads the
+ * copy (whose weight has the norm weight folded in) this replaces an RMSNorm stage between the two projections
+ * (the reference folds the norm the same way for its BF16 model: native_pi0/model.py:163-164,203-204 and the
+ * rms_factors of native_pi0/dense.cu:86-89). */
+int configure_resident_fp4_stream(void* handle, const void* bias, const void* residual, void* out, void* copy_fp4,
+                                  void* copy_scales, float copy_global_scale, float* sumsq);
+/* extension: every accumulator row r is multiplied by rsqrt(sum(sumsq[r, 0..parts)) / width + eps); parts % 4 == 0.
+ * The sum runs in index order, so the factor has the same bits on every launch. */
+int configure_resident_fp4_row_rms(void* handle, const float* sumsq, int parts, int width, float eps);
 /* extension: logical row count (rows >= this are never stored; with at most 64 rows only 64 rows of A are
  * copied per tile) and output tile width (128 or 64). */
 int configure_resident_fp4_rows(void* handle, int rows);

@@ -225,10 +225,12 @@ def site_of(parameter):
 
 class Pi0Torch:
     def __init__(self, dims: Pi0Dims, state_dict, mode="bf16", compute_dtype=torch.bfloat16, rope_inv_freq_dtype=torch.float32,
-                 precision=None):
+                 precision=None, fold_norms=True):
         """``precision`` (mode "nvfp4" only): dict of fnmatch patterns over site names -> "nvfp4" | "bf16" with an optional
         "default", as the engine takes it; BF16 sites multiply BF16 operands with FP32 accumulation and round the way the
-        engine's BF16 epilogues do."""
+        engine's BF16 epilogues do.  ``fold_norms`` (mode "nvfp4"): an RMSNorm between two NVFP4 projections is evaluated
+        the way the engine folds it - the un-normalised BF16 rows are quantised, the weight columns carry ``1 + w`` and
+        the accumulator rows are multiplied by ``rsqrt(mean square + eps)``."""
         assert mode in ("bf16", "nvfp4")
         self.d, self.sd, self.mode = dims, state_dict, mode
         precision = precision or {}
@@ -237,6 +239,7 @@ class Pi0Torch:
         self._precision_map = [(k, v) for k, v in precision.items() if k != "default"]
         self._precision_default = precision.get("default", "nvfp4")
         self._site_cache = {}
+        self.fold_norms = bool(fold_norms) and mode == "nvfp4"
         self.dt = compute_dtype                 # activation dtype of the bf16 mode (float32 for a fast CPU baseline)
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self._wq = {}
@@ -270,7 +273,12 @@ class Pi0Torch:
             return (o.to(torch.bfloat16).float() + x.float()).to(torch.bfloat16)
         return (o + x.float()).to(torch.bfloat16)
 
-    def _fused_scale(self, name, w):
+    @staticmethod
+    def _folded(w, gamma):
+        """Weight with the norm weight folded into its columns, stored in BF16 like every weight the engine packs."""
+        return w if gamma is None else (w.float() * gamma.float()[None, :]).to(torch.bfloat16)
+
+    def _fused_scale(self, name, w, gamma=None):
         """The engine packs q|k|v (k|v for the last prefix layer) and gate|up as ONE NVFP4 tensor, so the members of
         a fused projection share one tensor scale: amax over the fused matrix / (6*448)."""
         base, leaf = name.rsplit(".", 1)
@@ -279,14 +287,27 @@ class Pi0Torch:
         elif leaf in ("gate_proj", "up_proj"):
             members = ["gate_proj", "up_proj"]
         else:
-            return weight_global_scale(w)
-        return max(weight_global_scale(self.sd[f"{base}.{m}.weight"]) for m in members)
+            return weight_global_scale(self._folded(w, gamma))
+        return max(weight_global_scale(self._folded(self.sd[f"{base}.{m}.weight"], gamma)) for m in members)
 
-    def _qweight(self, name, w):
-        if name not in self._wq:
-            gs = self._fused_scale(name, w)
-            self._wq[name] = fake_quant(pad_cols(w.float(), 64), "ceil", gs)
-        return self._wq[name]
+    def _qweight(self, name, w, gamma=None):
+        key = (name, gamma is not None)
+        if key not in self._wq:
+            gs = self._fused_scale(name, w, gamma)
+            self._wq[key] = fake_quant(pad_cols(self._folded(w, gamma).float(), 64), "ceil", gs)
+        return self._wq[key]
+
+    def folded_linear(self, x, name, gamma):
+        """NVFP4 projection of UN-normalised BF16 rows ``x`` through a weight that carries ``gamma`` (= 1 + norm weight)
+        in its columns, times the rows' ``rsqrt(mean square + eps)``: the engine's folded RMSNorm.  FP32, not rounded."""
+        xf = x.to(torch.bfloat16).float()
+        wq = self._qweight(name, self.sd[name + ".weight"], gamma)
+        y = fake_quant(pad_cols(xf, 64), "nearest", 1.0) @ wq.T
+        return y * torch.rsqrt(xf.square().mean(-1, keepdim=True) + self.d.rms_eps)
+
+    def folds(self, producer, consumer):
+        """True when the norm between the projections ``producer`` and ``consumer`` (parameter prefixes) is folded."""
+        return self.fold_norms and not self.bf16_site(producer) and not self.bf16_site(consumer)
 
     def linear(self, x, name, bias=True, weight=None):
         """BF16 mode: y = x W^T + b in the activation dtype.  NVFP4 mode: FP32 accumulator of fake-quantised
@@ -385,10 +406,17 @@ class Pi0Torch:
         ``name`` (the engine's stage prefix, e.g. ``prefix.3`` or ``expert.0.3``) labels the operator outputs kept by ``rec``."""
         d, sd = self.d, self.sd
         p = f"{prefix}layers.{i}."
-        y = self.rms(x, sd[p + "input_layernorm.weight"])
-        self.rec(f"{name}.norm1", y)
-        k = self.act(self.linear(y, p + "self_attn.k_proj", bias=False)).reshape(-1, 1, d.head_dim)
-        v = self.act(self.linear(y, p + "self_attn.v_proj", bias=False)).reshape(-1, 1, d.head_dim)
+        # the input norm is folded when the previous layer's down projection and this QKV projection are NVFP4 sites
+        fold1 = i > 0 and self.folds(f"{prefix}layers.{i - 1}.mlp.down_proj", p + "self_attn.q_proj")
+        if fold1:
+            g1 = 1.0 + sd[p + "input_layernorm.weight"].float()
+            project = lambda leaf: self.folded_linear(x, p + "self_attn." + leaf, g1)
+        else:
+            y = self.rms(x, sd[p + "input_layernorm.weight"])
+            self.rec(f"{name}.norm1", y)
+            project = lambda leaf: self.linear(y, p + "self_attn." + leaf, bias=False)
+        k = self.act(project("k_proj")).reshape(-1, 1, d.head_dim)
+        v = self.act(project("v_proj")).reshape(-1, 1, d.head_dim)
         k = apply_rope(k, cos, sin)
         self.rec(f"{name}.qkv.k", k)
         self.rec(f"{name}.qkv.v", v)
@@ -398,7 +426,7 @@ class Pi0Torch:
             k_all, v_all = k, v
         if kv_only:
             return x, (k, v)
-        q = self.act(self.linear(y, p + "self_attn.q_proj", bias=False)).reshape(-1, d.heads, d.head_dim)
+        q = self.act(project("q_proj")).reshape(-1, d.heads, d.head_dim)
         q = apply_rope(q, cos, sin)
         self.rec(f"{name}.qkv.q", q)
         a = self.attention(q, k_all, v_all, d.head_dim ** -0.5, mask).reshape(x.shape[0], -1)
@@ -406,10 +434,15 @@ class Pi0Torch:
         o = self.linear(a, p + "self_attn.o_proj", bias=False)
         x = self.add_residual(o, x, p + "self_attn.o_proj")
         self.rec(f"{name}.o_proj", x)
-        y = self.rms(x, sd[p + "post_attention_layernorm.weight"])
-        self.rec(f"{name}.norm2", y)
-        gate = self.linear(y, p + "mlp.gate_proj", bias=False)
-        up = self.linear(y, p + "mlp.up_proj", bias=False)
+        if self.folds(p + "self_attn.o_proj", p + "mlp.gate_proj"):
+            g2 = 1.0 + sd[p + "post_attention_layernorm.weight"].float()
+            gate = self.folded_linear(x, p + "mlp.gate_proj", g2)
+            up = self.folded_linear(x, p + "mlp.up_proj", g2)
+        else:
+            y = self.rms(x, sd[p + "post_attention_layernorm.weight"])
+            self.rec(f"{name}.norm2", y)
+            gate = self.linear(y, p + "mlp.gate_proj", bias=False)
+            up = self.linear(y, p + "mlp.up_proj", bias=False)
         if self.mode != "nvfp4":
             h = F.gelu(gate, approximate="tanh") * up
         elif self.bf16_site(p + "mlp.down_proj"):

@@ -219,11 +219,9 @@ __device__ __forceinline__ float gelu_sigmoid(float x) {
 // (Instantiated per epilogue kind: each accumulator drain carries only its own arithmetic and registers.)
 template <int EPI>
 __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const uint32_t (&raw)[32], int row, int col0,
-                                                    bool row_ok) {
+                                                    bool row_ok, float row_scale, float& sumsq) {
     float v[32];
     if (!row_ok) return;
-    // alpha, and for a projection of un-normalised rows the row's 1/rms (the norm weight is folded into B)
-    const float row_scale = g.row_factor ? g.alpha * __ldcg(g.row_factor + row) : g.alpha;
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(raw[i]) * row_scale;
     if constexpr (EPI == EPI_GEGLU_FP4) {
@@ -299,6 +297,38 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         float4* dst = reinterpret_cast<float4*>(static_cast<float*>(g.out) + static_cast<size_t>(row) * g.ldo + col0);
 #pragma unroll
         for (int i = 0; i < 8; i++) dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        return;
+    }
+    if constexpr (EPI == EPI_STREAM) {
+        // the residual stream in BF16 ...
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) w[i] = pack_bf16x2(v[2 * i], v[2 * i + 1]);
+        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(row) * g.ldo + col0);
+#pragma unroll
+        for (int i = 0; i < 4; i++) dst[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
+        // ... and, from the rounded values a norm stage would have read back, the sum of squares and the NVFP4 copy
+        uint32_t words[4];
+        uint32_t codes = 0;
+#pragma unroll
+        for (int half = 0; half < 2; half++) {
+            float h[16];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float2 f = unpack_bf16x2(w[8 * half + i]);
+                sumsq = __fmaf_rn(f.x, f.x, sumsq);
+                sumsq = __fmaf_rn(f.y, f.y, sumsq);
+                h[2 * i] = f.x * g.out_inv_gs;
+                h[2 * i + 1] = f.y * g.out_inv_gs;
+            }
+            uint32_t code;
+            uint2 bytes = quantize_block16(h, 0, code);
+            words[2 * half] = bytes.x;
+            words[2 * half + 1] = bytes.y;
+            codes |= code << (8 * half);
+        }
+        *reinterpret_cast<uint4*>(g.copy_fp4 + static_cast<size_t>(row) * g.ld_copy + (col0 >> 1)) = make_uint4(words[0], words[1], words[2], words[3]);
+        *reinterpret_cast<uint16_t*>(g.out_scales + scale_offset(row, col0 >> 4, g.out_blocks)) = static_cast<uint16_t>(codes);
         return;
     }
     if constexpr (EPI == EPI_BF16 || EPI == EPI_BF16_EXT) {
@@ -419,6 +449,20 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
         if (stamp && t == first && threadIdx.x == 128) stamp[6] = static_cast<long long>(global_ns());
         const uint32_t taddr = tmem + buf * 128u + (static_cast<uint32_t>(quarter * 32) << 16);
         const int chunks = g.block_n >> 5;
+        // alpha, times the row's 1/rms where the projection reads un-normalised rows (norm weight folded into B): given
+        // as a factor, or as the producer's per-tile sums of squares (complete: the operands behind this accumulator
+        // were only copied after the producer stage had finished)
+        float row_scale = g.alpha, sumsq = 0.f;
+        if (row_ok && g.row_factor) row_scale *= __ldcg(g.row_factor + row);
+        if (row_ok && g.row_sumsq) {
+            const float4* part = reinterpret_cast<const float4*>(g.row_sumsq + static_cast<size_t>(row) * g.sumsq_parts);
+            float total = 0.f;
+            for (int i = 0; i < (g.sumsq_parts >> 2); ++i) {         // fixed order: the same bits on every launch
+                const float4 q = __ldcg(part + i);
+                total += q.x; total += q.y; total += q.z; total += q.w;
+            }
+            row_scale *= rsqrtf(total * g.sumsq_inv_width + g.sumsq_eps);
+        }
         for (int c = 0; c < chunks; ++c) {
             uint32_t raw[32];
             tmem_ld32(taddr + c * 32, raw);
@@ -429,8 +473,9 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
             }
-            gemm_epilogue_chunk<EPI>(g, raw, row, n_tile * g.block_n + c * 32, row_ok);
+            gemm_epilogue_chunk<EPI>(g, raw, row, n_tile * g.block_n + c * 32, row_ok, row_scale, sumsq);
         }
+        if (EPI == EPI_STREAM && row_ok) g.sumsq_out[static_cast<size_t>(row) * g.n_tiles + n_tile] = sumsq;
         // each epilogue warp publishes its own 32 rows (a GEMM tile counts 4 units): no CTA barrier on this path
         if (stamp && t == first + count - 1 && threadIdx.x == 128) stamp[7] = static_cast<long long>(global_ns());
         fence_proxy_async_global();
@@ -461,6 +506,7 @@ __device__ __forceinline__ void gemm_instruction(const VmProgram& prog, Ctl* ctl
             case EPI_FP4: gemm_epilogue<EPI_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
             case EPI_GEGLU_FP4: gemm_epilogue<EPI_GEGLU_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
             case EPI_GEGLU_BF16: gemm_epilogue<EPI_GEGLU_BF16>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
+            case EPI_STREAM: gemm_epilogue<EPI_STREAM>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
             default: gemm_epilogue<EPI_QKV_ROPE>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
         }
         if (stamp && threadIdx.x == 128) stamp[2] = static_cast<long long>(global_ns());

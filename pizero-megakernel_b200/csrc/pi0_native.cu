@@ -520,6 +520,37 @@ extern "C" int configure_resident_fp4_qkv_rope(void* handle, void* out_q, int ld
     op->solo_dirty = true;
     return cudaSuccess;
 }
+// Residual-stream epilogue: BF16 rows (+bias +residual) and, from those rounded rows, an un-normalised NVFP4 copy plus the
+// per-tile sums of squares [M, N / tile width] that let the next projection apply RMSNorm as a row factor.
+extern "C" int configure_resident_fp4_stream(void* handle, const void* bias, const void* residual, void* out, void* copy_fp4,
+                                             void* copy_scales, float copy_global_scale, float* sumsq) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || !out || !copy_fp4 || !copy_scales || !sumsq || !std::isfinite(copy_global_scale) ||
+        copy_global_scale <= 0 || !aligned16(out) || !aligned16(copy_fp4) || !aligned16(bias) || !aligned16(residual) || !aligned16(sumsq))
+        return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    g.epilogue = EPI_STREAM;
+    g.round_before_residual = 0; g.gelu_cols = 0;
+    g.bias = bias; g.residual = residual; g.ldr = op->n;
+    g.out = out; g.ldo = op->n;
+    g.copy_fp4 = static_cast<uint8_t*>(copy_fp4); g.ld_copy = op->n / 2;
+    g.out_scales = static_cast<uint8_t*>(copy_scales);
+    g.out_blocks = op->n / 16;
+    g.out_inv_gs = 1.f / copy_global_scale;
+    g.sumsq_out = sumsq;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+// Consumer side: multiply every accumulator row by rsqrt(sum(sumsq[row, 0..parts)) / width + eps); parts a multiple of 4.
+extern "C" int configure_resident_fp4_row_rms(void* handle, const float* sumsq, int parts, int width, float eps) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || !sumsq || parts < 4 || parts % 4 || width < 1 || !std::isfinite(eps) || eps <= 0 || !aligned16(sumsq))
+        return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    g.row_sumsq = sumsq; g.sumsq_parts = parts; g.sumsq_inv_width = 1.f / static_cast<float>(width); g.sumsq_eps = eps;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
 extern "C" int configure_resident_fp4_rows(void* handle, int rows) {
     Op* op = as_op(handle);
     if (!op || op->desc.kind != OP_GEMM || rows < 1 || rows > op->m) return cudaErrorInvalidValue;

@@ -37,7 +37,8 @@ enum GemmEpilogue : int {
     EPI_GEGLU_FP4 = 3,  // gelu_tanh(gate)*up on interleaved columns -> NVFP4, width N/2
     EPI_QKV_ROPE = 4,   // BF16, RoPE on Q/K heads, K/V rows appended to the KV cache
     EPI_GEGLU_BF16 = 5, // bf16(gelu_tanh(bf16 gate)) * bf16(up) on interleaved columns -> BF16, width N/2
-    EPI_BF16_EXT = 6    // EPI_BF16 with the BF16 model's options: round before the residual add, GELU with a column limit
+    EPI_BF16_EXT = 6,   // EPI_BF16 with the BF16 model's options: round before the residual add, GELU with a column limit
+    EPI_STREAM = 7      // EPI_BF16 (residual stream) + an NVFP4 copy of the stored rows + per-tile sums of their squares
 };
 
 enum GemmOperands : int {
@@ -66,6 +67,16 @@ struct GemmParams {
     const float* row_factor;     // FP32 [M] multiplied into every accumulator row (1/rms of the input row) or null
     int round_before_residual;   // EPI_BF16: (+bias) round to BF16, then add the residual and round again
     int gelu_cols;               // EPI_BF16: > 0 applies GELU(tanh) to bf16(value) in columns < gelu_cols and stores 0 beyond
+    // EPI_STREAM: the BF16 rows are also quantised, un-normalised, to NVFP4 (out_scales / out_blocks / out_inv_gs describe
+    // the copy) and every tile stores the sum of squares of its part of each row, so that the projection that follows can
+    // apply the RMS normalisation as a row factor instead of running behind a norm stage
+    uint8_t* copy_fp4;           // packed codes [M_pad, ld_copy bytes]
+    int ld_copy;
+    float* sumsq_out;            // FP32 [M_pad, n_tiles]
+    // consumer side: row factor rsqrt(sum(row_sumsq[row, 0..sumsq_parts)) * sumsq_inv_width + sumsq_eps), times alpha
+    const float* row_sumsq;
+    int sumsq_parts;
+    float sumsq_inv_width, sumsq_eps;
     int rows;                    // logical rows (rows >= this are written as zero codes / skipped)
     void* out;                   // FP32 / BF16 / packed FP4
     int ldo;                     // elements (FP32/BF16) or bytes (FP4) per output row

@@ -118,7 +118,8 @@ class NativePi0:
 
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
                  library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=64,
-                 rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="spread"):
+                 rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="spread",
+                 fold_norms=True):
         config = getattr(model, "config", None)
         if config is None or getattr(config, "pi05", False):
             raise ValueError("This engine runs ordinary pi0 (not pi0.5)")
@@ -145,6 +146,7 @@ class NativePi0:
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self.keep_debug_outputs = keep_debug_outputs
         self.tile_weights = tile_weights
+        self.fold_norms = bool(fold_norms)
         if schedule not in ("spread", "linear"):
             raise ValueError("schedule must be 'spread' or 'linear'")
         self.schedule = schedule
@@ -254,11 +256,15 @@ class NativePi0:
         return handle
 
     def gemm(self, name, a: Activation, w, *, rows, sources, out=None, bias=None, residual=None,
-             out_act: Activation = None, out_precision=None, activation=0, act_cols=None, rope=None, block_n=128):
+             out_act: Activation = None, out_precision=None, activation=0, act_cols=None, rope=None, block_n=128,
+             stream=None, row_rms=None):
         """One projection stage.  ``w`` decides the operand format (``Fp4Matrix``: NVFP4 on ``a.fp4``; ``DenseMatrix``:
         BF16 on ``a.bf16``).  The result goes to ``out`` (BF16, + bias + residual), to the fused QKV destinations
         (``rope``), or to ``out_act`` in the format ``out_precision`` of the consuming site with ``activation``
-        0 none / 1 GELU / 2 GeGLU over interleaved gate/up columns (``act_cols``: logical width for the GELU)."""
+        0 none / 1 GELU / 2 GeGLU over interleaved gate/up columns (``act_cols``: logical width for the GELU).
+        ``stream=(copy, sumsq)``: besides ``out`` the stage writes the un-normalised NVFP4 copy of its rows into the
+        ``Activation`` ``copy`` and per-tile sums of squares into ``sumsq``; ``row_rms=(sumsq, parts, width, eps)``: the
+        stage reads such a copy and applies the RMS row factor itself (its weight carries the norm weight)."""
         h = C.c_void_p()
         dense = isinstance(w, DenseMatrix)
         src = a.bf16 if dense else a.fp4
@@ -302,12 +308,21 @@ class NativePi0:
                 if activation == 1:
                     _native.check(self.lib.configure_dense_gelu(h, act_cols if act_cols is not None else cols), name)
             outs = [StageOutput(name, "bf16", target, rows, cols // 2 if activation == 2 else cols)]
+        elif stream is not None:
+            copy, sumsq = stream
+            _native.check(self.lib.configure_resident_fp4_stream(h, _native.ptr(bias), _native.ptr(residual), out.data_ptr(),
+                                                                 copy.fp4.data.data_ptr(), copy.fp4.scales.data_ptr(),
+                                                                 copy.fp4.global_scale, sumsq.data_ptr()), name)
+            outs = [StageOutput(name, "bf16", out, rows, cols), StageOutput(name, "fp4", copy.fp4, rows, cols)]
         else:
             _native.check(self.lib.configure_resident_fp4_bf16(h, _native.ptr(bias), _native.ptr(residual), out.data_ptr()), name)
             if dense and residual is not None:
                 # the BF16 model rounds the projection before the residual add (OpenPI eager: x + o in BF16)
                 _native.check(self.lib.configure_dense_round_before_residual(h), name)
             outs = [StageOutput(name, "bf16", out, rows, cols)]
+        if row_rms is not None:
+            sumsq, parts, width, eps = row_rms
+            _native.check(self.lib.configure_resident_fp4_row_rms(h, sumsq.data_ptr(), parts, width, float(eps)), name)
         _native.check(self.lib.configure_resident_fp4_rows(h, rows), name)
         if block_n != 128:
             _native.check(self.lib.configure_resident_fp4_tile(h, block_n), name)
@@ -459,30 +474,47 @@ class NativePi0:
         return max(1, min(4, self.workers // groups))
 
     def _gemma_layer(self, name, site, prefix, i, x_in, x_mid, bufs, *, rows, s_x, extra_sources, cos, sin, cache, cache_base,
-                     attention_rows, mask_prefix, splits, kv_only, block_n, prefix_cache_stage=None):
+                     attention_rows, mask_prefix, splits, kv_only, block_n, prefix_cache_stage=None, streamed_in=None,
+                     next_site=None):
         """One Gemma decoder layer.  ``name`` labels the stages (``expert.<step>.<layer>``), ``site`` the weights
-        (``expert.<layer>``: one operand format for all Euler steps)."""
+        (``expert.<layer>``: one operand format for all Euler steps).
+
+        Folded norms (``fold_norms``, NVFP4 sites): an RMSNorm between two NVFP4 projections is not a stage.  The
+        producing projection (o_proj, down) also writes the NVFP4 copy of its un-normalised BF16 rows and per-tile
+        sums of their squares; the consuming projection (gate/up, the next layer's QKV), whose weight columns carry
+        ``1 + w`` of the norm, multiplies every accumulator row by ``rsqrt(mean square + eps)``.  ``streamed_in`` is
+        the ``(sumsq, parts)`` left by the previous layer's down projection (None: this layer runs its input norm);
+        ``next_site`` names the layer that follows, whose QKV projection decides whether this layer's down projection
+        streams.  Returns (last stage, KV stage, streamed_out)."""
         c, sd, lib = self.config, self.sd, self.lib
         p = f"{prefix}layers.{i}."
+        width = x_in.shape[1]
         H, hd = c.heads, c.head_dim
         a1, a2, a3, a4, qbuf = bufs
         p_qkv, p_o, p_gu, p_dn = [self.site(f"{site}.{n}") for n in ("qkv", "o_proj", "gate_up", "down")]
         tile = lambda precision: block_n if precision == "nvfp4" else 128       # BF16 sites use full-width tiles
-        g1 = self.cached(p + "g1", lambda: (1.0 + sd[p + "input_layernorm.weight"].float()).contiguous())
-        s_n1 = self.norm(f"{name}.norm1", x_in, a1.only(p_qkv), rows=rows, sources=[(s_x, SAME)] + extra_sources, kind="rms", gamma=g1, eps=c.rms_eps)
+        sums = lambda key, parts: self.cached((key, x_in.shape[0], parts), lambda: self.tensor((x_in.shape[0], parts), torch.float32))
+        gamma1 = lambda: (1.0 + sd[p + "input_layernorm.weight"].float()).contiguous()
+        if streamed_in is None:
+            g1 = self.cached(p + "g1", gamma1)
+            s_n1 = self.norm(f"{name}.norm1", x_in, a1.only(p_qkv), rows=rows, sources=[(s_x, SAME)] + extra_sources, kind="rms", gamma=g1, eps=c.rms_eps)
+            fold1 = None
+        else:
+            s_n1, fold1 = s_x, (streamed_in[0], streamed_in[1], width, c.rms_eps)
         def make_qkv():
             wk = self._interleave_heads(sd[p + "self_attn.k_proj.weight"])
             wv = sd[p + "self_attn.v_proj.weight"]
-            if kv_only:
-                return self.weight(torch.cat((wk, wv)), block_n=tile(p_qkv), precision=p_qkv)
-            return self.weight(torch.cat((self._interleave_heads(sd[p + "self_attn.q_proj.weight"]), wk, wv)), block_n=tile(p_qkv), precision=p_qkv)
+            w = torch.cat((wk, wv)) if kv_only else torch.cat((self._interleave_heads(sd[p + "self_attn.q_proj.weight"]), wk, wv))
+            if fold1 is not None:
+                w = w.float() * gamma1()[None, :]
+            return self.weight(w, block_n=tile(p_qkv), precision=p_qkv)
 
         wqkv = self.cached(p + "qkv", make_qkv)
         q_cols, q = (0, None) if kv_only else (H * hd, qbuf)
-        s_qkv = self.gemm(f"{name}.qkv", a1, wqkv, rows=rows, sources=[(s_n1, SAME)], block_n=tile(p_qkv),
+        s_qkv = self.gemm(f"{name}.qkv", a1, wqkv, rows=rows, sources=[(s_n1, SAME)], block_n=tile(p_qkv), row_rms=fold1,
                           rope=dict(q=q, cos=cos, sin=sin, cache_k=cache[0], cache_v=cache[1], q_cols=q_cols, cache_base=cache_base))
         if kv_only:
-            return s_qkv, s_qkv
+            return s_qkv, s_qkv, None
         attn_out = a2.bf16
         h = C.c_void_p()
         _native.check(lib.create_attention(C.byref(h), qbuf.data_ptr(), cache[0].data_ptr(), cache[1].data_ptr(), None, None, None,
@@ -502,19 +534,42 @@ class NativePi0:
             _native.check(lib.configure_attention_fused_merge(h, 1), f"{name}.attention")
         s_att = self.add(1, h, f"{name}.attention", att_sources, outs)
         wo = self.cached(p + "o", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=tile(p_o), precision=p_o))
-        s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=tile(p_o))
-        g2 = self.cached(p + "g2", lambda: (1.0 + sd[p + "post_attention_layernorm.weight"].float()).contiguous())
-        s_n2 = self.norm(f"{name}.norm2", x_mid, a3.only(p_gu), rows=rows, sources=[(s_o, SAME)], kind="rms", gamma=g2, eps=c.rms_eps)
+        # ---- attention output projection; the post-attention norm is folded when both neighbours are NVFP4 sites
+        fold2 = self.fold_norms and p_o == "nvfp4" and p_gu == "nvfp4"
+        gamma2 = lambda: (1.0 + sd[p + "post_attention_layernorm.weight"].float()).contiguous()
+        if fold2:
+            parts2 = width // tile(p_o)
+            ss2 = sums("sumsq2", parts2)
+            s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=tile(p_o),
+                            stream=(a3.require("nvfp4"), ss2))
+            s_n2, rms2 = s_o, (ss2, parts2, width, c.rms_eps)
+        else:
+            s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=tile(p_o))
+            g2 = self.cached(p + "g2", gamma2)
+            s_n2 = self.norm(f"{name}.norm2", x_mid, a3.only(p_gu), rows=rows, sources=[(s_o, SAME)], kind="rms", gamma=g2, eps=c.rms_eps)
+            rms2 = None
         def make_gate_up():
             gate, up = sd[p + "mlp.gate_proj.weight"], sd[p + "mlp.up_proj.weight"]
-            return self.weight(torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], gate.shape[1]), block_n=tile(p_gu), precision=p_gu)
+            w = torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], gate.shape[1])
+            if fold2:
+                w = w.float() * gamma2()[None, :]
+            return self.weight(w, block_n=tile(p_gu), precision=p_gu)
 
         wgu = self.cached(p + "gate_up", make_gate_up)
         s_gu = self.gemm(f"{name}.gate_up", a3, wgu, rows=rows, sources=[(s_n2, SAME)], out_act=a4.require(p_dn), out_precision=p_dn,
-                         activation=2, block_n=tile(p_gu))
+                         activation=2, block_n=tile(p_gu), row_rms=rms2)
         wd = self.cached(p + "down", lambda: self.weight(sd[p + "mlp.down_proj.weight"], block_n=tile(p_dn), precision=p_dn))
-        s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=tile(p_dn))
-        return s_dn, s_qkv
+        # ---- down projection; streams for the next layer's QKV when that reads NVFP4 too
+        streamed_out = None
+        if self.fold_norms and next_site is not None and p_dn == "nvfp4" and self.site(f"{next_site}.qkv") == "nvfp4":
+            parts1 = width // tile(p_dn)
+            ss1 = sums("sumsq1", parts1)
+            s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=tile(p_dn),
+                             stream=(a1.require("nvfp4"), ss1))
+            streamed_out = (ss1, parts1)
+        else:
+            s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=tile(p_dn))
+        return s_dn, s_qkv, streamed_out
 
     def _build(self):
         c, sd, lib = self.config, self.sd, self.lib
@@ -552,11 +607,13 @@ class NativePi0:
         bufs = (Activation(self, P_pad, c.width), Activation(self, P_pad, H * hd), Activation(self, P_pad, c.width),
                 Activation(self, P_pad, c.mlp), self.tensor((P_pad, H * hd)))
         bufs[1].bf16 = self.tensor((P_pad, H * hd))          # attention output rows (BF16), always written
-        cache_stage = []
+        cache_stage, streamed = [], None
         for i in range(c.prefix_layers):
-            s_x, s_kv = self._gemma_layer(f"prefix.{i}", f"prefix.{i}", LANGUAGE, i, x_a, x_b, bufs, rows=P, s_x=s_x, extra_sources=extra if i == 0 else [],
-                                          cos=cos_p, sin=sin_p, cache=self.caches[i], cache_base=0, attention_rows=P, mask_prefix=-1,
-                                          splits=self._prefix_splits(P), kv_only=(i == c.prefix_layers - 1), block_n=128)
+            s_x, s_kv, streamed = self._gemma_layer(
+                f"prefix.{i}", f"prefix.{i}", LANGUAGE, i, x_a, x_b, bufs, rows=P, s_x=s_x, extra_sources=extra if i == 0 else [],
+                cos=cos_p, sin=sin_p, cache=self.caches[i], cache_base=0, attention_rows=P, mask_prefix=-1,
+                splits=self._prefix_splits(P), kv_only=(i == c.prefix_layers - 1), block_n=128, streamed_in=streamed,
+                next_site=f"prefix.{i + 1}" if i + 1 < c.prefix_layers else None)
             cache_stage.append(s_kv)
             if i == 0:
                 self.mark("prefix.0.q", bufs[4]), self.mark("prefix.0.attention", bufs[1].bf16)
@@ -604,8 +661,9 @@ class NativePi0:
                                 sources=[(s_t1, ALL), (s_state, ALL)], out_bf16=True)
             _native.check(lib.configure_linear32_extra_row(self.handles[-1], state_emb.data_ptr(), xe_a.data_ptr()), "state row")
             self.mark(f"expert.{step}.input", xe_a)
+            streamed = None
             for i in range(c.expert_layers):
-                s_x, _ = self._expert_layer(step, i, xe_a, xe_b, ebufs, S, P, s_x, cos_s, sin_s, cache_stage[i])
+                s_x, _, streamed = self._expert_layer(step, i, xe_a, xe_b, ebufs, S, P, s_x, cos_s, sin_s, cache_stage[i], streamed)
                 self.mark(f"expert.{step}.{i}", xe_a)
             s_prev = self.linear32(f"expert.{step}.euler", xe_a, final_w, final_b, actions, rows=self.chunk_size, sources=[(s_x, ALL)],
                                    ldx=W, x_bf16=True, rms=True, euler=True, prev=None if first else actions,
@@ -631,11 +689,13 @@ class NativePi0:
         if self.verbose:
             print("NativePi0 static program:", self.plan, flush=True)
 
-    def _expert_layer(self, step, i, x_in, x_mid, bufs, S, P, s_x, cos, sin, prefix_cache_stage):
+    def _expert_layer(self, step, i, x_in, x_mid, bufs, S, P, s_x, cos, sin, prefix_cache_stage, streamed):
         """Every Euler step wires its own stages; the NVFP4 weights are shared through the keyed weight cache."""
+        last = i + 1 == self.config.expert_layers
         return self._gemma_layer(f"expert.{step}.{i}", f"expert.{i}", EXPERT, i, x_in, x_mid, bufs, rows=S, s_x=s_x, extra_sources=[], cos=cos, sin=sin,
                                  cache=self.caches[i], cache_base=P, attention_rows=P + S, mask_prefix=P, splits=self._expert_splits(P + S),
-                                 kv_only=False, block_n=self.expert_block_n, prefix_cache_stage=prefix_cache_stage)
+                                 kv_only=False, block_n=self.expert_block_n, prefix_cache_stage=prefix_cache_stage, streamed_in=streamed,
+                                 next_site=None if last else f"expert.{i + 1}")
 
     # ------------------------------------------------------------------------------------------ running
     def _check_inputs(self, images, state, noise, tokens):

@@ -99,6 +99,20 @@ def test_site_precisions(small_model, precision, policy):
         assert nrmse(out, eager) <= 1.3 * max(nrmse(emulation, eager), 0.05)
 
 
+def test_norm_stages_instead_of_folded_norms(small_model):
+    """``fold_norms=False`` keeps every RMSNorm as a stage of its own (normalised rows are quantised, plain weights):
+    more stages, and agreement with the oracle emulating that arithmetic."""
+    dims, cfg, sd = small_model
+    x = inputs(3, 50, 0, dims.vocab)
+    emulation = Pi0Torch(dims, sd, mode="nvfp4", fold_norms=False).sample_actions(*x)
+    with NativePi0(StateDictModel(cfg, sd), fold_norms=False) as plain, NativePi0(StateDictModel(cfg, sd)) as folded:
+        out = plain.forward(*x).clone()
+        assert plain.status()["code"] == 0
+        assert len(plain.stages) > len(folded.stages)
+        assert any(n.endswith("norm2") for n in plain.stage_names) and not any(n.endswith("norm2") for n in folded.stage_names)
+    assert nrmse(out, emulation) <= 0.1
+
+
 def test_partitioned_and_stage_range_launches_are_bit_exact(small_model):
     dims, cfg, sd = small_model
     x = inputs(3, 50, 0, dims.vocab)

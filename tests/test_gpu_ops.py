@@ -249,6 +249,46 @@ def test_gemma_mlp_block_at_full_shape():
                 np.testing.assert_array_equal(z, y)
 
 
+def test_residual_stream_epilogue_and_row_rms_consumer():
+    """A folded RMSNorm between two NVFP4 projections: the producer writes its BF16 rows, their un-normalised NVFP4 copy
+    and per-tile sums of squares; the consumer multiplies its accumulator rows by rsqrt(mean square + eps)."""
+    lib = _native.load()
+    rng = np.random.default_rng(97)
+    m, k, n, n2 = 256, 512, 1024, 384
+    a, w = rng.normal(size=(m, k)).astype(np.float32), rng.normal(scale=0.05, size=(n, k)).astype(np.float32)
+    w2 = rng.normal(scale=0.05, size=(n2, n)).astype(np.float32)
+    res = bf16(rng.normal(size=(m, n)))
+    pa, pw, pw2 = pack_nvfp4(a), pack_nvfp4(w, scale_policy="ceil"), pack_nvfp4(w2, scale_policy="ceil")
+    placeholder = pack_nvfp4(np.zeros((m, n), np.float32))
+    for block_n in (128, 64):
+        parts = n // block_n
+        with ResidentNVFP4(None, pa, pw, workers=16, output_dtype=torch.bfloat16, residual=res, block_n=block_n) as plain, \
+                ResidentNVFP4(None, pa, pw, workers=16, output_dtype=torch.bfloat16, residual=res, block_n=block_n) as producer:
+            want = plain.forward().clone()
+            copy = torch.zeros(m, n // 2, dtype=torch.uint8, device="cuda")
+            copy_scales = torch.zeros((m // 128) * (n // 64) * 512, dtype=torch.uint8, device="cuda")
+            sumsq = torch.full((m, parts), float("nan"), dtype=torch.float32, device="cuda")
+            _native.check(lib.configure_resident_fp4_stream(producer.handle, None, producer.residual.data_ptr(), producer.output.data_ptr(),
+                                                            copy.data_ptr(), copy_scales.data_ptr(), 0.5, sumsq.data_ptr()), "stream")
+            out = producer.forward()
+            torch.cuda.synchronize()
+            assert producer.status()["code"] == 0
+            assert torch.equal(out, want)                                   # the BF16 rows are those of the plain epilogue
+            ref = pack_nvfp4(out.float().cpu().numpy(), global_scale=0.5)   # the copy is the packer's image of those rows
+            np.testing.assert_array_equal(copy.cpu().numpy(), ref.data)
+            np.testing.assert_array_equal(unswizzle_scales(copy_scales.cpu().numpy(), m, n // 16), ref.scales)
+            tiles = out.float().reshape(m, parts, block_n).square().sum(-1)
+            assert relrms(sumsq.cpu().numpy(), tiles.cpu().numpy()) < 1e-6
+            with ResidentNVFP4(None, placeholder, pw2, workers=8, activation_buffers=(copy, copy_scales)) as raw, \
+                    ResidentNVFP4(None, placeholder, pw2, workers=8, activation_buffers=(copy, copy_scales)) as consumer:
+                base = raw.forward().clone() * 0.5                        # (the wrapper's alpha assumes tensor scale 1 for the bound copy)
+                _native.check(lib.configure_resident_fp4_row_rms(consumer.handle, sumsq.data_ptr(), parts, n, 1e-6), "row rms")
+                got = consumer.forward() * 0.5
+                factor = torch.rsqrt(out.float().square().mean(-1, keepdim=True) + 1e-6)
+                assert relrms((got).cpu().numpy(), (base * factor).cpu().numpy()) < 1e-5
+                assert lib.configure_resident_fp4_row_rms(consumer.handle, sumsq.data_ptr(), 6, n, 1e-6) == 1
+
+
 def test_gemm_qkv_rope_epilogue():
     lib = _native.load()
     rng = np.random.default_rng(71)
