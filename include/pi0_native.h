@@ -155,6 +155,15 @@ int configure_attention_cache(void* handle, const void* cache_k, const void* cac
 /* extension: also quantise the output rows to NVFP4 (head_dim 256 only). */
 int configure_attention_fp4_output(void* handle, void* out_fp4, void* scales, int ld_bytes, int out_blocks,
                                    float global_scale);
+/* extension: tile implementation.  -1 (default) picks the tcgen05 tiles (Q, K, V by TMA, S / P / O in tensor memory)
+ * whenever the geometry allows them - heads that occupy 128 or 256 elements in memory, at most 256 keys per tile (use KV
+ * splits beyond that), no fused NVFP4 output without splits - and the mma.sync tiles otherwise; 0 forces the mma.sync
+ * tiles, 1 the tcgen05 tiles (cudaErrorInvalidValue when the geometry does not allow them). */
+int configure_attention_path(void* handle, int path);
+/* extension: every head occupies `elements` (128 or 256) elements in q, k and v, zeros beyond head_dim (what a projection
+ * with configure_dense_head_pad writes); the row strides given at creation must cover heads * elements.  Lets 72-wide
+ * SigLIP heads run on the tcgen05 tiles.  Output rows stay head_dim wide. */
+int configure_attention_head_pad(void* handle, int elements);
 /* extension: handle of the merge stage owned by an attention handle with splits > 1 (NULL otherwise). */
 int attention_merge_handle(void* handle, void** merge);
 /* Development diagnostics of a split attention handle (splits >= 2), never part of a forward pass.

@@ -80,9 +80,10 @@ __device__ void attn_tile(const AttnParams& a, int tile, uint8_t* data, long lon
     const int k_begin = split * per, k_end = min(a.nk, k_begin + per);
     const int nchunks = (max(k_end - k_begin, 0) + kAttnChunk - 1) / kAttnChunk;
 
-    const __nv_bfloat16* qsrc = static_cast<const __nv_bfloat16*>(a.q) + static_cast<size_t>(batch) * a.q_batch_rows * a.ldq + head * a.head_dim;
-    const __nv_bfloat16* ksrc = static_cast<const __nv_bfloat16*>(a.k) + static_cast<size_t>(batch) * a.kv_batch_rows * a.ldkv + kvh * a.head_dim;
-    const __nv_bfloat16* vsrc = static_cast<const __nv_bfloat16*>(a.v) + static_cast<size_t>(batch) * a.kv_batch_rows * a.ldkv + kvh * a.head_dim;
+    const int head_stride = a.hd_pad > a.head_dim ? a.hd_pad : a.head_dim;       // elements from one head to the next in q / k / v
+    const __nv_bfloat16* qsrc = static_cast<const __nv_bfloat16*>(a.q) + static_cast<size_t>(batch) * a.q_batch_rows * a.ldq + head * head_stride;
+    const __nv_bfloat16* ksrc = static_cast<const __nv_bfloat16*>(a.k) + static_cast<size_t>(batch) * a.kv_batch_rows * a.ldkv + kvh * head_stride;
+    const __nv_bfloat16* vsrc = static_cast<const __nv_bfloat16*>(a.v) + static_cast<size_t>(batch) * a.kv_batch_rows * a.ldkv + kvh * head_stride;
 
     attn_load_rows<HD>(sQ, qsrc, a.ldq, kAttnQRows, q0, q_valid, a.head_dim);
     if (nchunks > 0) {
@@ -505,12 +506,21 @@ __device__ __forceinline__ void merge_instruction(const VmProgram& prog, Ctl* ct
 // resident on different SMs at the same time) meet on a per-group ticket counter that grows by `splits` per launch; once all partials of
 // the head are published, every tile merges its share of the query rows (row % splits == split), so the merge
 // costs neither a stage of its own nor a serial tail on one SM.
-__device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
-                                                 int stage_index, int first, int count, long long* stamp) {
+template <int HDP>
+__device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& a, int tile, uint8_t* data, uint32_t tmem,
+                             uint32_t uses, int stage, long long* stamp);
+
+__device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem, uint32_t& tc_tiles,
+                                                 const StageDesc& st, int stage_index, int first, int count, long long* stamp) {
     const AttnParams& a = st.p.attn;
     for (int t = first; t < first + count; ++t) {
         long long* stamp_t = t == first ? stamp : nullptr;
-        if (a.head_dim > 128) attn_tile<256>(a, t, data, stamp_t);
+        if (a.tc) {
+            const bool ok = a.hd_pad > 128 ? attn_tile_tc<256>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t)
+                                           : attn_tile_tc<128>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t);
+            tc_tiles++;
+            if (!ok) return;                                   // uniform: a wait gave up, the abort flag is set
+        } else if (a.head_dim > 128) attn_tile<256>(a, t, data, stamp_t);
         else attn_tile<80>(a, t, data, stamp_t);
         if (a.splits > 1 && a.fused_merge) {
             const int split = t % a.splits, group = t / a.splits;         // group: one head of one 128-query tile

@@ -87,6 +87,20 @@ int encode_tiled(CUtensorMap* map, const void* base, int total_rows, int box_row
     return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
+// BF16 matrix [rows, ld] with boxes of 64 columns (128 bytes, 128-byte swizzle) x box_rows rows: attention operands.
+int encode_bf16_rows(CUtensorMap* map, const void* base, size_t rows, int ld, int box_rows) {
+    EncodeTiled fn = encoder();
+    if (!fn) return cudaErrorNotSupported;
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(ld), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2u};
+    cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
 struct Program;
 
 struct Op {
@@ -105,6 +119,8 @@ struct Op {
     uint16_t* partial_o = nullptr;
     float* partial_ml = nullptr;
     size_t partial_bytes = 0, stat_bytes = 0;
+    CUtensorMap* attn_maps = nullptr;  // device: Q, K, V maps of the tensor-core path
+    int attn_path = -1;                // -1 choose by geometry, 0 mma.sync tiles, 1 tcgen05 tiles
     Program* solo = nullptr;           // lazily built one/two-stage program for stand-alone launches
     bool solo_dirty = true;
 };
@@ -327,6 +343,7 @@ void free_op(Op* op) {
     cudaFree(op->maps);
     cudaFree(op->partial_o);
     cudaFree(op->partial_ml);
+    cudaFree(op->attn_maps);
     op->magic = 0;
     delete op;
 }
@@ -798,7 +815,10 @@ extern "C" int configure_norm_layout(void* handle, int ld_in, int ld_out, int ou
 }
 
 // =====================================================================================================
-static void attention_geometry(Op* op) {
+// Tile geometry of an attention operator and the choice between the two tile implementations.  The tcgen05 tiles need
+// heads that occupy 128 or 256 elements in memory (hd_pad), at most 256 keys per tile (more keys: more KV splits) and,
+// without splits, no fused NVFP4 output; everything else runs on the mma.sync tiles.
+static int attention_geometry(Op* op) {
     AttnParams& a = op->desc.p.attn;
     const int qtiles = (a.nq + kAttnQRows - 1) / kAttnQRows;
     op->desc.tiles = a.batches * qtiles * a.heads * a.splits;
@@ -806,6 +826,28 @@ static void attention_geometry(Op* op) {
     op->desc.band_div = a.heads * a.splits;
     op->cost = std::max(64, ((a.nk / a.splits) * a.head_dim / 64 + 63) / 64 * 64);
     op->solo_dirty = true;
+    const int per = (a.nk + a.splits - 1) / a.splits;
+    const bool layout_ok = (a.hd_pad == 128 || a.hd_pad == 256) && a.hd_pad >= a.head_dim && a.head_dim % 8 == 0 &&
+                           a.ldq >= a.heads * a.hd_pad && a.ldkv >= a.kv_heads * a.hd_pad;
+    const bool eligible = layout_ok && per <= 256 && !(a.splits == 1 && a.out_fp4) && (a.splits == 1 || a.head_dim == a.hd_pad);
+    a.tc = op->attn_path == 0 ? 0 : eligible ? 1 : 0;
+    if (op->attn_path == 1 && !eligible) return cudaErrorInvalidValue;
+    if (!a.tc) return cudaSuccess;
+    a.q_box = std::min(128, (std::min(a.nq, 128) + 7) / 8 * 8);
+    a.k_box = std::min(256, (per + 15) / 16 * 16);
+    CUtensorMap host[3];
+    int e = encode_bf16_rows(&host[0], a.q, static_cast<size_t>(a.batches) * a.q_batch_rows, a.ldq, a.q_box);
+    if (!e) e = encode_bf16_rows(&host[1], a.k, static_cast<size_t>(a.batches) * a.kv_batch_rows, a.ldkv, a.k_box);
+    if (!e) e = encode_bf16_rows(&host[2], a.v, static_cast<size_t>(a.batches) * a.kv_batch_rows, a.ldkv, a.k_box);
+    if (e) return e;
+    if (!op->attn_maps) {
+        cudaError_t ce = cudaMalloc(&op->attn_maps, sizeof(host));
+        if (ce != cudaSuccess) return ce;
+    }
+    cudaError_t ce = cudaMemcpy(op->attn_maps, host, sizeof(host), cudaMemcpyHostToDevice);
+    if (ce != cudaSuccess) return ce;
+    a.tmap_q = op->attn_maps; a.tmap_k = op->attn_maps + 1; a.tmap_v = op->attn_maps + 2;
+    return cudaSuccess;
 }
 extern "C" int create_attention(void** handle, const void* q, const void* k, const void* v, const void* q_bias, const void* k_bias,
                                 const void* v_bias, const void* q_cos, const void* q_sin, const void* k_cos, const void* k_sin,
@@ -835,7 +877,9 @@ extern "C" int create_attention(void** handle, const void* q, const void* k, con
     a.prefix = prefix >= 0 ? prefix : -1;
     a.splits = 1;
     a.out_inv_gs = 1.f;
-    attention_geometry(op);
+    a.hd_pad = head_dim == 256 ? 256 : 0;           // other head sizes use the tensor-core tiles only in a padded layout
+    e = attention_geometry(op);
+    if (e) { free_op(op); return e; }
     *handle = op;
     return cudaSuccess;
 }
@@ -903,8 +947,7 @@ extern "C" int configure_attention_splits(void* handle, int splits) {
         g.out_fp4 = a.out_fp4; g.out_scales = a.out_scales; g.out_blocks = a.out_blocks; g.out_inv_gs = a.out_inv_gs; g.ld_fp4 = a.ld_fp4;
         op->merge = mg;
     }
-    attention_geometry(op);
-    return cudaSuccess;
+    return attention_geometry(op);
 }
 // Fill the split-KV scratch (partial rows and their softmax statistics) with 0xFF bytes - NaN patterns in both
 // formats - so a run that read a partial it had not written in the same launch would show it in its output.
@@ -967,8 +1010,7 @@ extern "C" int configure_attention_cache(void* handle, const void* cache_k, cons
     AttnParams& a = op->desc.p.attn;
     if (a.batches != 1 || a.kv_heads != 1) return cudaErrorInvalidValue;
     a.k = cache_k; a.v = cache_v; a.ldkv = a.head_dim; a.nk = rows; a.kv_batch_rows = rows;
-    attention_geometry(op);
-    return cudaSuccess;
+    return attention_geometry(op);
 }
 extern "C" int configure_attention_fp4_output(void* handle, void* out_fp4, void* scales, int ld_bytes, int out_blocks, float global_scale) {
     Op* op = as_op(handle);
@@ -981,8 +1023,29 @@ extern "C" int configure_attention_fp4_output(void* handle, void* out_fp4, void*
         MergeParams& g = op->merge->desc.p.merge;
         g.out_fp4 = a.out_fp4; g.out_scales = a.out_scales; g.ld_fp4 = ld_bytes; g.out_blocks = out_blocks; g.out_inv_gs = a.out_inv_gs;
     }
-    op->solo_dirty = true;
-    return cudaSuccess;
+    return attention_geometry(op);
+}
+// extension: choose the tile implementation: -1 by geometry (default), 0 mma.sync tiles, 1 tcgen05 tiles (an error when the
+// geometry does not allow them).
+extern "C" int configure_attention_path(void* handle, int path) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN || path < -1 || path > 1) return cudaErrorInvalidValue;
+    const int before = op->attn_path;
+    op->attn_path = path;
+    const int e = attention_geometry(op);
+    if (e) { op->attn_path = before; attention_geometry(op); }
+    return e;
+}
+// extension: declare that every head occupies `elements` (128 or 256) elements in q, k and v, the columns beyond
+// head_dim being zeros (as a projection with the head-padded epilogue writes them).  The row strides given at creation
+// must cover heads * elements.  Output rows stay head_dim wide.
+extern "C" int configure_attention_head_pad(void* handle, int elements) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN || (elements != 128 && elements != 256) || elements < op->desc.p.attn.head_dim) return cudaErrorInvalidValue;
+    AttnParams& a = op->desc.p.attn;
+    if (a.ldq < a.heads * elements || a.ldkv < a.kv_heads * elements) return cudaErrorInvalidValue;
+    a.hd_pad = elements;
+    return attention_geometry(op);
 }
 extern "C" int attention_merge_handle(void* handle, void** merge) {
     Op* op = as_op(handle);

@@ -39,6 +39,7 @@ struct Ctl {
     uint64_t acc_empty[2];
     uint64_t ready[kRing];       // slot filled (32 asynchronous-copy arrivals of the prefetch warp)
     uint64_t release[kRing];     // slot no longer read (one arrival per warp)
+    uint64_t attn_bar[4];        // tensor-core attention: Q+K landed, S complete, V landed, O complete (one use each per tile)
     uint64_t gather;             // all warps have reached a CTA-wide operator (one arrival per warp)
     uint64_t done;               // all warps have left the instruction loop
     uint32_t tmem_base;

@@ -6,7 +6,7 @@
 // wait on a shared-memory barrier, read the descriptor, poll the (precomputed) producer counters in parallel and
 // start.  A slot is recycled once all eight warps have released it.
 #pragma once
-#include "op_attention.cuh"
+#include "op_attention_tc.cuh"
 #include "op_gemm.cuh"
 #include "op_norm.cuh"
 #include "op_small.cuh"
@@ -65,6 +65,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
             mbar_init(&ctl->ready[r], 32);         // every lane of the prefetch warp
             mbar_init(&ctl->release[r], kThreads / 32);
         }
+        for (int b = 0; b < 4; b++) mbar_init(&ctl->attn_bar[b], 1);
         mbar_init(&ctl->gather, kThreads / 32);
         mbar_init(&ctl->done, kThreads / 32);
         ctl->abort = 0;
@@ -99,6 +100,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
 
     PipeState ps;
     uint32_t gathers = 0;        // CTA-wide operators executed so far (phase of the gather barrier)
+    uint32_t tc_tiles = 0;       // tensor-core attention tiles executed so far (phase of their barriers)
     for (uint32_t seq = 0;; ++seq) {
         if (warp == kPrefetchWarp) {
             if (!prefetch_slot(prog, ctl, stream, seq + kAhead, ip0 + seq + kAhead, pending)) break;
@@ -144,7 +146,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
             if (!cta_wait_sources(prog, ctl, st, ins.y, ins.z, ins.w, stamp)) break;
             switch (st.kind) {
                 case OP_NORM: norm_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
-                case OP_ATTN: attn_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w, stamp); break;
+                case OP_ATTN: attn_instruction(prog, ctl, data, tmem, tc_tiles, st, ins.y, ins.z, ins.w, stamp); break;
                 case OP_MERGE: merge_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
                 case OP_PATCH: patch_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
                 case OP_EMBED: embed_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;

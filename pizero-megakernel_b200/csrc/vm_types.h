@@ -141,6 +141,13 @@ struct AttnParams {
     // by `splits` per launch and are reset with them); 0 / null selects the separate OP_MERGE stage
     unsigned int* tickets;
     int fused_merge;
+    // Tensor-core path (tcgen05, operands by TMA): chosen by the host when the geometry allows it
+    int tc;                      // 0: mma.sync tiles, 1: tcgen05 tiles
+    int hd_pad;                  // elements one head occupies in q / k / v (128 or 256; >= head_dim, the rest zeros)
+    int q_box, k_box;            // rows per TMA box of Q (<= 128) and of K / V (keys per tile rounded up to 16, <= 256)
+    const void* tmap_q;          // CUtensorMaps in global memory: BF16 [rows, ld] with boxes of 64 columns
+    const void* tmap_k;
+    const void* tmap_v;
 };
 
 struct MergeParams {

@@ -82,6 +82,8 @@ _SIGNATURES = {
     "configure_attention_cache": [_P, _P, _P, _I, _I],
     "configure_attention_fused_merge": [_P, _I],
     "configure_attention_fp4_output": [_P, _P, _P, _I, _I, _F],
+    "configure_attention_path": [_P, _I],
+    "configure_attention_head_pad": [_P, _I],
     "attention_merge_handle": [_P, C.POINTER(_P)],
     "attention_poison_partials": [_P, _P],
     "attention_split_diagnostics": [_P, _P, _I, C.POINTER(C.c_uint)],

@@ -4,6 +4,11 @@ Constructor-compatible with the reference ``ResidentAttention`` (``native_pi0/at
 the pi0 cases: BF16 tensors ``q [B, Nq, H, d]``, ``k, v [B, Nk, Hk, d]`` (views with a common row stride
 are accepted), optional pi0 suffix mask (``prefix``), optional KV cache, optional split-KV with merge.
 Biases, in-kernel RoPE tables and boolean masks are rejected: RoPE is fused into the QKV projection.
+
+Two tile implementations sit behind the one operator: tcgen05 tiles (operands by TMA, scores, probabilities and
+output in tensor memory) where the geometry allows them - heads that occupy 128 or 256 elements in memory and at most
+256 keys per tile - and mma.sync tiles otherwise; ``path`` forces one of them.  ``head_dim`` smaller than the last
+tensor dimension declares a padded layout (e.g. SigLIP's 72-wide heads stored 128 apart, zeros behind them).
 """
 import ctypes
 
@@ -15,17 +20,20 @@ from native_pi0 import _native
 class ResidentAttention:
     def __init__(self, library, q, k, v, *, workers=16, scale=None, prefix=None, splits=1, kv_cache=None,
                  cached_prefix_rows=0, output=None, q_bias=None, k_bias=None, v_bias=None, q_rope=None,
-                 k_rope=None, mask=None, fp4_output=None, fused_merge=False):
+                 k_rope=None, mask=None, fp4_output=None, fused_merge=False, path=None, head_dim=None):
         if any(x is not None for x in (q_bias, k_bias, v_bias, q_rope, k_rope, mask)):
             raise ValueError("Biases, RoPE tables and boolean masks are fused elsewhere in the NVFP4 engine")
         for t in (q, k, v):
             if t.dtype != torch.bfloat16 or t.ndim != 4 or not t.is_cuda or t.stride(-1) != 1:
                 raise ValueError("q, k, v must be CUDA BF16 [batch, rows, heads, dim] with contiguous dim")
-        b, nq, h, d = q.shape
+        b, nq, h, stored = q.shape
         bk, nk, hk, dk = k.shape
-        if v.shape != k.shape or bk != b or dk != d or h % hk or d not in (72, 256):
+        d = stored if head_dim is None else int(head_dim)
+        if v.shape != k.shape or bk != b or dk != stored or h % hk or d not in (72, 256) or d > stored or (d < stored and stored not in (128, 256)):
             raise ValueError("Unsupported attention geometry (head_dim 72 or 256, heads a multiple of kv heads)")
-        if q.stride(2) != d or k.stride(2) != d or v.stride(2) != d or k.stride(1) != v.stride(1):
+        if path not in (None, "mma.sync", "tcgen05"):
+            raise ValueError("path is None, 'mma.sync' or 'tcgen05'")
+        if q.stride(2) != stored or k.stride(2) != stored or v.stride(2) != stored or k.stride(1) != v.stride(1):
             raise ValueError("Heads must be adjacent and K/V must share a row stride")
         if b > 1 and (q.stride(0) != nq * q.stride(1) or k.stride(0) != nk * k.stride(1) or v.stride(0) != nk * v.stride(1)):
             raise ValueError("Batches must be stacked rows")
@@ -46,6 +54,8 @@ class ResidentAttention:
                 output.data_ptr(), None, b, nq, nk, h, hk, d, q.stride(1), k.stride(1), output.stride(1), 0, workers,
                 -1 if prefix is None else int(prefix), self.scale), "Native attention setup")
             try:
+                if d < stored:
+                    _native.check(self.library.configure_attention_head_pad(self.handle, stored), "Native attention head padding")
                 if kv_cache is not None:
                     ck, cv = kv_cache
                     rows = cached_prefix_rows + nk
@@ -60,6 +70,8 @@ class ResidentAttention:
                     _native.check(self.library.configure_attention_splits(self.handle, int(splits)), "Native attention splits")
                     if fused_merge:
                         _native.check(self.library.configure_attention_fused_merge(self.handle, 1), "Native attention fused merge")
+                if path is not None:
+                    _native.check(self.library.configure_attention_path(self.handle, int(path == "tcgen05")), "Native attention path")
             except Exception:
                 self.close()
                 raise

@@ -427,6 +427,75 @@ def test_attention(b, nq, nk, h, hk, hd, prefix, splits):
         np.testing.assert_array_equal(other[:, 0], got[:, 0])
 
 
+TC_ATTENTION_CASES = [
+    # batches, nq, nk, heads, kv_heads, head_dim, stored, prefix, splits
+    (1, 768, 768, 8, 1, 256, 256, None, 3),      # Gemma prefix: 256 keys per tile
+    (1, 784, 784, 8, 1, 256, 256, None, 4),      # with a 16-token prompt: 196 keys per tile, ragged last query tile
+    (1, 200, 200, 4, 2, 256, 256, None, 1),      # GQA, one tile of keys, ragged rows
+    (1, 51, 819, 8, 1, 256, 256, 768, 8),        # action suffix over the cache, state-row mask, 103 keys per tile
+    (1, 51, 819, 8, 1, 256, 256, 768, 13),
+    (1, 300, 500, 4, 1, 256, 256, None, 3),
+    (1, 1, 5, 1, 1, 256, 256, 2, 1),
+    (3, 256, 256, 16, 16, 72, 128, None, 1),     # SigLIP heads stored 128 apart
+    (2, 40, 100, 4, 4, 72, 128, None, 1),
+]
+
+
+@pytest.mark.parametrize("b,nq,nk,h,hk,hd,stored,prefix,splits", TC_ATTENTION_CASES)
+def test_attention_tensor_core_tiles(b, nq, nk, h, hk, hd, stored, prefix, splits):
+    """The tcgen05 tiles (TMA operands, S / P / O in tensor memory) against the FP32 oracle and against the mma.sync
+    tiles of the same operator."""
+    torch.manual_seed(1000 + nq + nk + splits)
+    def heads(rows, count):
+        t = torch.zeros(b, rows, count, stored)
+        t[..., :hd] = torch.randn(b, rows, count, hd)
+        return t.bfloat16().cuda()
+    q, k, v = heads(nq, h), heads(nk, hk), heads(nk, hk)
+    want = oracle_ops.attention(q[..., :hd], k[..., :hd], v[..., :hd], hd ** -0.5, prefix).numpy()
+    kw = dict(workers=148, prefix=prefix, splits=splits, head_dim=hd)
+    with ResidentAttention(None, q, k, v, path="tcgen05", **kw) as op:
+        for launch in range(2):
+            op.output.fill_(float("nan"))
+            if splits > 1:
+                op.poison_partials()
+            got = op.forward().float().cpu().numpy()
+            assert op.status()["code"] == 0
+            assert np.isfinite(got).all()
+            assert relrms(got, want) <= 1e-2
+            if launch:
+                np.testing.assert_array_equal(got, first)
+            first = got
+    with ResidentAttention(None, q, k, v, path="mma.sync", **kw) as op:
+        legacy = op.forward().float().cpu().numpy()
+    assert relrms(got, legacy) <= 5e-3                      # two evaluations in BF16 probabilities: rounding apart
+    tiles = b * ((nq + 127) // 128) * h * splits
+    if splits > 1 and tiles <= 148:                         # (the tiles of a head meet inside the stage: one worker each)
+        with ResidentAttention(None, q, k, v, path="tcgen05", fused_merge=True, **kw) as op:
+            fused = op.forward().float().cpu().numpy()
+            assert op.status()["code"] == 0
+        np.testing.assert_array_equal(fused, got)           # the merge inside the stage: same bits as the merge stage
+    if prefix is not None and nq > 1:
+        k2, v2 = k.clone(), v.clone()
+        k2[:, prefix + 1:] = 9.0
+        v2[:, prefix + 1:] = -9.0
+        with ResidentAttention(None, q, k2, v2, path="tcgen05", **kw) as op:
+            other = op.forward().float().cpu().numpy()
+        np.testing.assert_array_equal(other[:, 0], got[:, 0])
+
+
+def test_attention_path_selection():
+    q = torch.randn(1, 64, 2, 256).bfloat16().cuda()
+    k = torch.randn(1, 600, 1, 256).bfloat16().cuda()
+    with pytest.raises(RuntimeError):
+        ResidentAttention(None, q, k, k, path="tcgen05")    # 600 keys in one tile: needs KV splits
+    with ResidentAttention(None, q, k, k, path="tcgen05", splits=3) as op:
+        op.forward()
+        assert op.status()["code"] == 0
+    small = torch.randn(1, 8, 2, 72).bfloat16().cuda()
+    with pytest.raises(RuntimeError):
+        ResidentAttention(None, small, small, small, path="tcgen05")     # 72-wide heads need the padded layout
+
+
 def test_attention_fused_fp4_output():
     torch.manual_seed(5)
     nq, nk, h, hd = 100, 300, 8, 256
