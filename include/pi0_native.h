@@ -102,6 +102,11 @@ int configure_dense_skinny(void* handle);
  * the cache are then in that same pair order, which attention over them does not see. */
 int configure_dense_qkv_rope(void* handle, const void* cos, const void* sin, void* cache_k, void* cache_v, int logical_rows,
                              int key_offset, int cache_base);
+/* extension: head-padded BF16 output - column c is stored at (c / from) * to + c % from of a row of ld elements, so
+ * heads of `from` columns start `to` columns apart (from, to multiples of 8); the gaps are never written: zero the
+ * buffer once and they stay zero.  Gives 72-wide SigLIP heads the 128-element pitch the tcgen05 attention tiles read
+ * (configure_attention_head_pad).  No residual. */
+int configure_dense_head_pad(void* handle, int from, int to, int ld);
 /* extension: logical row count and output tile width (128 or 64) of a dense projection.  The NVFP4 GEMM's
  * configure_resident_fp4_{bf16, quantized, qkv_rope, rows, tile} calls accept dense handles too (a dense projection
  * may emit NVFP4 for an NVFP4 consumer); configure_resident_fp4_weight_layout does not. */
@@ -184,7 +189,7 @@ int attention_split_diagnostics(void* handle, unsigned long long* counts, int ca
  * q BF16 [nq, heads*256] (row stride ldq), k and v BF16 [nk, kv_heads*256] (row stride ldkv), out BF16 [nq, heads*256]
  * (row stride out_ld); prefix >= 0 selects the pi0 suffix mask, < 0 none.  Limits (cudaErrorInvalidValue beyond them):
  * head_dim == 256, nq <= 128, splits >= 1, heads * splits <= 64; all four pointers 16-byte aligned.  Same arithmetic as
- * create_attention + configure_attention_splits; with splits == 1 every head is one tile that writes `out` directly
+ * create_attention + configure_attention_splits on the mma.sync tiles (configure_attention_path 0); with splits == 1 every head is one tile that writes `out` directly
  * and the array is not touched.
  * The first call on a device looks up the array's device address and raises the kernel's shared-memory limit; make
  * that first call before any stream capture begins.  All calls on a GPU share the one array, which keeps the last

@@ -336,6 +336,18 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
 #pragma unroll
             for (int i = 0; i < 32; i++) v[i] = col0 + i < g.gelu_cols ? gelu_tanh(bf16_round(v[i])) : 0.f;
         }
+        if (EPI == EPI_BF16_EXT && g.pad_from > 0) {
+            // heads written pad_to columns apart (8-column pieces never straddle a head: pad_from is a multiple of 8)
+            __nv_bfloat16* base = static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(row) * g.ldo;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const int c = col0 + 8 * i, head = c / g.pad_from;
+                *reinterpret_cast<uint4*>(base + head * g.pad_to + (c - head * g.pad_from)) =
+                    make_uint4(pack_bf16x2(v[8 * i], v[8 * i + 1]), pack_bf16x2(v[8 * i + 2], v[8 * i + 3]),
+                               pack_bf16x2(v[8 * i + 4], v[8 * i + 5]), pack_bf16x2(v[8 * i + 6], v[8 * i + 7]));
+            }
+            return;
+        }
         uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(g.out) + static_cast<size_t>(row) * g.ldo + col0);
 #pragma unroll
         for (int i = 0; i < 4; i++)

@@ -496,7 +496,7 @@ extern "C" int configure_resident_fp4_bf16(void* handle, const void* bias, const
     if (!op || op->desc.kind != OP_GEMM || !out) return cudaErrorInvalidValue;
     GemmParams& g = op->desc.p.gemm;
     g.epilogue = EPI_BF16;
-    g.round_before_residual = 0; g.gelu_cols = 0;
+    g.round_before_residual = 0; g.gelu_cols = 0; g.pad_from = 0; g.pad_to = 0;
     g.bias = bias; g.residual = residual; g.ldr = op->n;
     g.out = out; g.ldo = op->n;
     op->solo_dirty = true;
@@ -722,6 +722,20 @@ extern "C" int configure_dense_qkv_rope(void* handle, const void* cos, const voi
     g.cache_k = cache_k; g.cache_v = cache_v;
     g.q_cols = key_offset; g.head_dim = 256; g.cache_base = cache_base;
     g.rows = std::min(g.rows, logical_rows);
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+// extension: store the BF16 output with every group of `from` columns (a head) starting `to` columns after the previous
+// one, in rows of `ld` elements; the columns between the heads are not written (keep them zero).  No residual.
+extern "C" int configure_dense_head_pad(void* handle, int from, int to, int ld) {
+    Op* op = dense_bf16(handle);
+    if (!op) return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    if ((g.epilogue != EPI_BF16 && g.epilogue != EPI_BF16_EXT) || g.residual || from < 8 || from % 8 || to < from || to % 8 ||
+        ld < (op->n + from - 1) / from * to || ld % 8)
+        return cudaErrorInvalidValue;
+    g.epilogue = EPI_BF16_EXT;
+    g.pad_from = from; g.pad_to = to; g.ldo = ld;
     op->solo_dirty = true;
     return cudaSuccess;
 }

@@ -67,6 +67,8 @@ struct GemmParams {
     const float* row_factor;     // FP32 [M] multiplied into every accumulator row (1/rms of the input row) or null
     int round_before_residual;   // EPI_BF16: (+bias) round to BF16, then add the residual and round again
     int gelu_cols;               // EPI_BF16: > 0 applies GELU(tanh) to bf16(value) in columns < gelu_cols and stores 0 beyond
+    int pad_from, pad_to;        // EPI_BF16_EXT: > 0 stores column c at (c / pad_from) * pad_to + c % pad_from (heads of pad_from
+                                 // columns written pad_to apart, the gap left untouched); pad_from a multiple of 8
     // EPI_STREAM: the BF16 rows are also quantised, un-normalised, to NVFP4 (out_scales / out_blocks / out_inv_gs describe
     // the copy) and every tile stores the sum of squares of its part of each row, so that the projection that follows can
     // apply the RMS normalisation as a row factor instead of running behind a norm stage

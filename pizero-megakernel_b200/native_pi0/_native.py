@@ -66,6 +66,7 @@ _SIGNATURES = {
     "configure_dense_rms_factor": [_P, _P],
     "configure_dense_skinny": [_P],
     "configure_dense_qkv_rope": [_P] * 5 + [_I] * 3,
+    "configure_dense_head_pad": [_P, _I, _I, _I],
     "configure_dense_rows": [_P, _I],
     "configure_dense_tile": [_P, _I],
     "create_norm": [C.POINTER(_P)] + [_P] * 8 + [_I] * 9 + [_F] * 2,

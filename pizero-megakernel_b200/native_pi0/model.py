@@ -89,12 +89,14 @@ class Activation:
 class StageOutput:
     """What one stage writes, for validators that compare or replace a stage's result: ``name`` is the stage name
     (suffixed ``.q`` / ``.k`` / ``.v`` for the three parts of a fused QKV projection), ``kind`` one of ``bf16``,
-    ``f32``, ``fp4`` (an ``Fp4Matrix``), ``q_rope`` (BF16 query heads, rotation partners adjacent), ``k_cache`` (the
+    ``f32``, ``fp4`` (an ``Fp4Matrix``), ``sumsq`` (FP32 sums of squares of the BF16 rows per output tile, ``head`` =
+    (tile width,)), ``q_rope`` (BF16 query heads, rotation partners adjacent), ``k_cache`` (the
     same layout, rows ``base..base+rows`` of the layer's key cache) and ``v_cache``; ``rows`` x ``cols`` is the
     logical extent inside the padded buffer."""
 
-    def __init__(self, name, kind, buffer, rows, cols, base=0):
+    def __init__(self, name, kind, buffer, rows, cols, base=0, head=None):
         self.name, self.kind, self.buffer, self.rows, self.cols, self.base = name, kind, buffer, rows, cols, base
+        self.head = head            # kind "bf16": (head width, pitch) when heads are stored apart with zeros between them
 
 
 class NativePi0:
@@ -119,7 +121,7 @@ class NativePi0:
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
                  library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=64,
                  rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="spread",
-                 fold_norms=True):
+                 fold_norms=True, attention_path=None):
         config = getattr(model, "config", None)
         if config is None or getattr(config, "pi05", False):
             raise ValueError("This engine runs ordinary pi0 (not pi0.5)")
@@ -147,6 +149,9 @@ class NativePi0:
         self.keep_debug_outputs = keep_debug_outputs
         self.tile_weights = tile_weights
         self.fold_norms = bool(fold_norms)
+        if attention_path not in (None, "mma.sync", "tcgen05"):
+            raise ValueError("attention_path is None (by geometry), 'mma.sync' or 'tcgen05'")
+        self.attention_path = attention_path
         if schedule not in ("spread", "linear"):
             raise ValueError("schedule must be 'spread' or 'linear'")
         self.schedule = schedule
@@ -257,7 +262,7 @@ class NativePi0:
 
     def gemm(self, name, a: Activation, w, *, rows, sources, out=None, bias=None, residual=None,
              out_act: Activation = None, out_precision=None, activation=0, act_cols=None, rope=None, block_n=128,
-             stream=None, row_rms=None):
+             stream=None, row_rms=None, head_pad=None):
         """One projection stage.  ``w`` decides the operand format (``Fp4Matrix``: NVFP4 on ``a.fp4``; ``DenseMatrix``:
         BF16 on ``a.bf16``).  The result goes to ``out`` (BF16, + bias + residual), to the fused QKV destinations
         (``rope``), or to ``out_act`` in the format ``out_precision`` of the consuming site with ``activation``
@@ -313,13 +318,16 @@ class NativePi0:
             _native.check(self.lib.configure_resident_fp4_stream(h, _native.ptr(bias), _native.ptr(residual), out.data_ptr(),
                                                                  copy.fp4.data.data_ptr(), copy.fp4.scales.data_ptr(),
                                                                  copy.fp4.global_scale, sumsq.data_ptr()), name)
-            outs = [StageOutput(name, "bf16", out, rows, cols), StageOutput(name, "fp4", copy.fp4, rows, cols)]
+            outs = [StageOutput(name, "bf16", out, rows, cols), StageOutput(name, "fp4", copy.fp4, rows, cols),
+                    StageOutput(name, "sumsq", sumsq, rows, sumsq.shape[1], head=(block_n,))]
         else:
             _native.check(self.lib.configure_resident_fp4_bf16(h, _native.ptr(bias), _native.ptr(residual), out.data_ptr()), name)
             if dense and residual is not None:
                 # the BF16 model rounds the projection before the residual add (OpenPI eager: x + o in BF16)
                 _native.check(self.lib.configure_dense_round_before_residual(h), name)
-            outs = [StageOutput(name, "bf16", out, rows, cols)]
+            if head_pad is not None:
+                _native.check(self.lib.configure_dense_head_pad(h, head_pad[0], head_pad[1], out.stride(0)), name)
+            outs = [StageOutput(name, "bf16", out, rows, cols, head=head_pad)]
         if row_rms is not None:
             sumsq, parts, width, eps = row_rms
             _native.check(self.lib.configure_resident_fp4_row_rms(h, sumsq.data_ptr(), parts, width, float(eps)), name)
@@ -407,7 +415,12 @@ class NativePi0:
         self.mark("patch", xa)
         mlp_pad = padded(c.vision_mlp, 128)
         a_ln, a_att, a_ln2, a_h = Activation(self, M, W), Activation(self, M, W), Activation(self, M, W), Activation(self, M, mlp_pad)
-        qkv = [self.tensor((M, 3 * W)), self.tensor((M, 3 * W))]
+        # Q | K | V with every 72-wide head on a 128-element pitch (zeros between): full 128-byte chunks for the TMA boxes of
+        # the tensor-core attention tiles; with the mma.sync tiles the heads are adjacent
+        padded_heads = self.attention_path != "mma.sync"
+        pitch = 128 if padded_heads else hd
+        WP = c.vision_heads * pitch
+        qkv = [self.tensor((M, 3 * WP)), self.tensor((M, 3 * WP))]
         a_att.bf16 = self.tensor((M, W))                    # the attention stage always writes BF16 rows
         att = a_att.bf16
         for i in range(c.vision_layers):
@@ -427,13 +440,17 @@ class NativePi0:
             self.buffers.extend((g1, b1, g2, b2, bqkv, bo, bias1, bias2))
             buf = qkv[i & 1]
             s_ln = self.norm(f"vision.{i}.ln1", xa, a_ln.only(p_qkv), rows=M, sources=[(s_x, SAME)], kind="layer", gamma=g1, beta=b1, eps=c.ln_eps)
-            s_qkv = self.gemm(f"vision.{i}.qkv", a_ln, wqkv, rows=M, sources=[(s_ln, SAME)], out=buf, bias=bqkv)
+            s_qkv = self.gemm(f"vision.{i}.qkv", a_ln, wqkv, rows=M, sources=[(s_ln, SAME)], out=buf, bias=bqkv,
+                              head_pad=(hd, pitch) if padded_heads else None)
             h = C.c_void_p()
-            q, k, v = buf[:, :W], buf[:, W:2 * W], buf[:, 2 * W:]
+            q, k, v = buf[:, :WP], buf[:, WP:2 * WP], buf[:, 2 * WP:]
             _native.check(lib.create_attention(C.byref(h), q.data_ptr(), k.data_ptr(), v.data_ptr(), None, None, None, None, None,
                                                None, None, att.data_ptr(), None, V, 256, 256, c.vision_heads, c.vision_heads, hd,
-                                               3 * W, 3 * W, W, 0, self.workers, -1, float(hd ** -0.5)), "vision attention")
+                                               3 * WP, 3 * WP, W, 0, self.workers, -1, float(hd ** -0.5)), "vision attention")
             self._own(h)
+            if padded_heads:
+                _native.check(lib.configure_attention_head_pad(h, pitch), "vision attention")
+            self._attention_path(h, "vision attention")
             s_att = self.add(1, h, f"vision.{i}.attention", [(s_qkv, ALL)], [StageOutput(f"vision.{i}.attention", "bf16", att, M, W)])
             if p_out == "nvfp4":
                 # the 72-wide heads do not quantise inside the attention stage: a quantiser stage of its own
@@ -466,12 +483,22 @@ class NativePi0:
         return max(1, min(16, (self.workers - qkv_tiles) // c.heads, keys // 32))
 
     def _prefix_splits(self, rows):
-        """KV splits of the prefix attention: as many as keep every tile of the stage on a worker of its own (the
-        tiles of a head meet inside the stage to merge their partial results), at most four."""
-        if self.prefix_splits is not None:
-            return int(self.prefix_splits)
+        """KV splits of the prefix attention.  The tensor-core tiles hold at most 256 keys, so the split count is
+        ceil(rows / 256); with the mma.sync tiles: as many as keep every tile of the stage on a worker of its own, at
+        most four.  Returns (splits, fused): the merge runs inside the attention stage (the tiles of a head meet on a
+        ticket) only when every tile has a worker of its own, otherwise as a stage behind it."""
         groups = -(-rows // 128) * self.config.heads
-        return max(1, min(4, self.workers // groups))
+        if self.prefix_splits is not None:
+            splits = int(self.prefix_splits)
+        elif self.attention_path == "mma.sync":
+            splits = max(1, min(4, self.workers // groups))
+        else:
+            splits = -(-rows // 256)
+        return splits, splits > 1 and groups * splits <= self.workers
+
+    def _attention_path(self, handle, name):
+        if self.attention_path is not None:
+            _native.check(self.lib.configure_attention_path(handle, int(self.attention_path == "tcgen05")), name)
 
     def _gemma_layer(self, name, site, prefix, i, x_in, x_mid, bufs, *, rows, s_x, extra_sources, cos, sin, cache, cache_base,
                      attention_rows, mask_prefix, splits, kv_only, block_n, prefix_cache_stage=None, streamed_in=None,
@@ -528,11 +555,21 @@ class NativePi0:
                                                              fp4.k // 16, fp4.global_scale), f"{name}.attention")
             outs.append(StageOutput(f"{name}.attention", "fp4", fp4, rows, H * hd))
         att_sources = [(s_qkv, ALL)] + ([(prefix_cache_stage, ALL)] if prefix_cache_stage is not None else [])
+        splits, fused = splits if isinstance(splits, tuple) else (splits, splits > 1)
         if splits > 1:
-            # split-KV with the merge inside the attention stage: the tiles of a head meet on a ticket and each merges its share of rows
             _native.check(lib.configure_attention_splits(h, splits), f"{name}.attention")
-            _native.check(lib.configure_attention_fused_merge(h, 1), f"{name}.attention")
-        s_att = self.add(1, h, f"{name}.attention", att_sources, outs)
+            if fused:
+                # the merge inside the attention stage: the tiles of a head meet on a ticket and each merges its share of rows
+                _native.check(lib.configure_attention_fused_merge(h, 1), f"{name}.attention")
+        self._attention_path(h, f"{name}.attention")
+        if splits > 1 and not fused:
+            # more tiles than workers: partial rows first, the merge as a stage of its own behind them
+            s_part = self.add(1, h, f"{name}.attention_tiles", att_sources)
+            merge = C.c_void_p()
+            _native.check(lib.attention_merge_handle(h, C.byref(merge)), f"{name}.attention")
+            s_att = self.add(4, merge, f"{name}.attention", [(s_part, ALL)], outs)
+        else:
+            s_att = self.add(1, h, f"{name}.attention", att_sources, outs)
         wo = self.cached(p + "o", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=tile(p_o), precision=p_o))
         # ---- attention output projection; the post-attention norm is folded when both neighbours are NVFP4 sites
         fold2 = self.fold_norms and p_o == "nvfp4" and p_gu == "nvfp4"

@@ -7,7 +7,8 @@
 one launch of the persistent kernel touches ~0.25 GB of NVFP4 weights (more than the 126 MB L2), finishes in a
 few milliseconds and holds well under 2 GB on the device, so a multi-pass capture ends by itself quickly.
 ``gemm_gate_up`` is the Gemma-2B gate/up projection with the fused GeGLU -> NVFP4 epilogue
-(M 768, N 32768, K 2048) on 148 workers; ``attention_prefix`` is the 768 x 768 MQA prefix attention.  The other
+(M 768, N 32768, K 2048) on 148 workers; ``attention_prefix`` is the 768 x 768 MQA prefix attention with three KV
+splits (tcgen05 tiles; the ``*_mma_sync`` cases force the mma.sync tiles on the same shapes).  The other
 cases are the stand-alone operator shapes the reference publishes timings for: ``gemm_expert_qkv`` (51 rows padded
 to 128, N 2560, K 1024, BF16 out), ``gemm_prefix_qkv`` (768 x 2560 x 2048), ``gemm_vision_qkv`` (256 x 3456 x 1152),
 ``geglu_expert`` (51 x 8192 x 1024), ``attention_expert`` (51 queries over 819 keys, unsplit) and
@@ -39,13 +40,11 @@ def gemm_gate_up(launches):
 
 
 def attention_prefix(launches):
-    from native_pi0.attention import ResidentAttention
-    torch.manual_seed(0)
-    q = torch.randn(1, 768, 8, 256, device="cuda").bfloat16()
-    k = torch.randn(1, 768, 1, 256, device="cuda").bfloat16()
-    v = torch.randn(1, 768, 1, 256, device="cuda").bfloat16()
-    with ResidentAttention(None, q, k, v, workers=148) as op:
-        return timed(op.forward, launches, op.status)
+    return _attention(1, 768, 768, 8, 1, 256, launches, splits=3)
+
+
+def attention_prefix_mma_sync(launches):
+    return _attention(1, 768, 768, 8, 1, 256, launches, splits=3, path="mma.sync")
 
 
 def _random_packed(rng, rows, k):
@@ -78,13 +77,19 @@ def geglu_expert(launches):
     return _gemm(128, 8192, 1024, launches, rows=51, block_n=64, output_dtype=torch.uint8, output_geglu=True)
 
 
-def _attention(b, nq, nk, h, hk, hd, launches, *, prefix=None, splits=1, workers=148):
+def _attention(b, nq, nk, h, hk, hd, launches, *, prefix=None, splits=1, workers=148, stored=None, path=None):
+    """``stored``: elements a head occupies in memory (zeros behind the head); ``path``: None (by geometry), "mma.sync" or "tcgen05"."""
     from native_pi0.attention import ResidentAttention
     torch.manual_seed(0)
-    q = torch.randn(b, nq, h, hd, device="cuda").bfloat16()
-    k = torch.randn(b, nk, hk, hd, device="cuda").bfloat16()
-    v = torch.randn(b, nk, hk, hd, device="cuda").bfloat16()
-    with ResidentAttention(None, q, k, v, workers=workers, prefix=prefix, splits=splits, fused_merge=splits > 1) as op:
+    stored = stored or hd
+    def heads(rows, count):
+        t = torch.zeros(b, rows, count, stored, device="cuda")
+        t[..., :hd] = torch.randn(b, rows, count, hd, device="cuda")
+        return t.bfloat16()
+    q, k, v = heads(nq, h), heads(nk, hk), heads(nk, hk)
+    tiles = b * ((nq + 127) // 128) * h * splits
+    with ResidentAttention(None, q, k, v, workers=workers, prefix=prefix, splits=splits, fused_merge=splits > 1 and tiles <= workers,
+                           head_dim=hd, path=path) as op:
         return timed(op.forward, launches, op.status)
 
 
@@ -97,7 +102,19 @@ def attention_expert_split8(launches):
 
 
 def attention_vision(launches):
+    return _attention(3, 256, 256, 16, 16, 72, launches, stored=128)
+
+
+def attention_vision_mma_sync(launches):
     return _attention(3, 256, 256, 16, 16, 72, launches)
+
+
+def attention_expert_split13(launches):
+    return _attention(1, 51, 819, 8, 1, 256, launches, prefix=768, splits=13)
+
+
+def attention_expert_split13_mma_sync(launches):
+    return _attention(1, 51, 819, 8, 1, 256, launches, prefix=768, splits=13, path="mma.sync")
 
 
 def _norm(rows, width, launches):
@@ -153,7 +170,9 @@ def timed(call, launches, status):
 CASES = {"model_small": model_small, "gemm_gate_up": gemm_gate_up, "attention_prefix": attention_prefix,
          "gemm_expert_qkv": gemm_expert_qkv, "gemm_prefix_qkv": gemm_prefix_qkv, "gemm_vision_qkv": gemm_vision_qkv,
          "geglu_expert": geglu_expert, "attention_expert": attention_expert, "attention_expert_split8": attention_expert_split8,
-         "attention_vision": attention_vision, "norm_prefix": norm_prefix, "norm_expert": norm_expert, "mlp_block": mlp_block}
+         "attention_vision": attention_vision, "attention_vision_mma_sync": attention_vision_mma_sync,
+         "attention_prefix_mma_sync": attention_prefix_mma_sync, "attention_expert_split13": attention_expert_split13,
+         "attention_expert_split13_mma_sync": attention_expert_split13_mma_sync, "norm_prefix": norm_prefix, "norm_expert": norm_expert, "mlp_block": mlp_block}
 
 
 def main():
