@@ -114,11 +114,15 @@ int configure_dense_rows(void* handle, int rows);
 int configure_dense_tile(void* handle, int block_n);
 
 /* ------------------------------------------------------------------------------------------------------
- * LayerNorm / RMSNorm producer -> NVFP4 (format 4) or BF16 (format 16).
+ * LayerNorm / RMSNorm producer -> NVFP4 (format 4: packed codes + swizzled scales), FP8 E4M3 (format 8: value / global
+ * scale, [rows, width] bytes), BF16 (format 16) or only the FP32 row factor 1 / sqrt(mean square + eps) (format 17,
+ * output FP32 [rows]).  Optional fused residual: input + residual (BF16 [rows, width]) is normalised, the sum is stored
+ * to residual_output when given, and with round_residual the statistics continue from its BF16 rounding.  gamma / beta
+ * / inverse_scale (an AWQ-style per-channel factor applied after gamma and beta) are FP32 [width]; RMSNorm gamma
+ * already holds 1+w.
  * Replaces: native_pi0/norm.cu:138-176 (create_norm, launch_norm, destroy_norm), bound in
- * native_pi0/normalization.py:43-66.  Supported subset: BF16 input (fp16 == 0), no fused residual
- * (residual, residual_output NULL), no AWQ inverse scale, formats 4 and 16, legacy_ties == 0; anything
- * else returns cudaErrorInvalidValue.  gamma/beta are FP32 [width]; RMSNorm gamma already holds 1+w.
+ * native_pi0/normalization.py:43-66.  Not offered: FP16 input (fp16 == 1) and legacy_ties == 1 (a rounding variant of
+ * an older quantiser) return cudaErrorInvalidValue.
  */
 int create_norm(void** handle, const void* input, const void* residual, const float* gamma, const float* beta,
                 const float* inverse_scale, void* residual_output, void* output, void* scales, int rows, int width,

@@ -35,7 +35,50 @@ __device__ __forceinline__ void load_block16(const __nv_bfloat16* src, float (&v
     }
 }
 
+// Input block (row, block): x, plus the residual when one is bound; the sum is stored for the next residual connection
+// and, with round_residual, the statistics continue from its BF16 rounding.
+__device__ __forceinline__ void load_input16(const NormParams& n, int row, int block, float (&v)[16]) {
+    load_block16(static_cast<const __nv_bfloat16*>(n.in) + static_cast<size_t>(row) * n.ld_in + block * 16, v);
+    if (n.residual) {
+        float r[16];
+        load_block16(static_cast<const __nv_bfloat16*>(n.residual) + static_cast<size_t>(row) * n.width + block * 16, r);
+        uint32_t w[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float a = v[2 * i] + r[2 * i], b = v[2 * i + 1] + r[2 * i + 1];
+            __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+            const float2 back = __bfloat1622float2(h);
+            v[2 * i] = n.round_residual ? back.x : a;
+            v[2 * i + 1] = n.round_residual ? back.y : b;
+        }
+        if (n.residual_out) {
+            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(n.residual_out) + static_cast<size_t>(row) * n.width + block * 16);
+            dst[0] = make_uint4(w[0], w[1], w[2], w[3]);
+            dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        }
+    }
+}
+
 __device__ __forceinline__ void store_block16(const NormParams& n, int row, int block, float (&v)[16]) {
+    if (n.inv_scale) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const float4 s4 = __ldg(reinterpret_cast<const float4*>(n.inv_scale + block * 16) + q);
+            v[4 * q] *= s4.x; v[4 * q + 1] *= s4.y; v[4 * q + 2] *= s4.z; v[4 * q + 3] *= s4.w;
+        }
+        if (n.round_norm) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) v[i] = bf16_round(v[i]);
+        }
+    }
+    if (n.out_fp8) {
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            w[i >> 2] |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] * n.inv_gs, __NV_SATFINITE, __NV_E4M3)) << (8 * (i & 3));
+        *reinterpret_cast<uint4*>(n.out_fp8 + static_cast<size_t>(row) * n.width + block * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
     if (n.out_bf16) {
         uint32_t w[8];
 #pragma unroll
@@ -75,7 +118,7 @@ __device__ __forceinline__ void norm_row(const NormParams& n, int row) {
     for (int j = 0; j < kNormMaxBlocksPerLane; j++) {
         const int b = lane + 32 * j;
         if (b < blocks) {
-            load_block16(src + b * 16, cache[j]);
+            load_input16(n, row, b, cache[j]);
 #pragma unroll
             for (int i = 0; i < 16; i++) sum += cache[j][i];
         }
@@ -95,6 +138,10 @@ __device__ __forceinline__ void norm_row(const NormParams& n, int row) {
         }
     }
     const float rstd = rsqrtf(warp_sum(sq) * inv_width + n.eps);
+    if (n.out_factor) {                      // only the row factor is wanted
+        if (lane == 0) n.out_factor[row] = rstd;
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < kNormMaxBlocksPerLane; j++) {
         const int b = lane + 32 * j;
@@ -112,7 +159,7 @@ __device__ __forceinline__ void norm_row(const NormParams& n, int row) {
                 float y = (cache[j][i] - mean) * rstd;
                 if (n.gamma) y *= gm[i];
                 if (n.beta) y += bt[i];
-                v[i] = n.round_norm ? bf16_round(y) : y;
+                v[i] = (n.round_norm && !n.inv_scale) ? bf16_round(y) : y;     // (with an inverse scale the rounding follows it)
             }
             store_block16(n, row, b, v);
         }
@@ -141,7 +188,7 @@ __device__ __forceinline__ void norm_row_pair(const NormParams& n, int row, int 
     for (int j = 0; j < kNormPairBlocksPerLane; j++) {
         const int b = part * 32 + lane + 64 * j;
         if (valid && b < blocks) {
-            load_block16(src + b * 16, cache[j]);
+            load_input16(n, row, b, cache[j]);
 #pragma unroll
             for (int i = 0; i < 16; i++) sum += cache[j][i];
         }
@@ -171,6 +218,10 @@ __device__ __forceinline__ void norm_row_pair(const NormParams& n, int row, int 
     __syncthreads();
     const float rstd = rsqrtf((red[8 + local_row * 2] + red[8 + local_row * 2 + 1]) * inv_width + n.eps);
     if (!valid) return;
+    if (n.out_factor) {                      // only the row factor is wanted
+        if (part == 0 && lane == 0) n.out_factor[row] = rstd;
+        return;
+    }
 #pragma unroll
     for (int j = 0; j < kNormPairBlocksPerLane; j++) {
         const int b = part * 32 + lane + 64 * j;
@@ -188,7 +239,7 @@ __device__ __forceinline__ void norm_row_pair(const NormParams& n, int row, int 
                 float y = (cache[j][i] - mean) * rstd;
                 if (n.gamma) y *= gm[i];
                 if (n.beta) y += bt[i];
-                v[i] = n.round_norm ? bf16_round(y) : y;
+                v[i] = (n.round_norm && !n.inv_scale) ? bf16_round(y) : y;     // (with an inverse scale the rounding follows it)
             }
             store_block16(n, row, b, v);
         }

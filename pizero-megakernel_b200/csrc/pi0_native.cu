@@ -759,12 +759,13 @@ extern "C" int create_norm(void** handle, const void* input, const void* residua
                            const float* inverse_scale, void* residual_output, void* output, void* scales, int rows, int width,
                            int workers, int fp16, int format, int layer, int round_norm, int round_residual, int legacy_ties,
                            float epsilon, float global_scale) {
-    (void)round_residual;
     if (!handle) return cudaErrorInvalidValue;
     *handle = nullptr;
-    if (!input || !output || rows < 1 || width < 16 || width % 16 || (format != 4 && format != 16) || (format == 4 && !scales) ||
-        fp16 || residual || residual_output || inverse_scale || legacy_ties || !std::isfinite(epsilon) || epsilon <= 0 ||
-        !std::isfinite(global_scale) || global_scale <= 0 || width > 2048)
+    const bool known_format = format == 4 || format == 8 || format == 16 || format == 17;
+    if (!input || !output || rows < 1 || width < 16 || width % 16 || !known_format || (format == 4 && !scales) || fp16 ||
+        (residual_output && !residual) || legacy_ties || !std::isfinite(epsilon) || epsilon <= 0 ||
+        !std::isfinite(global_scale) || global_scale <= 0 || width > 2048 || !aligned16(input) || !aligned16(residual) ||
+        !aligned16(residual_output) || !aligned16(output) || !aligned16(gamma) || !aligned16(beta) || !aligned16(inverse_scale))
         return cudaErrorInvalidValue;
     Op* op = nullptr;
     int e = new_op(&op, workers);
@@ -779,6 +780,8 @@ extern "C" int create_norm(void** handle, const void* input, const void* residua
     NormParams& n = d.p.norm;
     n.rows_per_tile = rows_per_tile;
     n.in = input; n.gamma = gamma; n.beta = beta;
+    n.residual = residual; n.residual_out = residual_output; n.round_residual = round_residual;
+    n.inv_scale = inverse_scale;
     n.rows = rows; n.width = width;
     n.mode = layer ? 1 : 0;
     n.round_norm = round_norm;
@@ -786,7 +789,9 @@ extern "C" int create_norm(void** handle, const void* input, const void* residua
     n.inv_gs = 1.f / global_scale;
     n.policy = 0;
     if (format == 4) { n.out = static_cast<uint8_t*>(output); n.out_scales = static_cast<uint8_t*>(scales); }
-    else n.out_bf16 = output;
+    else if (format == 8) n.out_fp8 = static_cast<uint8_t*>(output);
+    else if (format == 16) n.out_bf16 = output;
+    else n.out_factor = static_cast<float*>(output);
     n.out_blocks = width / 16;
     n.ld_in = width;
     n.ld_out = width / 2;

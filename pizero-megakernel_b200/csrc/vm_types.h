@@ -116,6 +116,12 @@ struct NormParams {
     int ld_in;                   // input row stride in elements
     int ld_out;                  // FP4 output row stride in bytes
     int rows_per_tile;           // 4 (RMSNorm stages) or 8 (LayerNorm, quantise-only); two warps share a row
+    const void* residual;        // BF16 [rows, width] added to the input before the statistics, or null
+    void* residual_out;          // BF16 [rows, width]: the sum (what the next residual connection reads), or null
+    int round_residual;          // continue from the BF16-rounded sum (what a separate add kernel would have stored)
+    const float* inv_scale;      // FP32 [width] multiplied in after gamma / beta (AWQ-style inverse smoothing scale) or null
+    uint8_t* out_fp8;            // E4M3 [rows, width] of value / global scale (format 8), or null
+    float* out_factor;           // FP32 [rows]: only 1 / sqrt(mean square + eps) of every row (format 17), or null
 };
 
 struct AttnParams {

@@ -110,3 +110,35 @@ def fp32_descale(activation_scale, weight_scale):
     if not np.isfinite(product) or min(a, w, product) <= 0:
         raise ValueError("Descale factors must be finite and positive")
     return product
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Extensions: from a finished calibration to the engine's per-site operand formats, and a file cache for it.
+NVFP4_AMAX_LIMIT = 6.0 * 448.0          # largest magnitude an NVFP4 block can hold with tensor scale 1 (E2M1 6 x E4M3 448)
+
+
+def site_precisions(report, *, sensitive=("*.qkv",), amax_limit=NVFP4_AMAX_LIMIT, default="nvfp4"):
+    """Precision dict for ``NativePi0(precision=...)`` from ``ActivationCalibration.finalize()``.
+
+    ``sensitive`` site patterns run on BF16 operands regardless of statistics (query / key projections lose the most
+    under 4-bit operands: their error moves the softmax).  Every calibrated operation whose selected |max| exceeds
+    ``amax_limit`` - it would saturate an NVFP4 block at tensor scale 1 - runs in BF16 as well.  Operation names are the
+    engine's site names (``prefix.3.down``, ``expert.7.qkv``, ...)."""
+    chosen = {pattern: "bf16" for pattern in sensitive}
+    for operation in sorted(report):
+        if float(report[operation]["selected_amax"]) > amax_limit:
+            chosen[operation] = "bf16"
+    chosen["default"] = default
+    return chosen
+
+
+def cached_calibration(directory, key, build):
+    """``build()`` -> report, stored as ``<directory>/<key>.json`` and read back on the next call with the same key
+    (``cache_key`` of checkpoint digest, engine configuration and observation set)."""
+    path = Path(directory) / f"{key}.json"
+    if path.exists():
+        return json.loads(path.read_text())
+    report = build()
+    path.parent.mkdir(parents=True, exist_ok=True)
+    path.write_text(json.dumps(report, sort_keys=True, indent=1))
+    return report

@@ -105,8 +105,11 @@ class NativePi0:
                     precision="auto", library=None, **kwargs):
         """Load an OpenPI ``model.safetensors`` (parameter names of ``PI0Pytorch``) straight into the engine."""
         from safetensors.torch import load_file
-        sd = load_file(str(checkpoint_path), device="cuda")
-        config = Pi0Config(action_dim=sd["action_out_proj.weight"].shape[0])
+        path = Path(checkpoint_path)
+        if path.is_dir():
+            path = path / "model.safetensors"
+        sd = load_file(str(path), device="cuda")
+        config = kwargs.pop("config", None) or Pi0Config.from_state_dict(sd)
         return cls(StateDictModel(config, sd), num_views=num_views, prompt_len=prompt_len, chunk_size=chunk_size,
                    flow_steps=flow_steps, precision=precision, library=library, **kwargs)
 
@@ -121,7 +124,7 @@ class NativePi0:
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
                  library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=64,
                  rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="spread",
-                 fold_norms=True, attention_path=None):
+                 fold_norms=True, attention_path=None, weight_store=None):
         config = getattr(model, "config", None)
         if config is None or getattr(config, "pi05", False):
             raise ValueError("This engine runs ordinary pi0 (not pi0.5)")
@@ -167,6 +170,9 @@ class NativePi0:
         self.workers = min(sms, 148) if workers is None else workers
         self.sd = sd
         self.buffers, self.handles, self._cache = [], [], {}
+        # packed weights, keyed by parameter and operand format: engines of different shapes (views, prompt, chunk) that
+        # are given the same store share one copy of every weight (EngineCache)
+        self._weights = weight_store if weight_store is not None else {}
         self.stages, self.stage_tiles, self.stage_cost, self.stage_names, self.stage_outputs = [], [], [], [], []
         self.landmarks, self.landmark_stage = {}, {}
         self.handle = C.c_void_p()
@@ -200,10 +206,12 @@ class NativePi0:
         return m
 
     def cached(self, key, make):
-        """Build a derived tensor (quantised weight, folded gamma) once per parameter and share it between stages."""
-        if key not in self._cache:
-            self._cache[key] = make()
-        return self._cache[key]
+        """Build a derived tensor once and share it between stages: string keys name weights (quantised matrices, folded
+        gammas; also shared between engines through ``weight_store``), other keys name buffers of this engine."""
+        store = self._weights if isinstance(key, str) else self._cache
+        if key not in store:
+            store[key] = make()
+        return store[key]
 
     def weight(self, w, *, rows_to=128, block_n=128, precision="nvfp4"):
         """BF16/FP32 [N, K] -> the site's operand format on the device: NVFP4 (ceil block scales, tensor scale
@@ -428,14 +436,14 @@ class NativePi0:
             p_qkv, p_out, p_fc1, p_fc2 = [self.site(f"vision.{i}.{n}") for n in ("qkv", "out", "fc1", "fc2")]
             g1, b1 = sd[p + "layer_norm1.weight"].float().contiguous(), sd[p + "layer_norm1.bias"].float().contiguous()
             g2, b2 = sd[p + "layer_norm2.weight"].float().contiguous(), sd[p + "layer_norm2.bias"].float().contiguous()
-            wqkv = self.weight(torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"]), precision=p_qkv)
+            wqkv = self.cached(p + "qkv." + p_qkv, lambda: self.weight(torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"]), precision=p_qkv))
             bqkv = torch.cat([sd[p + f"self_attn.{n}_proj.bias"] for n in "qkv"]).to(torch.bfloat16).contiguous()
-            wo = self.weight(sd[p + "self_attn.out_proj.weight"], precision=p_out)
+            wo = self.cached(p + "out." + p_out, lambda: self.weight(sd[p + "self_attn.out_proj.weight"], precision=p_out))
             bo = sd[p + "self_attn.out_proj.bias"].to(torch.bfloat16).contiguous()
-            w1 = self.weight(sd[p + "mlp.fc1.weight"], precision=p_fc1)
+            w1 = self.cached(p + "fc1." + p_fc1, lambda: self.weight(sd[p + "mlp.fc1.weight"], precision=p_fc1))
             bias1 = torch.zeros(mlp_pad, device=self.device, dtype=torch.bfloat16)
             bias1[:c.vision_mlp] = sd[p + "mlp.fc1.bias"].to(torch.bfloat16)
-            w2 = self.weight(sd[p + "mlp.fc2.weight"], precision=p_fc2)
+            w2 = self.cached(p + "fc2." + p_fc2, lambda: self.weight(sd[p + "mlp.fc2.weight"], precision=p_fc2))
             bias2 = sd[p + "mlp.fc2.bias"].to(torch.bfloat16).contiguous()
             self.buffers.extend((g1, b1, g2, b2, bqkv, bo, bias1, bias2))
             buf = qkv[i & 1]
@@ -536,7 +544,7 @@ class NativePi0:
                 w = w.float() * gamma1()[None, :]
             return self.weight(w, block_n=tile(p_qkv), precision=p_qkv)
 
-        wqkv = self.cached(p + "qkv", make_qkv)
+        wqkv = self.cached(f"{p}qkv.{p_qkv}.{int(fold1 is not None)}.{int(kv_only)}.{tile(p_qkv)}", make_qkv)
         q_cols, q = (0, None) if kv_only else (H * hd, qbuf)
         s_qkv = self.gemm(f"{name}.qkv", a1, wqkv, rows=rows, sources=[(s_n1, SAME)], block_n=tile(p_qkv), row_rms=fold1,
                           rope=dict(q=q, cos=cos, sin=sin, cache_k=cache[0], cache_v=cache[1], q_cols=q_cols, cache_base=cache_base))
@@ -570,7 +578,7 @@ class NativePi0:
             s_att = self.add(4, merge, f"{name}.attention", [(s_part, ALL)], outs)
         else:
             s_att = self.add(1, h, f"{name}.attention", att_sources, outs)
-        wo = self.cached(p + "o", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=tile(p_o), precision=p_o))
+        wo = self.cached(f"{p}o.{p_o}.{tile(p_o)}", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=tile(p_o), precision=p_o))
         # ---- attention output projection; the post-attention norm is folded when both neighbours are NVFP4 sites
         fold2 = self.fold_norms and p_o == "nvfp4" and p_gu == "nvfp4"
         gamma2 = lambda: (1.0 + sd[p + "post_attention_layernorm.weight"].float()).contiguous()
@@ -592,10 +600,10 @@ class NativePi0:
                 w = w.float() * gamma2()[None, :]
             return self.weight(w, block_n=tile(p_gu), precision=p_gu)
 
-        wgu = self.cached(p + "gate_up", make_gate_up)
+        wgu = self.cached(f"{p}gate_up.{p_gu}.{int(fold2)}.{tile(p_gu)}", make_gate_up)
         s_gu = self.gemm(f"{name}.gate_up", a3, wgu, rows=rows, sources=[(s_n2, SAME)], out_act=a4.require(p_dn), out_precision=p_dn,
                          activation=2, block_n=tile(p_gu), row_rms=rms2)
-        wd = self.cached(p + "down", lambda: self.weight(sd[p + "mlp.down_proj.weight"], block_n=tile(p_dn), precision=p_dn))
+        wd = self.cached(f"{p}down.{p_dn}.{tile(p_dn)}", lambda: self.weight(sd[p + "mlp.down_proj.weight"], block_n=tile(p_dn), precision=p_dn))
         # ---- down projection; streams for the next layer's QKV when that reads NVFP4 too
         streamed_out = None
         if self.fold_norms and next_site is not None and p_dn == "nvfp4" and self.site(f"{next_site}.qkv") == "nvfp4":
@@ -619,7 +627,7 @@ class NativePi0:
         # ---------------- vision tower + projector -> prefix rows [0, V*256)
         s_pl, a_post = self._vision()
         x_a, x_b = self.tensor((P_pad, c.width)), self.tensor((P_pad, c.width))
-        wproj = self.weight(sd[PROJECTOR + "weight"], precision=self.site("vision.projector"))
+        wproj = self.cached(PROJECTOR + self.site("vision.projector"), lambda: self.weight(sd[PROJECTOR + "weight"], precision=self.site("vision.projector")))
         bproj = sd[PROJECTOR + "bias"].to(torch.bfloat16).contiguous()
         self.buffers.append(bproj)
         s_x = self.gemm("vision.projector", a_post, wproj, rows=V * 256, sources=[(s_pl, SAME)], out=x_a, bias=bproj)
@@ -810,21 +818,37 @@ class NativePi0:
         """Per-stage wall span of the last timed launch: list of (name, ready_ns, end_ns, instructions) where
         ready is the earliest moment a worker had the stage's producers complete and end the last worker's finish,
         relative to the earliest stamp (device global timer).  Call ``enable_timings()`` before the launch."""
-        stamps = self.read_timings()
-        live = self.code[:, :, 0] != 0
-        stage_of = self.code[:, :, 1]
-        start, end = stamps[:, :, 1], stamps[:, :, 2]
-        valid = live & (start > 0) & (end > 0)
-        if not valid.any():
-            return []
-        origin = start[valid].min()
-        first = np.full(len(self.stages), np.iinfo(np.int64).max, dtype=np.int64)
-        last = np.zeros(len(self.stages), dtype=np.int64)
-        count = np.zeros(len(self.stages), dtype=np.int64)
-        np.minimum.at(first, stage_of[valid], start[valid] - origin)
-        np.maximum.at(last, stage_of[valid], end[valid] - origin)
-        np.add.at(count, stage_of[valid], 1)
-        return [(self.stage_names[i], int(first[i]), int(last[i]), int(count[i])) for i in range(len(self.stages)) if count[i]]
+        from native_pi0.timing import stage_spans
+        return stage_spans(self.read_timings(), self.code, self.stage_names)
+
+    def calibrate(self, calibration, sample, images, state, noise, tokens):
+        """Record the |max| of every projection's BF16 output for one observation into an ``ActivationCalibration``:
+        the forward runs stage by stage (one launch each) and every BF16 / FP32 stage output is observed under its
+        site name, expert stages with their Euler step.  Meant for an engine built with ``precision="bf16"``, whose
+        activations are unquantised; ``native_pi0.calibration.site_precisions`` turns the finished record into the
+        ``precision`` argument of the serving engine."""
+        self._check_inputs(images, state, noise, tokens)
+        for s in range(len(self.stages)):
+            self.launch_range(s, s + 1, images, state, noise, tokens, new_epoch=(s == 0))
+            for out in self.stage_outputs[s]:
+                if out.kind not in ("bf16", "f32") or out.head is not None:
+                    continue
+                parts = out.name.split(".")
+                step = None
+                if parts[0] == "expert" and len(parts) == 4:          # expert.<step>.<layer>.<operation>
+                    step, parts = int(parts[1]), [parts[0]] + parts[2:]
+                if len(parts) != 3:
+                    continue
+                value = float(out.buffer[:out.rows, :out.cols].float().abs().max())
+                calibration.observe(".".join(parts), [value], sample=sample, step=step)
+        self.epoch += 1
+        return calibration
+
+    def operation_report(self):
+        """Per phase and operation type: layers, median active workers, median busy time and the chain time of the
+        last timed launch (``native_pi0.timing.operation_report``)."""
+        from native_pi0.timing import operation_report
+        return operation_report(self.read_timings(), self.code, self.stage_names)
 
     def close(self):
         if getattr(self, "handle", None) is not None and self.handle.value:
@@ -837,6 +861,47 @@ class NativePi0:
                     self.lib.destroy_op(h)
                 h.value = None
         self.handles = []
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *_):
+        self.close()
+
+
+class EngineCache:
+    """Engines for several input shapes over one set of packed weights.
+
+    A program is compiled for fixed (views, prompt length, chunk size); a deployment that sees a few shapes keeps one
+    engine per shape.  The engines share a ``weight_store``, so every weight is packed and resident once (1.46 GB in
+    NVFP4) and an additional shape costs only its activations, KV caches and instruction streams.  At most
+    ``capacity`` engines stay alive; the least recently used one is closed when another shape arrives.  The state dict
+    is kept for building further shapes.
+    """
+
+    def __init__(self, model, *, capacity=4, **engine_options):
+        if capacity < 1:
+            raise ValueError("capacity >= 1")
+        self.model, self.capacity, self.options = model, capacity, dict(engine_options)
+        self.weights, self.engines = {}, {}
+
+    def get(self, num_views=3, prompt_len=0, chunk_size=50):
+        key = (int(num_views), int(prompt_len), int(chunk_size))
+        engine = self.engines.pop(key, None)
+        if engine is None:
+            while len(self.engines) >= self.capacity:
+                oldest = next(iter(self.engines))
+                self.engines.pop(oldest).close()
+            engine = NativePi0(self.model, num_views=key[0], prompt_len=key[1], chunk_size=key[2], weight_store=self.weights,
+                               **self.options)
+        self.engines[key] = engine                          # most recently used last
+        return engine
+
+    def close(self):
+        for engine in self.engines.values():
+            engine.close()
+        self.engines.clear()
+        self.weights.clear()
 
     def __enter__(self):
         return self

@@ -1,9 +1,11 @@
 """Fused LayerNorm / RMSNorm -> NVFP4 producer.
 
-Constructor-compatible with the reference ``ResidentNorm`` (``native_pi0/normalization.py:9-82``) for
-the cases the pi0 path uses: BF16 input, ``precision`` ``"fp4"`` or ``"bf16"``, FP32 gamma/beta.
-RMSNorm gamma must already contain ``1 + w``.  FP8 output, the FP32 row-factor output, fused residual
-adds and AWQ inverse scales belong to the reference's BF16/FP8 model and are rejected here.
+Constructor-compatible with the reference ``ResidentNorm`` (``native_pi0/normalization.py:9-82``): BF16 input,
+``precision`` ``"fp4"`` (packed NVFP4 + swizzled block scales), ``"fp8"`` (E4M3 of value / global scale), ``"bf16"`` or
+``"factor"`` (only the FP32 ``1 / sqrt(mean square + eps)`` per row, for projections whose weight has the norm weight
+folded in), FP32 ``gamma`` / ``beta`` / ``inverse_scale`` (an AWQ-style per-channel factor applied after the affine
+part), optional fused ``residual`` add (the sum is kept in ``residual_output``).  RMSNorm gamma must already contain
+``1 + w``.  Not offered: FP16 input and the ``legacy_ties`` rounding variant.
 """
 import ctypes
 
@@ -24,10 +26,12 @@ class ResidentNorm:
         rows, width = inputs.shape
         if rows < 1 or width < 16 or width % 16 or (width > 2048 and not quantize_only):
             raise ValueError("Width must be a multiple of 16 up to 2048")
-        if kind not in ("rms", "layer") or precision not in ("fp4", "bf16"):
-            raise ValueError("Unknown normalization or precision (this engine emits fp4 or bf16)")
-        if inverse_scale is not None or residual is not None or legacy_ties:
-            raise ValueError("Fused residual, AWQ inverse scale and legacy ties are not part of the NVFP4 engine")
+        if kind not in ("rms", "layer") or precision not in ("fp4", "fp8", "bf16", "factor"):
+            raise ValueError("Unknown normalization or precision (fp4, fp8, bf16 or factor)")
+        if legacy_ties:
+            raise ValueError("The legacy tie-breaking variant of the quantiser is not offered")
+        if precision == "factor" and (kind != "rms" or any(x is not None for x in (gamma, beta, inverse_scale, residual))):
+            raise ValueError("The RMS factor output takes raw rows: no affine parameters, no residual")
         if not isinstance(row_alignment, int) or row_alignment < 1:
             raise ValueError("Invalid row alignment")
         if kind == "rms" and beta is not None:
@@ -47,12 +51,23 @@ class ResidentNorm:
         self.handle = ctypes.c_void_p()
         with torch.cuda.device(self.device):
             self.inputs = inputs.to(self.device).contiguous()
-            self.gamma, self.beta = [None if v is None else torch.as_tensor(v, dtype=torch.float32, device=self.device).contiguous()
-                                     for v in (gamma, beta)]
-            for vec in (self.gamma, self.beta):
+            self.gamma, self.beta, self.inverse_scale = [
+                None if v is None else torch.as_tensor(v, dtype=torch.float32, device=self.device).contiguous()
+                for v in (gamma, beta, inverse_scale)]
+            for vec in (self.gamma, self.beta, self.inverse_scale):
                 if vec is not None and tuple(vec.shape) != (width,):
-                    raise ValueError("Affine vector shape mismatch")
-            if precision == "fp4":
+                    raise ValueError("Affine / inverse-scale vector shape mismatch")
+            self.residual = self.residual_output = None
+            if residual is not None:
+                self.residual = torch.as_tensor(residual, dtype=torch.bfloat16, device=self.device).contiguous()
+                if self.residual.shape != self.inputs.shape:
+                    raise ValueError("Residual shape mismatch")
+                self.residual_output = torch.empty_like(self.inputs)
+            if precision == "factor":
+                self.output, self.output_scales = torch.zeros(out_rows, dtype=torch.float32, device=self.device), None
+            elif precision == "fp8":
+                self.output, self.output_scales = torch.zeros((out_rows, width), dtype=torch.float8_e4m3fn, device=self.device), None
+            elif precision == "fp4":
                 self.output = packed_tma_buffer((out_rows, width // 2), device=self.device)
                 self.output_scales = torch.zeros(((out_rows + 127) // 128) * ((width // 16 + 3) // 4) * 512,
                                                  dtype=torch.uint8, device=self.device)
@@ -61,10 +76,10 @@ class ResidentNorm:
                 self.output_scales = None
             self.normalized = torch.zeros((out_rows, width), dtype=torch.bfloat16, device=self.device) if keep_bf16 else None
             code = self.library.create_norm(
-                ctypes.byref(self.handle), self.inputs.data_ptr(), None, _native.ptr(self.gamma), _native.ptr(self.beta),
-                None, None, self.output.data_ptr(), _native.ptr(self.output_scales), rows, width, workers, 0,
-                4 if precision == "fp4" else 16, int(kind == "layer"), int(round_normalized), int(round_residual), 0,
-                float(epsilon), float(self.global_scale))
+                ctypes.byref(self.handle), self.inputs.data_ptr(), _native.ptr(self.residual), _native.ptr(self.gamma), _native.ptr(self.beta),
+                _native.ptr(self.inverse_scale), _native.ptr(self.residual_output), self.output.data_ptr(), _native.ptr(self.output_scales),
+                rows, width, workers, 0, {"fp4": 4, "fp8": 8, "bf16": 16, "factor": 17}[precision], int(kind == "layer"),
+                int(round_normalized), int(round_residual), 0, float(epsilon), float(self.global_scale))
             _native.check(code, "Native norm setup")
             try:
                 if quantize_only:

@@ -40,6 +40,32 @@ class Pi0Config:
     rope_base: float = 10000.0
     pi05: bool = False
 
+    @classmethod
+    def from_state_dict(cls, sd, **overrides):
+        """Dimensions read off the tensors of a checkpoint (layer counts, widths, MLP sizes, head_dim from the single
+        KV head, action_dim); head counts follow from the widths, everything else keeps its default."""
+        def layers(prefix):
+            return 1 + max(int(k[len(prefix):].split(".")[0]) for k in sd if k.startswith(prefix))
+
+        vw = sd[VISION + "embeddings.patch_embedding.weight"].shape[0]
+        head_dim = sd[LANGUAGE + "layers.0.self_attn.k_proj.weight"].shape[0]
+        found = dict(
+            vision_layers=layers(VISION + "encoder.layers."), vision_width=vw,
+            vision_mlp=sd[VISION + "encoder.layers.0.mlp.fc1.weight"].shape[0],
+            width=sd[LANGUAGE + "layers.0.self_attn.o_proj.weight"].shape[0],
+            mlp=sd[LANGUAGE + "layers.0.mlp.gate_proj.weight"].shape[0],
+            head_dim=head_dim, heads=sd[LANGUAGE + "layers.0.self_attn.q_proj.weight"].shape[0] // head_dim,
+            prefix_layers=layers(LANGUAGE + "layers."),
+            expert_width=sd[EXPERT + "layers.0.self_attn.o_proj.weight"].shape[0],
+            expert_mlp=sd[EXPERT + "layers.0.mlp.gate_proj.weight"].shape[0],
+            expert_layers=layers(EXPERT + "layers."),
+            action_dim=sd["action_out_proj.weight"].shape[0])
+        table = sd.get(LANGUAGE + "embed_tokens.weight")
+        if table is not None:
+            found["vocab"] = table.shape[0]
+        found.update(overrides)
+        return cls(**found)
+
 
 def parameter_shapes(cfg: Pi0Config):
     """name -> (shape, kept_in_fp32, mean) for every parameter of the model."""

@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 
 from native_pi0 import _native
 from native_pi0.linear import NativeLinearProgram
-from native_pi0.model import NativePi0
+from native_pi0.model import EngineCache, NativePi0
 from native_pi0.primitives import ResidentNVFP4
 from native_pi0.quantization import PackedNVFP4, pack_nvfp4, unswizzle_scales
 from native_pi0.weights import Pi0Config, StateDictModel
@@ -97,6 +97,61 @@ def test_site_precisions(small_model, precision, policy):
     else:
         assert nrmse(out, emulation) <= 0.1
         assert nrmse(out, eager) <= 1.3 * max(nrmse(emulation, eager), 0.05)
+
+
+def test_checkpoint_file_and_calibrated_precisions(small_model, tmp_path):
+    """The checkpoint path: a ``model.safetensors`` with OpenPI parameter names is read by ``from_openpi`` (dimensions
+    from the tensors) and gives the same bits as the in-memory state dict; a BF16 engine records activation maxima for
+    two observations, and the finished calibration picks the operand formats of the serving engine (cached by key)."""
+    from safetensors.torch import save_file
+    from native_pi0.calibration import ActivationCalibration, cache_key, cached_calibration, checkpoint_digest, site_precisions
+    dims, cfg, sd = small_model
+    path = tmp_path / "model.safetensors"
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(path))
+    x = inputs(3, 50, 0, dims.vocab)
+    with NativePi0.from_openpi(tmp_path) as loaded, NativePi0(StateDictModel(cfg, sd)) as direct:
+        assert loaded.config.vision_layers == cfg.vision_layers and loaded.config.mlp == cfg.mlp and loaded.config.expert_mlp == cfg.expert_mlp
+        assert torch.equal(loaded.forward(*x), direct.forward(*x))
+
+    def observe():
+        record = ActivationCalibration()
+        with NativePi0.from_openpi(path, precision="bf16", flow_steps=3) as reference:
+            for n in range(2):
+                reference.calibrate(record, f"observation-{n}", *inputs(3, 50, 0, dims.vocab, seed=40 + n))
+            assert reference.status()["code"] == 0
+        return record.finalize(required_steps=range(3))
+
+    key = cache_key(checkpoint_digest([path]), {"views": 3, "chunk": 50, "steps": 3}, "two-synthetic-observations")
+    report = cached_calibration(tmp_path / "calibration", key, observe)
+    assert report == cached_calibration(tmp_path / "calibration", key, lambda: pytest.fail("cache miss"))
+    assert "expert.1.down" in report and report["expert.1.down"]["records"] == 6 and "prefix.0.o_proj" in report
+    chosen = site_precisions(report)
+    assert chosen["*.qkv"] == "bf16" and chosen["default"] == "nvfp4"
+    forced = site_precisions(report, amax_limit=0.5 * report["prefix.1.down"]["selected_amax"])
+    assert forced["prefix.1.down"] == "bf16"
+    with NativePi0.from_openpi(path, precision=chosen) as engine:
+        out = engine.forward(*x)
+        assert engine.status()["code"] == 0 and engine.precision_policy == "mixed" and torch.isfinite(out).all()
+        assert engine.site_precisions["prefix.0.qkv"] == "bf16" and engine.site_precisions["prefix.0.down"] == "nvfp4"
+
+
+def test_engine_cache_shares_weights_between_shapes(small_model):
+    """Several (views, prompt, chunk) shapes over one weight store: same bits as engines built alone, one packed copy of
+    every weight, least recently used shape evicted."""
+    dims, cfg, sd = small_model
+    shapes = [(3, 0, 50), (3, 16, 63), (1, 3, 7)]
+    with EngineCache(StateDictModel(cfg, sd), capacity=2) as cache:
+        first = cache.get(*shapes[0])
+        packed = len(cache.weights)
+        second = cache.get(*shapes[1])
+        assert len(cache.weights) == packed and cache.get(*shapes[0]) is first               # no weight was packed a second time
+        for shape, engine in ((shapes[0], first), (shapes[1], second)):
+            x = inputs(shape[0], shape[2], shape[1], dims.vocab)
+            with NativePi0(StateDictModel(cfg, sd), num_views=shape[0], prompt_len=shape[1], chunk_size=shape[2]) as alone:
+                assert torch.equal(engine.forward(*x), alone.forward(*x))
+        third = cache.get(*shapes[2])                       # capacity 2: the least recently used shape (the second) is closed
+        assert not second.handle.value and first.handle.value and third.handle.value
+        assert set(cache.engines) == {shapes[0], shapes[2]}
 
 
 def test_norm_stages_instead_of_folded_norms(small_model):

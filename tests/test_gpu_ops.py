@@ -356,6 +356,39 @@ def test_norm_to_nvfp4(rows, width, kind):
     assert not data[rows:].any() and not scales[rows:].any()
 
 
+def test_norm_residual_inverse_scale_fp8_and_factor_outputs():
+    """The reference operator's remaining outputs (``scripts/validate_norm.py:95-130``): fused residual add with the sum
+    kept for the next connection, AWQ-style inverse scale, FP8 E4M3 rows and the FP32 row factor."""
+    torch.manual_seed(89)
+    rows, width = 200, 1024
+    x, r = torch.randn(rows, width).bfloat16(), (torch.randn(rows, width) * 0.1).bfloat16()
+    gamma, awq = 1 + torch.randn(width) * 0.05, 0.5 + torch.rand(width)
+    total = (x.float() + r.float()).bfloat16()
+    want = oracle_ops.norm(total, "rms", gamma, None, round_normalized=False) * awq
+    want = want.bfloat16().float()
+    with ResidentNorm(None, x, kind="rms", precision="bf16", gamma=gamma, inverse_scale=awq, residual=r, workers=64) as op:
+        got = op.forward()[:rows].float().cpu()
+        assert op.status()["code"] == 0
+        assert torch.equal(op.residual_output.cpu(), total)                 # the sum, rounded once, bit for bit
+    assert relrms(got.numpy(), want.numpy()) < 5e-3 and float((got != want).float().mean()) < 0.02
+    with ResidentNorm(None, x, kind="rms", precision="fp4", gamma=gamma, residual=r, workers=64, row_alignment=128, keep_bf16=True) as op:
+        op.forward()
+        torch.cuda.synchronize()
+        ref = pack_nvfp4(op.normalized[:rows].float().cpu().numpy(), row_alignment=128)
+        np.testing.assert_array_equal(op.output.cpu().numpy(), ref.data)
+        assert relrms(op.normalized[:rows].float().cpu().numpy(), oracle_ops.norm(total, "rms", gamma, None).numpy()) < 5e-3
+    y = oracle_ops.norm(x, "layer", gamma, awq * 0.1)                       # (beta reused from the random vector)
+    with ResidentNorm(None, x, kind="layer", precision="fp8", gamma=gamma, beta=awq * 0.1, workers=64, global_scale=0.25) as op:
+        fp8 = op.forward()[:rows].float().cpu() * 0.25
+    assert relrms(fp8.numpy(), y.numpy()) < 0.04                            # E4M3: three mantissa bits
+    assert float(((y / 0.25).to(torch.float8_e4m3fn).float() * 0.25 != fp8).float().mean()) < 0.02
+    with ResidentNorm(None, x, kind="rms", precision="factor", workers=64) as op:
+        factor = op.forward()[:rows].cpu()
+    torch.testing.assert_close(factor, torch.rsqrt(x.float().square().mean(-1) + 1e-6), rtol=2e-6, atol=0)
+    with pytest.raises(ValueError):
+        ResidentNorm(None, x, kind="rms", precision="factor", gamma=gamma)
+
+
 def test_norm_argument_errors():
     x = torch.randn(4, 64).bfloat16()
     with pytest.raises(ValueError):
@@ -363,7 +396,7 @@ def test_norm_argument_errors():
     with pytest.raises(ValueError):
         ResidentNorm(None, x, kind="rms", beta=torch.zeros(64))
     with pytest.raises(ValueError):
-        ResidentNorm(None, x, precision="fp8")
+        ResidentNorm(None, x, precision="int8")
     with pytest.raises(ValueError):
         ResidentNorm(None, torch.randn(4, 40).bfloat16())
 

@@ -125,3 +125,31 @@ def test_checkpoint_identity():
         assert k != cache_key(after, {"steps": 5, "views": 3}, "observations-v1")
         with pytest.raises(ValueError):
             checkpoint_digest([])
+
+
+def test_timing_reducer_on_recorded_stamps():
+    """The per-stage reduction of instruction time stamps (``native_pi0.timing``) on a hand-made recording: three stages
+    over four workers, one worker idle, one instruction that never ran (zero stamps)."""
+    from native_pi0.timing import operation_report, stage_spans, stage_statistics, worker_spans
+    names = ["prefix.0.qkv", "prefix.0.attention", "prefix.1.qkv"]
+    code = np.zeros((4, 3, 32), dtype=np.int32)
+    stamps = np.zeros((4, 3, 8), dtype=np.int64)
+
+    def put(worker, slot, stage, start, ready, end):
+        code[worker, slot, :4] = (1, stage, 0, 1)
+        stamps[worker, slot, :3] = (start, ready, end)
+
+    put(0, 0, 0, 1000, 1100, 1600); put(1, 0, 0, 1000, 1150, 1700); put(2, 0, 0, 1000, 1100, 1500)
+    put(0, 1, 1, 1600, 1750, 2600); put(1, 1, 1, 1700, 1760, 2900)
+    put(2, 1, 2, 1500, 2950, 3300)
+    code[2, 2, :4] = (1, 2, 1, 1)                      # scheduled, but no stamps: ignored
+    spans = stage_spans(stamps, code, names)
+    assert spans == [("prefix.0.qkv", 0, 600, 3), ("prefix.0.attention", 650, 1800, 2), ("prefix.1.qkv", 1850, 2200, 1)]
+    stats = stage_statistics(stamps, code, names)
+    assert stats[0] == {"name": "prefix.0.qkv", "active_workers": 3, "instructions": 3, "busy_ns_median": 500, "busy_ns_max": 550}
+    assert stats[1]["busy_ns_max"] == 1140 and stats[2]["active_workers"] == 1
+    report = operation_report(stamps, code, names)
+    assert report["prefix"]["qkv"]["layers"] == 2 and report["prefix"]["attention"]["chain_ns_total"] == 1200
+    assert report["prefix"]["qkv"]["chain_ns_total"] == 400            # the second qkv ends 400 ns after the attention before it
+    assert worker_spans(stamps, code) == [1600, 1900, 2300]
+    assert stage_spans(np.zeros_like(stamps), code, names) == []
