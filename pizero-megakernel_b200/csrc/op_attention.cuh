@@ -510,18 +510,22 @@ template <int HDP>
 __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& a, int tile, uint8_t* data, uint32_t tmem,
                              uint32_t uses, int stage, long long* stamp);
 
+// LEAN: kernel variant for programs whose attention stages all run on the tcgen05 tiles (no mma.sync tile code).
+template <bool LEAN>
 __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem, uint32_t& tc_tiles,
                                                  const StageDesc& st, int stage_index, int first, int count, long long* stamp) {
     const AttnParams& a = st.p.attn;
     for (int t = first; t < first + count; ++t) {
         long long* stamp_t = t == first ? stamp : nullptr;
-        if (a.tc) {
+        if (LEAN || a.tc) {
             const bool ok = a.hd_pad > 128 ? attn_tile_tc<256>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t)
                                            : attn_tile_tc<128>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t);
             tc_tiles++;
             if (!ok) return;                                   // uniform: a wait gave up, the abort flag is set
-        } else if (a.head_dim > 128) attn_tile<256>(a, t, data, stamp_t);
-        else attn_tile<80>(a, t, data, stamp_t);
+        } else if constexpr (!LEAN) {
+            if (a.head_dim > 128) attn_tile<256>(a, t, data, stamp_t);
+            else attn_tile<80>(a, t, data, stamp_t);
+        }
         if (a.splits > 1 && a.fused_merge) {
             const int split = t % a.splits, group = t / a.splits;         // group: one head of one 128-query tile
             // The barrier orders every thread's partial stores before thread 0's release increment below, which

@@ -498,6 +498,9 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
 }
 
 // Dispatch of one GEMM instruction onto the warp roles. Warps 2 and 3 have no role and fall through.
+// LEAN: the kernel variant for programs made only of NVFP4 projections with the pi0 model's epilogues (the host checks
+// this when it builds a program); it carries neither the dense issue loops nor the other drain loops.
+template <bool LEAN>
 __device__ __forceinline__ void gemm_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem,
                                                  const StageDesc& st, int stage_index, int first, int count,
                                                  PipeState& ps, long long* stamp) {
@@ -507,20 +510,19 @@ __device__ __forceinline__ void gemm_instruction(const VmProgram& prog, Ctl* ctl
         if (stamp && threadIdx.x == 0) stamp[3] = static_cast<long long>(global_ns());
     } else if (warp == 1) {
         const int operands = st.p.gemm.operands;
-        if (operands == GEMM_NVFP4) gemm_mma<GEMM_NVFP4>(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
+        if (LEAN || operands == GEMM_NVFP4) gemm_mma<GEMM_NVFP4>(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
         else if (operands == GEMM_BF16) gemm_mma<GEMM_BF16>(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
         else gemm_mma<GEMM_FP8>(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
     } else if (warp >= 4) {
-        switch (st.p.gemm.epilogue) {                   // one drain loop per epilogue kind: only its own arithmetic and registers
-            case EPI_F32: gemm_epilogue<EPI_F32>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
-            case EPI_BF16: gemm_epilogue<EPI_BF16>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
-            case EPI_BF16_EXT: gemm_epilogue<EPI_BF16_EXT>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
-            case EPI_FP4: gemm_epilogue<EPI_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
-            case EPI_GEGLU_FP4: gemm_epilogue<EPI_GEGLU_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
-            case EPI_GEGLU_BF16: gemm_epilogue<EPI_GEGLU_BF16>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
-            case EPI_STREAM: gemm_epilogue<EPI_STREAM>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
-            default: gemm_epilogue<EPI_QKV_ROPE>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp); break;
-        }
+        const int epilogue = st.p.gemm.epilogue;            // one drain loop per epilogue kind: only its own arithmetic and registers
+        if (epilogue == EPI_BF16) gemm_epilogue<EPI_BF16>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (epilogue == EPI_STREAM) gemm_epilogue<EPI_STREAM>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (epilogue == EPI_GEGLU_FP4) gemm_epilogue<EPI_GEGLU_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (epilogue == EPI_FP4) gemm_epilogue<EPI_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (LEAN || epilogue == EPI_QKV_ROPE) gemm_epilogue<EPI_QKV_ROPE>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (epilogue == EPI_F32) gemm_epilogue<EPI_F32>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (epilogue == EPI_BF16_EXT) gemm_epilogue<EPI_BF16_EXT>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else gemm_epilogue<EPI_GEGLU_BF16>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         if (stamp && threadIdx.x == 128) stamp[2] = static_cast<long long>(global_ns());
     }
 }

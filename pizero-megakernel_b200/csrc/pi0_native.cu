@@ -138,6 +138,7 @@ struct Program {
     VmStatus* d_status = nullptr;
     long long* d_timings = nullptr;
     bool timings_on = false;
+    bool lean = false;                 // every stage is one the lean kernel variant runs
     unsigned int epoch = 0;
     unsigned long long budget_ns = 2000000000ull;
     int* h_debug = nullptr;            // host-mapped progress marks (enable_native_model_debug)
@@ -187,6 +188,18 @@ std::vector<int> compile_streams(const std::vector<std::pair<int, int>>& work, i
     for (int w = 0; w < workers; w++) std::copy(rows[w].begin(), rows[w].end(), code.begin() + static_cast<size_t>(w) * length * 4);
     *length_out = static_cast<int>(length);
     return code;
+}
+
+// Stages the lean kernel variant runs: NVFP4 projections with the model's epilogues, attention on the tcgen05 tiles, and
+// every operator without variants (norm, merge, patch, embed, FP32 linear, suffix).
+bool lean_stage(const StageDesc& d) {
+    if (d.kind == OP_GEMM) {
+        const GemmParams& g = d.p.gemm;
+        return g.operands == GEMM_NVFP4 && (g.epilogue == EPI_BF16 || g.epilogue == EPI_STREAM || g.epilogue == EPI_GEGLU_FP4 ||
+                                            g.epilogue == EPI_FP4 || g.epilogue == EPI_QKV_ROPE);
+    }
+    if (d.kind == OP_ATTN) return d.p.attn.tc != 0;
+    return true;
 }
 
 // Build a program from stage descriptors (sources already set) and compact int4 instructions.
@@ -270,9 +283,12 @@ int build_program(Program** out, int device, const std::vector<StageDesc>& stage
     if (e == cudaSuccess) {
         static bool configured[64] = {};
         if (device < 64 && !configured[device]) {
-            e = cudaFuncSetAttribute(pi0_vm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+            e = cudaFuncSetAttribute(pi0_vm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(pi0_vm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
             configured[device] = e == cudaSuccess;
         }
+        prog->lean = true;
+        for (const auto& d : prog->stages) prog->lean = prog->lean && lean_stage(d);
     }
     if (e != cudaSuccess) return e;
     *out = prog.release();
@@ -311,7 +327,8 @@ int launch_program(Program* prog, cudaStream_t stream, LaunchInputs in, int begi
     p.wait_budget_ns = prog->budget_ns;
     p.in = in;
     p.debug = prog->h_debug;
-    pi0_vm_kernel<<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
+    if (prog->lean) pi0_vm_kernel<true><<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
+    else pi0_vm_kernel<false><<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }
 
@@ -592,7 +609,7 @@ extern "C" int resident_fp4_resources(void* handle, int* values, int count) {
     Op* op = as_op(handle);
     if (!op || !values || count < 8) return cudaErrorInvalidValue;
     cudaFuncAttributes attr{};
-    cudaError_t e = cudaFuncGetAttributes(&attr, pi0_vm_kernel);
+    cudaError_t e = cudaFuncGetAttributes(&attr, pi0_vm_kernel<false>);
     if (e != cudaSuccess) return e;
     cudaDeviceProp prop{};
     e = cudaGetDeviceProperties(&prop, op->device);
@@ -911,7 +928,7 @@ extern "C" int destroy_attention(void* handle) { return destroy_checked(handle);
 extern "C" int attention_resources(int* values, int count) {
     if (!values || count < 4) return cudaErrorInvalidValue;
     cudaFuncAttributes attr{};
-    cudaError_t e = cudaFuncGetAttributes(&attr, pi0_vm_kernel);
+    cudaError_t e = cudaFuncGetAttributes(&attr, pi0_vm_kernel<false>);
     if (e != cudaSuccess) return e;
     values[0] = attr.numRegs;
     values[1] = static_cast<int>(attr.localSizeBytes);

@@ -45,6 +45,9 @@ __device__ __forceinline__ bool prefetch_slot(const VmProgram& prog, Ctl* ctl, c
     return true;
 }
 
+// LEAN = true: the variant for programs made of the pi0 model's own NVFP4 operators only (what build_program calls
+// lean); LEAN = false runs every operator and option.  Same VM, same protocol; the lean one is simply a smaller kernel.
+template <bool LEAN>
 __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_constant__ VmProgram prog) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -121,7 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         if (stamp && threadIdx.x == 0) stamp[0] = static_cast<long long>(global_ns());
         if (st.kind == OP_GEMM) {
             mark(prog, 800000 + ins.y);
-            gemm_instruction(prog, ctl, data, tmem, st, ins.y, ins.z, ins.w, ps, stamp);
+            gemm_instruction<LEAN>(prog, ctl, data, tmem, st, ins.y, ins.z, ins.w, ps, stamp);
             // one decision per warp: the lanes with a role return later than the others and must not leave alone
             if (__any_sync(0xffffffffu, ctl->abort != 0)) break;
         } else {
@@ -146,7 +149,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
             if (!cta_wait_sources(prog, ctl, st, ins.y, ins.z, ins.w, stamp)) break;
             switch (st.kind) {
                 case OP_NORM: norm_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
-                case OP_ATTN: attn_instruction(prog, ctl, data, tmem, tc_tiles, st, ins.y, ins.z, ins.w, stamp); break;
+                case OP_ATTN: attn_instruction<LEAN>(prog, ctl, data, tmem, tc_tiles, st, ins.y, ins.z, ins.w, stamp); break;
                 case OP_MERGE: merge_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
                 case OP_PATCH: patch_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
                 case OP_EMBED: embed_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
