@@ -28,6 +28,7 @@ from __future__ import annotations
 import math
 from dataclasses import dataclass
 
+import numpy as np
 import torch
 import torch.nn.functional as F
 
@@ -515,11 +516,11 @@ class Pi0Torch:
         prefix_rows = caches[0][0].shape[0]
         state_emb = F.linear(state.float(), self.sd["state_proj.weight"].float(), self.sd["state_proj.bias"].float())
         x = noise[0].float().clone()
-        t = torch.tensor(1.0, dtype=torch.float32)
-        dt = torch.tensor(-1.0 / steps, dtype=torch.float32)
+        # FP32 time and step, kept on the host (no host-to-device copy inside the loop: the pass can be captured in a CUDA graph)
+        t, dt = np.float32(1.0), np.float32(-1.0 / steps)
         for step in range(steps):
             v = self.denoise_step(caches, state_emb, x, float(t), prefix_rows, tag=step)
-            x = x + dt.to(x.device) * v
+            x = x + float(dt) * v
             self.landmarks[f"actions.{step}"] = x.clone()
-            t = t + dt
+            t = np.float32(t + dt)
         return x[None]
