@@ -161,12 +161,19 @@ int configure_attention_splits(void* handle, int splits);
 int configure_attention_fused_merge(void* handle, int enable);
 /* Read keys/values from a KV cache [rows, head_dim] (BF16) instead of k/v; rows = total keys visible. */
 int configure_attention_cache(void* handle, const void* cache_k, const void* cache_v, int rows, int prefix_rows);
-/* extension: also quantise the output rows to NVFP4 (head_dim 256 only). */
+/* extension: also quantise the output rows to NVFP4: every head occupies `pitch` columns of the FP4 rows (head_dim unless
+ * configure_attention_fp4_pitch was called first), ld_bytes >= heads * pitch / 2, out_blocks >= heads * pitch / 16. */
 int configure_attention_fp4_output(void* handle, void* out_fp4, void* scales, int ld_bytes, int out_blocks,
                                    float global_scale);
+/* extension: head pitch of the FP4 output (a multiple of 16 with head_dim <= pitch <= the padded head size of
+ * configure_attention_head_pad); columns from head_dim up to the pitch are stored as zeros, so a projection whose weight has
+ * zero columns at the same places reads the rows as they are - 72-wide SigLIP heads on an 80-column pitch feed the output
+ * projection without a separate quantisation stage.  Before configure_attention_fp4_output; a pitch other than head_dim
+ * exists only in the unsplit tcgen05 tiles (cudaErrorInvalidValue otherwise). */
+int configure_attention_fp4_pitch(void* handle, int pitch);
 /* extension: tile implementation.  -1 (default) picks the tcgen05 tiles (Q, K, V by TMA, S / P / O in tensor memory)
  * whenever the geometry allows them - heads that occupy 128 or 256 elements in memory, at most 256 keys per tile (use KV
- * splits beyond that), no fused NVFP4 output without splits - and the mma.sync tiles otherwise; 0 forces the mma.sync
+ * splits beyond that) - and the mma.sync tiles otherwise; 0 forces the mma.sync
  * tiles, 1 the tcgen05 tiles (cudaErrorInvalidValue when the geometry does not allow them). */
 int configure_attention_path(void* handle, int path);
 /* extension: every head occupies `elements` (128 or 256) elements in q, k and v, zeros beyond head_dim (what a projection
@@ -263,6 +270,10 @@ int read_native_model_timings(void* handle, long long* out, size_t count);
 int read_native_model_status(void* handle, int* values, int count);
 /* extension: counters uint32 [n] and the expected value per counter for the current epoch. */
 int read_native_model_counters(void* handle, unsigned int* counts, unsigned int* expected, int n, int* total);
+/* extension: which kernel variant the program launches: *lean = 1 for the smaller kernel that carries only the NVFP4
+ * projections with the pi0 model's epilogues and the tcgen05 attention tiles (chosen when every stage allows it), 0 for
+ * the kernel with every operator and option.  Same protocol, same results. */
+int native_model_kernel_variant(void* handle, int* lean);
 /* extension (debugging): host-mapped progress marks, one word per warp of every worker, written as the warp moves
  * through its instruction loop; readable while a launch is still running.  Off by default. */
 int enable_native_model_debug(void* handle, int enable);

@@ -226,12 +226,15 @@ def site_of(parameter):
 
 class Pi0Torch:
     def __init__(self, dims: Pi0Dims, state_dict, mode="bf16", compute_dtype=torch.bfloat16, rope_inv_freq_dtype=torch.float32,
-                 precision=None, fold_norms=True):
+                 precision=None, fold_norms=True, head_blocks=True):
         """``precision`` (mode "nvfp4" only): dict of fnmatch patterns over site names -> "nvfp4" | "bf16" with an optional
         "default", as the engine takes it; BF16 sites multiply BF16 operands with FP32 accumulation and round the way the
         engine's BF16 epilogues do.  ``fold_norms`` (mode "nvfp4"): an RMSNorm between two NVFP4 projections is evaluated
         the way the engine folds it - the un-normalised BF16 rows are quantised, the weight columns carry ``1 + w`` and
-        the accumulator rows are multiplied by ``rsqrt(mean square + eps)``."""
+        the accumulator rows are multiplied by ``rsqrt(mean square + eps)``.  ``head_blocks`` (mode "nvfp4"): the SigLIP
+        attention rows and the output projection's weight are quantised with every 72-wide head on a pitch of 80 columns,
+        i.e. in blocks that do not straddle heads, as the engine's tensor-core attention tiles write them; False keeps
+        the plain 16-column partition of the 1152-wide rows (the engine with ``attention_path="mma.sync"``)."""
         assert mode in ("bf16", "nvfp4")
         self.d, self.sd, self.mode = dims, state_dict, mode
         precision = precision or {}
@@ -241,6 +244,7 @@ class Pi0Torch:
         self._precision_default = precision.get("default", "nvfp4")
         self._site_cache = {}
         self.fold_norms = bool(fold_norms) and mode == "nvfp4"
+        self.head_blocks = bool(head_blocks) and mode == "nvfp4"
         self.dt = compute_dtype                 # activation dtype of the bf16 mode (float32 for a fast CPU baseline)
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self._wq = {}
@@ -310,9 +314,10 @@ class Pi0Torch:
         """True when the norm between the projections ``producer`` and ``consumer`` (parameter prefixes) is folded."""
         return self.fold_norms and not self.bf16_site(producer) and not self.bf16_site(consumer)
 
-    def linear(self, x, name, bias=True, weight=None):
+    def linear(self, x, name, bias=True, weight=None, head=None):
         """BF16 mode: y = x W^T + b in the activation dtype.  NVFP4 mode: FP32 accumulator of fake-quantised
-        operands (+ bias), *not yet rounded* - the caller applies the epilogue."""
+        operands (+ bias), *not yet rounded* - the caller applies the epilogue.  ``head=(width, pitch)``: the K axis
+        is made of heads ``width`` wide that are quantised on a pitch of ``pitch`` columns (zeros between them)."""
         w = self.sd[name + ".weight"] if weight is None else weight
         b = self.sd.get(name + ".bias") if bias else None
         if self.mode == "bf16":
@@ -320,7 +325,15 @@ class Pi0Torch:
         if self.bf16_site(name):
             y = x.to(torch.bfloat16).float() @ w.to(torch.bfloat16).float().T
             return y if b is None else y + b.to(torch.bfloat16).float()
-        wq = self._qweight(name, w)
+        if head is not None:
+            width, pitch = head
+            spread = lambda t: F.pad(t.float().reshape(t.shape[0], -1, width), (0, pitch - width)).reshape(t.shape[0], -1)
+            x = spread(x)
+            if (name, "spread") not in self._wq:
+                self._wq[(name, "spread")] = fake_quant(pad_cols(spread(w), 64), "ceil", weight_global_scale(w))
+            wq = self._wq[(name, "spread")]
+        else:
+            wq = self._qweight(name, w)
         xq = fake_quant(pad_cols(x.float(), 64), "nearest", 1.0)
         y = xq @ wq.T
         return y if b is None else y + b.float()
@@ -373,7 +386,7 @@ class Pi0Torch:
                                            v[sl].reshape(256, d.vision_heads, hd), hd ** -0.5))
             a = torch.cat(outs).reshape(-1, d.vision_width)
             self.rec(f"vision.{i}.attention", a)
-            o = self.linear(a, p + "self_attn.out_proj")
+            o = self.linear(a, p + "self_attn.out_proj", head=(hd, -(-hd // 16) * 16) if self.head_blocks and hd % 16 else None)
             x = self.add_residual(o, x, p + "self_attn.out_proj")
             self.rec(f"vision.{i}.out", x)
             y = F.layer_norm(x.float(), (d.vision_width,), sd[p + "layer_norm2.weight"].float(), sd[p + "layer_norm2.bias"].float(), d.ln_eps).to(x.dtype)

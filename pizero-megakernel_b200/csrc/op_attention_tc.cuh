@@ -230,6 +230,25 @@ __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& 
                                        pack2_bf16(__uint_as_float(raw[8 * u + 6]) * inv, __uint_as_float(raw[8 * u + 7]) * inv));
                 }
             }
+            if (a.out_fp4 && row_ok) {
+                // NVFP4 copy of the BF16-rounded rows: every head occupies fp4_pitch columns (a multiple of 16 >= head_dim;
+                // the accumulator columns beyond head_dim are exact zeros because V is zero there)
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+                    const int cb = c0 + 16 * half;
+                    if (cb < a.fp4_pitch) {
+                        float v[16];
+#pragma unroll
+                        for (int e = 0; e < 16; e++)
+                            v[e] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(raw[16 * half + e]) * inv)) * a.out_inv_gs;
+                        uint32_t code;
+                        const uint2 bytes = quantize_block16(v, 0, code);
+                        const int col = head * a.fp4_pitch + cb;
+                        *reinterpret_cast<uint2*>(a.out_fp4 + grow * a.ld_fp4 + (col >> 1)) = bytes;
+                        a.out_scales[scale_offset(static_cast<int>(grow), col >> 4, a.out_blocks)] = static_cast<uint8_t>(code);
+                    }
+                }
+            }
         }
     }
     tc_fence_before();

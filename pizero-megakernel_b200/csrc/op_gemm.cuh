@@ -519,9 +519,9 @@ __device__ __forceinline__ void gemm_instruction(const VmProgram& prog, Ctl* ctl
         else if (epilogue == EPI_STREAM) gemm_epilogue<EPI_STREAM>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         else if (epilogue == EPI_GEGLU_FP4) gemm_epilogue<EPI_GEGLU_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         else if (epilogue == EPI_FP4) gemm_epilogue<EPI_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
-        else if (LEAN || epilogue == EPI_QKV_ROPE) gemm_epilogue<EPI_QKV_ROPE>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (epilogue == EPI_QKV_ROPE) gemm_epilogue<EPI_QKV_ROPE>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (LEAN || epilogue == EPI_BF16_EXT) gemm_epilogue<EPI_BF16_EXT>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         else if (epilogue == EPI_F32) gemm_epilogue<EPI_F32>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
-        else if (epilogue == EPI_BF16_EXT) gemm_epilogue<EPI_BF16_EXT>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         else gemm_epilogue<EPI_GEGLU_BF16>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         if (stamp && threadIdx.x == 128) stamp[2] = static_cast<long long>(global_ns());
     }

@@ -196,7 +196,7 @@ bool lean_stage(const StageDesc& d) {
     if (d.kind == OP_GEMM) {
         const GemmParams& g = d.p.gemm;
         return g.operands == GEMM_NVFP4 && (g.epilogue == EPI_BF16 || g.epilogue == EPI_STREAM || g.epilogue == EPI_GEGLU_FP4 ||
-                                            g.epilogue == EPI_FP4 || g.epilogue == EPI_QKV_ROPE);
+                                            g.epilogue == EPI_FP4 || g.epilogue == EPI_QKV_ROPE || g.epilogue == EPI_BF16_EXT);
     }
     if (d.kind == OP_ATTN) return d.p.attn.tc != 0;
     return true;
@@ -865,9 +865,11 @@ static int attention_geometry(Op* op) {
     const int per = (a.nk + a.splits - 1) / a.splits;
     const bool layout_ok = (a.hd_pad == 128 || a.hd_pad == 256) && a.hd_pad >= a.head_dim && a.head_dim % 8 == 0 &&
                            a.ldq >= a.heads * a.hd_pad && a.ldkv >= a.kv_heads * a.hd_pad;
-    const bool eligible = layout_ok && per <= 256 && !(a.splits == 1 && a.out_fp4) && (a.splits == 1 || a.head_dim == a.hd_pad);
+    const bool eligible = layout_ok && per <= 256 && (a.splits == 1 || a.head_dim == a.hd_pad);
     a.tc = op->attn_path == 0 ? 0 : eligible ? 1 : 0;
     if (op->attn_path == 1 && !eligible) return cudaErrorInvalidValue;
+    // an FP4 output on a head pitch other than head_dim exists only in the unsplit tcgen05 tile
+    if (a.out_fp4 && a.fp4_pitch != a.head_dim && !(a.tc && a.splits == 1)) return cudaErrorInvalidValue;
     if (!a.tc) return cudaSuccess;
     a.q_box = std::min(128, (std::min(a.nq, 128) + 7) / 8 * 8);
     a.k_box = std::min(256, (per + 15) / 16 * 16);
@@ -913,6 +915,7 @@ extern "C" int create_attention(void** handle, const void* q, const void* k, con
     a.prefix = prefix >= 0 ? prefix : -1;
     a.splits = 1;
     a.out_inv_gs = 1.f;
+    a.fp4_pitch = head_dim;
     a.hd_pad = head_dim == 256 ? 256 : 0;           // other head sizes use the tensor-core tiles only in a padded layout
     e = attention_geometry(op);
     if (e) { free_op(op); return e; }
@@ -1052,13 +1055,25 @@ extern "C" int configure_attention_fp4_output(void* handle, void* out_fp4, void*
     Op* op = as_op(handle);
     if (!op || op->desc.kind != OP_ATTN || !out_fp4 || !scales || !std::isfinite(global_scale) || global_scale <= 0) return cudaErrorInvalidValue;
     AttnParams& a = op->desc.p.attn;
-    if (a.head_dim % 16 || ld_bytes < a.heads * a.head_dim / 2 || out_blocks < a.heads * a.head_dim / 16) return cudaErrorInvalidValue;
+    if (a.fp4_pitch % 16 || ld_bytes < a.heads * a.fp4_pitch / 2 || out_blocks < a.heads * a.fp4_pitch / 16) return cudaErrorInvalidValue;
     a.out_fp4 = static_cast<uint8_t*>(out_fp4); a.out_scales = static_cast<uint8_t*>(scales);
     a.ld_fp4 = ld_bytes; a.out_blocks = out_blocks; a.out_inv_gs = 1.f / global_scale;
     if (op->merge) {
         MergeParams& g = op->merge->desc.p.merge;
         g.out_fp4 = a.out_fp4; g.out_scales = a.out_scales; g.ld_fp4 = ld_bytes; g.out_blocks = out_blocks; g.out_inv_gs = a.out_inv_gs;
     }
+    return attention_geometry(op);
+}
+// extension: columns one head occupies in the FP4 output (a multiple of 16, head_dim <= pitch <= the padded head size).  The
+// columns from head_dim up to the pitch are written as zeros, so a following projection whose K is heads * pitch (zero weight
+// columns at the same places) reads the output directly.  Set it before configure_attention_fp4_output; only the unsplit
+// tcgen05 tiles offer a pitch other than head_dim.
+extern "C" int configure_attention_fp4_pitch(void* handle, int pitch) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN) return cudaErrorInvalidValue;
+    AttnParams& a = op->desc.p.attn;
+    if (pitch % 16 || pitch < a.head_dim || (pitch != a.head_dim && pitch > a.hd_pad) || a.out_fp4) return cudaErrorInvalidValue;
+    a.fp4_pitch = pitch;
     return attention_geometry(op);
 }
 // extension: choose the tile implementation: -1 by geometry (default), 0 mma.sync tiles, 1 tcgen05 tiles (an error when the
@@ -1313,6 +1328,14 @@ extern "C" int read_native_model_counters(void* handle, unsigned int* counts, un
     }
     if (expected)
         for (int i = 0; i < have; i++) expected[i] = prog->expected[i] * prog->epoch;
+    return cudaSuccess;
+}
+// extension: the kernel variant a program launches: 1 = the lean kernel (NVFP4 projections with the model's epilogues and
+// tcgen05 attention only), 0 = the kernel with every operator and option.
+extern "C" int native_model_kernel_variant(void* handle, int* lean) {
+    Program* prog = as_program(handle);
+    if (!prog || !lean) return cudaErrorInvalidValue;
+    *lean = prog->lean ? 1 : 0;
     return cudaSuccess;
 }
 extern "C" int enable_native_model_debug(void* handle, int enable) {

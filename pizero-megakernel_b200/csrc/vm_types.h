@@ -144,6 +144,7 @@ struct AttnParams {
     int out_blocks;
     float out_inv_gs;
     int ld_fp4;
+    int fp4_pitch;               // columns one head occupies in the FP4 output (a multiple of 16 >= head_dim; tcgen05 tiles only otherwise head_dim)
     // splits > 1 with the merge inside the attention stage: one arrival ticket per (128-query tile, head); once all
     // splits of a group have arrived every tile merges its share of the rows. Tickets are program counters (they grow
     // by `splits` per launch and are reset with them); 0 / null selects the separate OP_MERGE stage

@@ -85,6 +85,7 @@ _SIGNATURES = {
     "configure_attention_fp4_output": [_P, _P, _P, _I, _I, _F],
     "configure_attention_path": [_P, _I],
     "configure_attention_head_pad": [_P, _I],
+    "configure_attention_fp4_pitch": [_P, _I],
     "attention_merge_handle": [_P, C.POINTER(_P)],
     "attention_poison_partials": [_P, _P],
     "attention_split_diagnostics": [_P, _P, _I, C.POINTER(C.c_uint)],
@@ -103,6 +104,7 @@ _SIGNATURES = {
     "read_native_model_timings": [_P, _P, C.c_size_t],
     "read_native_model_status": [_P, C.POINTER(_I), _I],
     "read_native_model_counters": [_P, _P, _P, _I, C.POINTER(_I)],
+    "native_model_kernel_variant": [_P, C.POINTER(_I)],
     "enable_native_model_debug": [_P, _I],
     "read_native_model_debug": [_P, C.POINTER(_I), _I],
     "set_native_model_wait_budget": [_P, C.c_ulonglong],

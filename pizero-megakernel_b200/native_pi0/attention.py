@@ -20,7 +20,7 @@ from native_pi0 import _native
 class ResidentAttention:
     def __init__(self, library, q, k, v, *, workers=16, scale=None, prefix=None, splits=1, kv_cache=None,
                  cached_prefix_rows=0, output=None, q_bias=None, k_bias=None, v_bias=None, q_rope=None,
-                 k_rope=None, mask=None, fp4_output=None, fused_merge=False, path=None, head_dim=None):
+                 k_rope=None, mask=None, fp4_output=None, fused_merge=False, path=None, head_dim=None, fp4_pitch=None):
         if any(x is not None for x in (q_bias, k_bias, v_bias, q_rope, k_rope, mask)):
             raise ValueError("Biases, RoPE tables and boolean masks are fused elsewhere in the NVFP4 engine")
         for t in (q, k, v):
@@ -63,8 +63,11 @@ class ResidentAttention:
                                                                          cached_prefix_rows), "Native attention cache")
                 if fp4_output is not None:
                     data, scales, gs = fp4_output
+                    pitch = d if fp4_pitch is None else int(fp4_pitch)
+                    if pitch != d:
+                        _native.check(self.library.configure_attention_fp4_pitch(self.handle, pitch), "Native attention FP4 head pitch")
                     _native.check(self.library.configure_attention_fp4_output(
-                        self.handle, data.data_ptr(), scales.data_ptr(), data.stride(0), h * d // 16, float(gs)),
+                        self.handle, data.data_ptr(), scales.data_ptr(), data.stride(0), h * pitch // 16, float(gs)),
                         "Native attention FP4 output")
                 if splits != 1:
                     _native.check(self.library.configure_attention_splits(self.handle, int(splits)), "Native attention splits")

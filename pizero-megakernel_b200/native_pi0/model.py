@@ -431,6 +431,15 @@ class NativePi0:
         qkv = [self.tensor((M, 3 * WP)), self.tensor((M, 3 * WP))]
         a_att.bf16 = self.tensor((M, W))                    # the attention stage always writes BF16 rows
         att = a_att.bf16
+        # NVFP4 rows for the output projection straight from the tensor-core attention tiles: every head on a pitch of 80
+        # columns (the next multiple of the 16-element scale block), the projection's weight with zero columns to match
+        fp4_pitch = padded(hd, 16)
+        a_att_fp4 = Activation(self, M, c.vision_heads * fp4_pitch)
+
+        def spread_heads(w):
+            wide = torch.zeros((w.shape[0], c.vision_heads, fp4_pitch), device=w.device, dtype=w.dtype)
+            wide[:, :, :hd] = w.view(w.shape[0], c.vision_heads, hd)
+            return wide.view(w.shape[0], -1)
         for i in range(c.vision_layers):
             p = f"{VISION}encoder.layers.{i}."
             p_qkv, p_out, p_fc1, p_fc2 = [self.site(f"vision.{i}.{n}") for n in ("qkv", "out", "fc1", "fc2")]
@@ -438,7 +447,11 @@ class NativePi0:
             g2, b2 = sd[p + "layer_norm2.weight"].float().contiguous(), sd[p + "layer_norm2.bias"].float().contiguous()
             wqkv = self.cached(p + "qkv." + p_qkv, lambda: self.weight(torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"]), precision=p_qkv))
             bqkv = torch.cat([sd[p + f"self_attn.{n}_proj.bias"] for n in "qkv"]).to(torch.bfloat16).contiguous()
-            wo = self.cached(p + "out." + p_out, lambda: self.weight(sd[p + "self_attn.out_proj.weight"], precision=p_out))
+            quant_in_tile = padded_heads and p_out == "nvfp4"
+            if quant_in_tile:
+                wo = self.cached(p + "out.nvfp4.spread", lambda: self.weight(spread_heads(sd[p + "self_attn.out_proj.weight"])))
+            else:
+                wo = self.cached(p + "out." + p_out, lambda: self.weight(sd[p + "self_attn.out_proj.weight"], precision=p_out))
             bo = sd[p + "self_attn.out_proj.bias"].to(torch.bfloat16).contiguous()
             w1 = self.cached(p + "fc1." + p_fc1, lambda: self.weight(sd[p + "mlp.fc1.weight"], precision=p_fc1))
             bias1 = torch.zeros(mlp_pad, device=self.device, dtype=torch.bfloat16)
@@ -458,12 +471,20 @@ class NativePi0:
             self._own(h)
             if padded_heads:
                 _native.check(lib.configure_attention_head_pad(h, pitch), "vision attention")
+            outs = [StageOutput(f"vision.{i}.attention", "bf16", att, M, W)]
+            if quant_in_tile:
+                fp4 = a_att_fp4.require("nvfp4").fp4
+                _native.check(lib.configure_attention_fp4_pitch(h, fp4_pitch), "vision attention")
+                _native.check(lib.configure_attention_fp4_output(h, fp4.data.data_ptr(), fp4.scales.data_ptr(), fp4.data.stride(0),
+                                                                 fp4.k // 16, fp4.global_scale), "vision attention")
+                outs.append(StageOutput(f"vision.{i}.attention", "fp4", fp4, M, c.vision_heads * fp4_pitch, head=(hd, fp4_pitch)))
             self._attention_path(h, "vision attention")
-            s_att = self.add(1, h, f"vision.{i}.attention", [(s_qkv, ALL)], [StageOutput(f"vision.{i}.attention", "bf16", att, M, W)])
-            if p_out == "nvfp4":
-                # the 72-wide heads do not quantise inside the attention stage: a quantiser stage of its own
+            s_att = self.add(1, h, f"vision.{i}.attention", [(s_qkv, ALL)], outs)
+            if p_out == "nvfp4" and not quant_in_tile:
+                # the mma.sync tiles do not quantise 72-wide heads: a quantiser stage of its own
                 s_att = self.norm(f"vision.{i}.attention_quant", att, a_att.only("nvfp4"), rows=M, sources=[(s_att, SAME)], kind="none")
-            s_o = self.gemm(f"vision.{i}.out", a_att, wo, rows=M, sources=[(s_att, SAME)], out=xb, bias=bo, residual=xa)
+            s_o = self.gemm(f"vision.{i}.out", a_att_fp4 if quant_in_tile else a_att, wo, rows=M, sources=[(s_att, SAME)], out=xb,
+                            bias=bo, residual=xa)
             s_ln2 = self.norm(f"vision.{i}.ln2", xb, a_ln2.only(p_fc1), rows=M, sources=[(s_o, SAME)], kind="layer", gamma=g2, beta=b2, eps=c.ln_eps)
             s_fc1 = self.gemm(f"vision.{i}.fc1", a_ln2, w1, rows=M, sources=[(s_ln2, SAME)], out_act=a_h.require(p_fc2), out_precision=p_fc2,
                               bias=bias1, activation=1, act_cols=c.vision_mlp)
@@ -731,6 +752,9 @@ class NativePi0:
         specs = (NativeSpec * len(self.stages))(*self.stages)
         _native.check(lib.create_native_model(C.byref(self.handle), len(specs), C.cast(specs, C.c_void_p), self.code.ctypes.data,
                                               self.workers, self.code.shape[1]), "Native pi0 setup")
+        lean = C.c_int()
+        _native.check(lib.native_model_kernel_variant(self.handle, C.byref(lean)), "Native pi0 setup")
+        self.plan["kernel"] = "lean" if lean.value else "full"      # which variant of the persistent kernel the program launches
         if self.verbose:
             print("NativePi0 static program:", self.plan, flush=True)
 

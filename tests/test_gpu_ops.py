@@ -545,6 +545,38 @@ def test_attention_fused_fp4_output():
         np.testing.assert_array_equal(unswizzle_scales(scales.cpu().numpy(), 128, h * hd // 16), ref.scales)
 
 
+@pytest.mark.parametrize("b,nq,nk,h,hd,stored,pitch", [(1, 100, 200, 8, 256, 256, 256), (3, 256, 256, 16, 72, 128, 80), (1, 40, 100, 4, 72, 128, 80)])
+def test_attention_tensor_core_fp4_output(b, nq, nk, h, hd, stored, pitch):
+    """NVFP4 rows straight from the unsplit tcgen05 tile: the quantiser of the BF16 rows the same launch stores, with every
+    head on `pitch` columns (72-wide SigLIP heads on 80: zeros behind each head, no block straddles two heads)."""
+    torch.manual_seed(17 + nq)
+    def heads(rows):
+        t = torch.zeros(b, rows, h, stored)
+        t[..., :hd] = torch.randn(b, rows, h, hd)
+        return t.bfloat16().cuda()
+    q, k, v = heads(nq), heads(nk), heads(nk)
+    rows = b * nq
+    rows_pad = (rows + 127) // 128 * 128
+    data = torch.zeros(rows_pad, h * pitch // 2, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros((rows_pad // 128) * (h * pitch // 64) * 512, dtype=torch.uint8, device="cuda")
+    with ResidentAttention(None, q, k, v, workers=148, head_dim=hd, fp4_output=(data, scales, 0.5), fp4_pitch=pitch, path="tcgen05") as op:
+        for _ in range(2):
+            out = op.forward().float().cpu().numpy().reshape(rows, h, hd)
+            assert op.status()["code"] == 0
+    want = oracle_ops.attention(q[..., :hd], k[..., :hd], v[..., :hd], hd ** -0.5, None).numpy().reshape(rows, h, hd)
+    assert relrms(out, want) <= 1e-2
+    spread = np.zeros((rows, h, pitch), dtype=np.float32)
+    spread[..., :hd] = out
+    ref = pack_nvfp4(spread.reshape(rows, h * pitch), global_scale=0.5, row_alignment=128)
+    np.testing.assert_array_equal(data.cpu().numpy()[:rows], ref.data[:rows])
+    np.testing.assert_array_equal(unswizzle_scales(scales.cpu().numpy(), rows_pad, h * pitch // 16)[:rows], ref.scales[:rows])
+    if pitch != hd:
+        with pytest.raises(RuntimeError):                   # only the unsplit tcgen05 tile writes a pitch other than head_dim
+            ResidentAttention(None, q, k, v, head_dim=hd, fp4_output=(data, scales, 0.5), fp4_pitch=pitch, path="mma.sync")
+        with pytest.raises(RuntimeError):
+            ResidentAttention(None, q, k, v, head_dim=hd, fp4_output=(data, scales, 0.5), fp4_pitch=72)
+
+
 def test_small_operators():
     lib = _native.load()
     torch.manual_seed(11)
