@@ -92,75 +92,98 @@ __device__ __forceinline__ void embed_instruction(const VmProgram& prog, Ctl* ct
     }
 }
 
-// out[r, n] = f(sum_k x[r, k] * W[n, k]) in FP32.  A tile is 16 output columns for a block of rows (64; 32 or 16 when
-// that still leaves every tile a CTA of its own: each tile stages all of its x rows, so shorter blocks mean fewer
-// bytes per CTA, and an operator with few columns would otherwise occupy one or two CTAs). K runs in chunks of 128 through a four-deep
+// out[r, n] = f(sum_k x[r, k] * W[n, k]) in FP32.  A tile is 16 output columns for a block of 32 rows (16 for an operator
+// with few rows or few columns, which would otherwise occupy one or two CTAs). K runs in chunks of 128 through a four-deep
 // cp.async ring in shared memory (x rows as stored, FP32 or BF16, and the 16 weight rows), so the L2 latency of a
-// chunk is paid once per tile, not once per chunk. Thread (col = tid % 16, ty = tid / 16) owns rows ty, ty + 16, ...
-// of its column; every shared-memory read is a 16-byte broadcast or conflict-free access.
+// chunk is paid once per tile, not once per chunk.
+//
+// With eight warps per SM the operator is bound by instruction issue, so the inner loop is built for few instructions:
+// every warp owns one eighth of each K chunk (16 values) and computes the WHOLE tile for it - lane (rg = lane / 4,
+// cg = lane % 4) holds rows rg, rg + 8, ... and columns cg, cg + 4, cg + 8, cg + 12 - with packed FP32 multiply-adds
+// (fma.rn.f32x2: two products per instruction, accumulated as separate even / odd partial sums).  A step of four k
+// values costs RT + 4 16-byte shared-memory reads (conflict-free: rows are 132 floats apart) for 8 RT packed
+// multiply-adds.  The eight partial tiles meet in shared memory at the end and are added in a fixed order.
 constexpr int kLinCols = 16;
-constexpr int kLinRows = 64;
+constexpr int kLinRows = 32;
 constexpr int kLinChunk = 128;
 constexpr int kLinLd = kLinChunk + 4;                                  // floats per staged row (padded)
 constexpr int kLinStages = 4;
 constexpr int kLinStageBytes = (kLinRows + kLinCols) * kLinLd * 4;     // x block + weight rows
 static_assert(kLinStages * kLinStageBytes <= kDataBytes, "linear32 ring exceeds the data region");
+static_assert(8 * (kLinRows * kLinCols + kLinRows) * 4 <= kLinStages * kLinStageBytes, "partial sums exceed the ring");
 
-__device__ __forceinline__ void linear32_issue(const Linear32Params& p, const void* xbase, uint8_t* stage, int col0, int r0,
-                                               int row_block, int kc) {
-    const int kw = min(kLinChunk, p.k - kc);
-    float* xs = reinterpret_cast<float*>(stage);
-    float* ws = xs + kLinRows * kLinLd;
-    if (p.x_bf16) {
-        // BF16 rows are staged as stored (8 elements per 16-byte copy) in the first half of each padded row
-        const int per_row = kw >> 3;
-        const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(xbase);
-        for (int i = threadIdx.x; i < row_block * per_row; i += kThreads) {
-            const int r = i / per_row, c = i - r * per_row;
-            const bool ok = r0 + r < p.rows;
-            const __nv_bfloat16* from = ok ? src + static_cast<size_t>(r0 + r + p.x_row_offset) * p.ldx + kc + c * 8 : src;
-            cp_async16(reinterpret_cast<__nv_bfloat16*>(xs + r * kLinLd) + c * 8, from, ok);
-        }
-    } else {
-        const int per_row = kw >> 2;
-        const float* src = static_cast<const float*>(xbase);
-        for (int i = threadIdx.x; i < row_block * per_row; i += kThreads) {
-            const int r = i / per_row, c = i - r * per_row;
-            const bool ok = r0 + r < p.rows;
-            const float* from = ok ? src + static_cast<size_t>(r0 + r + p.x_row_offset) * p.ldx + kc + c * 4 : src;
-            cp_async16(xs + r * kLinLd + c * 4, from, ok);
-        }
-    }
-    const int per_row = kw >> 2;
-    for (int i = threadIdx.x; i < kLinCols * per_row; i += kThreads) {
-        const int r = i / per_row, c = i - r * per_row;
-        const bool ok = col0 + r < p.n;
-        const float* from = ok ? p.w + static_cast<size_t>(col0 + r) * p.k + kc + c * 4 : p.w;
-        cp_async16(ws + r * kLinLd + c * 4, from, ok);
-    }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;"
+        : "=l"(d)
+        : "l"(*reinterpret_cast<const uint64_t*>(&a)), "l"(*reinterpret_cast<const uint64_t*>(&b)), "l"(*reinterpret_cast<const uint64_t*>(&c)));
+    return *reinterpret_cast<float2*>(&d);
 }
 
-// Four groups of 64 threads split every K chunk between them; inside a group thread (tx = t % 4, ty = t / 4) owns
-// columns 4 tx .. 4 tx + 3 of rows ty, ty + 16, ... (16 R outputs), so a step of four k values costs 4 + R 16-byte
-// shared-memory reads for 16 R fused multiply-adds (the operator is bound by shared-memory bandwidth, not by the
-// FP32 pipe). The four partial sums of an output meet in shared memory at the end and are added in a fixed order.
-template <int R>
+// Geometry of one tile, read once from the (shared-memory) descriptor.
+struct LinTile {
+    const void* x;
+    const float* w;
+    int rows, n, k, ldx, x_row_offset, x_bf16;
+    int col0, r0;
+};
+
+// One K chunk into a ring stage: warp w copies rows w, w + 8, ...; lane l the l-th 16-byte piece of the row.
+__device__ __forceinline__ void linear32_issue(const LinTile& t, uint8_t* stage, int row_block, int kc) {
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    const int kw = min(kLinChunk, t.k - kc);
+    float* xs = reinterpret_cast<float*>(stage);
+    float* ws = xs + kLinRows * kLinLd;
+    if (t.x_bf16) {
+        // BF16 rows are staged as stored (8 elements per 16-byte copy) in the first half of each padded row
+        const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(t.x);
+        if (lane < (kw >> 3))
+            for (int r = warp; r < row_block; r += 8) {
+                const bool ok = t.r0 + r < t.rows;
+                const __nv_bfloat16* from = ok ? src + static_cast<size_t>(t.r0 + r + t.x_row_offset) * t.ldx + kc + lane * 8 : src;
+                cp_async16(reinterpret_cast<__nv_bfloat16*>(xs + r * kLinLd) + lane * 8, from, ok);
+            }
+    } else {
+        const float* src = static_cast<const float*>(t.x);
+        if (lane < (kw >> 2))
+            for (int r = warp; r < row_block; r += 8) {
+                const bool ok = t.r0 + r < t.rows;
+                const float* from = ok ? src + static_cast<size_t>(t.r0 + r + t.x_row_offset) * t.ldx + kc + lane * 4 : src;
+                cp_async16(xs + r * kLinLd + lane * 4, from, ok);
+            }
+    }
+    if (lane < (kw >> 2))
+        for (int r = warp; r < kLinCols; r += 8) {
+            const bool ok = t.col0 + r < t.n;
+            const float* from = ok ? t.w + static_cast<size_t>(t.col0 + r) * t.k + kc + lane * 4 : t.w;
+            cp_async16(ws + r * kLinLd + lane * 4, from, ok);
+        }
+}
+
+template <int RT>
 __device__ __forceinline__ void linear32_tile(const Linear32Params& p, const void* xbase, const float* prev, int tile,
                                               uint8_t* data, long long* stamp) {
-    constexpr int row_block = 16 * R;
+    constexpr int row_block = 8 * RT;
     const int col_tiles = (p.n + kLinCols - 1) / kLinCols;
-    const int ct = tile % col_tiles, r0 = (tile / col_tiles) * row_block;
-    const int col0 = ct * kLinCols;
-    const int kg = threadIdx.x >> 6, t64 = threadIdx.x & 63;
-    const int tx = t64 & 3, ty = t64 >> 2;
-    const int nchunks = (p.k + kLinChunk - 1) / kLinChunk;
-    const bool rms = p.rms != 0, x_bf16 = p.x_bf16 != 0;
-    float acc[R][4], ss[R];
+    LinTile t;
+    t.x = xbase; t.w = p.w;
+    t.rows = p.rows; t.n = p.n; t.k = p.k; t.ldx = p.ldx; t.x_row_offset = p.x_row_offset; t.x_bf16 = p.x_bf16;
+    t.col0 = (tile % col_tiles) * kLinCols;
+    t.r0 = (tile / col_tiles) * row_block;
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    const int rg = lane >> 2, cg = lane & 3;
+    const int nchunks = (t.k + kLinChunk - 1) / kLinChunk;
+    const bool rms = p.rms != 0, x_bf16 = t.x_bf16 != 0;
+    float2 acc[RT][4], ss[RT];
 #pragma unroll
-    for (int i = 0; i < R; i++) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; ss[i] = 0.f; }
+    for (int i = 0; i < RT; i++) {
+        ss[i] = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = make_float2(0.f, 0.f);
+    }
     __syncthreads();                                   // the previous tile's readers are done with the ring
     for (int s = 0; s < kLinStages - 1; ++s) {
-        if (s < nchunks) linear32_issue(p, xbase, data + s * kLinStageBytes, col0, r0, row_block, s * kLinChunk);
+        if (s < nchunks) linear32_issue(t, data + s * kLinStageBytes, row_block, s * kLinChunk);
         cp_async_commit();
     }
     for (int c = 0; c < nchunks; ++c) {
@@ -168,70 +191,79 @@ __device__ __forceinline__ void linear32_tile(const Linear32Params& p, const voi
         __syncthreads();                               // ... and everybody's; the buffer of chunk c - 1 is free
         if (stamp && c == 0 && threadIdx.x == 0) stamp[4] = static_cast<long long>(global_ns());
         const int next = c + kLinStages - 1;
-        if (next < nchunks) linear32_issue(p, xbase, data + (next % kLinStages) * kLinStageBytes, col0, r0, row_block, next * kLinChunk);
+        if (next < nchunks) linear32_issue(t, data + (next % kLinStages) * kLinStageBytes, row_block, next * kLinChunk);
         cp_async_commit();
         const float* xs = reinterpret_cast<const float*>(data + (c % kLinStages) * kLinStageBytes);
-        const float4* ws4 = reinterpret_cast<const float4*>(xs + kLinRows * kLinLd) + 4 * tx * (kLinLd / 4);
-        const int kw4 = min(kLinChunk, p.k - c * kLinChunk) >> 2;
-        const int q_end = min(kw4, kg * 8 + 8);
-#pragma unroll 2
-        for (int q = kg * 8; q < q_end; q++) {
-            float4 w4[4], x4[R];
+        const float* ws = xs + kLinRows * kLinLd;
+        const int kw4 = min(kLinChunk, t.k - c * kLinChunk) >> 2;
+#pragma unroll 1
+        for (int j = 0; j < 4; j++) {                  // (not unrolled: the operator runs a few times per pass, from a cold instruction cache)
+            const int q = warp * 4 + j;                // this warp's share of the chunk: k values 16 warp .. 16 warp + 15
+            if (q < kw4) {
+                float4 w4[4];
 #pragma unroll
-            for (int cc = 0; cc < 4; cc++) w4[cc] = ws4[cc * (kLinLd / 4) + q];
+                for (int cc = 0; cc < 4; cc++) w4[cc] = *reinterpret_cast<const float4*>(ws + (cg + 4 * cc) * kLinLd + q * 4);
+                constexpr int XB = RT < 4 ? RT : 4;    // rows in flight at a time (register budget)
 #pragma unroll
-            for (int i = 0; i < R; i++) {
-                if (x_bf16) {
-                    const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(xs + (ty + 16 * i) * kLinLd) + q * 4);
-                    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
-                    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
-                    x4[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
-                } else {
-                    x4[i] = *reinterpret_cast<const float4*>(xs + (ty + 16 * i) * kLinLd + q * 4);
+                for (int i0 = 0; i0 < RT; i0 += XB) {
+                    float4 x4[XB];
+#pragma unroll
+                    for (int i = 0; i < XB; i++) {
+                        if (x_bf16) {
+                            const uint2 u = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(xs + (rg + 8 * (i0 + i)) * kLinLd) + q * 4);
+                            const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+                            const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+                            x4[i] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                        } else {
+                            x4[i] = *reinterpret_cast<const float4*>(xs + (rg + 8 * (i0 + i)) * kLinLd + q * 4);
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < XB; i++) {
+                        const float2 xa = make_float2(x4[i].x, x4[i].y), xb = make_float2(x4[i].z, x4[i].w);
+#pragma unroll
+                        for (int cc = 0; cc < 4; cc++)
+                            acc[i0 + i][cc] = fma2(xb, make_float2(w4[cc].z, w4[cc].w), fma2(xa, make_float2(w4[cc].x, w4[cc].y), acc[i0 + i][cc]));
+                        if (rms) ss[i0 + i] = fma2(xb, xb, fma2(xa, xa, ss[i0 + i]));
+                    }
                 }
-            }
-#pragma unroll
-            for (int i = 0; i < R; i++) {
-#pragma unroll
-                for (int cc = 0; cc < 4; cc++)
-                    acc[i][cc] = fmaf(x4[i].x, w4[cc].x, fmaf(x4[i].y, w4[cc].y, fmaf(x4[i].z, w4[cc].z, fmaf(x4[i].w, w4[cc].w, acc[i][cc]))));
-                if (rms) ss[i] = fmaf(x4[i].x, x4[i].x, fmaf(x4[i].y, x4[i].y, fmaf(x4[i].z, x4[i].z, fmaf(x4[i].w, x4[i].w, ss[i]))));
             }
         }
     }
     cp_async_wait<0>();
     __syncthreads();                                   // the ring is free: it now holds the partial sums
     if (stamp && threadIdx.x == 0) stamp[5] = static_cast<long long>(global_ns());
-    float* red = reinterpret_cast<float*>(data);       // [4 groups][row_block][16 columns]
-    float* red_ss = red + 4 * row_block * kLinCols;    // [4 groups][row_block]
+    float* red = reinterpret_cast<float*>(data);       // [8 warps][row_block][16 columns]
+    float* red_ss = red + 8 * row_block * kLinCols;    // [8 warps][row_block]
 #pragma unroll
-    for (int i = 0; i < R; i++) {
-        *reinterpret_cast<float4*>(red + (kg * row_block + ty + 16 * i) * kLinCols + 4 * tx) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-        if (tx == 0) red_ss[kg * row_block + ty + 16 * i] = ss[i];
+    for (int i = 0; i < RT; i++) {
+#pragma unroll
+        for (int cc = 0; cc < 4; cc++) red[(warp * row_block + rg + 8 * i) * kLinCols + cg + 4 * cc] = acc[i][cc].x + acc[i][cc].y;
+        if (cg == 0) red_ss[warp * row_block + rg + 8 * i] = ss[i].x + ss[i].y;
     }
     __syncthreads();
     for (int o = threadIdx.x; o < row_block * kLinCols; o += kThreads) {
         const int rl = o >> 4, cl = o & 15;
-        const int r = r0 + rl, n = col0 + cl;
-        if (r >= p.rows || n >= p.n) continue;
+        const int r = t.r0 + rl, n = t.col0 + cl;
+        if (r >= t.rows || n >= t.n) continue;
         float v = 0.f, sq = 0.f;
 #pragma unroll
-        for (int k4 = 0; k4 < 4; k4++) {
-            v += red[(k4 * row_block + rl) * kLinCols + cl];
-            sq += red_ss[k4 * row_block + rl];
+        for (int k8 = 0; k8 < 8; k8++) {
+            v += red[(k8 * row_block + rl) * kLinCols + cl];
+            sq += red_ss[k8 * row_block + rl];
         }
-        if (rms) v *= rsqrtf(sq / static_cast<float>(p.k) + p.eps);
+        if (rms) v *= rsqrtf(sq / static_cast<float>(t.k) + p.eps);
         if (p.bias) v += p.bias[n];
         if (p.silu) v = v / (1.f + expf(-v));
-        if (p.euler) v = __fadd_rn(__ldcg(prev + static_cast<size_t>(r) * p.n + n), __fmul_rn(p.dt, v));
+        if (p.euler) v = __fadd_rn(__ldcg(prev + static_cast<size_t>(r) * t.n + n), __fmul_rn(p.dt, v));
         if (p.out_bf16) static_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = __float2bfloat16_rn(v);
         else static_cast<float*>(p.out)[static_cast<size_t>(r) * p.ldo + n] = v;
     }
     if (stamp && threadIdx.x == 0) stamp[6] = static_cast<long long>(global_ns());
     // Optional extra row: FP32 values of this tile's columns copied (as BF16) to the row in front of the output,
     // which is how the state token joins the action tokens without a stage of its own.
-    if (p.row0_src && r0 == 0 && threadIdx.x < kLinCols && col0 + threadIdx.x < p.n)
-        static_cast<__nv_bfloat16*>(p.row0_dst)[col0 + threadIdx.x] = __float2bfloat16_rn(__ldcg(p.row0_src + col0 + threadIdx.x));
+    if (p.row0_src && t.r0 == 0 && threadIdx.x < kLinCols && t.col0 + threadIdx.x < t.n)
+        static_cast<__nv_bfloat16*>(p.row0_dst)[t.col0 + threadIdx.x] = __float2bfloat16_rn(__ldcg(p.row0_src + t.col0 + threadIdx.x));
 }
 
 __device__ __forceinline__ void linear32_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st,
@@ -242,8 +274,7 @@ __device__ __forceinline__ void linear32_instruction(const VmProgram& prog, Ctl*
     const float* prev = p.prev_slot == 3 ? prog.in.noise : p.prev;
     for (int t = first; t < first + count; ++t) {
         long long* stamp_t = t == first ? stamp : nullptr;
-        if (p.row_block == 16) linear32_tile<1>(p, xbase, prev, t, data, stamp_t);
-        else if (p.row_block == 32) linear32_tile<2>(p, xbase, prev, t, data, stamp_t);
+        if (p.row_block == 16) linear32_tile<2>(p, xbase, prev, t, data, stamp_t);
         else linear32_tile<4>(p, xbase, prev, t, data, stamp_t);
         cta_publish_tile(prog, st, t);
     }

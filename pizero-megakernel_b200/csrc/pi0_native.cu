@@ -1160,8 +1160,7 @@ extern "C" int create_linear32(void** handle, const void* x, const float* w, con
     d.kind = OP_LINEAR32;
     finish_desc(d);
     // few columns (the action head): blocks of 16 rows, so that more than one or two CTAs share the operator
-    const int col_tiles = (n + kLinCols - 1) / kLinCols;
-    const int row_block = (n <= 64 && rows > 16) ? 16 : (rows > 32 && rows <= 64 && 2 * col_tiles <= op->workers) ? 32 : kLinRows;
+    const int row_block = (rows <= 16 || n <= 64) ? 16 : kLinRows;
     d.tiles = ((n + kLinCols - 1) / kLinCols) * ((rows + row_block - 1) / row_block);
     d.bands = 1;
     d.band_div = d.tiles;

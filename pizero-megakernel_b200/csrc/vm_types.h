@@ -201,7 +201,7 @@ struct Linear32Params {
     int euler;                   // out = prev + dt * value   (separately rounded mul and add)
     int slot, prev_slot;         // 0 pointer, 2 state, 3 noise
     int x_row_offset;            // first input row
-    int row_block;               // rows per tile: 64, 32 or 16
+    int row_block;               // rows per tile: 32 or 16
     const float* row0_src;       // optional FP32 [n] row ...
     void* row0_dst;              // ... stored as BF16 [n] by the tiles of the first row block (null: none)
     float dt, eps;

@@ -151,6 +151,34 @@ def mlp_block(launches):
         return timed(program.forward, launches, program.status)
 
 
+def _linear32(rows, n, k, flags, launches):
+    """The FP32 linear operator of the expert's head and tail (flags: 1 BF16 input, 2 BF16 output, 4 SiLU, 8 RMS factor,
+    16 Euler update)."""
+    import ctypes
+    from native_pi0 import _native
+    lib = _native.load()
+    torch.manual_seed(0)
+    x = torch.randn(128, k, device="cuda")
+    x = x.bfloat16() if flags & 1 else x
+    w, b, prev = torch.randn(n, k, device="cuda") * 0.05, torch.randn(n, device="cuda"), torch.randn(rows, n, device="cuda")
+    out = torch.zeros(128, n, device="cuda", dtype=torch.bfloat16 if flags & 2 else torch.float32)
+    h = ctypes.c_void_p()
+    _native.check(lib.create_linear32(ctypes.byref(h), x.data_ptr(), w.data_ptr(), b.data_ptr(), prev.data_ptr() if flags & 16 else None,
+                                      out.data_ptr(), rows, n, k, k, n, flags, 0, 0, 0, -0.1, 1e-6, 148), "FP32 linear setup")
+    try:
+        return timed(lambda: _native.check(lib.launch_op(h, None), "launch"), launches, lambda: _native.status(lib, h))
+    finally:
+        lib.destroy_op(h)
+
+
+def linear_time_out(launches):
+    return _linear32(50, 1024, 1024, 2, launches)
+
+
+def linear_euler(launches):
+    return _linear32(50, 32, 1024, 1 | 8 | 16, launches)
+
+
 def timed(call, launches, status):
     for _ in range(3):
         call()
@@ -172,7 +200,8 @@ CASES = {"model_small": model_small, "gemm_gate_up": gemm_gate_up, "attention_pr
          "geglu_expert": geglu_expert, "attention_expert": attention_expert, "attention_expert_split8": attention_expert_split8,
          "attention_vision": attention_vision, "attention_vision_mma_sync": attention_vision_mma_sync,
          "attention_prefix_mma_sync": attention_prefix_mma_sync, "attention_expert_split13": attention_expert_split13,
-         "attention_expert_split13_mma_sync": attention_expert_split13_mma_sync, "norm_prefix": norm_prefix, "norm_expert": norm_expert, "mlp_block": mlp_block}
+         "attention_expert_split13_mma_sync": attention_expert_split13_mma_sync, "norm_prefix": norm_prefix, "norm_expert": norm_expert, "mlp_block": mlp_block,
+         "linear_time_out": linear_time_out, "linear_euler": linear_euler}
 
 
 def main():
