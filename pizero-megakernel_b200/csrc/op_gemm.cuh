@@ -469,9 +469,15 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
         if (row_ok && g.row_sumsq) {
             const float4* part = reinterpret_cast<const float4*>(g.row_sumsq + static_cast<size_t>(row) * g.sumsq_parts);
             float total = 0.f;
-            for (int i = 0; i < (g.sumsq_parts >> 2); ++i) {         // fixed order: the same bits on every launch
-                const float4 q = __ldcg(part + i);
-                total += q.x; total += q.y; total += q.z; total += q.w;
+            const int quads = g.sumsq_parts >> 2;
+            for (int i0 = 0; i0 < quads; i0 += 8) {                  // eight loads in flight: one L2 round trip per 128 bytes
+                float4 q[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) q[j] = i0 + j < quads ? __ldcg(part + i0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {                        // fixed order: the same bits on every launch
+                    if (i0 + j < quads) { total += q[j].x; total += q[j].y; total += q[j].z; total += q[j].w; }
+                }
             }
             row_scale *= rsqrtf(total * g.sumsq_inv_width + g.sumsq_eps);
         }
