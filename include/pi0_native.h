@@ -60,7 +60,11 @@ int configure_resident_fp4_stream(void* handle, const void* bias, const void* re
  * The sum runs in index order, so the factor has the same bits on every launch. */
 int configure_resident_fp4_row_rms(void* handle, const float* sumsq, int parts, int width, float eps);
 /* extension: logical row count (rows >= this are never stored; with at most 64 rows only 64 rows of A are
- * copied per tile) and output tile width (128 or 64). */
+ * copied per tile) and output tile width: 128, 64, or 32 (NVFP4 operands only).  With 32-wide tiles the weight scales
+ * given at creation are read in a layout of their own: one 512-byte atom per (32-row tile, group of four 16-element
+ * blocks) - [N / 32][K / 64][512] - holding the tile's 32 rows in the first 32-row sub-column of the atom (bytes
+ * 16 r + b for row r, block b) and zeros elsewhere, i.e. four times the bytes of the standard layout.  Narrow tiles are
+ * for projections of a few rows, whose time is the bytes one SM takes in and the serial epilogue of one tile. */
 int configure_resident_fp4_rows(void* handle, int rows);
 int configure_resident_fp4_tile(void* handle, int block_n);
 /* extension: tiled = 1 declares that B is stored tile-major (K a multiple of 256): for every output tile n and every

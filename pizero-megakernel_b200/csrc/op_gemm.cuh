@@ -48,7 +48,8 @@ __device__ __forceinline__ void gemm_producer(const VmProgram& prog, Ctl* ctl, u
     for (int t = first; t < first + count; ++t) {
         const int m_tile = t / g.n_tiles, n_tile = t - m_tile * g.n_tiles;
         const int band = tile_band(st, t);
-        const int sfb_tile = (n_tile * g.block_n) >> 7;
+        // B scales: the 128-row atom that holds the tile's rows, or - 32-wide tiles - an atom of the tile's own
+        const int sfb_tile = g.block_n == 32 ? n_tile : (n_tile * g.block_n) >> 7;
         int early = 0;                                               // slots whose weight half is already in flight
         int alive = 1;
         if (band != current_band) {
@@ -145,8 +146,9 @@ __device__ __forceinline__ void gemm_mma(const VmProgram& prog, Ctl* ctl, uint8_
         if (!mbar_wait_warp(prog, ctl, &ctl->acc_empty[buf], acc_phase ^ 1u, stage_index)) return;
         tc_fence_after();
         const uint32_t d = tmem + buf * 128u;
-        // Scale rows of a narrow B tile sit in the 32-row sub-column of their 128-row atom.
-        const uint32_t sfb_sub = static_cast<uint32_t>((n_tile * block_n) & 127) >> 5;
+        // Scale rows of a 64-wide B tile sit in the 32-row sub-columns 0 or 2 of their 128-row atom (the scale operand of
+        // the MMA must start at an even sub-column); 32-wide tiles bring atoms of their own with the rows in sub-column 0.
+        const uint32_t sfb_sub = block_n == 32 ? 0u : static_cast<uint32_t>((n_tile * block_n) & 127) >> 5;
         for (int ks = 0; ks < slots; ++ks) {
             const uint32_t s = slot;
             if (!mbar_wait_warp(prog, ctl, &ctl->full[s], (bits >> s) & 1u, stage_index)) return;

@@ -601,7 +601,9 @@ extern "C" int configure_resident_fp4_weight_layout(void* handle, int tiled) {
 }
 extern "C" int configure_resident_fp4_tile(void* handle, int block_n) {
     Op* op = as_op(handle);
-    if (!op || op->desc.kind != OP_GEMM || (block_n != 128 && block_n != 64)) return cudaErrorInvalidValue;
+    if (!op || op->desc.kind != OP_GEMM || (block_n != 128 && block_n != 64 && block_n != 32) ||
+        (block_n == 32 && op->operands != GEMM_NVFP4))
+        return cudaErrorInvalidValue;
     op->desc.p.gemm.block_n = block_n;
     return gemm_refresh(op);
 }

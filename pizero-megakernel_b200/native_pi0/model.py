@@ -122,7 +122,7 @@ class NativePi0:
         return cls(StateDictModel(config or Pi0Config(), state_dict), **kwargs)
 
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
-                 library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=64,
+                 library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=None,
                  rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="spread",
                  fold_norms=True, attention_path=None, weight_store=None):
         config = getattr(model, "config", None)
@@ -147,6 +147,11 @@ class NativePi0:
         self.partitioned = partitioned
         self.expert_splits = expert_splits
         self.prefix_splits = prefix_splits
+        # output tile widths of the action expert's projections: an int for all four, or a dict per operation.  The default
+        # gives the projections with few output columns 32-wide tiles (twice the workers, half the bytes of weight and half
+        # the serial epilogue per worker); gate/up already has 128 tiles of 64
+        if expert_block_n is None:
+            expert_block_n = {"qkv": 64, "o_proj": 32, "gate_up": 64, "down": 32}
         self.expert_block_n = expert_block_n
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self.keep_debug_outputs = keep_debug_outputs
@@ -233,6 +238,10 @@ class NativePi0:
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _native.check(self.lib.quantize_nvfp4(src.data_ptr(), m.data.data_ptr(), m.scales.data_ptr(), np_, kp, kp, kp // 16,
                                               m.global_scale, 1, stream), "weight quantisation")
+        if block_n == 32:
+            from native_pi0.primitives import narrow_tile_scales
+            m.scales = narrow_tile_scales(m.scales, np_, kp // 16)     # an atom of scales per 32-row tile
+        m.scale_tile = block_n if block_n == 32 else 128
         m.tiled = 0
         if self.tile_weights and kp % 256 == 0 and np_ % block_n == 0:
             tiled = m.data.view(np_ // block_n, block_n, kp // 256, 128).permute(0, 2, 1, 3).contiguous()
@@ -342,6 +351,8 @@ class NativePi0:
         _native.check(self.lib.configure_resident_fp4_rows(h, rows), name)
         if block_n != 128:
             _native.check(self.lib.configure_resident_fp4_tile(h, block_n), name)
+        if (block_n == 32) != (getattr(w, "scale_tile", 128) == 32):
+            raise ValueError(f"{name}: 32-wide tiles read weight scales laid out per tile, and only they do")
         if getattr(w, "tiled", 0):
             if w.tiled != block_n:
                 raise ValueError(f"{name}: weight tiled for {w.tiled}-wide tiles, used with {block_n}")
@@ -508,7 +519,8 @@ class NativePi0:
         if self.expert_splits is not None:
             return int(self.expert_splits)
         c = self.config
-        qkv_tiles = -(-(c.heads + 2) * c.head_dim // self.expert_block_n)
+        width = self.expert_block_n["qkv"] if isinstance(self.expert_block_n, dict) else self.expert_block_n
+        qkv_tiles = -(-(c.heads + 2) * c.head_dim // width)
         return max(1, min(16, (self.workers - qkv_tiles) // c.heads, keys // 32))
 
     def _prefix_splits(self, rows):
@@ -548,7 +560,9 @@ class NativePi0:
         H, hd = c.heads, c.head_dim
         a1, a2, a3, a4, qbuf = bufs
         p_qkv, p_o, p_gu, p_dn = [self.site(f"{site}.{n}") for n in ("qkv", "o_proj", "gate_up", "down")]
-        tile = lambda precision: block_n if precision == "nvfp4" else 128       # BF16 sites use full-width tiles
+        widths = block_n if isinstance(block_n, dict) else dict.fromkeys(("qkv", "o_proj", "gate_up", "down"), block_n)
+        p_of = dict(zip(("qkv", "o_proj", "gate_up", "down"), (p_qkv, p_o, p_gu, p_dn)))
+        tile = lambda op: widths[op] if p_of[op] == "nvfp4" else 128            # BF16 sites use full-width tiles
         sums = lambda key, parts: self.cached((key, x_in.shape[0], parts), lambda: self.tensor((x_in.shape[0], parts), torch.float32))
         gamma1 = lambda: (1.0 + sd[p + "input_layernorm.weight"].float()).contiguous()
         if streamed_in is None:
@@ -563,11 +577,11 @@ class NativePi0:
             w = torch.cat((wk, wv)) if kv_only else torch.cat((self._interleave_heads(sd[p + "self_attn.q_proj.weight"]), wk, wv))
             if fold1 is not None:
                 w = w.float() * gamma1()[None, :]
-            return self.weight(w, block_n=tile(p_qkv), precision=p_qkv)
+            return self.weight(w, block_n=tile("qkv"), precision=p_qkv)
 
-        wqkv = self.cached(f"{p}qkv.{p_qkv}.{int(fold1 is not None)}.{int(kv_only)}.{tile(p_qkv)}", make_qkv)
+        wqkv = self.cached(f"{p}qkv.{p_qkv}.{int(fold1 is not None)}.{int(kv_only)}.{tile("qkv")}", make_qkv)
         q_cols, q = (0, None) if kv_only else (H * hd, qbuf)
-        s_qkv = self.gemm(f"{name}.qkv", a1, wqkv, rows=rows, sources=[(s_n1, SAME)], block_n=tile(p_qkv), row_rms=fold1,
+        s_qkv = self.gemm(f"{name}.qkv", a1, wqkv, rows=rows, sources=[(s_n1, SAME)], block_n=tile("qkv"), row_rms=fold1,
                           rope=dict(q=q, cos=cos, sin=sin, cache_k=cache[0], cache_v=cache[1], q_cols=q_cols, cache_base=cache_base))
         if kv_only:
             return s_qkv, s_qkv, None
@@ -599,18 +613,18 @@ class NativePi0:
             s_att = self.add(4, merge, f"{name}.attention", [(s_part, ALL)], outs)
         else:
             s_att = self.add(1, h, f"{name}.attention", att_sources, outs)
-        wo = self.cached(f"{p}o.{p_o}.{tile(p_o)}", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=tile(p_o), precision=p_o))
+        wo = self.cached(f"{p}o.{p_o}.{tile("o_proj")}", lambda: self.weight(sd[p + "self_attn.o_proj.weight"], block_n=tile("o_proj"), precision=p_o))
         # ---- attention output projection; the post-attention norm is folded when both neighbours are NVFP4 sites
         fold2 = self.fold_norms and p_o == "nvfp4" and p_gu == "nvfp4"
         gamma2 = lambda: (1.0 + sd[p + "post_attention_layernorm.weight"].float()).contiguous()
         if fold2:
-            parts2 = width // tile(p_o)
+            parts2 = width // tile("o_proj")
             ss2 = sums("sumsq2", parts2)
-            s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=tile(p_o),
+            s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=tile("o_proj"),
                             stream=(a3.require("nvfp4"), ss2))
             s_n2, rms2 = s_o, (ss2, parts2, width, c.rms_eps)
         else:
-            s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=tile(p_o))
+            s_o = self.gemm(f"{name}.o_proj", a2, wo, rows=rows, sources=[(s_att, SAME)], out=x_mid, residual=x_in, block_n=tile("o_proj"))
             g2 = self.cached(p + "g2", gamma2)
             s_n2 = self.norm(f"{name}.norm2", x_mid, a3.only(p_gu), rows=rows, sources=[(s_o, SAME)], kind="rms", gamma=g2, eps=c.rms_eps)
             rms2 = None
@@ -619,22 +633,22 @@ class NativePi0:
             w = torch.stack((gate, up), dim=1).reshape(2 * gate.shape[0], gate.shape[1])
             if fold2:
                 w = w.float() * gamma2()[None, :]
-            return self.weight(w, block_n=tile(p_gu), precision=p_gu)
+            return self.weight(w, block_n=tile("gate_up"), precision=p_gu)
 
-        wgu = self.cached(f"{p}gate_up.{p_gu}.{int(fold2)}.{tile(p_gu)}", make_gate_up)
+        wgu = self.cached(f"{p}gate_up.{p_gu}.{int(fold2)}.{tile("gate_up")}", make_gate_up)
         s_gu = self.gemm(f"{name}.gate_up", a3, wgu, rows=rows, sources=[(s_n2, SAME)], out_act=a4.require(p_dn), out_precision=p_dn,
-                         activation=2, block_n=tile(p_gu), row_rms=rms2)
-        wd = self.cached(f"{p}down.{p_dn}.{tile(p_dn)}", lambda: self.weight(sd[p + "mlp.down_proj.weight"], block_n=tile(p_dn), precision=p_dn))
+                         activation=2, block_n=tile("gate_up"), row_rms=rms2)
+        wd = self.cached(f"{p}down.{p_dn}.{tile("down")}", lambda: self.weight(sd[p + "mlp.down_proj.weight"], block_n=tile("down"), precision=p_dn))
         # ---- down projection; streams for the next layer's QKV when that reads NVFP4 too
         streamed_out = None
         if self.fold_norms and next_site is not None and p_dn == "nvfp4" and self.site(f"{next_site}.qkv") == "nvfp4":
-            parts1 = width // tile(p_dn)
+            parts1 = width // tile("down")
             ss1 = sums("sumsq1", parts1)
-            s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=tile(p_dn),
+            s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=tile("down"),
                              stream=(a1.require("nvfp4"), ss1))
             streamed_out = (ss1, parts1)
         else:
-            s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=tile(p_dn))
+            s_dn = self.gemm(f"{name}.down", a4, wd, rows=rows, sources=[(s_gu, SAME)], out=x_in, residual=x_mid, block_n=tile("down"))
         return s_dn, s_qkv, streamed_out
 
     def _build(self):

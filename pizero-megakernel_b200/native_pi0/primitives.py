@@ -57,6 +57,17 @@ def _epilogue_kind(output_dtype, gelu, geglu, relu2, global_scale, bias, residua
     return kind, activation
 
 
+def narrow_tile_scales(swizzled, rows, blocks):
+    """Weight scales for 32-wide output tiles: from the standard swizzled layout (128-row x 4-block atoms, ``rows`` a
+    multiple of 128, ``blocks`` 16-element blocks per row, a multiple of 4) to one atom per (32-row tile, group of four
+    blocks) with the tile's rows in the first 32-row sub-column and zeros elsewhere (uint8 tensor, 4x the size)."""
+    atoms, groups = rows // 128, blocks // 4
+    standard = swizzled.view(atoms, groups, 32, 4, 4)                       # [atom, group, row % 32, row // 32 % 4, block % 4]
+    narrow = torch.zeros((atoms * 4, groups, 32, 4, 4), dtype=torch.uint8, device=swizzled.device)
+    narrow[:, :, :, 0, :] = standard.permute(0, 3, 1, 2, 4).reshape(atoms * 4, groups, 32, 4)
+    return narrow.reshape(-1)
+
+
 class ResidentNVFP4:
     def __init__(self, library, activation, weight, *, workers=16, device="cuda",
                  output_dtype=torch.float32, bias=None, residual=None,
@@ -78,6 +89,10 @@ class ResidentNVFP4:
         self._library = lib = _native.load(library)
         with torch.cuda.device(self.device):
             self._upload(activation, weight, activation_buffers, bias, residual, m, n)
+            if block_n == 32:
+                if k % 64:
+                    raise ValueError("32-wide tiles need K to be a multiple of 64")
+                self.sb = narrow_tile_scales(self.sb, n, k // 16)
             if kind == "fp4":
                 self.output = packed_tma_buffer((m, self.output_width // 2), device=self.device)
                 atoms = ((m + 127) // 128) * ((self.output_width // 16 + 3) // 4)

@@ -122,7 +122,7 @@ def test_gemm_bias_residual_and_tiles():
     ref = oracle.gemm(pa.data, pa.scales, 1.0, pb.data, pb.scales, 1.0, m, n, k) + bias.float().numpy()[None] + res.float().numpy()
     expect = bf16(ref).float().numpy()
     results = []
-    for block_n, tiled in ((128, False), (64, False), (128, True), (64, True)):
+    for block_n, tiled in ((128, False), (64, False), (128, True), (64, True), (32, False), (32, True)):
         with ResidentNVFP4(None, pa, pb, workers=7, output_dtype=torch.bfloat16, bias=bias, residual=res, block_n=block_n,
                            tiled_weight=tiled) as op:
             y = op.forward().float().cpu().numpy()
@@ -134,7 +134,7 @@ def test_gemm_bias_residual_and_tiles():
     for y in results[1:]:                                   # tile width and weight layout do not change a single bit
         np.testing.assert_array_equal(y, results[0])
     with pytest.raises(RuntimeError):
-        ResidentNVFP4(None, pa, pb, block_n=32)             # 32-wide tiles are not offered
+        ResidentNVFP4(None, pa, pb, block_n=16)             # tiles are 128, 64 or 32 columns wide
 
 
 def _decode(op, rows, width):
@@ -260,7 +260,7 @@ def test_residual_stream_epilogue_and_row_rms_consumer():
     res = bf16(rng.normal(size=(m, n)))
     pa, pw, pw2 = pack_nvfp4(a), pack_nvfp4(w, scale_policy="ceil"), pack_nvfp4(w2, scale_policy="ceil")
     placeholder = pack_nvfp4(np.zeros((m, n), np.float32))
-    for block_n in (128, 64):
+    for block_n in (128, 64, 32):
         parts = n // block_n
         with ResidentNVFP4(None, pa, pw, workers=16, output_dtype=torch.bfloat16, residual=res, block_n=block_n) as plain, \
                 ResidentNVFP4(None, pa, pw, workers=16, output_dtype=torch.bfloat16, residual=res, block_n=block_n) as producer:
