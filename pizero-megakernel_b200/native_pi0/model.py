@@ -122,7 +122,7 @@ class NativePi0:
         return cls(StateDictModel(config or Pi0Config(), state_dict), **kwargs)
 
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
-                 library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=None,
+                 library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=None, vision_block_n=64,
                  rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="spread",
                  fold_norms=True, attention_path=None, weight_store=None):
         config = getattr(model, "config", None)
@@ -147,6 +147,7 @@ class NativePi0:
         self.partitioned = partitioned
         self.expert_splits = expert_splits
         self.prefix_splits = prefix_splits
+        self.vision_block_n = vision_block_n
         # output tile widths of the action expert's projections: an int for all four, or a dict per operation.  The default
         # gives the projections with few output columns 32-wide tiles (twice the workers, half the bytes of weight and half
         # the serial epilogue per worker); gate/up already has 128 tiles of 64
@@ -444,6 +445,9 @@ class NativePi0:
         att = a_att.bf16
         # NVFP4 rows for the output projection straight from the tensor-core attention tiles: every head on a pitch of 80
         # columns (the next multiple of the 16-element scale block), the projection's weight with zero columns to match
+        # the projections back to the 1152-wide stream have 9 column tiles of 128 per row band - 54 tiles for 148 workers: 64-wide
+        # tiles double the workers that share their weight stream
+        narrow = lambda precision: self.vision_block_n if precision == "nvfp4" else 128
         fp4_pitch = padded(hd, 16)
         a_att_fp4 = Activation(self, M, c.vision_heads * fp4_pitch)
 
@@ -460,14 +464,14 @@ class NativePi0:
             bqkv = torch.cat([sd[p + f"self_attn.{n}_proj.bias"] for n in "qkv"]).to(torch.bfloat16).contiguous()
             quant_in_tile = padded_heads and p_out == "nvfp4"
             if quant_in_tile:
-                wo = self.cached(p + "out.nvfp4.spread", lambda: self.weight(spread_heads(sd[p + "self_attn.out_proj.weight"])))
+                wo = self.cached(p + "out.nvfp4.spread", lambda: self.weight(spread_heads(sd[p + "self_attn.out_proj.weight"]), block_n=narrow("nvfp4")))
             else:
-                wo = self.cached(p + "out." + p_out, lambda: self.weight(sd[p + "self_attn.out_proj.weight"], precision=p_out))
+                wo = self.cached(p + "out." + p_out, lambda: self.weight(sd[p + "self_attn.out_proj.weight"], block_n=narrow(p_out), precision=p_out))
             bo = sd[p + "self_attn.out_proj.bias"].to(torch.bfloat16).contiguous()
             w1 = self.cached(p + "fc1." + p_fc1, lambda: self.weight(sd[p + "mlp.fc1.weight"], precision=p_fc1))
             bias1 = torch.zeros(mlp_pad, device=self.device, dtype=torch.bfloat16)
             bias1[:c.vision_mlp] = sd[p + "mlp.fc1.bias"].to(torch.bfloat16)
-            w2 = self.cached(p + "fc2." + p_fc2, lambda: self.weight(sd[p + "mlp.fc2.weight"], precision=p_fc2))
+            w2 = self.cached(p + "fc2." + p_fc2, lambda: self.weight(sd[p + "mlp.fc2.weight"], block_n=narrow(p_fc2), precision=p_fc2))
             bias2 = sd[p + "mlp.fc2.bias"].to(torch.bfloat16).contiguous()
             self.buffers.extend((g1, b1, g2, b2, bqkv, bo, bias1, bias2))
             buf = qkv[i & 1]
@@ -495,11 +499,12 @@ class NativePi0:
                 # the mma.sync tiles do not quantise 72-wide heads: a quantiser stage of its own
                 s_att = self.norm(f"vision.{i}.attention_quant", att, a_att.only("nvfp4"), rows=M, sources=[(s_att, SAME)], kind="none")
             s_o = self.gemm(f"vision.{i}.out", a_att_fp4 if quant_in_tile else a_att, wo, rows=M, sources=[(s_att, SAME)], out=xb,
-                            bias=bo, residual=xa)
+                            bias=bo, residual=xa, block_n=narrow(p_out))
             s_ln2 = self.norm(f"vision.{i}.ln2", xb, a_ln2.only(p_fc1), rows=M, sources=[(s_o, SAME)], kind="layer", gamma=g2, beta=b2, eps=c.ln_eps)
             s_fc1 = self.gemm(f"vision.{i}.fc1", a_ln2, w1, rows=M, sources=[(s_ln2, SAME)], out_act=a_h.require(p_fc2), out_precision=p_fc2,
                               bias=bias1, activation=1, act_cols=c.vision_mlp)
-            s_x = self.gemm(f"vision.{i}.fc2", a_h, w2, rows=M, sources=[(s_fc1, SAME)], out=xa, bias=bias2, residual=xb)
+            s_x = self.gemm(f"vision.{i}.fc2", a_h, w2, rows=M, sources=[(s_fc1, SAME)], out=xa, bias=bias2, residual=xb,
+                            block_n=narrow(p_fc2))
             if i == 0:
                 self.mark("vision.0.qkv", buf), self.mark("vision.0.attention", att)
             self.mark(f"vision.{i}", xa)
