@@ -59,6 +59,17 @@ int configure_resident_fp4_stream(void* handle, const void* bias, const void* re
 /* extension: every accumulator row r is multiplied by rsqrt(sum(sumsq[r, 0..parts)) / width + eps); parts % 4 == 0.
  * The sum runs in index order, so the factor has the same bits on every launch. */
 int configure_resident_fp4_row_rms(void* handle, const float* sumsq, int parts, int width, float eps);
+/* extension: LayerNorm folded the same way.  configure_resident_fp4_stream_sums (after configure_resident_fp4_stream and
+ * the tile width) makes the producing projection also leave the per-tile SUMS of its rounded rows, and gives both
+ * statistics arrays a row stride of ld floats (>= N / tile width, a multiple of 4; slots beyond the tile count are never
+ * written: zero them once).  configure_resident_fp4_row_layernorm on the reading projection turns every accumulator row
+ * r into rstd_r * (alpha * acc - mean_r * center[n]), mean and variance (E[x^2] - mean^2) from the two sums over `width`
+ * values, center FP32 [N] = the sum over K of weight row n as the MMA reads it (dequantised); the weight columns carry
+ * the norm's gamma and the bias, added afterwards as always, its beta (bias + W beta).  Offered by the BF16 epilogue
+ * with extended options (head-padded store, GELU column limit) and by the NVFP4-output epilogue. */
+int configure_resident_fp4_stream_sums(void* handle, float* sums, int ld);
+int configure_resident_fp4_row_layernorm(void* handle, const float* sumsq, const float* sums, int parts, int width, float eps,
+                                         const float* center);
 /* extension: logical row count (rows >= this are never stored; with at most 64 rows only 64 rows of A are
  * copied per tile) and output tile width: 128, 64, or 32 (NVFP4 operands only).  With 32-wide tiles the weight scales
  * given at creation are read in a layout of their own: one 512-byte atom per (32-row tile, group of four 16-element

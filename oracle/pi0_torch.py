@@ -226,7 +226,7 @@ def site_of(parameter):
 
 class Pi0Torch:
     def __init__(self, dims: Pi0Dims, state_dict, mode="bf16", compute_dtype=torch.bfloat16, rope_inv_freq_dtype=torch.float32,
-                 precision=None, fold_norms=True, head_blocks=True):
+                 precision=None, fold_norms=True, head_blocks=True, fold_layernorms=True):
         """``precision`` (mode "nvfp4" only): dict of fnmatch patterns over site names -> "nvfp4" | "bf16" with an optional
         "default", as the engine takes it; BF16 sites multiply BF16 operands with FP32 accumulation and round the way the
         engine's BF16 epilogues do.  ``fold_norms`` (mode "nvfp4"): an RMSNorm between two NVFP4 projections is evaluated
@@ -234,7 +234,10 @@ class Pi0Torch:
         the accumulator rows are multiplied by ``rsqrt(mean square + eps)``.  ``head_blocks`` (mode "nvfp4"): the SigLIP
         attention rows and the output projection's weight are quantised with every 72-wide head on a pitch of 80 columns,
         i.e. in blocks that do not straddle heads, as the engine's tensor-core attention tiles write them; False keeps
-        the plain 16-column partition of the 1152-wide rows (the engine with ``attention_path="mma.sync"``)."""
+        the plain 16-column partition of the 1152-wide rows (the engine with ``attention_path="mma.sync"``).
+        ``fold_layernorms`` (with ``fold_norms``): SigLIP's LayerNorms between two NVFP4 projections are folded the same
+        way - un-normalised rows quantised, gamma in the weight columns, ``bias + W beta`` as bias, and the accumulator
+        rows turned into ``rstd * (acc - mean * sum_k W'[n, k])`` with the variance as ``E[x^2] - mean^2``."""
         assert mode in ("bf16", "nvfp4")
         self.d, self.sd, self.mode = dims, state_dict, mode
         precision = precision or {}
@@ -245,6 +248,7 @@ class Pi0Torch:
         self._site_cache = {}
         self.fold_norms = bool(fold_norms) and mode == "nvfp4"
         self.head_blocks = bool(head_blocks) and mode == "nvfp4"
+        self.fold_layernorms = bool(fold_layernorms) and self.fold_norms
         self.dt = compute_dtype                 # activation dtype of the bf16 mode (float32 for a fast CPU baseline)
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self._wq = {}
@@ -310,6 +314,19 @@ class Pi0Torch:
         y = fake_quant(pad_cols(xf, 64), "nearest", 1.0) @ wq.T
         return y * torch.rsqrt(xf.square().mean(-1, keepdim=True) + self.d.rms_eps)
 
+    def folded_layernorm_linear(self, x, name, gamma, beta, eps):
+        """NVFP4 projection (with its bias) of LayerNorm(x) evaluated the way the engine folds it: the UN-normalised BF16
+        rows ``x`` are quantised, the weight columns carry ``gamma``, the bias becomes ``b + W beta`` (BF16), and the
+        accumulator rows are centred and scaled afterwards.  FP32, not rounded."""
+        xf = x.to(torch.bfloat16).float()
+        w, b = self.sd[name + ".weight"], self.sd[name + ".bias"]
+        wq = self._qweight(name, w, gamma)
+        acc = fake_quant(pad_cols(xf, 64), "nearest", 1.0) @ wq.T
+        mean = xf.mean(-1, keepdim=True)
+        rstd = torch.rsqrt((xf.square().mean(-1, keepdim=True) - mean * mean).clamp_min(0.0) + eps)
+        bias = (b.float() + w.to(torch.bfloat16).float() @ beta.float()).to(torch.bfloat16).float()
+        return rstd * (acc - mean * wq.sum(-1)[None, :]) + bias
+
     def folds(self, producer, consumer):
         """True when the norm between the projections ``producer`` and ``consumer`` (parameter prefixes) is folded."""
         return self.fold_norms and not self.bf16_site(producer) and not self.bf16_site(consumer)
@@ -373,11 +390,16 @@ class Pi0Torch:
         views = images.shape[0]
         for i in range(d.vision_layers):
             p = f"{VP}encoder.layers.{i}."
-            y = F.layer_norm(x.float(), (d.vision_width,), sd[p + "layer_norm1.weight"].float(), sd[p + "layer_norm1.bias"].float(), d.ln_eps).to(x.dtype)
-            self.rec(f"vision.{i}.ln1", y)
-            q = self.act(self.linear(y, p + "self_attn.q_proj"))
-            k = self.act(self.linear(y, p + "self_attn.k_proj"))
-            v = self.act(self.linear(y, p + "self_attn.v_proj"))
+            g1, b1 = sd[p + "layer_norm1.weight"].float(), sd[p + "layer_norm1.bias"].float()
+            # the first layer's norm reads the patch embedding and stays a norm; later ones fold between fc2 and q|k|v
+            if i > 0 and self.fold_layernorms and self.folds(f"{VP}encoder.layers.{i - 1}.mlp.fc2", p + "self_attn.q_proj"):
+                q, k, v = [self.act(self.folded_layernorm_linear(x, p + f"self_attn.{n}_proj", g1, b1, d.ln_eps)) for n in "qkv"]
+            else:
+                y = F.layer_norm(x.float(), (d.vision_width,), g1, b1, d.ln_eps).to(x.dtype)
+                self.rec(f"vision.{i}.ln1", y)
+                q = self.act(self.linear(y, p + "self_attn.q_proj"))
+                k = self.act(self.linear(y, p + "self_attn.k_proj"))
+                v = self.act(self.linear(y, p + "self_attn.v_proj"))
             self.rec(f"vision.{i}.qkv", torch.cat((q, k, v), dim=-1))
             outs = []
             for b in range(views):
@@ -389,9 +411,13 @@ class Pi0Torch:
             o = self.linear(a, p + "self_attn.out_proj", head=(hd, -(-hd // 16) * 16) if self.head_blocks and hd % 16 else None)
             x = self.add_residual(o, x, p + "self_attn.out_proj")
             self.rec(f"vision.{i}.out", x)
-            y = F.layer_norm(x.float(), (d.vision_width,), sd[p + "layer_norm2.weight"].float(), sd[p + "layer_norm2.bias"].float(), d.ln_eps).to(x.dtype)
-            self.rec(f"vision.{i}.ln2", y)
-            h = self.linear(y, p + "mlp.fc1")
+            g2, b2 = sd[p + "layer_norm2.weight"].float(), sd[p + "layer_norm2.bias"].float()
+            if self.fold_layernorms and self.folds(p + "self_attn.out_proj", p + "mlp.fc1"):
+                h = self.folded_layernorm_linear(x, p + "mlp.fc1", g2, b2, d.ln_eps)
+            else:
+                y = F.layer_norm(x.float(), (d.vision_width,), g2, b2, d.ln_eps).to(x.dtype)
+                self.rec(f"vision.{i}.ln2", y)
+                h = self.linear(y, p + "mlp.fc1")
             if self.mode != "nvfp4":
                 h = F.gelu(h, approximate="tanh")
             elif self.bf16_site(p + "mlp.fc2"):

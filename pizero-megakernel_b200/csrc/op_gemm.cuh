@@ -221,11 +221,25 @@ __device__ __forceinline__ float gelu_sigmoid(float x) {
 // (Instantiated per epilogue kind: each accumulator drain carries only its own arithmetic and registers.)
 template <int EPI>
 __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const uint32_t (&raw)[32], int row, int col0,
-                                                    bool row_ok, float row_scale, float& sumsq) {
+                                                    bool row_ok, float row_scale, float row_shift, float& sumsq, float& sum) {
     float v[32];
     if (!row_ok) return;
 #pragma unroll
     for (int i = 0; i < 32; i++) v[i] = __uint_as_float(raw[i]) * row_scale;
+    if constexpr (EPI == EPI_BF16_EXT || EPI == EPI_FP4) {
+        if (g.col_center) {
+            // folded LayerNorm: subtract the row mean's share, mean * rstd * (sum over K of weight row n)
+            const float4* c4 = reinterpret_cast<const float4*>(g.col_center + col0);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float4 c = __ldg(c4 + i);
+                v[4 * i] = fmaf(row_shift, c.x, v[4 * i]);
+                v[4 * i + 1] = fmaf(row_shift, c.y, v[4 * i + 1]);
+                v[4 * i + 2] = fmaf(row_shift, c.z, v[4 * i + 2]);
+                v[4 * i + 3] = fmaf(row_shift, c.w, v[4 * i + 3]);
+            }
+        }
+    }
     if constexpr (EPI == EPI_GEGLU_FP4) {
         // interleaved (gate, up) column pairs -> 16 outputs = one scale block
         float h[16];
@@ -320,6 +334,8 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
                 const float2 f = unpack_bf16x2(w[8 * half + i]);
                 sumsq = __fmaf_rn(f.x, f.x, sumsq);
                 sumsq = __fmaf_rn(f.y, f.y, sumsq);
+                sum += f.x;
+                sum += f.y;
                 h[2 * i] = f.x * g.out_inv_gs;
                 h[2 * i + 1] = f.y * g.out_inv_gs;
             }
@@ -466,7 +482,7 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
         // alpha, times the row's 1/rms where the projection reads un-normalised rows (norm weight folded into B): given
         // as a factor, or as the producer's per-tile sums of squares (complete: the operands behind this accumulator
         // were only copied after the producer stage had finished)
-        float row_scale = g.alpha, sumsq = 0.f;
+        float row_scale = g.alpha, row_shift = 0.f, sumsq = 0.f, sum = 0.f;
         if (row_ok && g.row_factor) row_scale *= __ldcg(g.row_factor + row);
         if (row_ok && g.row_sumsq) {
             const float4* part = reinterpret_cast<const float4*>(g.row_sumsq + static_cast<size_t>(row) * g.sumsq_parts);
@@ -481,7 +497,26 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
                     if (i0 + j < quads) { total += q[j].x; total += q[j].y; total += q[j].z; total += q[j].w; }
                 }
             }
-            row_scale *= rsqrtf(total * g.sumsq_inv_width + g.sumsq_eps);
+            if (g.row_sum) {
+                // LayerNorm: the mean from the per-tile sums (same layout, same order), the variance as E[x^2] - mean^2
+                const float4* spart = reinterpret_cast<const float4*>(g.row_sum + static_cast<size_t>(row) * g.sumsq_parts);
+                float stotal = 0.f;
+                for (int i0 = 0; i0 < quads; i0 += 8) {
+                    float4 q[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) q[j] = i0 + j < quads ? __ldcg(spart + i0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        if (i0 + j < quads) { stotal += q[j].x; stotal += q[j].y; stotal += q[j].z; stotal += q[j].w; }
+                    }
+                }
+                const float mean = stotal * g.sumsq_inv_width;
+                const float rstd = rsqrtf(fmaxf(total * g.sumsq_inv_width - mean * mean, 0.f) + g.sumsq_eps);
+                row_scale *= rstd;
+                row_shift = -mean * rstd;
+            } else {
+                row_scale *= rsqrtf(total * g.sumsq_inv_width + g.sumsq_eps);
+            }
         }
         for (int c = 0; c < chunks; ++c) {
             uint32_t raw[32];
@@ -493,9 +528,12 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
             }
-            gemm_epilogue_chunk<EPI>(g, raw, row, n_tile * g.block_n + c * 32, row_ok, row_scale, sumsq);
+            gemm_epilogue_chunk<EPI>(g, raw, row, n_tile * g.block_n + c * 32, row_ok, row_scale, row_shift, sumsq, sum);
         }
-        if (EPI == EPI_STREAM && row_ok) g.sumsq_out[static_cast<size_t>(row) * g.n_tiles + n_tile] = sumsq;
+        if (EPI == EPI_STREAM && row_ok) {
+            g.sumsq_out[static_cast<size_t>(row) * g.sumsq_ld + n_tile] = sumsq;
+            if (g.sum_out) g.sum_out[static_cast<size_t>(row) * g.sumsq_ld + n_tile] = sum;
+        }
         // each epilogue warp publishes its own 32 rows (a GEMM tile counts 4 units): no CTA barrier on this path
         if (stamp && t == first + count - 1 && threadIdx.x == 128) stamp[7] = static_cast<long long>(global_ns());
         fence_proxy_async_global();

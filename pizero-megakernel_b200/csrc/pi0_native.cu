@@ -388,6 +388,7 @@ int gemm_refresh(Op* op) {
     g.tmap_b = op->maps + 1;
     g.m_tiles = op->m / 128;
     g.n_tiles = op->n / g.block_n;
+    if (!g.sum_out || g.sumsq_ld < g.n_tiles) g.sumsq_ld = g.n_tiles;      // statistics rows: one slot per column tile
     g.operands = op->operands;
     g.k_groups = static_cast<int>(row_bytes / 32);
     // Operand ring: a slot holds kChunks chunks of the rows that are actually copied (A: a_box_rows, B: block_n) and,
@@ -572,6 +573,21 @@ extern "C" int configure_resident_fp4_stream(void* handle, const void* bias, con
     g.out_blocks = op->n / 16;
     g.out_inv_gs = 1.f / copy_global_scale;
     g.sumsq_out = sumsq;
+    g.sum_out = nullptr;
+    g.sumsq_ld = op->n / g.block_n;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+// extension: a residual-stream projection also leaves the per-tile SUMS of its rounded rows (for a LayerNorm folded into
+// the projection that follows), and the row stride of both statistics arrays becomes ld floats (>= N / tile width, a multiple
+// of 4; slots beyond the tile count are never written: zero them once).  After configure_resident_fp4_stream and the tile width.
+extern "C" int configure_resident_fp4_stream_sums(void* handle, float* sums, int ld) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || op->desc.p.gemm.epilogue != EPI_STREAM || !sums || !aligned16(sums)) return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    if (ld < op->n / g.block_n || ld % 4) return cudaErrorInvalidValue;
+    g.sum_out = sums;
+    g.sumsq_ld = ld;
     op->solo_dirty = true;
     return cudaSuccess;
 }
@@ -582,6 +598,27 @@ extern "C" int configure_resident_fp4_row_rms(void* handle, const float* sumsq, 
         return cudaErrorInvalidValue;
     GemmParams& g = op->desc.p.gemm;
     g.row_sumsq = sumsq; g.sumsq_parts = parts; g.sumsq_inv_width = 1.f / static_cast<float>(width); g.sumsq_eps = eps;
+    g.row_sum = nullptr; g.col_center = nullptr;
+    op->solo_dirty = true;
+    return cudaSuccess;
+}
+// extension: the LayerNorm form of configure_resident_fp4_row_rms.  sums / sumsq FP32 [M, parts] are the per-tile sums and sums
+// of squares a residual-stream projection left (configure_resident_fp4_stream_sums); every accumulator row r becomes
+// rstd_r * (alpha * acc - mean_r * center[n]) with mean and variance (E[x^2] - mean^2) of the `width` values of row r, and
+// center FP32 [N] the sum over K of weight row n as the MMA reads it (dequantised).  The weight columns carry the norm's
+// gamma, the bias (added afterwards, as always) its beta: bias + W beta.  Epilogues: BF16 with the extended options
+// (a head-padded store or a GELU column limit selects them) and NVFP4 output.
+extern "C" int configure_resident_fp4_row_layernorm(void* handle, const float* sumsq, const float* sums, int parts, int width,
+                                                    float eps, const float* center) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_GEMM || !sumsq || !sums || !center || parts < 4 || parts % 4 || width < 1 || !std::isfinite(eps) ||
+        eps <= 0 || !aligned16(sumsq) || !aligned16(sums) || !aligned16(center))
+        return cudaErrorInvalidValue;
+    GemmParams& g = op->desc.p.gemm;
+    if (g.epilogue == EPI_BF16) g.epilogue = EPI_BF16_EXT;           // (the drain loop that carries the correction)
+    if (g.epilogue != EPI_BF16_EXT && g.epilogue != EPI_FP4) return cudaErrorInvalidValue;
+    g.row_sumsq = sumsq; g.row_sum = sums; g.col_center = center;
+    g.sumsq_parts = parts; g.sumsq_inv_width = 1.f / static_cast<float>(width); g.sumsq_eps = eps;
     op->solo_dirty = true;
     return cudaSuccess;
 }

@@ -74,9 +74,16 @@ struct GemmParams {
     // apply the RMS normalisation as a row factor instead of running behind a norm stage
     uint8_t* copy_fp4;           // packed codes [M_pad, ld_copy bytes]
     int ld_copy;
-    float* sumsq_out;            // FP32 [M_pad, n_tiles]
-    // consumer side: row factor rsqrt(sum(row_sumsq[row, 0..sumsq_parts)) * sumsq_inv_width + sumsq_eps), times alpha
+    float* sumsq_out;            // FP32 [M_pad, sumsq_ld] (sumsq_ld >= n_tiles: slot n of a row belongs to column tile n)
+    float* sum_out;              // FP32 [M_pad, sumsq_ld] or null: per-tile sums of the same rounded rows (LayerNorm consumers)
+    int sumsq_ld;
+    // consumer side: row factor rsqrt(sum(row_sumsq[row, 0..sumsq_parts)) * sumsq_inv_width + sumsq_eps), times alpha.
+    // With row_sum (per-tile sums, same layout) the rows are LayerNorm-ed instead: mean m and variance from the two sums,
+    // acc * alpha * rstd - m * rstd * col_center[n], where col_center[n] is the sum over K of the weight row n as the MMA
+    // reads it (the weight columns carry the norm's gamma, the bias its beta)
     const float* row_sumsq;
+    const float* row_sum;
+    const float* col_center;     // FP32 [N]
     int sumsq_parts;
     float sumsq_inv_width, sumsq_eps;
     int rows;                    // logical rows (rows >= this are written as zero codes / skipped)

@@ -52,6 +52,8 @@ _SIGNATURES = {
     "configure_resident_fp4_qkv_rope": [_P, _P, _I, _P, _P, _P, _P, _I, _I, _I],
     "configure_resident_fp4_stream": [_P] * 6 + [_F, _P],
     "configure_resident_fp4_row_rms": [_P, _P, _I, _I, _F],
+    "configure_resident_fp4_stream_sums": [_P, _P, _I],
+    "configure_resident_fp4_row_layernorm": [_P, _P, _P, _I, _I, _F, _P],
     "configure_resident_fp4_rows": [_P, _I],
     "configure_resident_fp4_tile": [_P, _I],
     "configure_resident_fp4_weight_layout": [_P, _I],

@@ -289,6 +289,64 @@ def test_residual_stream_epilogue_and_row_rms_consumer():
                 assert lib.configure_resident_fp4_row_rms(consumer.handle, sumsq.data_ptr(), 6, n, 1e-6) == 1
 
 
+def test_folded_layernorm_between_two_projections():
+    """LayerNorm folded into the projection that follows: the producer leaves per-tile sums and sums of squares (row
+    stride padded to a multiple of 4 slots), the consumer - weight columns times gamma, bias + W beta - turns its
+    accumulator rows into rstd * (acc - mean * sum_k W'[n, k]).  Checked against LayerNorm + projection in FP32 on the
+    operands the MMA reads (the dequantised copy and weight), for the BF16 and the NVFP4-output epilogue."""
+    lib = _native.load()
+    rng = np.random.default_rng(131)
+    m, k, n, n2 = 256, 512, 1152, 384                        # 1152 / 64 = 18 tiles: the statistics rows are padded to 20 slots
+    a, w = rng.normal(size=(m, k)).astype(np.float32), rng.normal(scale=0.05, size=(n, k)).astype(np.float32)
+    res = bf16(rng.normal(loc=0.7, size=(m, n)))            # a row mean well away from zero
+    gamma, beta = rng.normal(loc=1.0, scale=0.2, size=n).astype(np.float32), rng.normal(scale=0.3, size=n).astype(np.float32)
+    w2 = rng.normal(scale=0.05, size=(n2, n)).astype(np.float32)
+    b2 = rng.normal(scale=0.2, size=n2).astype(np.float32)
+    folded = bf16(w2 * gamma[None, :]).float().numpy()
+    pa, pw, pw2 = pack_nvfp4(a), pack_nvfp4(w, scale_policy="ceil"), pack_nvfp4(folded, scale_policy="ceil")
+    w2_deq = oracle.dequantize(pw2.data, pw2.scales, pw2.global_scale, (n2, n))
+    center = torch.from_numpy(w2_deq.sum(1).astype(np.float32)).cuda()
+    bias2 = bf16(b2 + w2 @ beta)
+    placeholder = pack_nvfp4(np.zeros((m, n), np.float32))
+    block_n, ld = 64, 20
+    with ResidentNVFP4(None, pa, pw, workers=16, output_dtype=torch.bfloat16, residual=res, block_n=block_n) as producer:
+        copy = torch.zeros(m, n // 2, dtype=torch.uint8, device="cuda")
+        copy_scales = torch.zeros((m // 128) * (n // 64) * 512, dtype=torch.uint8, device="cuda")
+        sumsq, sums = torch.zeros((m, ld), device="cuda"), torch.zeros((m, ld), device="cuda")
+        _native.check(lib.configure_resident_fp4_stream(producer.handle, None, producer.residual.data_ptr(), producer.output.data_ptr(),
+                                                        copy.data_ptr(), copy_scales.data_ptr(), 1.0, sumsq.data_ptr()), "stream")
+        _native.check(lib.configure_resident_fp4_stream_sums(producer.handle, sums.data_ptr(), ld), "stream sums")
+        assert lib.configure_resident_fp4_stream_sums(producer.handle, sums.data_ptr(), 16) == 1       # fewer slots than tiles
+        out = producer.forward().float()
+        torch.cuda.synchronize()
+        assert producer.status()["code"] == 0
+        tiles = out.reshape(m, n // block_n, block_n)
+        assert relrms(sums[:, :18].cpu().numpy(), tiles.sum(-1).cpu().numpy()) < 1e-5
+        assert relrms(sumsq[:, :18].cpu().numpy(), tiles.square().sum(-1).cpu().numpy()) < 1e-6
+        assert not sums[:, 18:].any() and not sumsq[:, 18:].any()
+        x_deq = oracle.dequantize(copy.cpu().numpy(), unswizzle_scales(copy_scales.cpu().numpy(), m, n // 16), 1.0, (m, n))
+        mean = out.mean(-1, keepdim=True).cpu().numpy()
+        rstd = 1.0 / np.sqrt(out.var(-1, unbiased=False, keepdim=True).cpu().numpy() + 1e-6)
+        want = rstd * (x_deq @ w2_deq.T - mean * w2_deq.sum(1)[None, :]) + bias2.float().numpy()[None, :]
+        # the same thing the long way round: LayerNorm of the rows the MMA reads, then the projection
+        direct = ((x_deq - mean) * rstd) @ w2_deq.T + bias2.float().numpy()[None, :]
+        assert relrms(want, direct) < 1e-5
+        for fp4_out in (False, True):
+            kw = dict(output_dtype=torch.uint8, output_gelu=True, output_global_scale=0.5) if fp4_out else dict(output_dtype=torch.bfloat16)
+            with ResidentNVFP4(None, placeholder, pw2, workers=8, bias=bias2, activation_buffers=(copy, copy_scales), **kw) as consumer:
+                _native.check(lib.configure_resident_fp4_row_layernorm(consumer.handle, sumsq.data_ptr(), sums.data_ptr(), ld, n, 1e-6,
+                                                                       center.data_ptr()), "row layernorm")
+                got = consumer.forward()
+                torch.cuda.synchronize()
+                assert consumer.status()["code"] == 0
+                if fp4_out:
+                    got = oracle.dequantize(got.cpu().numpy(), unswizzle_scales(consumer.output_scales.cpu().numpy(), m, n2 // 16), 0.5, (m, n2))
+                    ref = oracle_ops.gelu_tanh(torch.from_numpy(want)).numpy()
+                    assert relrms(got, ref) < 0.12                               # one NVFP4 rounding of the activations
+                else:
+                    assert relrms(got.float().cpu().numpy(), want) < 4e-3        # BF16 rounding of the result
+
+
 def test_gemm_qkv_rope_epilogue():
     lib = _native.load()
     rng = np.random.default_rng(71)
