@@ -474,6 +474,8 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
                 prefetch_l1(cs); prefetch_l1(cs + (hd >> 1)); prefetch_l1(sn); prefetch_l1(sn + (hd >> 1));
             }
         }
+        if ((EPI == EPI_BF16_EXT || EPI == EPI_FP4) && g.col_center && lane < (g.block_n >> 5))
+            prefetch_l1(g.col_center + n_tile * g.block_n + lane * 32);    // constant data: close by when the accumulator is ready
         if (!mbar_wait_warp(prog, ctl, &ctl->acc_full[buf], phase, stage_index)) return;
         tc_fence_after();
         if (stamp && t == first && threadIdx.x == 128) stamp[6] = static_cast<long long>(global_ns());
@@ -486,28 +488,26 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
         if (row_ok && g.row_factor) row_scale *= __ldcg(g.row_factor + row);
         if (row_ok && g.row_sumsq) {
             const float4* part = reinterpret_cast<const float4*>(g.row_sumsq + static_cast<size_t>(row) * g.sumsq_parts);
-            float total = 0.f;
             const int quads = g.sumsq_parts >> 2;
-            for (int i0 = 0; i0 < quads; i0 += 8) {                  // eight loads in flight: one L2 round trip per 128 bytes
-                float4 q[8];
-#pragma unroll
-                for (int j = 0; j < 8; j++) q[j] = i0 + j < quads ? __ldcg(part + i0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                for (int j = 0; j < 8; j++) {                        // fixed order: the same bits on every launch
-                    if (i0 + j < quads) { total += q[j].x; total += q[j].y; total += q[j].z; total += q[j].w; }
-                }
-            }
-            if (g.row_sum) {
-                // LayerNorm: the mean from the per-tile sums (same layout, same order), the variance as E[x^2] - mean^2
+            float total = 0.f;
+            if ((EPI == EPI_BF16_EXT || EPI == EPI_FP4) && g.row_sum) {
+                // LayerNorm: the per-tile sums (same layout) are requested together with the sums of squares; the mean
+                // from the sums, the variance as E[x^2] - mean^2
                 const float4* spart = reinterpret_cast<const float4*>(g.row_sum + static_cast<size_t>(row) * g.sumsq_parts);
                 float stotal = 0.f;
-                for (int i0 = 0; i0 < quads; i0 += 8) {
-                    float4 q[8];
+                for (int i0 = 0; i0 < quads; i0 += 4) {
+                    float4 q[4], sq[4];
 #pragma unroll
-                    for (int j = 0; j < 8; j++) q[j] = i0 + j < quads ? __ldcg(spart + i0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int j = 0; j < 4; j++) {
+                        q[j] = i0 + j < quads ? __ldcg(part + i0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                        sq[j] = i0 + j < quads ? __ldcg(spart + i0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        if (i0 + j < quads) { stotal += q[j].x; stotal += q[j].y; stotal += q[j].z; stotal += q[j].w; }
+                    for (int j = 0; j < 4; j++) {                    // fixed order: the same bits on every launch
+                        if (i0 + j < quads) {
+                            total += q[j].x; total += q[j].y; total += q[j].z; total += q[j].w;
+                            stotal += sq[j].x; stotal += sq[j].y; stotal += sq[j].z; stotal += sq[j].w;
+                        }
                     }
                 }
                 const float mean = stotal * g.sumsq_inv_width;
@@ -515,6 +515,15 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
                 row_scale *= rstd;
                 row_shift = -mean * rstd;
             } else {
+                for (int i0 = 0; i0 < quads; i0 += 8) {              // eight loads in flight: one L2 round trip per 128 bytes
+                    float4 q[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) q[j] = i0 + j < quads ? __ldcg(part + i0 + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {                    // fixed order: the same bits on every launch
+                        if (i0 + j < quads) { total += q[j].x; total += q[j].y; total += q[j].z; total += q[j].w; }
+                    }
+                }
                 row_scale *= rsqrtf(total * g.sumsq_inv_width + g.sumsq_eps);
             }
         }

@@ -122,7 +122,7 @@ class NativePi0:
         return cls(StateDictModel(config or Pi0Config(), state_dict), **kwargs)
 
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
-                 library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=None, vision_block_n=64,
+                 library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=None, vision_block_n=64, fold_layernorms=True,
                  rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="spread",
                  fold_norms=True, attention_path=None, weight_store=None):
         config = getattr(model, "config", None)
@@ -148,6 +148,7 @@ class NativePi0:
         self.expert_splits = expert_splits
         self.prefix_splits = prefix_splits
         self.vision_block_n = vision_block_n
+        self.fold_layernorms = bool(fold_layernorms)
         # output tile widths of the action expert's projections: an int for all four, or a dict per operation.  The default
         # gives the projections with few output columns 32-wide tiles (twice the workers, half the bytes of weight and half
         # the serial epilogue per worker); gate/up already has 128 tiles of 64
@@ -219,7 +220,7 @@ class NativePi0:
             store[key] = make()
         return store[key]
 
-    def weight(self, w, *, rows_to=128, block_n=128, precision="nvfp4"):
+    def weight(self, w, *, rows_to=128, block_n=128, precision="nvfp4", row_sums=False):
         """BF16/FP32 [N, K] -> the site's operand format on the device: NVFP4 (ceil block scales, tensor scale
         amax/(6*448)) or zero-padded BF16.
 
@@ -239,6 +240,8 @@ class NativePi0:
         stream = torch.cuda.current_stream(self.device).cuda_stream
         _native.check(self.lib.quantize_nvfp4(src.data_ptr(), m.data.data_ptr(), m.scales.data_ptr(), np_, kp, kp, kp // 16,
                                               m.global_scale, 1, stream), "weight quantisation")
+        if row_sums:
+            m.row_sums = self._fp4_row_sums(m, np_, kp)     # sum over K of every row as the MMA reads it (folded LayerNorm)
         if block_n == 32:
             from native_pi0.primitives import narrow_tile_scales
             m.scales = narrow_tile_scales(m.scales, np_, kp // 16)     # an atom of scales per 32-row tile
@@ -251,6 +254,18 @@ class NativePi0:
         torch.cuda.current_stream(self.device).synchronize()
         self.buffers.append(m)
         return m
+
+    def _fp4_row_sums(self, m, rows, k):
+        """FP32 [rows]: the sum over K of every row of a freshly quantised NVFP4 matrix (codes row-major, scales in the
+        standard atom layout), decoded exactly as the tensor core decodes it."""
+        from native_pi0.quantization import E2M1, UE4M3, scale_offsets
+        values = torch.tensor(np.concatenate((E2M1, -E2M1)), device=self.device)
+        data = m.data[:rows, :k // 2].long()
+        pairs = values[data & 15] + values[data >> 4]                      # [rows, k / 2]: two elements per byte
+        blocks = pairs.view(rows, k // 16, 8).sum(-1)
+        where = torch.from_numpy(scale_offsets(rows, k // 16).astype(np.int64)).to(self.device)
+        scale = torch.tensor(UE4M3, device=self.device)[m.scales[where].long()]
+        return ((blocks * scale).sum(-1) * np.float32(m.global_scale)).float().contiguous()
 
     # ------------------------------------------------------------------------------------------ stages
     def add(self, kind, handle, name, sources=(), outputs=()):
@@ -280,14 +295,16 @@ class NativePi0:
 
     def gemm(self, name, a: Activation, w, *, rows, sources, out=None, bias=None, residual=None,
              out_act: Activation = None, out_precision=None, activation=0, act_cols=None, rope=None, block_n=128,
-             stream=None, row_rms=None, head_pad=None):
+             stream=None, row_rms=None, row_ln=None, head_pad=None):
         """One projection stage.  ``w`` decides the operand format (``Fp4Matrix``: NVFP4 on ``a.fp4``; ``DenseMatrix``:
         BF16 on ``a.bf16``).  The result goes to ``out`` (BF16, + bias + residual), to the fused QKV destinations
         (``rope``), or to ``out_act`` in the format ``out_precision`` of the consuming site with ``activation``
         0 none / 1 GELU / 2 GeGLU over interleaved gate/up columns (``act_cols``: logical width for the GELU).
         ``stream=(copy, sumsq)``: besides ``out`` the stage writes the un-normalised NVFP4 copy of its rows into the
         ``Activation`` ``copy`` and per-tile sums of squares into ``sumsq``; ``row_rms=(sumsq, parts, width, eps)``: the
-        stage reads such a copy and applies the RMS row factor itself (its weight carries the norm weight)."""
+        stage reads such a copy and applies the RMS row factor itself (its weight carries the norm weight).  The LayerNorm
+        form: ``stream=(copy, sumsq, sums)`` (statistics rows ``sumsq.shape[1]`` slots long) and
+        ``row_ln=(sumsq, sums, width, eps, center)`` with ``center`` the row sums of the weight."""
         h = C.c_void_p()
         dense = isinstance(w, DenseMatrix)
         src = a.bf16 if dense else a.fp4
@@ -332,12 +349,14 @@ class NativePi0:
                     _native.check(self.lib.configure_dense_gelu(h, act_cols if act_cols is not None else cols), name)
             outs = [StageOutput(name, "bf16", target, rows, cols // 2 if activation == 2 else cols)]
         elif stream is not None:
-            copy, sumsq = stream
+            copy, sumsq = stream[:2]
             _native.check(self.lib.configure_resident_fp4_stream(h, _native.ptr(bias), _native.ptr(residual), out.data_ptr(),
                                                                  copy.fp4.data.data_ptr(), copy.fp4.scales.data_ptr(),
                                                                  copy.fp4.global_scale, sumsq.data_ptr()), name)
             outs = [StageOutput(name, "bf16", out, rows, cols), StageOutput(name, "fp4", copy.fp4, rows, cols),
-                    StageOutput(name, "sumsq", sumsq, rows, sumsq.shape[1], head=(block_n,))]
+                    StageOutput(name, "sumsq", sumsq, rows, n // block_n, head=(block_n,))]
+            if len(stream) > 2:
+                outs.append(StageOutput(name, "sum", stream[2], rows, n // block_n, head=(block_n,)))
         else:
             _native.check(self.lib.configure_resident_fp4_bf16(h, _native.ptr(bias), _native.ptr(residual), out.data_ptr()), name)
             if dense and residual is not None:
@@ -358,6 +377,12 @@ class NativePi0:
             if w.tiled != block_n:
                 raise ValueError(f"{name}: weight tiled for {w.tiled}-wide tiles, used with {block_n}")
             _native.check(self.lib.configure_resident_fp4_weight_layout(h, 1), name)
+        if stream is not None and len(stream) > 2:
+            _native.check(self.lib.configure_resident_fp4_stream_sums(h, stream[2].data_ptr(), stream[1].shape[1]), name)
+        if row_ln is not None:
+            sumsq, sums, width, eps, center = row_ln
+            _native.check(self.lib.configure_resident_fp4_row_layernorm(h, sumsq.data_ptr(), sums.data_ptr(), sumsq.shape[1], width,
+                                                                        float(eps), center.data_ptr()), name)
         return self.add(0, h, name, sources, outs)
 
     def norm(self, name, x, out: Activation, *, rows, sources, kind, gamma=None, beta=None, eps=1e-6):
@@ -455,29 +480,62 @@ class NativePi0:
             wide = torch.zeros((w.shape[0], c.vision_heads, fp4_pitch), device=w.device, dtype=w.dtype)
             wide[:, :, :hd] = w.view(w.shape[0], c.vision_heads, hd)
             return wide.view(w.shape[0], -1)
+        # Folded LayerNorms (``fold_norms`` and ``fold_layernorms``, NVFP4 sites): the projection in front of a norm (out, fc2)
+        # also leaves the NVFP4 copy of its un-normalised rows and per-tile sums and sums of squares; the projection behind
+        # it (fc1, the next layer's q|k|v) carries gamma in its weight columns and ``bias + W beta`` as bias, and centres and
+        # scales its accumulator rows.  The first layer's norm reads the patch embedding and stays a stage.
+        fold_ln = self.fold_norms and self.fold_layernorms
+        slots = padded(W // self.vision_block_n, 4)          # statistics slots per row: one per column tile, padded to a multiple of 4
+        stats = lambda key: self.cached((key, M, slots), lambda: self.tensor((M, slots), torch.float32))
+
+        def folded(weight, bias, gamma, beta, rows_pad=None):
+            """(gamma in the columns, bias + W beta in BF16 padded to rows_pad) of a projection behind a folded LayerNorm."""
+            w = weight.to(torch.bfloat16).float()
+            shifted = bias.float() + w @ beta
+            out = torch.zeros(rows_pad or shifted.numel(), device=self.device, dtype=torch.bfloat16)
+            out[:shifted.numel()] = shifted.to(torch.bfloat16)
+            return (w * gamma[None, :]).to(torch.bfloat16), out
+
+        fold1 = False                                        # this layer's first norm is folded (decided by the layer before)
         for i in range(c.vision_layers):
             p = f"{VISION}encoder.layers.{i}."
             p_qkv, p_out, p_fc1, p_fc2 = [self.site(f"vision.{i}.{n}") for n in ("qkv", "out", "fc1", "fc2")]
             g1, b1 = sd[p + "layer_norm1.weight"].float().contiguous(), sd[p + "layer_norm1.bias"].float().contiguous()
             g2, b2 = sd[p + "layer_norm2.weight"].float().contiguous(), sd[p + "layer_norm2.bias"].float().contiguous()
-            wqkv = self.cached(p + "qkv." + p_qkv, lambda: self.weight(torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"]), precision=p_qkv))
-            bqkv = torch.cat([sd[p + f"self_attn.{n}_proj.bias"] for n in "qkv"]).to(torch.bfloat16).contiguous()
+            fold2 = fold_ln and p_out == "nvfp4" and p_fc1 == "nvfp4"
+            fold1_next = fold_ln and p_fc2 == "nvfp4" and i + 1 < c.vision_layers and self.site(f"vision.{i + 1}.qkv") == "nvfp4"
+            w_qkv_raw = lambda: torch.cat([sd[p + f"self_attn.{n}_proj.weight"] for n in "qkv"])
+            b_qkv_raw = torch.cat([sd[p + f"self_attn.{n}_proj.bias"] for n in "qkv"])
+            if fold1:
+                wqkv = self.cached(p + "qkv.nvfp4.ln", lambda: self.weight(folded(w_qkv_raw(), b_qkv_raw, g1, b1)[0], row_sums=True))
+                bqkv = folded(w_qkv_raw(), b_qkv_raw, g1, b1)[1]
+            else:
+                wqkv = self.cached(p + "qkv." + p_qkv, lambda: self.weight(w_qkv_raw(), precision=p_qkv))
+                bqkv = b_qkv_raw.to(torch.bfloat16).contiguous()
             quant_in_tile = padded_heads and p_out == "nvfp4"
             if quant_in_tile:
                 wo = self.cached(p + "out.nvfp4.spread", lambda: self.weight(spread_heads(sd[p + "self_attn.out_proj.weight"]), block_n=narrow("nvfp4")))
             else:
                 wo = self.cached(p + "out." + p_out, lambda: self.weight(sd[p + "self_attn.out_proj.weight"], block_n=narrow(p_out), precision=p_out))
             bo = sd[p + "self_attn.out_proj.bias"].to(torch.bfloat16).contiguous()
-            w1 = self.cached(p + "fc1." + p_fc1, lambda: self.weight(sd[p + "mlp.fc1.weight"], precision=p_fc1))
-            bias1 = torch.zeros(mlp_pad, device=self.device, dtype=torch.bfloat16)
-            bias1[:c.vision_mlp] = sd[p + "mlp.fc1.bias"].to(torch.bfloat16)
+            if fold2:
+                w1 = self.cached(p + "fc1.nvfp4.ln", lambda: self.weight(folded(sd[p + "mlp.fc1.weight"], sd[p + "mlp.fc1.bias"], g2, b2)[0], row_sums=True))
+                bias1 = folded(sd[p + "mlp.fc1.weight"], sd[p + "mlp.fc1.bias"], g2, b2, mlp_pad)[1]
+            else:
+                w1 = self.cached(p + "fc1." + p_fc1, lambda: self.weight(sd[p + "mlp.fc1.weight"], precision=p_fc1))
+                bias1 = torch.zeros(mlp_pad, device=self.device, dtype=torch.bfloat16)
+                bias1[:c.vision_mlp] = sd[p + "mlp.fc1.bias"].to(torch.bfloat16)
             w2 = self.cached(p + "fc2." + p_fc2, lambda: self.weight(sd[p + "mlp.fc2.weight"], block_n=narrow(p_fc2), precision=p_fc2))
             bias2 = sd[p + "mlp.fc2.bias"].to(torch.bfloat16).contiguous()
             self.buffers.extend((g1, b1, g2, b2, bqkv, bo, bias1, bias2))
             buf = qkv[i & 1]
-            s_ln = self.norm(f"vision.{i}.ln1", xa, a_ln.only(p_qkv), rows=M, sources=[(s_x, SAME)], kind="layer", gamma=g1, beta=b1, eps=c.ln_eps)
+            if fold1:
+                s_ln, ln1 = s_x, (stats("vision.sumsq1"), stats("vision.sum1"), W, c.ln_eps, wqkv.row_sums)
+            else:
+                s_ln, ln1 = self.norm(f"vision.{i}.ln1", xa, a_ln.only(p_qkv), rows=M, sources=[(s_x, SAME)], kind="layer", gamma=g1,
+                                      beta=b1, eps=c.ln_eps), None
             s_qkv = self.gemm(f"vision.{i}.qkv", a_ln, wqkv, rows=M, sources=[(s_ln, SAME)], out=buf, bias=bqkv,
-                              head_pad=(hd, pitch) if padded_heads else None)
+                              head_pad=(hd, pitch) if padded_heads else None, row_ln=ln1)
             h = C.c_void_p()
             q, k, v = buf[:, :WP], buf[:, WP:2 * WP], buf[:, 2 * WP:]
             _native.check(lib.create_attention(C.byref(h), q.data_ptr(), k.data_ptr(), v.data_ptr(), None, None, None, None, None,
@@ -499,12 +557,19 @@ class NativePi0:
                 # the mma.sync tiles do not quantise 72-wide heads: a quantiser stage of its own
                 s_att = self.norm(f"vision.{i}.attention_quant", att, a_att.only("nvfp4"), rows=M, sources=[(s_att, SAME)], kind="none")
             s_o = self.gemm(f"vision.{i}.out", a_att_fp4 if quant_in_tile else a_att, wo, rows=M, sources=[(s_att, SAME)], out=xb,
-                            bias=bo, residual=xa, block_n=narrow(p_out))
-            s_ln2 = self.norm(f"vision.{i}.ln2", xb, a_ln2.only(p_fc1), rows=M, sources=[(s_o, SAME)], kind="layer", gamma=g2, beta=b2, eps=c.ln_eps)
+                            bias=bo, residual=xa, block_n=narrow(p_out),
+                            stream=(a_ln2.require("nvfp4"), stats("vision.sumsq2"), stats("vision.sum2")) if fold2 else None)
+            if fold2:
+                s_ln2, ln2 = s_o, (stats("vision.sumsq2"), stats("vision.sum2"), W, c.ln_eps, w1.row_sums)
+            else:
+                s_ln2, ln2 = self.norm(f"vision.{i}.ln2", xb, a_ln2.only(p_fc1), rows=M, sources=[(s_o, SAME)], kind="layer", gamma=g2,
+                                       beta=b2, eps=c.ln_eps), None
             s_fc1 = self.gemm(f"vision.{i}.fc1", a_ln2, w1, rows=M, sources=[(s_ln2, SAME)], out_act=a_h.require(p_fc2), out_precision=p_fc2,
-                              bias=bias1, activation=1, act_cols=c.vision_mlp)
+                              bias=bias1, activation=1, act_cols=c.vision_mlp, row_ln=ln2)
             s_x = self.gemm(f"vision.{i}.fc2", a_h, w2, rows=M, sources=[(s_fc1, SAME)], out=xa, bias=bias2, residual=xb,
-                            block_n=narrow(p_fc2))
+                            block_n=narrow(p_fc2),
+                            stream=(a_ln.require("nvfp4"), stats("vision.sumsq1"), stats("vision.sum1")) if fold1_next else None)
+            fold1 = fold1_next
             if i == 0:
                 self.mark("vision.0.qkv", buf), self.mark("vision.0.attention", att)
             self.mark(f"vision.{i}", xa)
