@@ -9,14 +9,14 @@ namespace pi0 {
 // atoms. One slot is filled by four copies (A, B, SFA, SFB). The ring is laid out per GEMM by the host (slot size from
 // the rows that are really copied, as many slots as fit): kStages slots of kStageBytes for full tiles, up to
 // kMaxStages for the narrowest ones.
-constexpr int kStages = 2;                                   // slots in flight with full-size tiles (128 rows of A and of B)
+constexpr int kStages = 3;                                   // slots in flight with full-size tiles (128 rows of A and of B)
 constexpr int kMaxStages = 5;                                // slots in flight with the narrowest tiles (64 rows of each)
 constexpr int kChunks = 2;                                   // 256-wide K chunks per slot
 constexpr int kTileABytes = 128 * 128;                       // one chunk of one operand: 128 rows x 128 bytes
 constexpr int kSfBytes = kChunks * 4 * 512;                  // scale atoms of one operand: four 64-wide K groups per chunk
 constexpr int kStageBytes = 2 * kChunks * kTileABytes + 2 * kSfBytes;   // largest slot: 72 KiB
 constexpr int kCtlBytes = 3072;
-constexpr int kDataBytes = 214 * 1024;                       // operator scratch behind the control block
+constexpr int kDataBytes = 216 * 1024;                       // operator scratch behind the control block: three full-size slots
 constexpr int kSmemBytes = kCtlBytes + kDataBytes + 1024;    // + slack for 1 KiB alignment
 constexpr int kTmemCols = 512;
 constexpr int kSfCol0 = 256;                                 // accumulators use columns [0,256)
