@@ -4,7 +4,7 @@
 // each operand row (64 FP4, 16 BF16 or 32 FP8 elements), so the copy ring and the issue loop are the same code.
 //
 //   warp 0 / lane 0 : TMA producer  - operand tiles (128 B swizzled rows) and scale atoms into a ring of slots; the ring
-//                                     is laid out per GEMM: 2 slots of 72 KiB for full NVFP4 tiles, up to 5 for narrow ones
+//                                     is laid out per GEMM: 3 slots of 72 KiB for full NVFP4 tiles, up to 5 for narrow ones
 //   warp 1          : MMA issuer    - warp-uniform loop, one elected lane issues tcgen05.cp (scales smem->TMEM, NVFP4
 //                                     only) and tcgen05.mma, 32 operand bytes of K each
 //   warps 4..7      : epilogue      - tcgen05.ld of a 128xN FP32 accumulator (one row per thread), fused math, stores
