@@ -168,6 +168,29 @@ def test_norm_stages_instead_of_folded_norms(small_model):
     assert nrmse(out, emulation) <= 0.1
 
 
+@pytest.mark.parametrize("engine_kw,oracle_kw", [
+    (dict(fold_layernorms=False), dict(fold_layernorms=False)),                      # SigLIP norms as stages, RMSNorms folded
+    (dict(attention_path="mma.sync"), dict(head_blocks=False)),                      # quantiser stage behind the SigLIP attention
+    (dict(expert_block_n=64, vision_block_n=128), dict()),                           # one tile width everywhere
+    (dict(expert_block_n={"qkv": 32, "o_proj": 32, "gate_up": 64, "down": 32}), dict()),
+])
+def test_engine_options_against_their_emulation(small_model, engine_kw, oracle_kw):
+    """Constructor options that change the arithmetic (what is quantised where) agree with the oracle run the same way;
+    options that only change the tiling agree with the default oracle."""
+    dims, cfg, sd = small_model
+    x = inputs(3, 50, 0, dims.vocab)
+    emulation = Pi0Torch(dims, sd, mode="nvfp4", **oracle_kw).sample_actions(*x)
+    with NativePi0(StateDictModel(cfg, sd), **engine_kw) as engine:
+        out = engine.forward(*x).clone()
+        assert engine.status()["code"] == 0
+        names = engine.stage_names
+    assert torch.isfinite(out).all() and nrmse(out, emulation) <= 0.1
+    if engine_kw.get("fold_layernorms") is False:
+        assert sum(n.endswith(".ln1") or n.endswith(".ln2") for n in names) == 2 * cfg.vision_layers
+    if engine_kw.get("attention_path") == "mma.sync":
+        assert any(n.endswith("attention_quant") for n in names)
+
+
 def test_partitioned_and_stage_range_launches_are_bit_exact(small_model):
     dims, cfg, sd = small_model
     x = inputs(3, 50, 0, dims.vocab)
