@@ -392,14 +392,38 @@ __device__ __forceinline__ void merge_item(const MergeParams& g, int group, int 
         const int grow = (group / g.heads) * kAttnQRows + r;          // row in the output
         const float* ml = g.partial_ml + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * 2;
         const __nv_bfloat16* po = reinterpret_cast<const __nv_bfloat16*>(g.partial_o) + (static_cast<size_t>(group) * g.splits * kAttnQRows + r) * g.head_dim + b * 16;
-        float big = -INFINITY;
-#pragma unroll 8
-        for (int s = 0; s < g.splits; s++) big = fmaxf(big, __ldcg(ml + static_cast<size_t>(s) * kAttnQRows * 2));
-        const float ref = big == -INFINITY ? 0.f : big;
         float acc[16];
 #pragma unroll
         for (int e = 0; e < 16; e++) acc[e] = 0.f;
         float denom = 0.f;
+        if (g.splits <= 4) {
+            // everything the item needs in one batch of independent loads: one round trip to L2 (the reference maximum
+            // comes from the same pairs)
+            float2 pair[4];
+            uint4 x[4][2];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int s = min(j, g.splits - 1);
+                pair[j] = __ldcg(reinterpret_cast<const float2*>(ml + static_cast<size_t>(s) * kAttnQRows * 2));
+                const uint4* src = reinterpret_cast<const uint4*>(po + static_cast<size_t>(s) * kAttnQRows * g.head_dim);
+                x[j][0] = __ldcg(src);
+                x[j][1] = __ldcg(src + 1);
+            }
+            const float big = fmaxf(fmaxf(pair[0].x, pair[1].x), fmaxf(pair[2].x, pair[3].x));
+            const float ref = big == -INFINITY ? 0.f : big;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float w = j < g.splits ? exp2f(pair[j].x - ref) : 0.f;          // 0 for a fully masked split
+                denom += w * pair[j].y;
+                merge_accumulate(acc, w, x[j]);
+            }
+            merge_store(g, head, grow, b, acc, denom);
+            return;
+        }
+        float big = -INFINITY;
+#pragma unroll 8
+        for (int s = 0; s < g.splits; s++) big = fmaxf(big, __ldcg(ml + static_cast<size_t>(s) * kAttnQRows * 2));
+        const float ref = big == -INFINITY ? 0.f : big;
         // four splits at a time: their (m, l) pairs and their 16 output values are requested together, the
         // weights are computed afterwards, so no load waits for arithmetic
         for (int s0 = 0; s0 < g.splits; s0 += 4) {
