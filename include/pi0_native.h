@@ -320,6 +320,29 @@ int begin_launch_trace(void** handle);
 int end_launch_trace(void* handle, int* count, char* symbol, int symbol_bytes);
 const char* launch_trace_error(int code);
 
+/* ------------------------------------------------------------------------------------------------------
+ * Self-contained probes with HOST pointers: each call allocates device memory, copies the operands, launches, copies
+ * the results back and frees.  Development and validation aids, never on the path of a forward pass.
+ * Replaces: native_pi0/tcgen_probe.cu (run_tcgen_probe, run_fp8_probe, run_k_probe, run_grid_probe; bound by
+ * scripts/validate_tcgen.py:26-83), native_pi0/nvfp4_probe.cu:293-299 (scripts/validate_nvfp4.py:31-72) and
+ * native_pi0/vm_probe.cu:34 (scripts/validate_vm.py:23-36).
+ * GEMM probes: a [m, k] and b [n, k] row major - BF16 (precision 0), FP8 E4M3 (precision 1) or packed NVFP4 with
+ * swizzled scale atoms sa / sb; out FP32 [repetitions, m, n], every repetition one launch = alpha * a b^T with
+ * alpha = a_scale * w_scale (1 for run_tcgen_probe); m, n multiples of 128, k a multiple of 64; the single-tile probes
+ * are m = n = 128 (k = 64 unless given).
+ * run_vm_probe: `workers` CTAs run `instructions` instructions each in one launch; host_output int32 [workers,
+ * instructions, 16] receives the CTA's tensor-memory base + 1 per instruction and reporting slot (this kernel has eight
+ * warps: warp w fills slots w and w + 8), so every entry is positive and all entries of a worker are equal. */
+int run_tcgen_probe(const void* a, const void* b, float* out, int repetitions);
+int run_fp8_probe(const void* a, const void* b, float* out, int repetitions, float a_scale, float w_scale);
+int run_k_probe(const void* a, const void* b, float* out, int repetitions, int k, int precision, float a_scale, float w_scale);
+int run_grid_probe(const void* a, const void* b, float* out, int repetitions, int m, int n, int k, int workers, int precision,
+                   float a_scale, float w_scale);
+int run_nvfp4_probe(const void* a, const void* b, const void* sa, const void* sb, float* out, int repetitions, float alpha, int k);
+int run_nvfp4_grid_probe(const void* a, const void* b, const void* sa, const void* sb, float* out, int repetitions, int m, int n,
+                         int k, int workers, float alpha);
+int run_vm_probe(int workers, int instructions, int* host_output);
+
 #ifdef __cplusplus
 }
 #endif

@@ -296,4 +296,19 @@ __device__ __forceinline__ void suffix_instruction(const VmProgram& prog, Ctl* c
     }
 }
 
+// Resource probe (run_vm_probe): for every tile - one instruction each - every warp writes the CTA's tensor-memory base
+// + 1 into its two slots, so the host sees that all eight warps took part in every instruction and that the allocation
+// they saw never changed.
+__device__ __forceinline__ void probe_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, uint32_t tmem, int first, int count) {
+    const ProbeParams& p = st.p.probe;
+    const int warp = threadIdx.x >> 5;
+    for (int t = first; t < first + count; ++t) {
+        if (lane_id() == 0) {
+            p.out[t * 16 + warp] = static_cast<int>(tmem) + 1;
+            p.out[t * 16 + warp + 8] = static_cast<int>(tmem) + 1;
+        }
+        cta_publish_tile(prog, st, t);
+    }
+}
+
 }  // namespace pi0

@@ -1579,3 +1579,124 @@ extern "C" int attention_split_noalloc(const void* q, const void* k, const void*
     noalloc_merge_kernel<<<heads * ((nq + kMergeRows - 1) / kMergeRows), kThreads, 0, s>>>(g);
     return cudaGetLastError();
 }
+
+// =====================================================================================================
+// Self-contained probes with HOST pointers (the reference builds them as separate libraries for its validation
+// scripts: native_pi0/vm_probe.cu, tcgen_probe.cu, nvfp4_probe.cu).  Each call allocates, copies, launches, copies back
+// and frees; nothing of it is on the path of a forward pass.
+namespace {
+struct DeviceBuffers {                               // frees whatever a probe allocated, on every return path
+    std::vector<void*> owned;
+    ~DeviceBuffers() { for (void* p : owned) cudaFree(p); }
+    cudaError_t get(void** out, size_t bytes) {
+        cudaError_t e = cudaMalloc(out, std::max<size_t>(bytes, 16));
+        if (e == cudaSuccess) { owned.push_back(*out); e = cudaMemset(*out, 0, std::max<size_t>(bytes, 16)); }
+        return e;
+    }
+};
+
+// `repetitions` launches of one projection, each result copied to its own [m, n] FP32 slab of the host output.
+// operands: GEMM_NVFP4 (sfa / sfb swizzled scale atoms), GEMM_BF16 or GEMM_FP8; k_pad >= k is the device row length.
+int probe_gemm(int operands, const void* a, const void* b, const void* sfa, const void* sfb, float* out, int repetitions, int m,
+               int n, int k, int workers, float alpha) {
+    if (!a || !b || !out || repetitions < 1 || m < 128 || m % 128 || n < 128 || n % 128 || k < 64 || k % 64 || workers < 1 ||
+        (operands == GEMM_NVFP4 && (!sfa || !sfb)) || !std::isfinite(alpha) || alpha <= 0)
+        return cudaErrorInvalidValue;
+    const int k_pad = operands == GEMM_FP8 ? (k + 127) / 128 * 128 : k;
+    const size_t row = operand_row_bytes(operands, k), row_pad = operand_row_bytes(operands, k_pad);
+    DeviceBuffers mem;
+    void *da = nullptr, *db = nullptr, *dsa = nullptr, *dsb = nullptr, *dout = nullptr;
+    cudaError_t e = mem.get(&da, row_pad * m);
+    if (e == cudaSuccess) e = mem.get(&db, row_pad * n);
+    if (e == cudaSuccess) e = mem.get(&dout, sizeof(float) * m * n);
+    if (e == cudaSuccess) e = cudaMemcpy2D(da, row_pad, a, row, row, m, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy2D(db, row_pad, b, row, row, n, cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && operands == GEMM_NVFP4) {
+        const size_t groups = (static_cast<size_t>(k) / 16 + 3) / 4;
+        const size_t bytes_a = static_cast<size_t>(m / 128) * groups * 512, bytes_b = static_cast<size_t>(n / 128) * groups * 512;
+        e = mem.get(&dsa, bytes_a);
+        if (e == cudaSuccess) e = mem.get(&dsb, bytes_b);
+        if (e == cudaSuccess) e = cudaMemcpy(dsa, sfa, bytes_a, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(dsb, sfb, bytes_b, cudaMemcpyHostToDevice);
+    }
+    if (e != cudaSuccess) return e;
+    void* handle = nullptr;
+    int code = operands == GEMM_NVFP4 ? create_resident_fp4(&handle, da, db, dsa, dsb, dout, m, n, k, workers, alpha)
+                                      : create_dense(&handle, da, db, dout, nullptr, nullptr, m, n, k_pad, workers, operands == GEMM_FP8, 0, alpha);
+    if (code) return code;
+    for (int r = 0; r < repetitions && !code; r++) {
+        code = cudaMemsetAsync(dout, 0xFF, sizeof(float) * m * n, nullptr);          // a repetition that stored nothing would show
+        if (!code) code = launch_solo(handle, nullptr);
+        if (!code) code = cudaMemcpy(out + static_cast<size_t>(r) * m * n, dout, sizeof(float) * m * n, cudaMemcpyDeviceToHost);
+        int status[8] = {};
+        if (!code) code = read_native_model_status(handle, status, 8);
+        if (!code && status[0]) code = cudaErrorLaunchFailure;
+    }
+    const int freed = destroy_checked(handle);
+    return code ? code : freed;
+}
+}  // namespace
+
+// Replaces: native_pi0/tcgen_probe.cu (run_tcgen_probe, run_fp8_probe, run_k_probe, run_grid_probe) - BF16 (precision 0) or
+// FP8 E4M3 (precision 1) host operands a [m, k], b [n, k]; out FP32 [repetitions, m, n] = (a_scale * w_scale) * a b^T.
+extern "C" int run_tcgen_probe(const void* a, const void* b, float* out, int repetitions) {
+    return probe_gemm(GEMM_BF16, a, b, nullptr, nullptr, out, repetitions, 128, 128, 64, 1, 1.f);
+}
+extern "C" int run_fp8_probe(const void* a, const void* b, float* out, int repetitions, float a_scale, float w_scale) {
+    return probe_gemm(GEMM_FP8, a, b, nullptr, nullptr, out, repetitions, 128, 128, 64, 1, a_scale * w_scale);
+}
+extern "C" int run_k_probe(const void* a, const void* b, float* out, int repetitions, int k, int precision, float a_scale, float w_scale) {
+    if (precision != 0 && precision != 1) return cudaErrorInvalidValue;
+    return probe_gemm(precision ? GEMM_FP8 : GEMM_BF16, a, b, nullptr, nullptr, out, repetitions, 128, 128, k, 1, a_scale * w_scale);
+}
+extern "C" int run_grid_probe(const void* a, const void* b, float* out, int repetitions, int m, int n, int k, int workers, int precision,
+                              float a_scale, float w_scale) {
+    if (precision != 0 && precision != 1) return cudaErrorInvalidValue;
+    return probe_gemm(precision ? GEMM_FP8 : GEMM_BF16, a, b, nullptr, nullptr, out, repetitions, m, n, k, workers, a_scale * w_scale);
+}
+// Replaces: native_pi0/nvfp4_probe.cu:293-299 - packed NVFP4 host operands with swizzled scale atoms.
+extern "C" int run_nvfp4_probe(const void* a, const void* b, const void* sa, const void* sb, float* out, int repetitions, float alpha, int k) {
+    return probe_gemm(GEMM_NVFP4, a, b, sa, sb, out, repetitions, 128, 128, k, 1, alpha);
+}
+extern "C" int run_nvfp4_grid_probe(const void* a, const void* b, const void* sa, const void* sb, float* out, int repetitions, int m, int n,
+                                    int k, int workers, float alpha) {
+    return probe_gemm(GEMM_NVFP4, a, b, sa, sb, out, repetitions, m, n, k, workers, alpha);
+}
+// Replaces: native_pi0/vm_probe.cu:34 - `workers` CTAs run `instructions` instructions each; host_output int32
+// [workers, instructions, 16] receives, per instruction and reporting slot, the CTA's tensor-memory base + 1 (this kernel has
+// eight warps: warp w fills slots w and w + 8), so every entry is positive and equal within a worker.
+extern "C" int run_vm_probe(int workers, int instructions, int* host_output) {
+    if (workers < 1 || instructions < 1 || !host_output) return cudaErrorInvalidValue;
+    int device = 0;
+    int code = check_device(&device);
+    if (code) return code;
+    if (workers > sm_count(device)) return cudaErrorInvalidConfiguration;
+    const size_t count = static_cast<size_t>(workers) * instructions;
+    DeviceBuffers mem;
+    void* dout = nullptr;
+    cudaError_t e = mem.get(&dout, count * 16 * sizeof(int));
+    if (e != cudaSuccess) return e;
+    StageDesc d{};
+    d.kind = OP_PROBE;
+    finish_desc(d);
+    d.tiles = static_cast<int>(count);
+    d.bands = 1;
+    d.band_div = d.tiles;
+    d.p.probe.out = static_cast<int*>(dout);
+    std::vector<int> code4(count * 4);
+    for (int w = 0; w < workers; w++)
+        for (int i = 0; i < instructions; i++) {
+            int* ins = &code4[(static_cast<size_t>(w) * instructions + i) * 4];
+            ins[0] = 1; ins[1] = 0; ins[2] = w * instructions + i; ins[3] = 1;
+        }
+    Program* prog = nullptr;
+    code = build_program(&prog, device, std::vector<StageDesc>{d}, code4, workers, instructions);
+    if (code) return code;
+    std::unique_ptr<Program> owner(prog);
+    code = launch_program(prog, nullptr, LaunchInputs{}, 0, 1, true);
+    int status[8] = {};
+    if (!code) code = read_status(prog, status, 8);
+    if (!code && status[0]) code = cudaErrorLaunchFailure;
+    if (!code) code = cudaMemcpy(host_output, dout, count * 16 * sizeof(int), cudaMemcpyDeviceToHost);
+    return code;
+}

@@ -25,6 +25,7 @@ enum OpKind : int {
     OP_EMBED = 6,       // token embedding rows * sqrt(width)
     OP_LINEAR32 = 7,    // small FP32 linear (+bias, SiLU, RMS factor, Euler update)
     OP_SUFFIX = 8,      // assemble expert input rows: state token + action tokens
+    OP_PROBE = 9,       // resource probe: every warp reports the CTA's tensor-memory base for every instruction
     OP_KINDS
 };
 
@@ -221,6 +222,10 @@ struct SuffixParams {
     int chunk, width;
 };
 
+struct ProbeParams {
+    int* out;                    // int32 [tiles, 16]: slots w and w + 8 of a tile belong to warp w
+};
+
 struct alignas(16) StageDesc {
     int kind;
     int tiles;
@@ -246,6 +251,7 @@ struct alignas(16) StageDesc {
         EmbedParams embed;
         Linear32Params lin;
         SuffixParams suffix;
+        ProbeParams probe;
     } p;
 };
 

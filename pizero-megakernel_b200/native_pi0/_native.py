@@ -107,6 +107,13 @@ _SIGNATURES = {
     "read_native_model_status": [_P, C.POINTER(_I), _I],
     "read_native_model_counters": [_P, _P, _P, _I, C.POINTER(_I)],
     "native_model_kernel_variant": [_P, C.POINTER(_I)],
+    "run_tcgen_probe": [_P, _P, _P, _I],
+    "run_fp8_probe": [_P, _P, _P, _I, _F, _F],
+    "run_k_probe": [_P, _P, _P, _I, _I, _I, _F, _F],
+    "run_grid_probe": [_P, _P, _P] + [_I] * 6 + [_F, _F],
+    "run_nvfp4_probe": [_P] * 5 + [_I, _F, _I],
+    "run_nvfp4_grid_probe": [_P] * 5 + [_I] * 5 + [_F],
+    "run_vm_probe": [_I, _I, _P],
     "enable_native_model_debug": [_P, _I],
     "read_native_model_debug": [_P, C.POINTER(_I), _I],
     "set_native_model_wait_budget": [_P, C.c_ulonglong],
