@@ -156,10 +156,17 @@ int configure_norm_layout(void* handle, int ld_in, int ld_out, int out_blocks);
  * Attention (MHA / GQA / MQA), BF16 in, FP32 softmax, BF16 out.
  * Replaces: native_pi0/attention.cu:544-666 (create_attention, launch_attention, destroy_attention,
  * configure_attention_splits, configure_attention_cache, attention_resources), bound in
- * native_pi0/attention.py:60-110.  Supported subset: BF16 (fp16 == 0); biases, in-kernel RoPE tables and
- * boolean masks must be NULL (RoPE is fused into the QKV projection epilogue); head_dim 72 or 256.
- * prefix >= 0 selects the pi0 suffix mask (query 0 sees keys [0, prefix]); prefix < 0: no mask.
+ * native_pi0/attention.py:60-110.  BF16 only (fp16 == 0); head_dim a multiple of 8 up to 256 (the reference: 64, 72,
+ * 128, 256).  prefix >= 0 selects the pi0 suffix mask (query 0 sees keys [0, prefix]); prefix < 0: none.
  * Element (b, r, h, d) of q is q[((b*nq + r)*ldq) + h*hd + d]; keys likewise with ldkv and nk.
+ * Optional arguments as in the reference: q_bias / k_bias / v_bias BF16 [heads, head_dim] ([kv_heads, head_dim] for K and
+ * V) added to the operands; q_cos / q_sin BF16 [batches * nq, head_dim] and k_cos / k_sin [batches * nk, head_dim]:
+ * rotate-half RoPE with the first half of each table; mask: bytes [batches, nq, nk], non-zero = visible, applied on top
+ * of the suffix mask (a query with no visible key gives a zero row).  Biases, tables and head sizes other than 72 / 256
+ * add an operand-preparation stage (attention_prepare_handle) that writes Q, K and V - bias added, rotated, FP32
+ * arithmetic rounded to BF16 - into library-owned buffers with every head on a 128- or 256-element pitch.  Prepared
+ * operands and the mask run on the tcgen05 tiles only: at most 256 keys per tile (use configure_attention_splits beyond
+ * that; cudaErrorInvalidValue otherwise), no KV cache, and programs that contain them launch the full kernel variant.
  */
 int create_attention(void** handle, const void* q, const void* k, const void* v, const void* q_bias, const void* k_bias,
                      const void* v_bias, const void* q_cos, const void* q_sin, const void* k_cos, const void* k_sin,
@@ -195,6 +202,12 @@ int configure_attention_path(void* handle, int path);
  * with configure_dense_head_pad writes); the row strides given at creation must cover heads * elements.  Lets 72-wide
  * SigLIP heads run on the tcgen05 tiles.  Output rows stay head_dim wide. */
 int configure_attention_head_pad(void* handle, int elements);
+/* extension: handle of the operand-preparation stage owned by an attention handle created with biases, rotary tables
+ * or a head size other than 72 / 256 (NULL otherwise); a program lists it as a stage in front of the attention. */
+int attention_prepare_handle(void* handle, void** prepare);
+/* extension: cudaSuccess when the handle can run as configured - an operator with prepared operands or a mask whose key
+ * range per tile exceeds 256 (or whose path was forced to mma.sync) cannot; launches and programs refuse it too. */
+int attention_validate(void* handle);
 /* extension: handle of the merge stage owned by an attention handle with splits > 1 (NULL otherwise). */
 int attention_merge_handle(void* handle, void** merge);
 /* Development diagnostics of a split attention handle (splits >= 2), never part of a forward pass.

@@ -530,7 +530,7 @@ __device__ __forceinline__ void merge_instruction(const VmProgram& prog, Ctl* ct
 // resident on different SMs at the same time) meet on a per-group ticket counter that grows by `splits` per launch; once all partials of
 // the head are published, every tile merges its share of the query rows (row % splits == split), so the merge
 // costs neither a stage of its own nor a serial tail on one SM.
-template <int HDP>
+template <int HDP, bool MASK>
 __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& a, int tile, uint8_t* data, uint32_t tmem,
                              uint32_t uses, int stage, long long* stamp);
 
@@ -542,8 +542,15 @@ __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl
     for (int t = first; t < first + count; ++t) {
         long long* stamp_t = t == first ? stamp : nullptr;
         if (LEAN || a.tc) {
-            const bool ok = a.hd_pad > 128 ? attn_tile_tc<256>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t)
-                                           : attn_tile_tc<128>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t);
+            bool ok = false;
+            if (!LEAN && a.mask) {
+                if constexpr (!LEAN)
+                    ok = a.hd_pad > 128 ? attn_tile_tc<256, true>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t)
+                                        : attn_tile_tc<128, true>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t);
+            } else {
+                ok = a.hd_pad > 128 ? attn_tile_tc<256, false>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t)
+                                    : attn_tile_tc<128, false>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t);
+            }
             tc_tiles++;
             if (!ok) return;                                   // uniform: a wait gave up, the abort flag is set
         } else if constexpr (!LEAN) {

@@ -39,7 +39,8 @@ __device__ __forceinline__ bool cta_wait_phase(const VmProgram& prog, Ctl* ctl, 
 
 // HDP: elements per head in memory and in the MMAs (128 or 256); a.head_dim: logical width that is stored.
 // `uses` counts the tensor-core attention tiles this CTA has run (phase parity of the four barriers).
-template <int HDP>
+// MASK: the operator's boolean visibility mask is consulted (instantiated for the full kernel variant only).
+template <int HDP, bool MASK = false>
 __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& a, int tile, uint8_t* data, uint32_t tmem,
                              uint32_t uses, int stage, long long* stamp) {
     constexpr int CHUNKS = HDP / 64;
@@ -119,14 +120,26 @@ __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& 
     const float sl2 = a.scale * 1.4426950408889634f;
     const int chunks32 = (n_s + 31) >> 5;
     const int visible_end = (a.prefix >= 0 && qrow == 0) ? min(keys, a.prefix + 1 - k_begin) : keys;   // keys [0, visible_end) of this tile
+    // bit i of the result: key j * 32 + i of this tile is visible to this thread's query row under the boolean mask
+    auto mask_bits = [&](int j) -> uint32_t {
+        if constexpr (!MASK) return 0xffffffffu;
+        if (qrow >= a.nq) return 0u;
+        const uint8_t* m = a.mask + (static_cast<size_t>(batch) * a.nq + qrow) * a.nk + k_begin + j * 32;
+        uint32_t bits = 0u;
+#pragma unroll 8
+        for (int i = 0; i < 32; i++)
+            if (j * 32 + i < keys && __ldg(m + i)) bits |= 1u << i;
+        return bits;
+    };
     float m_part = -INFINITY;
     for (int j = wg; j < chunks32; j += 2) {
         uint32_t raw[32];
         tmem_ld32(tmem + lane_addr + j * 32, raw);
+        const uint32_t vis = mask_bits(j);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; i++)
-            if (j * 32 + i < visible_end) m_part = fmaxf(m_part, __uint_as_float(raw[i]));
+            if (j * 32 + i < visible_end && ((vis >> i) & 1u)) m_part = fmaxf(m_part, __uint_as_float(raw[i]));
     }
     xm[wg * 128 + row] = m_part;
     __syncthreads();
@@ -136,13 +149,14 @@ __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& 
     for (int j = wg; j < chunks32; j += 2) {
         uint32_t raw[32];
         tmem_ld32(tmem + lane_addr + j * 32, raw);
+        const uint32_t vis = mask_bits(j);
         tmem_ld_wait();
         uint32_t packed[16];
 #pragma unroll
         for (int i = 0; i < 16; i++) {
             const int k0 = j * 32 + 2 * i;
-            const float p0 = k0 < visible_end ? exp2f(__uint_as_float(raw[2 * i]) * sl2 - m_use) : 0.f;
-            const float p1 = k0 + 1 < visible_end ? exp2f(__uint_as_float(raw[2 * i + 1]) * sl2 - m_use) : 0.f;
+            const float p0 = k0 < visible_end && ((vis >> (2 * i)) & 1u) ? exp2f(__uint_as_float(raw[2 * i]) * sl2 - m_use) : 0.f;
+            const float p1 = k0 + 1 < visible_end && ((vis >> (2 * i + 1)) & 1u) ? exp2f(__uint_as_float(raw[2 * i + 1]) * sl2 - m_use) : 0.f;
             l_part += p0 + p1;
             packed[i] = pack2_bf16(p0, p1);
         }

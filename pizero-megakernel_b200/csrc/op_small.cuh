@@ -296,6 +296,45 @@ __device__ __forceinline__ void suffix_instruction(const VmProgram& prog, Ctl* c
     }
 }
 
+// Attention operand preparation: a tile is eight rows (a warp each) of the concatenated row space Q | K | V.
+constexpr int kPrepRows = 8;
+__device__ __forceinline__ int prep_tiles(const PrepParams& p) {
+    return (p.rows[0] + kPrepRows - 1) / kPrepRows + (p.rows[1] + kPrepRows - 1) / kPrepRows + (p.rows[2] + kPrepRows - 1) / kPrepRows;
+}
+__device__ __forceinline__ void prep_instruction(const VmProgram& prog, Ctl* ctl, const StageDesc& st, int first, int count) {
+    const PrepParams& p = st.p.prep;
+    const int warp = threadIdx.x >> 5, lane = lane_id();
+    const int tq = (p.rows[0] + kPrepRows - 1) / kPrepRows, tk = (p.rows[1] + kPrepRows - 1) / kPrepRows;
+    const int half = p.head_dim >> 1;
+    for (int t = first; t < first + count; ++t) {
+        const int part = t < tq ? 0 : (t < tq + tk ? 1 : 2);
+        const int row = (t - (part == 0 ? 0 : part == 1 ? tq : tq + tk)) * kPrepRows + warp;
+        if (row < p.rows[part]) {
+            const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.src[part]) + static_cast<size_t>(row) * p.ld_src[part];
+            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.dst[part]) + static_cast<size_t>(row) * p.ld_dst[part];
+            const __nv_bfloat16* bias = static_cast<const __nv_bfloat16*>(p.bias[part]);
+            const __nv_bfloat16* cs = part < 2 && p.cos[part] ? static_cast<const __nv_bfloat16*>(p.cos[part]) + static_cast<size_t>(row) * p.head_dim : nullptr;
+            const __nv_bfloat16* sn = part < 2 && p.sin[part] ? static_cast<const __nv_bfloat16*>(p.sin[part]) + static_cast<size_t>(row) * p.head_dim : nullptr;
+            for (int i = lane; i < p.heads[part] * half; i += 32) {
+                const int h = i / half, d = i - h * half;
+                float lo = __bfloat162float(src[h * p.src_pitch + d]), hi = __bfloat162float(src[h * p.src_pitch + half + d]);
+                if (bias) {
+                    lo += __bfloat162float(bias[h * p.head_dim + d]);
+                    hi += __bfloat162float(bias[h * p.head_dim + half + d]);
+                }
+                if (cs) {
+                    const float c = __bfloat162float(cs[d]), s = __bfloat162float(sn[d]);
+                    const float rl = lo * c - hi * s, rh = hi * c + lo * s;
+                    lo = rl; hi = rh;
+                }
+                dst[h * p.pitch + d] = __float2bfloat16_rn(lo);
+                dst[h * p.pitch + half + d] = __float2bfloat16_rn(hi);
+            }
+        }
+        cta_publish_tile(prog, st, t);
+    }
+}
+
 // Resource probe (run_vm_probe): for every tile - one instruction each - every warp writes the CTA's tensor-memory base
 // + 1 into its two slots, so the host sees that all eight warps took part in every instruction and that the allocation
 // they saw never changed.

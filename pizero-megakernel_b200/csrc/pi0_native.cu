@@ -121,6 +121,8 @@ struct Op {
     size_t partial_bytes = 0, stat_bytes = 0;
     CUtensorMap* attn_maps = nullptr;  // device: Q, K, V maps of the tensor-core path
     int attn_path = -1;                // -1 choose by geometry, 0 mma.sync tiles, 1 tcgen05 tiles
+    Op* prep = nullptr;                // owned operand-preparation stage (bias / RoPE / head sizes other than 72 and 256)
+    void* prep_scratch = nullptr;      // its padded BF16 copies of Q, K and V
     Program* solo = nullptr;           // lazily built one/two-stage program for stand-alone launches
     bool solo_dirty = true;
 };
@@ -198,8 +200,8 @@ bool lean_stage(const StageDesc& d) {
         return g.operands == GEMM_NVFP4 && (g.epilogue == EPI_BF16 || g.epilogue == EPI_STREAM || g.epilogue == EPI_GEGLU_FP4 ||
                                             g.epilogue == EPI_FP4 || g.epilogue == EPI_QKV_ROPE || g.epilogue == EPI_BF16_EXT);
     }
-    if (d.kind == OP_ATTN) return d.p.attn.tc != 0;
-    return true;
+    if (d.kind == OP_ATTN) return d.p.attn.tc != 0 && !d.p.attn.mask;
+    return d.kind != OP_ATTN_PREP;
 }
 
 // Build a program from stage descriptors (sources already set) and compact int4 instructions.
@@ -356,6 +358,8 @@ int new_op(Op** out, int workers) {
 void free_op(Op* op) {
     if (!op) return;
     if (op->merge) free_op(op->merge);
+    if (op->prep) free_op(op->prep);
+    cudaFree(op->prep_scratch);
     delete op->solo;
     cudaFree(op->maps);
     cudaFree(op->partial_o);
@@ -423,11 +427,20 @@ int solo_program(Op* op) {
     if (op->solo && !op->solo_dirty) return cudaSuccess;
     delete op->solo;
     op->solo = nullptr;
-    std::vector<StageDesc> stages{op->desc};
-    std::vector<std::pair<int, int>> work{{op->desc.tiles, op->cost}};
+    std::vector<StageDesc> stages;
+    std::vector<std::pair<int, int>> work;
+    StageDesc self = op->desc;
+    if (op->prep) {                                    // operand preparation first; the attention stage waits for all of it
+        stages.push_back(op->prep->desc);
+        work.push_back({op->prep->desc.tiles, 64});
+        self.src[0] = 0;
+        self.src_mode[0] = SRC_ALL_BANDS;
+    }
+    stages.push_back(self);
+    work.push_back({op->desc.tiles, op->cost});
     if (op->merge && !op->desc.p.attn.fused_merge) {
         StageDesc m = op->merge->desc;
-        m.src[0] = 0;
+        m.src[0] = static_cast<int>(stages.size()) - 1;
         m.src_mode[0] = SRC_ALL_BANDS;
         stages.push_back(m);
         work.push_back({m.tiles, 64});
@@ -904,7 +917,7 @@ static int attention_geometry(Op* op) {
     const int per = (a.nk + a.splits - 1) / a.splits;
     const bool layout_ok = (a.hd_pad == 128 || a.hd_pad == 256) && a.hd_pad >= a.head_dim && a.head_dim % 8 == 0 &&
                            a.ldq >= a.heads * a.hd_pad && a.ldkv >= a.kv_heads * a.hd_pad;
-    const bool eligible = layout_ok && per <= 256 && (a.splits == 1 || a.head_dim == a.hd_pad);
+    const bool eligible = layout_ok && per <= 256 && (a.splits == 1 || a.head_dim % 16 == 0);    // (the merge works on 16-column blocks)
     a.tc = op->attn_path == 0 ? 0 : eligible ? 1 : 0;
     if (op->attn_path == 1 && !eligible) return cudaErrorInvalidValue;
     // an FP4 output on a head pitch other than head_dim exists only in the unsplit tcgen05 tile
@@ -932,12 +945,16 @@ extern "C" int create_attention(void** handle, const void* q, const void* k, con
                                 int ldq, int ldkv, int out_ld, int fp16, int workers, int prefix, float scale) {
     if (!handle) return cudaErrorInvalidValue;
     *handle = nullptr;
-    if (!q || !k || !v || !out || q_bias || k_bias || v_bias || q_cos || q_sin || k_cos || k_sin || mask || fp16 || batches < 1 ||
-        nq < 1 || nk < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads || (head_dim != 72 && head_dim != 256) ||
+    if (!q || !k || !v || !out || fp16 || batches < 1 || nq < 1 || nk < 1 || heads < 1 || kv_heads < 1 || heads % kv_heads ||
+        head_dim < 8 || head_dim > 256 || head_dim % 8 || (q_cos == nullptr) != (q_sin == nullptr) || (k_cos == nullptr) != (k_sin == nullptr) ||
         ldq < heads * head_dim || ldq % 8 || ldkv < kv_heads * head_dim || ldkv % 8 || out_ld < heads * head_dim || out_ld % 8 ||
         !std::isfinite(scale) || scale <= 0 || (prefix >= 0 && batches != 1) ||
         !aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(out))     // rows move in 16-byte pieces
         return cudaErrorInvalidValue;
+    // Biases, rotary tables and head sizes other than 72 / 256 go through an operand-preparation stage that writes Q, K and V
+    // (bias added, rotated) into library-owned buffers with every head on a 128- or 256-element pitch, which the tcgen05
+    // tiles read; the boolean mask is applied inside those tiles.
+    const bool prepared = q_bias || k_bias || v_bias || q_cos || k_cos || (head_dim != 72 && head_dim != 256);
     Op* op = nullptr;
     int e = new_op(&op, workers);
     if (e) return e;
@@ -945,6 +962,35 @@ extern "C" int create_attention(void** handle, const void* q, const void* k, con
     d.kind = OP_ATTN;
     finish_desc(d);
     AttnParams& a = d.p.attn;
+    a.mask = static_cast<const uint8_t*>(mask);
+    if (prepared) {
+        const int pitch = head_dim <= 128 ? 128 : 256;
+        const size_t q_elems = static_cast<size_t>(batches) * nq * heads * pitch, kv_elems = static_cast<size_t>(batches) * nk * kv_heads * pitch;
+        cudaError_t ce = cudaMalloc(&op->prep_scratch, (q_elems + 2 * kv_elems) * sizeof(uint16_t));
+        if (ce == cudaSuccess) ce = cudaMemset(op->prep_scratch, 0, (q_elems + 2 * kv_elems) * sizeof(uint16_t));
+        if (ce != cudaSuccess) { free_op(op); return ce; }
+        uint16_t* base = static_cast<uint16_t*>(op->prep_scratch);
+        e = new_op(&op->prep, workers);
+        if (e) { free_op(op); return e; }
+        StageDesc& pd = op->prep->desc;
+        pd.kind = OP_ATTN_PREP;
+        finish_desc(pd);
+        PrepParams& pp = pd.p.prep;
+        pp.src[0] = q; pp.src[1] = k; pp.src[2] = v;
+        pp.dst[0] = base; pp.dst[1] = base + q_elems; pp.dst[2] = base + q_elems + kv_elems;
+        pp.bias[0] = q_bias; pp.bias[1] = k_bias; pp.bias[2] = v_bias;
+        pp.cos[0] = q_cos; pp.sin[0] = q_sin; pp.cos[1] = k_cos; pp.sin[1] = k_sin;
+        pp.rows[0] = batches * nq; pp.rows[1] = pp.rows[2] = batches * nk;
+        pp.heads[0] = heads; pp.heads[1] = pp.heads[2] = kv_heads;
+        pp.ld_src[0] = ldq; pp.ld_src[1] = pp.ld_src[2] = ldkv;
+        pp.ld_dst[0] = heads * pitch; pp.ld_dst[1] = pp.ld_dst[2] = kv_heads * pitch;
+        pp.head_dim = head_dim; pp.src_pitch = head_dim; pp.pitch = pitch;
+        pd.tiles = (pp.rows[0] + 7) / 8 + 2 * ((pp.rows[1] + 7) / 8);
+        pd.bands = 1;
+        pd.band_div = pd.tiles;
+        q = pp.dst[0]; k = pp.dst[1]; v = pp.dst[2];
+        ldq = pp.ld_dst[0]; ldkv = pp.ld_dst[1];
+    }
     a.q = q; a.k = k; a.v = v; a.out = out;
     a.ldq = ldq; a.ldkv = ldkv; a.ldo = out_ld;
     a.batches = batches; a.nq = nq; a.nk = nk;
@@ -955,15 +1001,25 @@ extern "C" int create_attention(void** handle, const void* q, const void* k, con
     a.splits = 1;
     a.out_inv_gs = 1.f;
     a.fp4_pitch = head_dim;
-    a.hd_pad = head_dim == 256 ? 256 : 0;           // other head sizes use the tensor-core tiles only in a padded layout
+    a.hd_pad = prepared ? (head_dim <= 128 ? 128 : 256) : head_dim == 256 ? 256 : 0;   // 72-wide heads as given: the tensor-core tiles only after configure_attention_head_pad
     e = attention_geometry(op);
     if (e) { free_op(op); return e; }
     *handle = op;
     return cudaSuccess;
 }
+// Prepared operands and the boolean mask exist for the tcgen05 tiles only (at most 256 keys per tile: use KV splits).  Checked when
+// the operator is launched or placed in a program, so that splits can still be configured after creation.
+static bool attention_runnable(const Op* op) {
+    const AttnParams& a = op->desc.p.attn;
+    return a.tc || !(a.mask || op->prep);
+}
+extern "C" int attention_validate(void* handle) {
+    Op* op = as_op(handle);
+    return op && op->desc.kind == OP_ATTN && attention_runnable(op) ? cudaSuccess : cudaErrorInvalidValue;
+}
 extern "C" int launch_attention(void* handle, void* stream) {
     Op* op = as_op(handle);
-    if (!op || op->desc.kind != OP_ATTN) return cudaErrorInvalidValue;
+    if (!op || op->desc.kind != OP_ATTN || !attention_runnable(op)) return cudaErrorInvalidValue;
     return launch_solo(handle, stream);
 }
 extern "C" int destroy_attention(void* handle) { return destroy_checked(handle); }
@@ -1086,7 +1142,7 @@ extern "C" int configure_attention_cache(void* handle, const void* cache_k, cons
         !aligned16(cache_k) || !aligned16(cache_v))
         return cudaErrorInvalidValue;
     AttnParams& a = op->desc.p.attn;
-    if (a.batches != 1 || a.kv_heads != 1) return cudaErrorInvalidValue;
+    if (a.batches != 1 || a.kv_heads != 1 || op->prep) return cudaErrorInvalidValue;    // (prepared operands are copies: no cache)
     a.k = cache_k; a.v = cache_v; a.ldkv = a.head_dim; a.nk = rows; a.kv_batch_rows = rows;
     return attention_geometry(op);
 }
@@ -1131,11 +1187,20 @@ extern "C" int configure_attention_path(void* handle, int path) {
 // must cover heads * elements.  Output rows stay head_dim wide.
 extern "C" int configure_attention_head_pad(void* handle, int elements) {
     Op* op = as_op(handle);
-    if (!op || op->desc.kind != OP_ATTN || (elements != 128 && elements != 256) || elements < op->desc.p.attn.head_dim) return cudaErrorInvalidValue;
+    if (!op || op->desc.kind != OP_ATTN || (elements != 128 && elements != 256) || elements < op->desc.p.attn.head_dim || op->prep)
+        return cudaErrorInvalidValue;
     AttnParams& a = op->desc.p.attn;
     if (a.ldq < a.heads * elements || a.ldkv < a.kv_heads * elements) return cudaErrorInvalidValue;
     a.hd_pad = elements;
     return attention_geometry(op);
+}
+// extension: handle of the operand-preparation stage an attention handle owns when it was created with biases, rotary
+// tables or a head size other than 72 / 256 (NULL otherwise); a program lists it in front of the attention stage.
+extern "C" int attention_prepare_handle(void* handle, void** prepare) {
+    Op* op = as_op(handle);
+    if (!op || op->desc.kind != OP_ATTN || !prepare) return cudaErrorInvalidValue;
+    *prepare = op->prep;
+    return cudaSuccess;
 }
 extern "C" int attention_merge_handle(void* handle, void** merge) {
     Op* op = as_op(handle);
@@ -1267,6 +1332,7 @@ extern "C" int create_native_model(void** handle, int count, const NativeSpec* s
         if (!op || op->device != device) return cudaErrorInvalidValue;
         const int want = op->desc.kind == OP_GEMM ? 0 : op->desc.kind == OP_ATTN ? 1 : op->desc.kind == OP_NORM ? 2 : op->desc.kind == OP_MERGE ? 4 : 3;
         if (specs[i].kind != want) return cudaErrorInvalidValue;
+        if (op->desc.kind == OP_ATTN && !attention_runnable(op)) return cudaErrorInvalidValue;
         StageDesc d = op->desc;
         for (int s = 0; s < kMaxSources; s++) {
             d.src[s] = specs[i].sources[s];

@@ -156,6 +156,9 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
                 case OP_LINEAR32: linear32_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w, stamp); break;
                 case OP_SUFFIX: suffix_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
                 case OP_PROBE: probe_instruction(prog, ctl, st, tmem, ins.z, ins.w); break;
+                case OP_ATTN_PREP:
+                    if constexpr (!LEAN) prep_instruction(prog, ctl, st, ins.z, ins.w);
+                    break;
                 default:
                     if (threadIdx.x == 0) { report(prog, 3, ins.y, -1, st.kind, 0); ctl->abort = 1; }
                     break;

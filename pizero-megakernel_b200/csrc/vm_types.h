@@ -26,6 +26,7 @@ enum OpKind : int {
     OP_LINEAR32 = 7,    // small FP32 linear (+bias, SiLU, RMS factor, Euler update)
     OP_SUFFIX = 8,      // assemble expert input rows: state token + action tokens
     OP_PROBE = 9,       // resource probe: every warp reports the CTA's tensor-memory base for every instruction
+    OP_ATTN_PREP = 10,  // attention operands with bias / rotate-half RoPE applied, copied into the padded head layout
     OP_KINDS
 };
 
@@ -162,6 +163,7 @@ struct AttnParams {
     int tc;                      // 0: mma.sync tiles, 1: tcgen05 tiles
     int hd_pad;                  // elements one head occupies in q / k / v (128 or 256; >= head_dim, the rest zeros)
     int q_box, k_box;            // rows per TMA box of Q (<= 128) and of K / V (keys per tile rounded up to 16, <= 256)
+    const uint8_t* mask;         // bool [batches, nq, nk], 1 = visible, or null (tcgen05 tiles of the full kernel variant only)
     const void* tmap_q;          // CUtensorMaps in global memory: BF16 [rows, ld] with boxes of 64 columns
     const void* tmap_k;
     const void* tmap_v;
@@ -222,6 +224,19 @@ struct SuffixParams {
     int chunk, width;
 };
 
+// Operand preparation of the attention operator: part p (0 Q, 1 K, 2 V) has rows[p] rows of heads[p] heads;
+// dst[r, h, :] = rope(src[r, h, :] + bias[h, :]) in FP32, rounded to BF16, every head on `pitch` elements (zeros behind
+// head_dim: the destination is zeroed once at set-up).  Rotate-half with the first half of the tables' angles.
+struct PrepParams {
+    const void* src[3];          // BF16, row r / head h at src + r * ld_src + h * src_pitch
+    void* dst[3];                // BF16, row r / head h at dst + r * ld_dst + h * pitch
+    const void* bias[3];         // BF16 [heads, head_dim] or null
+    const void* cos[2];          // BF16 [rows, head_dim] for Q and K, or null
+    const void* sin[2];
+    int rows[3], heads[3], ld_src[3], ld_dst[3];
+    int head_dim, src_pitch, pitch;
+};
+
 struct ProbeParams {
     int* out;                    // int32 [tiles, 16]: slots w and w + 8 of a tile belong to warp w
 };
@@ -252,6 +267,7 @@ struct alignas(16) StageDesc {
         Linear32Params lin;
         SuffixParams suffix;
         ProbeParams probe;
+        PrepParams prep;
     } p;
 };
 

@@ -87,6 +87,8 @@ _SIGNATURES = {
     "configure_attention_fp4_output": [_P, _P, _P, _I, _I, _F],
     "configure_attention_path": [_P, _I],
     "configure_attention_head_pad": [_P, _I],
+    "attention_prepare_handle": [_P, C.POINTER(_P)],
+    "attention_validate": [_P],
     "configure_attention_fp4_pitch": [_P, _I],
     "attention_merge_handle": [_P, C.POINTER(_P)],
     "attention_poison_partials": [_P, _P],

@@ -574,6 +574,66 @@ def test_attention_tensor_core_tiles(b, nq, nk, h, hk, hd, stored, prefix, split
         np.testing.assert_array_equal(other[:, 0], got[:, 0])
 
 
+@pytest.mark.parametrize("b,nq,nk,h,hk,hd,splits,bias,rope,mask,prefix", [
+    (2, 100, 180, 4, 2, 64, 1, True, True, False, None),     # the Cosmos head sizes, GQA, biases and rotary tables
+    (1, 200, 200, 4, 4, 128, 1, True, True, True, None),
+    (1, 300, 600, 4, 1, 128, 3, False, True, True, None),    # more than 256 keys: KV splits, merge stage
+    (2, 40, 100, 16, 16, 72, 1, True, False, True, None),    # 72-wide heads through the prepared (padded) layout
+    (1, 51, 819, 8, 1, 256, 8, False, False, True, 768),     # boolean mask on top of the suffix mask, no preparation stage
+    (1, 64, 64, 2, 2, 256, 1, True, True, False, None),
+])
+def test_attention_bias_rope_mask_and_head_sizes(b, nq, nk, h, hk, hd, splits, bias, rope, mask, prefix):
+    """The operator's optional arguments (``native_pi0/attention.py:19-20`` of the reference) against the FP32 oracle that
+    restates the reference validator: per-head biases, rotate-half tables, a boolean visibility mask (rows without a
+    visible key give zeros), head sizes 64 / 128."""
+    g = torch.Generator().manual_seed(2000 + nq + hd + splits)
+    rand = lambda *shape: torch.randn(*shape, generator=g)
+    q, k, v = rand(b, nq, h, hd).bfloat16().cuda(), rand(b, nk, hk, hd).bfloat16().cuda(), rand(b, nk, hk, hd).bfloat16().cuda()
+    biases = [(rand(n, hd) * 0.5).bfloat16() for n in (h, hk, hk)] if bias else None
+    def tables(rows):
+        angle = torch.rand(b, rows, hd, generator=g) * 6.28
+        return angle.cos().bfloat16(), angle.sin().bfloat16()
+    q_rope, k_rope = (tables(nq), tables(nk)) if rope else (None, None)
+    visible = None
+    if mask:
+        visible = torch.rand(b, nq, nk, generator=g) < 0.7
+        visible[:, 3] = False                                # a query that sees nothing
+        if prefix is not None:
+            visible[:, 0] = True
+    want = oracle_ops.attention(q, k, v, hd ** -0.5, prefix, bias=biases, q_rope=q_rope, k_rope=k_rope, mask=visible).numpy()
+    with ResidentAttention(None, q, k, v, workers=148, prefix=prefix, splits=splits, bias=biases, q_rope=q_rope, k_rope=k_rope,
+                           mask=visible) as op:
+        for launch in range(2):
+            op.output.fill_(float("nan"))
+            got = op.forward().float().cpu().numpy()
+            assert op.status()["code"] == 0
+            assert np.isfinite(got).all()
+            assert relrms(got, want) <= 1e-2
+            if mask:
+                assert not got[:, 3].any()
+            if launch:
+                np.testing.assert_array_equal(got, first)
+            first = got
+
+
+def test_attention_optional_argument_errors():
+    q = torch.randn(1, 64, 2, 128).bfloat16().cuda()
+    k = torch.randn(1, 600, 2, 128).bfloat16().cuda()
+    with pytest.raises(RuntimeError):
+        ResidentAttention(None, q, k, k)                     # 600 keys in one tcgen05 tile: prepared operands need KV splits
+    with pytest.raises(ValueError):
+        ResidentAttention(None, q, k, k, splits=3, bias=(torch.zeros(2, 64), None, None))      # bias shape
+    with pytest.raises(ValueError):
+        ResidentAttention(None, q, k, k, splits=3, q_rope=(torch.zeros(1, 64, 128), None))     # cosine without sine
+    with pytest.raises(ValueError):
+        ResidentAttention(None, q, k, k, splits=3, mask=torch.ones(1, 64, 599, dtype=torch.bool))
+    with ResidentAttention(None, q, k, k, splits=3, path="tcgen05") as op:
+        op.forward()
+        assert op.status()["code"] == 0
+    with pytest.raises(RuntimeError):
+        ResidentAttention(None, q, k, k, splits=3, path="mma.sync")                             # prepared operands: tcgen05 tiles only
+
+
 def test_attention_path_selection():
     q = torch.randn(1, 64, 2, 256).bfloat16().cuda()
     k = torch.randn(1, 600, 1, 256).bfloat16().cuda()
