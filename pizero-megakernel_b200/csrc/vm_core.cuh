@@ -43,6 +43,7 @@ struct Ctl {
     uint64_t gather;             // all warps have reached a CTA-wide operator (one arrival per warp)
     uint64_t done;               // all warps have left the instruction loop
     uint32_t tmem_base;
+    volatile uint32_t deps_seen; // GEMM instructions of this CTA whose sources its copy warp has seen complete (monotonic)
     volatile int abort;          // CTA-local copy of the abort decision
     volatile int dep_ok;         // broadcast slot for CTA-wide operators
     volatile int flag;           // second broadcast slot (outcome of the split-KV ticket wait)
@@ -60,6 +61,7 @@ struct PipeState {
     uint32_t mma_it = 0;         // K stages consumed by the MMA lane (rotates the scale columns in tensor memory)
     uint32_t mma_tile = 0;       // accumulator tiles produced
     uint32_t epi_tile = 0;       // accumulator tiles drained
+    uint32_t gemm_seq = 0;       // GEMM instructions this warp has been through (every warp counts them)
 };
 
 __device__ __forceinline__ void mark(const VmProgram& prog, int code) {
@@ -119,6 +121,34 @@ __device__ __forceinline__ bool mbar_wait_warp(const VmProgram& prog, Ctl* ctl, 
         }
     }
     return ok != 0;
+}
+
+// Wait (bounded, abort-aware, one decision per warp) until the copy warp of this CTA has seen the sources of GEMM instruction
+// number `seq` complete: from then on everything those sources wrote - and everything that was final before they ran - may
+// be read, so an epilogue warp can request its residual rows and row statistics while the operands are still on their way.
+__device__ __forceinline__ bool wait_deps_seen(const VmProgram& prog, Ctl* ctl, uint32_t seq, int stage) {
+    int ok = 1;
+    if (lane_id() == 0) {
+        unsigned long long start = 0;
+        for (uint32_t spin = 1;; ++spin) {
+            uint32_t seen;
+            asm volatile("ld.acquire.cta.shared.u32 %0, [%1];" : "=r"(seen) : "r"(smem_u32(const_cast<uint32_t*>(&ctl->deps_seen))) : "memory");
+            if (seen > seq) break;
+            if (ctl->abort) { ok = 0; break; }
+            __nanosleep(32);
+            if ((spin & 255u) == 0u) {
+                const unsigned long long now = global_ns();
+                if (start == 0) start = now;
+                if (now - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort)) {
+                    report(prog, 2, stage, -1, seq, 0);
+                    ctl->abort = 1;
+                    ok = 0;
+                    break;
+                }
+            }
+        }
+    }
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // Entry of a CTA-wide operator: all eight warps go in, or none does.

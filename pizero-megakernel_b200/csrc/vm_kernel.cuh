@@ -72,6 +72,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         mbar_init(&ctl->gather, kThreads / 32);
         mbar_init(&ctl->done, kThreads / 32);
         ctl->abort = 0;
+        ctl->deps_seen = 0;
         ctl->dep_ok = 1;
         ctl->gate = 0;
         mbar_fence_init();
