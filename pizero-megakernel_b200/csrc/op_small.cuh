@@ -93,19 +93,19 @@ __device__ __forceinline__ void embed_instruction(const VmProgram& prog, Ctl* ct
 }
 
 // out[r, n] = f(sum_k x[r, k] * W[n, k]) in FP32.  A tile is 16 output columns for a block of 32 rows (16 for an operator
-// with few rows or few columns, which would otherwise occupy one or two CTAs). K runs in chunks of 128 through a four-deep
+// with few rows or few columns, which would otherwise occupy one or two CTAs). K runs in chunks of 256 through a four-deep
 // cp.async ring in shared memory (x rows as stored, FP32 or BF16, and the 16 weight rows), so the L2 latency of a
 // chunk is paid once per tile, not once per chunk.
 //
 // With eight warps per SM the operator is bound by instruction issue, so the inner loop is built for few instructions:
-// every warp owns one eighth of each K chunk (16 values) and computes the WHOLE tile for it - lane (rg = lane / 4,
+// every warp owns one eighth of each K chunk (32 values) and computes the WHOLE tile for it - lane (rg = lane / 4,
 // cg = lane % 4) holds rows rg, rg + 8, ... and columns cg, cg + 4, cg + 8, cg + 12 - with packed FP32 multiply-adds
 // (fma.rn.f32x2: two products per instruction, accumulated as separate even / odd partial sums).  A step of four k
 // values costs RT + 4 16-byte shared-memory reads (conflict-free: rows are 132 floats apart) for 8 RT packed
 // multiply-adds.  The eight partial tiles meet in shared memory at the end and are added in a fixed order.
 constexpr int kLinCols = 16;
 constexpr int kLinRows = 32;
-constexpr int kLinChunk = 128;
+constexpr int kLinChunk = 256;
 constexpr int kLinLd = kLinChunk + 4;                                  // floats per staged row (padded)
 constexpr int kLinStages = 4;
 constexpr int kLinStageBytes = (kLinRows + kLinCols) * kLinLd * 4;     // x block + weight rows
@@ -137,26 +137,26 @@ __device__ __forceinline__ void linear32_issue(const LinTile& t, uint8_t* stage,
     if (t.x_bf16) {
         // BF16 rows are staged as stored (8 elements per 16-byte copy) in the first half of each padded row
         const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(t.x);
-        if (lane < (kw >> 3))
+        for (int c = lane; c < (kw >> 3); c += 32)
             for (int r = warp; r < row_block; r += 8) {
                 const bool ok = t.r0 + r < t.rows;
-                const __nv_bfloat16* from = ok ? src + static_cast<size_t>(t.r0 + r + t.x_row_offset) * t.ldx + kc + lane * 8 : src;
-                cp_async16(reinterpret_cast<__nv_bfloat16*>(xs + r * kLinLd) + lane * 8, from, ok);
+                const __nv_bfloat16* from = ok ? src + static_cast<size_t>(t.r0 + r + t.x_row_offset) * t.ldx + kc + c * 8 : src;
+                cp_async16(reinterpret_cast<__nv_bfloat16*>(xs + r * kLinLd) + c * 8, from, ok);
             }
     } else {
         const float* src = static_cast<const float*>(t.x);
-        if (lane < (kw >> 2))
+        for (int c = lane; c < (kw >> 2); c += 32)
             for (int r = warp; r < row_block; r += 8) {
                 const bool ok = t.r0 + r < t.rows;
-                const float* from = ok ? src + static_cast<size_t>(t.r0 + r + t.x_row_offset) * t.ldx + kc + lane * 4 : src;
-                cp_async16(xs + r * kLinLd + lane * 4, from, ok);
+                const float* from = ok ? src + static_cast<size_t>(t.r0 + r + t.x_row_offset) * t.ldx + kc + c * 4 : src;
+                cp_async16(xs + r * kLinLd + c * 4, from, ok);
             }
     }
-    if (lane < (kw >> 2))
+    for (int c = lane; c < (kw >> 2); c += 32)
         for (int r = warp; r < kLinCols; r += 8) {
             const bool ok = t.col0 + r < t.n;
-            const float* from = ok ? t.w + static_cast<size_t>(t.col0 + r) * t.k + kc + lane * 4 : t.w;
-            cp_async16(ws + r * kLinLd + lane * 4, from, ok);
+            const float* from = ok ? t.w + static_cast<size_t>(t.col0 + r) * t.k + kc + c * 4 : t.w;
+            cp_async16(ws + r * kLinLd + c * 4, from, ok);
         }
 }
 
@@ -197,8 +197,8 @@ __device__ __forceinline__ void linear32_tile(const Linear32Params& p, const voi
         const float* ws = xs + kLinRows * kLinLd;
         const int kw4 = min(kLinChunk, t.k - c * kLinChunk) >> 2;
 #pragma unroll 1
-        for (int j = 0; j < 4; j++) {                  // (not unrolled: the operator runs a few times per pass, from a cold instruction cache)
-            const int q = warp * 4 + j;                // this warp's share of the chunk: k values 16 warp .. 16 warp + 15
+        for (int j = 0; j < kLinChunk / 32; j++) {     // (not unrolled: the operator runs a few times per pass, from a cold instruction cache)
+            const int q = warp * (kLinChunk / 32) + j; // this warp's share of the chunk: k values 32 warp .. 32 warp + 31
             if (q < kw4) {
                 float4 w4[4];
 #pragma unroll
