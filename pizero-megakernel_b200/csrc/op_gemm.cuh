@@ -483,7 +483,10 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
         // computed while the operands are still on their way, instead of after the accumulator is ready.  (Requesting the
         // residual rows early as well was measured and lost: o_proj 7.9 vs 7.7 us.)
         const int chunks = g.block_n >> 5;
-        const bool early = count == 1 && (g.row_sumsq != nullptr || g.row_factor != nullptr);
+        // (compiled into the drains of the projections that stand behind a folded norm in the model; the others read their
+        // statistics, if they are given any, once the accumulator is ready)
+        constexpr bool kEarly = EPI == EPI_QKV_ROPE || EPI == EPI_GEGLU_FP4 || EPI == EPI_FP4 || EPI == EPI_BF16_EXT;
+        const bool early = kEarly && count == 1 && (g.row_sumsq != nullptr || g.row_factor != nullptr);
         if (early) {
             if (!wait_deps_seen(prog, ctl, ps.gemm_seq, stage_index)) return;
         } else {
