@@ -455,10 +455,13 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
     }
 }
 
-template <int EPI>
+// LEAN: the drain of the lean kernel variant; the residual-stream and plain BF16 drains there carry no row-statistics code
+// (the host sends programs that give those two epilogues row statistics to the full variant).
+template <int EPI, bool LEAN = false>
 __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, uint32_t tmem, const StageDesc& st,
                                               int stage_index, int first, int count, PipeState& ps, long long* stamp) {
     const GemmParams& g = st.p.gemm;
+    constexpr bool kStats = !(LEAN && (EPI == EPI_STREAM || EPI == EPI_BF16));
     const int quarter = (threadIdx.x >> 5) & 3;          // TMEM lane quarter this warp may read
     const int lane = lane_id();
     for (int t = first; t < first + count; ++t) {
@@ -496,8 +499,8 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
         // as a factor, or as the producer's per-tile sums of squares (complete: the operands behind this accumulator
         // were only copied after the producer stage had finished)
         float row_scale = g.alpha, row_shift = 0.f, sumsq = 0.f, sum = 0.f;
-        if (row_ok && g.row_factor) row_scale *= __ldcg(g.row_factor + row);
-        if (row_ok && g.row_sumsq) {
+        if (kStats && row_ok && g.row_factor) row_scale *= __ldcg(g.row_factor + row);
+        if (kStats && row_ok && g.row_sumsq) {
             const float4* part = reinterpret_cast<const float4*>(g.row_sumsq + static_cast<size_t>(row) * g.sumsq_parts);
             const int quads = g.sumsq_parts >> 2;
             float total = 0.f;
@@ -585,12 +588,12 @@ __device__ __forceinline__ void gemm_instruction(const VmProgram& prog, Ctl* ctl
         else gemm_mma<GEMM_FP8>(prog, ctl, data, tmem, st, stage_index, first, count, ps, stamp);
     } else if (warp >= 4) {
         const int epilogue = st.p.gemm.epilogue;            // one drain loop per epilogue kind: only its own arithmetic and registers
-        if (epilogue == EPI_BF16) gemm_epilogue<EPI_BF16>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
-        else if (epilogue == EPI_STREAM) gemm_epilogue<EPI_STREAM>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
-        else if (epilogue == EPI_GEGLU_FP4) gemm_epilogue<EPI_GEGLU_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
-        else if (epilogue == EPI_FP4) gemm_epilogue<EPI_FP4>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
-        else if (epilogue == EPI_QKV_ROPE) gemm_epilogue<EPI_QKV_ROPE>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
-        else if (LEAN || epilogue == EPI_BF16_EXT) gemm_epilogue<EPI_BF16_EXT>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        if (epilogue == EPI_BF16) gemm_epilogue<EPI_BF16, LEAN>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (epilogue == EPI_STREAM) gemm_epilogue<EPI_STREAM, LEAN>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (epilogue == EPI_GEGLU_FP4) gemm_epilogue<EPI_GEGLU_FP4, LEAN>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (epilogue == EPI_FP4) gemm_epilogue<EPI_FP4, LEAN>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (epilogue == EPI_QKV_ROPE) gemm_epilogue<EPI_QKV_ROPE, LEAN>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
+        else if (LEAN || epilogue == EPI_BF16_EXT) gemm_epilogue<EPI_BF16_EXT, LEAN>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         else if (epilogue == EPI_F32) gemm_epilogue<EPI_F32>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         else gemm_epilogue<EPI_GEGLU_BF16>(prog, ctl, tmem, st, stage_index, first, count, ps, stamp);
         if (stamp && threadIdx.x == 128) stamp[2] = static_cast<long long>(global_ns());

@@ -197,6 +197,8 @@ std::vector<int> compile_streams(const std::vector<std::pair<int, int>>& work, i
 bool lean_stage(const StageDesc& d) {
     if (d.kind == OP_GEMM) {
         const GemmParams& g = d.p.gemm;
+        const bool stats = g.row_sumsq || g.row_factor;     // (the lean residual-stream and plain BF16 drains read none)
+        if (stats && (g.epilogue == EPI_BF16 || g.epilogue == EPI_STREAM)) return false;
         return g.operands == GEMM_NVFP4 && (g.epilogue == EPI_BF16 || g.epilogue == EPI_STREAM || g.epilogue == EPI_GEGLU_FP4 ||
                                             g.epilogue == EPI_FP4 || g.epilogue == EPI_QKV_ROPE || g.epilogue == EPI_BF16_EXT);
     }
