@@ -221,7 +221,8 @@ __device__ __forceinline__ float gelu_sigmoid(float x) {
 
 // One 32-column chunk of one accumulator row (thread == row).
 // (Instantiated per epilogue kind: each accumulator drain carries only its own arithmetic and registers.)
-template <int EPI>
+// LEAN: without the options only the BF16 model uses (rounding before the residual, GELU on BF16 output) and without ReLU^2.
+template <int EPI, bool LEAN = false>
 __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const uint32_t (&raw)[32], int row, int col0,
                                                     bool row_ok, float row_scale, float row_shift, float& sumsq, float& sum) {
     float v[32];
@@ -268,7 +269,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         dst[1] = make_uint4(w[4], w[5], w[6], w[7]);
         return;
     }
-    const bool early_bias = EPI == EPI_BF16_EXT && g.bias && g.residual && g.round_before_residual;
+    const bool early_bias = !LEAN && EPI == EPI_BF16_EXT && g.bias && g.residual && g.round_before_residual;
     if (early_bias) {
         const uint4* b = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(g.bias) + col0);
 #pragma unroll
@@ -282,7 +283,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         }
     }
     if (g.residual) {
-        if (EPI == EPI_BF16_EXT && g.round_before_residual) {
+        if (!LEAN && EPI == EPI_BF16_EXT && g.round_before_residual) {
 #pragma unroll
             for (int i = 0; i < 32; i++) v[i] = bf16_round(v[i]);
         }
@@ -352,7 +353,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         return;
     }
     if constexpr (EPI == EPI_BF16 || EPI == EPI_BF16_EXT) {
-        if (EPI == EPI_BF16_EXT && g.gelu_cols > 0) {
+        if (!LEAN && EPI == EPI_BF16_EXT && g.gelu_cols > 0) {
 #pragma unroll
             for (int i = 0; i < 32; i++) v[i] = col0 + i < g.gelu_cols ? gelu_tanh(bf16_round(v[i])) : 0.f;
         }
@@ -379,7 +380,7 @@ __device__ __forceinline__ void gemm_epilogue_chunk(const GemmParams& g, const u
         if (g.act == 1) {
 #pragma unroll
             for (int i = 0; i < 32; i++) v[i] = gelu_sigmoid(v[i]);
-        } else if (g.act == 3) {
+        } else if (!LEAN && g.act == 3) {
 #pragma unroll
             for (int i = 0; i < 32; i++) { float r = fmaxf(v[i], 0.f); v[i] = r * r; }
         }
@@ -555,7 +556,7 @@ __device__ __forceinline__ void gemm_epilogue(const VmProgram& prog, Ctl* ctl, u
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
             }
-            gemm_epilogue_chunk<EPI>(g, raw, row, n_tile * g.block_n + c * 32, row_ok, row_scale, row_shift, sumsq, sum);
+            gemm_epilogue_chunk<EPI, LEAN>(g, raw, row, n_tile * g.block_n + c * 32, row_ok, row_scale, row_shift, sumsq, sum);
         }
         if (EPI == EPI_STREAM && row_ok) {
             g.sumsq_out[static_cast<size_t>(row) * g.sumsq_ld + n_tile] = sumsq;

@@ -199,6 +199,7 @@ bool lean_stage(const StageDesc& d) {
         const GemmParams& g = d.p.gemm;
         const bool stats = g.row_sumsq || g.row_factor;     // (the lean residual-stream and plain BF16 drains read none)
         if (stats && (g.epilogue == EPI_BF16 || g.epilogue == EPI_STREAM)) return false;
+        if (g.round_before_residual || g.gelu_cols > 0 || g.act == 3) return false;       // options the lean drains leave out
         return g.operands == GEMM_NVFP4 && (g.epilogue == EPI_BF16 || g.epilogue == EPI_STREAM || g.epilogue == EPI_GEGLU_FP4 ||
                                             g.epilogue == EPI_FP4 || g.epilogue == EPI_QKV_ROPE || g.epilogue == EPI_BF16_EXT);
     }
