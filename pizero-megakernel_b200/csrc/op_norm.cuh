@@ -37,9 +37,11 @@ __device__ __forceinline__ void load_block16(const __nv_bfloat16* src, float (&v
 
 // Input block (row, block): x, plus the residual when one is bound; the sum is stored for the next residual connection
 // and, with round_residual, the statistics continue from its BF16 rounding.
+// LEAN (here and below): the norm of the lean kernel variant - NVFP4 output only, no fused residual, no inverse scale.
+template <bool LEAN = false>
 __device__ __forceinline__ void load_input16(const NormParams& n, int row, int block, float (&v)[16]) {
     load_block16(static_cast<const __nv_bfloat16*>(n.in) + static_cast<size_t>(row) * n.ld_in + block * 16, v);
-    if (n.residual) {
+    if (!LEAN && n.residual) {
         float r[16];
         load_block16(static_cast<const __nv_bfloat16*>(n.residual) + static_cast<size_t>(row) * n.width + block * 16, r);
         uint32_t w[8];
@@ -60,8 +62,9 @@ __device__ __forceinline__ void load_input16(const NormParams& n, int row, int b
     }
 }
 
+template <bool LEAN = false>
 __device__ __forceinline__ void store_block16(const NormParams& n, int row, int block, float (&v)[16]) {
-    if (n.inv_scale) {
+    if (!LEAN && n.inv_scale) {
 #pragma unroll
         for (int q = 0; q < 4; q++) {
             const float4 s4 = __ldg(reinterpret_cast<const float4*>(n.inv_scale + block * 16) + q);
@@ -72,14 +75,14 @@ __device__ __forceinline__ void store_block16(const NormParams& n, int row, int 
             for (int i = 0; i < 16; i++) v[i] = bf16_round(v[i]);
         }
     }
-    if (n.out_fp8) {
+    if (!LEAN && n.out_fp8) {
         uint32_t w[4] = {0u, 0u, 0u, 0u};
 #pragma unroll
         for (int i = 0; i < 16; i++)
             w[i >> 2] |= static_cast<uint32_t>(__nv_cvt_float_to_fp8(v[i] * n.inv_gs, __NV_SATFINITE, __NV_E4M3)) << (8 * (i & 3));
         *reinterpret_cast<uint4*>(n.out_fp8 + static_cast<size_t>(row) * n.width + block * 16) = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    if (n.out_bf16) {
+    if (!LEAN && n.out_bf16) {
         uint32_t w[8];
 #pragma unroll
         for (int i = 0; i < 8; i++) {
@@ -168,6 +171,7 @@ __device__ __forceinline__ void norm_row(const NormParams& n, int row) {
 
 // Two warps per row: `part` (0/1) selects this warp's half of the blocks; `red` is shared memory for 2 x 4 x 2 floats.
 // Called by every warp of the CTA (it contains CTA barriers); `valid` is false for warps whose row does not exist.
+template <bool LEAN = false>
 __device__ __forceinline__ void norm_row_pair(const NormParams& n, int row, int local_row, int part, bool valid, float* red) {
     const int lane = lane_id();
     const int blocks = n.width >> 4;
@@ -177,7 +181,7 @@ __device__ __forceinline__ void norm_row_pair(const NormParams& n, int row, int 
             for (int b = part * 32 + lane; b < blocks; b += 64) {
                 float v[16];
                 load_block16(src + b * 16, v);
-                store_block16(n, row, b, v);
+                store_block16<LEAN>(n, row, b, v);
             }
         }
         return;
@@ -188,7 +192,7 @@ __device__ __forceinline__ void norm_row_pair(const NormParams& n, int row, int 
     for (int j = 0; j < kNormPairBlocksPerLane; j++) {
         const int b = part * 32 + lane + 64 * j;
         if (valid && b < blocks) {
-            load_input16(n, row, b, cache[j]);
+            load_input16<LEAN>(n, row, b, cache[j]);
 #pragma unroll
             for (int i = 0; i < 16; i++) sum += cache[j][i];
         }
@@ -218,7 +222,7 @@ __device__ __forceinline__ void norm_row_pair(const NormParams& n, int row, int 
     __syncthreads();
     const float rstd = rsqrtf((red[8 + local_row * 2] + red[8 + local_row * 2 + 1]) * inv_width + n.eps);
     if (!valid) return;
-    if (n.out_factor) {                      // only the row factor is wanted
+    if (!LEAN && n.out_factor) {             // only the row factor is wanted
         if (part == 0 && lane == 0) n.out_factor[row] = rstd;
         return;
     }
@@ -239,13 +243,14 @@ __device__ __forceinline__ void norm_row_pair(const NormParams& n, int row, int 
                 float y = (cache[j][i] - mean) * rstd;
                 if (n.gamma) y *= gm[i];
                 if (n.beta) y += bt[i];
-                v[i] = (n.round_norm && !n.inv_scale) ? bf16_round(y) : y;     // (with an inverse scale the rounding follows it)
+                v[i] = (n.round_norm && (LEAN || !n.inv_scale)) ? bf16_round(y) : y;     // (with an inverse scale the rounding follows it)
             }
-            store_block16(n, row, b, v);
+            store_block16<LEAN>(n, row, b, v);
         }
     }
 }
 
+template <bool LEAN = false>
 __device__ __forceinline__ void norm_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, const StageDesc& st, int stage_index,
                                                  int first, int count) {
     const NormParams& n = st.p.norm;
@@ -258,7 +263,7 @@ __device__ __forceinline__ void norm_instruction(const VmProgram& prog, Ctl* ctl
         for (int pass = 0; pass < passes; ++pass) {
             const int local_row = warp >> 1;
             const int row = t * n.rows_per_tile + pass * kNormPairRows + local_row;
-            norm_row_pair(n, row, local_row, warp & 1, row < n.rows, red);
+            norm_row_pair<LEAN>(n, row, local_row, warp & 1, row < n.rows, red);
             if (pass + 1 < passes) __syncthreads();      // `red` is reused by the next pass
         }
         cta_publish_tile(prog, st, t);          // (its barrier also separates this tile's use of `red` from the next one's)

@@ -204,7 +204,11 @@ bool lean_stage(const StageDesc& d) {
                                             g.epilogue == EPI_FP4 || g.epilogue == EPI_QKV_ROPE || g.epilogue == EPI_BF16_EXT);
     }
     if (d.kind == OP_ATTN) return d.p.attn.tc != 0 && !d.p.attn.mask;
-    return d.kind != OP_ATTN_PREP;
+    if (d.kind == OP_NORM) {                                 // the lean norm writes NVFP4 only: no fused residual, inverse scale, other outputs
+        const NormParams& n = d.p.norm;
+        return n.out && !n.residual && !n.inv_scale && !n.out_fp8 && !n.out_bf16 && !n.out_factor;
+    }
+    return d.kind != OP_ATTN_PREP && d.kind != OP_SUFFIX && d.kind != OP_PROBE;
 }
 
 // Build a program from stage descriptors (sources already set) and compact int4 instructions.

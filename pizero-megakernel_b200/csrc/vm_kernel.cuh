@@ -149,14 +149,18 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
             }
             if (!cta_wait_sources(prog, ctl, st, ins.y, ins.z, ins.w, stamp)) break;
             switch (st.kind) {
-                case OP_NORM: norm_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
+                case OP_NORM: norm_instruction<LEAN>(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
                 case OP_ATTN: attn_instruction<LEAN>(prog, ctl, data, tmem, tc_tiles, st, ins.y, ins.z, ins.w, stamp); break;
                 case OP_MERGE: merge_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
                 case OP_PATCH: patch_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
                 case OP_EMBED: embed_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
                 case OP_LINEAR32: linear32_instruction(prog, ctl, data, st, ins.y, ins.z, ins.w, stamp); break;
-                case OP_SUFFIX: suffix_instruction(prog, ctl, st, ins.y, ins.z, ins.w); break;
-                case OP_PROBE: probe_instruction(prog, ctl, st, tmem, ins.z, ins.w); break;
+                case OP_SUFFIX:
+                    if constexpr (!LEAN) suffix_instruction(prog, ctl, st, ins.y, ins.z, ins.w);
+                    break;
+                case OP_PROBE:
+                    if constexpr (!LEAN) probe_instruction(prog, ctl, st, tmem, ins.z, ins.w);
+                    break;
                 case OP_ATTN_PREP:
                     if constexpr (!LEAN) prep_instruction(prog, ctl, st, ins.z, ins.w);
                     break;
