@@ -71,7 +71,8 @@ __device__ __forceinline__ void mark(const VmProgram& prog, int code) {
     }
 }
 
-__device__ __forceinline__ void report(const VmProgram& prog, int code, int stage, int band, unsigned int observed,
+// (out of line: it runs once, when a launch gives up, and its stores need not sit in every wait loop)
+__device__ __noinline__ void report(const VmProgram& prog, int code, int stage, int band, unsigned int observed,
                                        unsigned int expected) {
     VmStatus* s = prog.status;
     if (atomicCAS(&s->abort, 0, 1) == 0) {
@@ -212,13 +213,13 @@ __device__ __forceinline__ bool warp_wait_sources(const VmProgram& prog, Ctl* ct
             lo = min(band_lo, sb - 1);
             hi = min(band_hi, sb - 1);
         }
-        for (int b = lo; b <= hi; b++, n++) {
-            if ((n & 31) == lane && mine == nullptr) {
-                mine = prog.counters + st.src_counter_base[i] + b;
-                target = (b == sb - 1 ? st.src_expected_last[i] : st.src_expected[i]) * prog.epoch;
-                my_band = b;
-            }
+        const int b = lo + lane - n;                 // lanes n .. n + (hi - lo) take this source's bands lo .. hi
+        if (b >= lo && b <= hi) {
+            mine = prog.counters + st.src_counter_base[i] + b;
+            target = (b == sb - 1 ? st.src_expected_last[i] : st.src_expected[i]) * prog.epoch;
+            my_band = b;
         }
+        n += hi - lo + 1;
     }
     mark(prog, 300000 + stage);
     // (a consumer never reads more than 32 counters; the host rejects programs that would)
