@@ -123,7 +123,7 @@ class NativePi0:
 
     def __init__(self, model, *, num_views=3, prompt_len=0, chunk_size=50, flow_steps=10, precision="auto",
                  library=None, workers=None, partitioned=False, expert_splits=None, prefix_splits=None, expert_block_n=None, vision_block_n=64, fold_layernorms=True,
-                 rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="spread",
+                 rope_inv_freq_dtype=torch.float32, keep_debug_outputs=False, verbose=False, tile_weights=True, schedule="affine",
                  fold_norms=True, attention_path=None, weight_store=None):
         config = getattr(model, "config", None)
         if config is None or getattr(config, "pi05", False):
@@ -162,8 +162,8 @@ class NativePi0:
         if attention_path not in (None, "mma.sync", "tcgen05"):
             raise ValueError("attention_path is None (by geometry), 'mma.sync' or 'tcgen05'")
         self.attention_path = attention_path
-        if schedule not in ("spread", "linear"):
-            raise ValueError("schedule must be 'spread' or 'linear'")
+        if schedule not in ("spread", "affine", "linear"):
+            raise ValueError("schedule must be 'spread', 'affine' or 'linear'")
         self.schedule = schedule
         self.verbose = verbose
         sd = model.state_dict()
@@ -826,8 +826,10 @@ class NativePi0:
         self.component_ranges = {"vision": (0, vision_end), "prefix": (vision_end, prefix_end), "expert": (prefix_end, len(self.stages))}
         # ---------------- static instruction streams + program
         work = [LinearWork(t, k) for t, k in zip(self.stage_tiles, self.stage_cost)]
-        if self.schedule == "spread":
-            self.code = spread_streams(work, self.workers, [[s for s in spec.sources] for spec in self.stages])
+        if self.schedule in ("spread", "affine"):
+            # "affine": workers also keep to the kinds of instruction they have run before (the stage name's last component)
+            kinds = [n.rsplit(".", 1)[-1] for n in self.stage_names] if self.schedule == "affine" else None
+            self.code = spread_streams(work, self.workers, [[s for s in spec.sources] for spec in self.stages], kinds)
         else:
             self.code = linear_streams(work, self.workers)
         validate_streams(self.code, self.stage_tiles)

@@ -52,7 +52,7 @@ def linear_streams(stages, workers):
     return code
 
 
-def spread_streams(stages, workers, sources):
+def spread_streams(stages, workers, sources, kinds=None):
     """Streams in the layout of ``linear_streams`` for a chain of short, dependent stages.
 
     ``linear_streams`` hands each stage to the least loaded workers. A worker that has just run a tile of a stage
@@ -61,7 +61,11 @@ def spread_streams(stages, workers, sources):
     difference of 2-3 microseconds per stage on B200). Here the tiles of a stage go first to workers whose previous
     instruction is NOT one of the stage's sources (``sources[i]``: indices of the stages stage ``i`` waits for);
     among those, to the least loaded, ties to the lower index. Stages with at least as many tiles as workers
-    are split exactly as in ``linear_streams``."""
+    are split exactly as in ``linear_streams``.
+
+    ``kinds`` (optional, one label per stage: the code path its tiles execute): among the workers that are not late,
+    those that have run the stage's kind before come first, so that a worker keeps to few kinds of instruction and its
+    SM's instruction cache to few code paths."""
     if not isinstance(workers, int) or workers < 1 or workers > MAX_WORKERS:
         raise ValueError("Expected 1..148 B200 workers")
     stages = tuple(stages)
@@ -71,12 +75,20 @@ def spread_streams(stages, workers, sources):
     last = np.full(workers, -1, dtype=np.int64)          # the stage of each worker's previous instruction
     rows = [[] for _ in range(workers)]
     index_of = np.arange(workers)
+    known = {}                                           # kind -> 1 for the workers that have run it
+    if kinds is not None and len(kinds) != len(stages):
+        raise ValueError("Expected one kind per stage")
     for index, work in enumerate(stages):
         parts = min(workers, work.tiles)
         small, extra = divmod(work.tiles, parts)
         src = [s for s in sources[index] if s is not None and s >= 0]
         late = np.isin(last, src).astype(np.int64) if src else np.zeros(workers, dtype=np.int64)
-        order = np.lexsort((index_of, load, late))[:parts]            # keys: late first, then load, then index
+        if kinds is None:
+            order = np.lexsort((index_of, load, late))[:parts]        # keys: late first, then load, then index
+        else:
+            ran = known.setdefault(kinds[index], np.zeros(workers, dtype=np.int64))
+            order = np.lexsort((index_of, load, 1 - ran, late))[:parts]
+            ran[order] = 1
         start = 0
         for rank, worker in enumerate(order.tolist()):
             count = small + (1 if rank < extra else 0)

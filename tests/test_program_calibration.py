@@ -57,6 +57,33 @@ def test_spread_streams_avoid_the_workers_of_a_stage_sources():
         spread_streams(work, 0, sources)
 
 
+def test_spread_streams_keep_workers_to_the_kinds_they_ran():
+    """With stage kinds the scheduler still never makes a worker late where it can be avoided, covers every tile once,
+    and a worker runs fewer kinds of instruction than without them."""
+    names = ["qkv", "attention", "o_proj", "gate_up", "down"]
+    tiles = [40, 104, 32, 128, 32] * 12
+    kinds = names * 12
+    work = [LinearWork(t, 1024) for t in tiles]
+    sources = [[i - 1, -1, -1, -1] for i in range(len(tiles))]
+
+    def kinds_per_worker(code):
+        validate_streams(code, tiles)
+        late = 0
+        seen = []
+        for worker in range(148):
+            stages = [row[1] for row in code[worker, :, :4].tolist() if row[0]]
+            late += sum(1 for a, b in zip(stages, stages[1:]) if b == a + 1 and tiles[a] + tiles[b] <= 148)
+            seen.append(len({kinds[s] for s in stages[len(stages) // 2:]}))
+        assert late == 0
+        return sum(seen) / 148.0
+
+    plain = kinds_per_worker(spread_streams(work, 148, sources))
+    affine = kinds_per_worker(spread_streams(work, 148, sources, kinds))
+    assert affine < plain - 0.5
+    with pytest.raises(ValueError):
+        spread_streams(work, 148, sources, kinds[:-1])
+
+
 def test_validator_rejects_corrupt_programs():
     code = linear_streams([LinearWork(10, 64), LinearWork(7, 128)], 4)
     tiles = [10, 7]
