@@ -403,7 +403,7 @@ int gemm_refresh(Op* op) {
     g.operands = op->operands;
     g.k_groups = static_cast<int>(row_bytes / 32);
     // Operand ring: a slot holds kChunks chunks of the rows that are actually copied (A: a_box_rows, B: block_n) and,
-    // for NVFP4, 4 KiB of scale atoms per operand. The MMA always reads 128 rows of A; with 64 copied rows the other 64 are
+    // for NVFP4, 4 KiB of scale atoms per operand. The MMA always reads 128 rows of A; with fewer copied rows the others are
     // whatever follows in the slot (B, scales) and end in accumulator rows that are never stored, so the read only
     // has to stay inside shared memory, which the slot's own B and scale regions guarantee.
     g.off_b = kChunks * 128 * g.a_box_rows;
@@ -646,7 +646,10 @@ extern "C" int configure_resident_fp4_rows(void* handle, int rows) {
     Op* op = as_op(handle);
     if (!op || op->desc.kind != OP_GEMM || rows < 1 || rows > op->m) return cudaErrorInvalidValue;
     op->desc.p.gemm.rows = rows;
-    op->desc.p.gemm.a_box_rows = (rows <= 64 && op->m == 128) ? 64 : 128;
+    // rows of A copied per tile: the logical rows in whole 8-row swizzle groups (at least 32, so that the 128 rows the MMA
+    // reads stay inside the slot for every tile width)
+    if (op->m == 128 && op->operands == GEMM_NVFP4) op->desc.p.gemm.a_box_rows = std::min(128, std::max(32, (rows + 7) / 8 * 8));
+    else op->desc.p.gemm.a_box_rows = (rows <= 64 && op->m == 128) ? 64 : 128;
     return gemm_refresh(op);
 }
 extern "C" int configure_resident_fp4_weight_layout(void* handle, int tiled) {

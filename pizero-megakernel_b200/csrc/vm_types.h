@@ -59,7 +59,7 @@ struct GemmParams {
     int k_groups;                // row_bytes / 32: one MMA each (64 FP4, 16 BF16 or 32 FP8 elements of K)
     int block_n;                 // 128 (default), 64 or 32
     int b_tiled;                 // B stored tile-major: block (n_tile, k_stage) is block_n contiguous 128-byte rows
-    int a_box_rows;              // rows of A copied per tile: 128, or 64 when the logical row count is <= 64
+    int a_box_rows;              // rows of A copied per tile: 128, or fewer (a multiple of 8) when there are fewer logical rows
     int ring_stages;             // operand ring of this GEMM: slots in flight (2..kMaxStages) ...
     int slot_stride;             // ... bytes from one slot to the next (multiple of 1024) ...
     int off_b, off_sfa, off_sfb; // ... and where B, the A scales and the B scales start inside a slot (A starts at 0)
