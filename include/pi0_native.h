@@ -303,7 +303,8 @@ int read_native_model_counters(void* handle, unsigned int* counts, unsigned int*
  * the kernel with every operator and option.  Same protocol, same results. */
 int native_model_kernel_variant(void* handle, int* lean);
 /* extension (debugging): host-mapped progress marks, one word per warp of every worker, written as the warp moves
- * through its instruction loop; readable while a launch is still running.  Off by default. */
+ * through its instruction loop (which instruction it has entered, where in the teardown it is); readable while a
+ * launch is still running.  Off by default; while on, the program launches the full kernel variant. */
 int enable_native_model_debug(void* handle, int enable);
 int read_native_model_debug(void* handle, int* out, int n);      /* n >= workers * 8 */
 /* extension: time budget of every device-side wait in nanoseconds (default 2e9). */

@@ -336,7 +336,7 @@ int launch_program(Program* prog, cudaStream_t stream, LaunchInputs in, int begi
     p.wait_budget_ns = prog->budget_ns;
     p.in = in;
     p.debug = prog->h_debug;
-    if (prog->lean) pi0_vm_kernel<true><<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
+    if (prog->lean && !prog->h_debug) pi0_vm_kernel<true><<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
     else pi0_vm_kernel<false><<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }
@@ -1449,7 +1449,7 @@ extern "C" int read_native_model_counters(void* handle, unsigned int* counts, un
 extern "C" int native_model_kernel_variant(void* handle, int* lean) {
     Program* prog = as_program(handle);
     if (!prog || !lean) return cudaErrorInvalidValue;
-    *lean = prog->lean ? 1 : 0;
+    *lean = (prog->lean && !prog->h_debug) ? 1 : 0;             // (progress marks are written by the full variant only)
     return cudaSuccess;
 }
 extern "C" int enable_native_model_debug(void* handle, int enable) {

@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         long long* stamp = prog.timings ? prog.timings + (static_cast<size_t>(blockIdx.x) * prog.length + ip0 + seq) * 8 : nullptr;
         if (stamp && threadIdx.x == 0) stamp[0] = static_cast<long long>(global_ns());
         if (st.kind == OP_GEMM) {
-            mark(prog, 800000 + ins.y);
+            if constexpr (!LEAN) mark(prog, 800000 + ins.y);
             gemm_instruction<LEAN>(prog, ctl, data, tmem, st, ins.y, ins.z, ins.w, ps, stamp);
             // one decision per warp: the lanes with a role return later than the others and must not leave alone
             if (__any_sync(0xffffffffu, ctl->abort != 0)) break;
@@ -133,11 +133,11 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
             // with a bounded, abort-aware wait and an all-or-nothing outcome (gather_enter). Behind the gate all
             // eight warps are present, so the hardware barriers of the operator body are safe; the next abort
             // decision is the CTA-wide one of cta_wait_sources.
-            mark(prog, 600000 + ins.y);
+            if constexpr (!LEAN) mark(prog, 600000 + ins.y);
             __syncwarp();
             if (!gather_enter(prog, ctl, gathers, ins.y)) break;
             gathers++;
-            mark(prog, 700000 + ins.y);
+            if constexpr (!LEAN) mark(prog, 700000 + ins.y);
             if (st.kind == OP_NORM) {
                 // the norm weights do not depend on any stage: fetch them while the CTA waits for its input rows
                 const NormParams& np = st.p.norm;
@@ -176,13 +176,13 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         if (lane_id() == 0) mbar_arrive(&ctl->release[slot]);
     }
 
-    mark(prog, 900001);
+    if constexpr (!LEAN) mark(prog, 900001);
     // Teardown. After an abort, give copies and MMAs that may still be in flight a bounded moment to land.
     if (ctl->abort) {
         const unsigned long long t0 = global_ns();
         while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
     }
-    mark(prog, 900002);
+    if constexpr (!LEAN) mark(prog, 900002);
     cp_async_wait<0>();
     tc_fence_before();
     __syncwarp();
@@ -191,11 +191,11 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         // the warp that allocated tensor memory frees it once every warp is out of the loop (bounded wait: after
         // an abort a warp may be late, the memory is still returned)
         mbar_wait_warp(prog, ctl, &ctl->done, 0u, -1);
-        mark(prog, 900003);
+        if constexpr (!LEAN) mark(prog, 900003);
         tc_fence_after();
         tmem_dealloc(tmem, kTmemCols);
     }
-    mark(prog, 900004);
+    if constexpr (!LEAN) mark(prog, 900004);
 }
 
 }  // namespace pi0

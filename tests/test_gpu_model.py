@@ -211,18 +211,47 @@ def test_schedules_and_split_counts_agree(small_model):
     BF16 partial rows), so different split counts agree only to the NVFP4 noise gate."""
     dims, cfg, sd = small_model
     x = inputs(3, 50, 0, dims.vocab)
-    with NativePi0(StateDictModel(cfg, sd), schedule="spread") as spread, NativePi0(StateDictModel(cfg, sd), schedule="linear") as linear:
+    with NativePi0(StateDictModel(cfg, sd), schedule="spread") as spread, NativePi0(StateDictModel(cfg, sd), schedule="linear") as linear, \
+            NativePi0(StateDictModel(cfg, sd)) as affine:
         a = spread.forward(*x).clone()
         b = linear.forward(*x).clone()
-        assert spread.status()["code"] == 0 and linear.status()["code"] == 0
-        assert not np.array_equal(spread.code, linear.code)
-        assert torch.equal(a, b)
+        c = affine.forward(*x).clone()
+        assert spread.status()["code"] == 0 and linear.status()["code"] == 0 and affine.status()["code"] == 0
+        assert affine.schedule == "affine"
+        assert not np.array_equal(spread.code, linear.code) and not np.array_equal(spread.code, affine.code)
+        assert torch.equal(a, b) and torch.equal(a, c)
     with NativePi0(StateDictModel(cfg, sd), expert_splits=4, prefix_splits=1) as other:
         c = other.forward(*x).clone()
         assert other.status()["code"] == 0
         assert nrmse(c, a) <= 0.1
     with pytest.raises(ValueError):
         NativePi0(StateDictModel(cfg, sd), schedule="random")
+
+
+def test_progress_marks_come_from_the_full_kernel_variant(small_model):
+    """Progress marks are off by default and the all-NVFP4 program launches the lean kernel variant; with marks on the
+    same program launches the full variant, gives the same bits, and every warp of every worker ends on the last
+    teardown mark."""
+    dims, cfg, sd = small_model
+    x = inputs(3, 50, 0, dims.vocab)
+    with NativePi0(StateDictModel(cfg, sd)) as engine:
+        lib = engine.lib
+        assert engine.plan["kernel"] == "lean"
+        a = engine.forward(*x).clone()
+        lean = C.c_int(-1)
+        _native.check(lib.enable_native_model_debug(engine.handle, 1), "marks on")
+        _native.check(lib.native_model_kernel_variant(engine.handle, C.byref(lean)), "variant")
+        assert lean.value == 0
+        b = engine.forward(*x).clone()
+        torch.cuda.synchronize()
+        assert engine.status()["code"] == 0 and torch.equal(a, b)
+        marks = (C.c_int * (engine.workers * 8))()
+        _native.check(lib.read_native_model_debug(engine.handle, marks, len(marks)), "marks")
+        assert set(marks) == {900004}
+        _native.check(lib.enable_native_model_debug(engine.handle, 0), "marks off")
+        _native.check(lib.native_model_kernel_variant(engine.handle, C.byref(lean)), "variant")
+        assert lean.value == 1
+        assert torch.equal(engine.forward(*x), a)
 
 
 def test_single_launch_is_counted_by_cupti(small_model):
