@@ -294,6 +294,7 @@ int build_program(Program** out, int device, const std::vector<StageDesc>& stage
         if (device < 64 && !configured[device]) {
             e = cudaFuncSetAttribute(pi0_vm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
             if (e == cudaSuccess) e = cudaFuncSetAttribute(pi0_vm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(pi0_vm_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
             configured[device] = e == cudaSuccess;
         }
         prog->lean = true;
@@ -336,7 +337,8 @@ int launch_program(Program* prog, cudaStream_t stream, LaunchInputs in, int begi
     p.wait_budget_ns = prog->budget_ns;
     p.in = in;
     p.debug = prog->h_debug;
-    if (prog->lean && !prog->h_debug) pi0_vm_kernel<true><<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
+    if (prog->lean && !prog->h_debug && !p.timings) pi0_vm_kernel<true, false><<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
+    else if (prog->lean && !prog->h_debug) pi0_vm_kernel<true><<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
     else pi0_vm_kernel<false><<<prog->workers, kThreads, kSmemBytes, stream>>>(p);
     return cudaGetLastError();
 }

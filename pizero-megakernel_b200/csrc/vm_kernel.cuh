@@ -47,7 +47,9 @@ __device__ __forceinline__ bool prefetch_slot(const VmProgram& prog, Ctl* ctl, c
 
 // LEAN = true: the variant for programs made of the pi0 model's own NVFP4 operators only (what build_program calls
 // lean); LEAN = false runs every operator and option.  Same VM, same protocol; the lean one is simply a smaller kernel.
-template <bool LEAN>
+// TIMED = false: without the per-instruction time stamps (the lean variant is built both ways, so that a stage profile
+// times the kernel that serves, and serving does not carry the stamp tests: 0.5 % of the pi0 forward).
+template <bool LEAN, bool TIMED = true>
 __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_constant__ VmProgram prog) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -121,7 +123,7 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
         const int4 ins = ctl->slot[slot].ins;
         if (ins.x == 0) break;
         const StageDesc& st = ctl->slot[slot].desc;
-        long long* stamp = prog.timings ? prog.timings + (static_cast<size_t>(blockIdx.x) * prog.length + ip0 + seq) * 8 : nullptr;
+        long long* stamp = !TIMED ? nullptr : prog.timings ? prog.timings + (static_cast<size_t>(blockIdx.x) * prog.length + ip0 + seq) * 8 : nullptr;
         if (stamp && threadIdx.x == 0) stamp[0] = static_cast<long long>(global_ns());
         if (st.kind == OP_GEMM) {
             if constexpr (!LEAN) mark(prog, 800000 + ins.y);
