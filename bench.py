@@ -49,11 +49,11 @@ WORKLOADS = {
     "cfg5": dict(views=3, prompt=16, chunk=63, steps=10, name="configs[4]: pi0 forward, 3 views, 16-token prompt, chunk 63, 10 Euler steps"),
 }
 # Algorithmic work of one forward (GEMM + attention FLOPs) and NVFP4 weight bytes read once.
-# dram_bytes: dram__bytes_read.sum + dram__bytes_write.sum of one launch from an ncu capture of this bench (3.53 GB read: the
+# dram_bytes: dram__bytes_read.sum + dram__bytes_write.sum of one launch from an ncu capture of this bench (3.52 GB read: the
 # 1.29 GB of vision/prefix weights once and the 0.17 GB of expert weights in each of the 10 Euler steps, plus scale atoms and
 # activations that had left L2; 1.02 GB written: activations and split-KV partials leaving the L2 behind the weight stream).
 # None: not captured.
-WORK = {"cfg4": dict(gflop=3997.0, weight_mb=1461.0, dram_bytes=4.55e9), "cfg5": dict(gflop=4136.0, weight_mb=1461.0, dram_bytes=None)}
+WORK = {"cfg4": dict(gflop=3997.0, weight_mb=1461.0, dram_bytes=4.54e9), "cfg5": dict(gflop=4136.0, weight_mb=1461.0, dram_bytes=None)}
 TRAFFIC_SOURCE = "constant from profiles/pi0_vm_kernel_bench_cfg4_launch_list.md (one ncu capture of this command), not measured in this run"
 # Dense NVFP4 tensor peak of a B200 as published (9 PFLOP/s; not measured on this pool) and the best rate this engine's
 # own NVFP4 GEMM has sustained stand-alone (gate/up + GeGLU, M 768, N 32768, K 2048; profiles/).
