@@ -12,8 +12,8 @@
 //
 // A tile holds all its keys' scores at once (at most 256 keys), so there is no running maximum and no rescaling of O;
 // longer key ranges are covered by KV splits and the split merge.  Heads of 72 (SigLIP) are stored padded to 128 with
-// zeros by the producing projection, so every chunk is a full 128-byte row.  Waits are bounded like all others: one
-// thread waits, the CTA adopts its verdict.
+// zeros by the producing projection, so every chunk is a full 128-byte row.  Waits are bounded like all others
+// (cta_wait_phase).
 #pragma once
 #include "op_attention.cuh"
 
@@ -24,17 +24,30 @@ constexpr int kTcKvBytes = 128 * 1024;                  // K chunks (later V chu
 constexpr int kTcScratch = kTcQBytes + kTcKvBytes;      // row maxima / sums of the two column halves: 2 x 2 x 128 floats
 static_assert(kTcScratch + 2048 <= kDataBytes, "tensor-core attention exceeds the data region");
 
-// One thread waits (bounded), everybody adopts the outcome and then observes the completed phase itself.
+// CTA-wide wait on a phase: every warp tries the barrier itself (so each thread has observed the completed phase);
+// warp 0 keeps the time budget and raises the CTA's abort flag, which ends every warp's spin; one hardware barrier
+// behind the spins makes the outcome the same for all threads.
 __device__ __forceinline__ bool cta_wait_phase(const VmProgram& prog, Ctl* ctl, uint64_t* bar, uint32_t parity, int stage) {
-    if (threadIdx.x == 0) ctl->flag = mbar_wait(prog, ctl, bar, parity, stage) ? 1 : 0;
-    __syncthreads();
-    const bool ok = ctl->flag != 0;
-    if (ok) {
-        while (!mbar_try_wait(bar, parity)) {
+    unsigned long long start = 0;
+    for (uint32_t spin = 1;; ++spin) {
+        if (__all_sync(0xffffffffu, mbar_try_wait(bar, parity))) break;
+        if (__any_sync(0xffffffffu, ctl->abort != 0)) break;
+        if (threadIdx.x < 32 && (spin & 15u) == 0u) {
+            int stop = 0;
+            if (threadIdx.x == 0) {
+                const unsigned long long now = global_ns();
+                if (start == 0) start = now;
+                if (now - start > prog.wait_budget_ns || ld_relaxed_int(&prog.status->abort)) {
+                    report(prog, 2, stage, -1, parity, 0);
+                    ctl->abort = 1;
+                    stop = 1;
+                }
+            }
+            if (__shfl_sync(0xffffffffu, stop, 0)) break;
         }
     }
-    __syncthreads();                                     // ctl->flag may be rewritten after this point
-    return ok;
+    __syncthreads();
+    return ctl->abort == 0;
 }
 
 // HDP: elements per head in memory and in the MMAs (128 or 256); a.head_dim: logical width that is stored.
