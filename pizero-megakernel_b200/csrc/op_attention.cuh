@@ -532,24 +532,28 @@ __device__ __forceinline__ void merge_instruction(const VmProgram& prog, Ctl* ct
 // costs neither a stage of its own nor a serial tail on one SM.
 template <int HDP, bool MASK>
 __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& a, int tile, uint8_t* data, uint32_t tmem,
-                             uint32_t uses, int stage, long long* stamp);
+                             uint32_t uses, int stage, long long* stamp, const StageDesc* deps, int dep_first, int dep_count);
 
 // LEAN: kernel variant for programs whose attention stages all run on the tcgen05 tiles (no mma.sync tile code).
+// The instruction waits for its sources itself (the instruction loop does not): the tcgen05 tile does so after its
+// index arithmetic, the other tiles up front.
 template <bool LEAN>
 __device__ __forceinline__ void attn_instruction(const VmProgram& prog, Ctl* ctl, uint8_t* data, uint32_t tmem, uint32_t& tc_tiles,
                                                  const StageDesc& st, int stage_index, int first, int count, long long* stamp) {
     const AttnParams& a = st.p.attn;
+    if (!(LEAN || a.tc) && !cta_wait_sources(prog, ctl, st, stage_index, first, count, stamp)) return;
     for (int t = first; t < first + count; ++t) {
         long long* stamp_t = t == first ? stamp : nullptr;
+        const StageDesc* deps = t == first ? &st : nullptr;
         if (LEAN || a.tc) {
             bool ok = false;
             if (!LEAN && a.mask) {
                 if constexpr (!LEAN)
-                    ok = a.hd_pad > 128 ? attn_tile_tc<256, true>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t)
-                                        : attn_tile_tc<128, true>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t);
+                    ok = a.hd_pad > 128 ? attn_tile_tc<256, true>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t, deps, first, count)
+                                        : attn_tile_tc<128, true>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t, deps, first, count);
             } else {
-                ok = a.hd_pad > 128 ? attn_tile_tc<256, false>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t)
-                                    : attn_tile_tc<128, false>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t);
+                ok = a.hd_pad > 128 ? attn_tile_tc<256, false>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t, deps, first, count)
+                                    : attn_tile_tc<128, false>(prog, ctl, a, t, data, tmem, tc_tiles, stage_index, stamp_t, deps, first, count);
             }
             tc_tiles++;
             if (!ok) return;                                   // uniform: a wait gave up, the abort flag is set

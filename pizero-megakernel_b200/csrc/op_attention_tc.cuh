@@ -54,8 +54,10 @@ __device__ __forceinline__ bool cta_wait_phase(const VmProgram& prog, Ctl* ctl, 
 // `uses` counts the tensor-core attention tiles this CTA has run (phase parity of the four barriers).
 // MASK: the operator's boolean visibility mask is consulted (instantiated for the full kernel variant only).
 template <int HDP, bool MASK = false>
+// deps: when not null, the stage whose sources this call waits for itself (tile range dep_first, dep_count) - after its
+// index arithmetic and just before the first copies, so that the arithmetic is off the dependent path.
 __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& a, int tile, uint8_t* data, uint32_t tmem,
-                             uint32_t uses, int stage, long long* stamp) {
+                             uint32_t uses, int stage, long long* stamp, const StageDesc* deps, int dep_first, int dep_count) {
     constexpr int CHUNKS = HDP / 64;
     uint8_t* sQ = data;                                  // Q, then P
     uint8_t* sKV = data + kTcQBytes;                     // K, then V
@@ -81,6 +83,8 @@ __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& 
     uint64_t* bar_s = &ctl->attn_bar[1];
     uint64_t* bar_v = &ctl->attn_bar[2];
     uint64_t* bar_o = &ctl->attn_bar[3];
+
+    if (deps && !cta_wait_sources(prog, ctl, *deps, stage, dep_first, dep_count, stamp)) return false;
 
     // ---- Q and K
     if (threadIdx.x == 0) {

@@ -149,7 +149,8 @@ __global__ void __launch_bounds__(kThreads, 1) pi0_vm_kernel(const __grid_consta
                     if (np.beta) prefetch_l1(np.beta + i * 32);
                 }
             }
-            if (!cta_wait_sources(prog, ctl, st, ins.y, ins.z, ins.w, stamp)) break;
+            // (an attention instruction waits for its sources itself, behind its index arithmetic)
+            if (st.kind != OP_ATTN && !cta_wait_sources(prog, ctl, st, ins.y, ins.z, ins.w, stamp)) break;
             switch (st.kind) {
                 case OP_NORM: norm_instruction<LEAN>(prog, ctl, data, st, ins.y, ins.z, ins.w); break;
                 case OP_ATTN: attn_instruction<LEAN>(prog, ctl, data, tmem, tc_tiles, st, ins.y, ins.z, ins.w, stamp); break;
