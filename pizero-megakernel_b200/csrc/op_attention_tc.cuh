@@ -97,14 +97,13 @@ __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& 
             tma_load_2d(sKV + c * k_bytes, a.tmap_k, bar_qk, kvh * HDP + c * 64, k_row);
         }
     }
-    if (!cta_wait_phase(prog, ctl, bar_qk, parity, stage)) return false;
-    if (stamp && threadIdx.x == 0) stamp[4] = static_cast<long long>(global_ns());
-
-    // ---- S = Q K^T
+    // ---- S = Q K^T  (only the issuing warp waits for Q and K: nobody else touches them; if its wait gives up, the abort
+    //      flag is set and the CTA-wide wait for S below ends for everybody)
     constexpr uint64_t kKMajor = (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);       // 128-byte swizzle, 8-row groups 1 KiB apart
     const uint32_t q16 = (smem_u32(sQ) & 0x3FFFFu) >> 4, kv16 = (smem_u32(sKV) & 0x3FFFFu) >> 4;
     const uint32_t kchunk16 = static_cast<uint32_t>(a.k_box) * 8u;                                  // one K/V chunk in 16-byte units
-    if (warp == 0) {
+    if (warp == 0 && mbar_wait_warp(prog, ctl, bar_qk, parity, stage)) {
+        if (stamp && lane == 0) stamp[4] = static_cast<long long>(global_ns());
         if (elect_one()) {
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n_s >> 3) << 17) | (8u << 24);
 #pragma unroll
@@ -189,11 +188,10 @@ __device__ bool attn_tile_tc(const VmProgram& prog, Ctl* ctl, const AttnParams& 
     tc_fence_before();
     fence_proxy_async_smem();                            // P (generic stores) must be visible to the tensor core's reads
     __syncthreads();
-    if (!cta_wait_phase(prog, ctl, bar_v, parity, stage)) return false;
-    if (stamp && threadIdx.x == 0) stamp[5] = static_cast<long long>(global_ns());
 
-    // ---- O = P V
-    if (warp == 0) {
+    // ---- O = P V  (again only the issuing warp waits for V)
+    if (warp == 0 && mbar_wait_warp(prog, ctl, bar_v, parity, stage)) {
+        if (stamp && lane == 0) stamp[5] = static_cast<long long>(global_ns());
         tc_fence_after();
         if (elect_one()) {
             // B = V with hd contiguous (MN-major): 64-element blocks of hd are one chunk (k_box rows x 128 bytes) apart,
