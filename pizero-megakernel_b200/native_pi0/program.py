@@ -64,8 +64,8 @@ def spread_streams(stages, workers, sources, kinds=None):
     are split exactly as in ``linear_streams``.
 
     ``kinds`` (optional, one label per stage: the code path its tiles execute): among the workers that are not late,
-    those that have run the stage's kind before come first, so that a worker keeps to few kinds of instruction and its
-    SM's instruction cache to few code paths."""
+    those that ran the stage's kind most recently come first, so that a worker keeps to few kinds of instruction and
+    its SM's instruction cache to few code paths."""
     if not isinstance(workers, int) or workers < 1 or workers > MAX_WORKERS:
         raise ValueError("Expected 1..148 B200 workers")
     stages = tuple(stages)
@@ -75,7 +75,7 @@ def spread_streams(stages, workers, sources, kinds=None):
     last = np.full(workers, -1, dtype=np.int64)          # the stage of each worker's previous instruction
     rows = [[] for _ in range(workers)]
     index_of = np.arange(workers)
-    known = {}                                           # kind -> 1 for the workers that have run it
+    known = {}                                           # kind -> per worker: the last stage of this kind it ran (-1: none)
     if kinds is not None and len(kinds) != len(stages):
         raise ValueError("Expected one kind per stage")
     for index, work in enumerate(stages):
@@ -86,9 +86,9 @@ def spread_streams(stages, workers, sources, kinds=None):
         if kinds is None:
             order = np.lexsort((index_of, load, late))[:parts]        # keys: late first, then load, then index
         else:
-            ran = known.setdefault(kinds[index], np.zeros(workers, dtype=np.int64))
-            order = np.lexsort((index_of, load, 1 - ran, late))[:parts]
-            ran[order] = 1
+            ran = known.setdefault(kinds[index], np.full(workers, -1, dtype=np.int64))
+            order = np.lexsort((index_of, load, -ran, late))[:parts]      # late, then most recent run of this kind, load, index
+            ran[order] = index
         start = 0
         for rank, worker in enumerate(order.tolist()):
             count = small + (1 if rank < extra else 0)
