@@ -151,9 +151,10 @@ class NativePi0:
         self.fold_layernorms = bool(fold_layernorms)
         # output tile widths of the action expert's projections: an int for all four, or a dict per operation.  The default
         # gives the projections with few output columns 32-wide tiles (twice the workers, half the bytes of weight and half
-        # the serial epilogue per worker); gate/up already has 128 tiles of 64
+        # the serial epilogue per worker); gate/up runs as 64 tiles of 128, which leaves its neighbours (32 tiles each)
+        # workers of their own, so that no tile of the three stages starts on a worker that has just run its source
         if expert_block_n is None:
-            expert_block_n = {"qkv": 64, "o_proj": 32, "gate_up": 64, "down": 32}
+            expert_block_n = {"qkv": 64, "o_proj": 32, "gate_up": 128, "down": 32}
         self.expert_block_n = expert_block_n
         self.rope_inv_freq_dtype = rope_inv_freq_dtype
         self.keep_debug_outputs = keep_debug_outputs
